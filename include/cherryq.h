@@ -1,0 +1,180 @@
+/*
+ * cherryq.h — C ABI of the B200 (sm_100a) CherryQ quantized-linear library.
+ *
+ * Everything here is `extern "C"`, takes plain device/host pointers and sizes,
+ * never throws and never aborts: every entry point returns a cq_status code
+ * (0 = success) and enqueues its work on the CUDA stream it is given (pass 0
+ * for the legacy default stream).  Pointers are DEVICE pointers unless a
+ * parameter is documented as host memory.
+ *
+ * The entry points replace, one for one, the operator interface of the
+ * reference project wangitu/Mixed-precision-CUDA-kernel (paths below are inside
+ * that project):
+ *
+ *   csrc/quant_cuda.cpp:41-54   vecquant3matmul_cherryq   -> cq_vecquant3matmul_cherryq
+ *   csrc/quant_cuda.cpp:56-69   vecquant4matmul_cherryq   -> cq_vecquant4matmul_cherryq
+ *   csrc/quant_cuda.cpp:26-38   Dequantize3Normal / Dequantize4Normal
+ *                                                         -> cq_dequantize3_normal / cq_dequantize4_normal
+ *   llama/qlinear.py:67-118     QuantLinear.pack          -> cq_pack
+ *   llama/qlinear.py:120-162    QuantLinear.unpack        -> cq_unpack_dense
+ *
+ * plus the prepared-layer interface (cq_layer_*) that the legacy calls use
+ * internally: the reference's uint8 buffers are re-packed ON THE GPU into a
+ * stream layout made for 16-byte shared-memory reads and tensor-core fragments,
+ * and the matvec runs on that.
+ *
+ * Reference buffer formats (llama/qlinear.py:43-58), all row-major, N contiguous:
+ *   qweight        uint8  (K'/8*bits, N)   K' = K - C compacted (cherry-free) columns
+ *   scales         fp16   (ceil(K'/G), N)
+ *   cherry_weight  fp16   (C, N)
+ *   cherry_indices int16  (C,)  sorted ascending
+ * with K = in_features, N = out_features, C = number of fp16 "cherry" columns,
+ * G = group size on the compacted axis, bits in {3, 4}.
+ */
+#ifndef CHERRYQ_H_
+#define CHERRYQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* cq_stream_t; /* a cudaStream_t */
+
+typedef enum cq_status {
+  CQ_OK = 0,
+  CQ_ERR_BAD_ARG = 1,       /* null pointer, negative size, misaligned pointer            */
+  CQ_ERR_BAD_BITS = 2,      /* bits is not 3 or 4                                         */
+  CQ_ERR_BAD_GROUP = 3,     /* group size is not 64 or a multiple of 128                  */
+  CQ_ERR_BAD_SHAPE = 4,     /* K % 8, N % 8, C % 8, K > 65534, C >= K ...                 */
+  CQ_ERR_TOO_LARGE = 5,     /* the layer does not fit the kernel's shared-memory plan     */
+  CQ_ERR_CUDA = 6,          /* a CUDA runtime call failed; see cq_last_cuda_error()       */
+  CQ_ERR_NO_DEVICE = 7,     /* no CUDA device, or device is not compute capability 10.x   */
+  CQ_ERR_DEVICE_TIMEOUT = 8,/* a bounded device-side wait ran out (reported by cq_poll)   */
+  CQ_ERR_UNSUPPORTED = 9    /* valid request that this build has no kernel for            */
+} cq_status;
+
+const char* cq_strerror(int status);
+/* cudaError_t of the last failing CUDA call on this thread, 0 if none. */
+int cq_last_cuda_error(void);
+/* Library ABI version (bumped when a signature changes). */
+int cq_abi_version(void);
+
+/* ------------------------------------------------------------------------
+ * Prepared layer: the B200 stream layout of one quantized linear.
+ * ---------------------------------------------------------------------- */
+typedef struct cq_layer {
+  /* problem */
+  int32_t bits, K, N, C, G;
+  /* derived (filled by cq_layer_init) */
+  int32_t Kc;          /* K - C, compacted width                                        */
+  int32_t Kp;          /* Kc rounded up to 128                                          */
+  int32_t Cp;          /* C rounded up to 16                                            */
+  int32_t n_gran;      /* 128-column granules per 16-row sub-tile = Kp / 128             */
+  int32_t n_sub;       /* 16-row sub-tiles = ceil(N / 16)                               */
+  int32_t sets;        /* scale sets per granule: 1 (G % 128 == 0) or 2 (G == 64)        */
+  int32_t gran_bytes;  /* bytes of one granule: 16 rows x 128 codes + scales             */
+  int32_t cher_bytes;  /* bytes of one sub-tile's cherry block                           */
+  /* sections of the device blob */
+  uint64_t off_stream, off_cherry, off_perm, off_cidx, blob_bytes;
+  void* blob;          /* device memory, blob_bytes long, 256-byte aligned               */
+} cq_layer;
+
+/* Fills the derived fields and section offsets for the given problem; no GPU work.
+ * blob may be NULL to query blob_bytes. */
+int cq_layer_init(cq_layer* layer, int bits, int K, int N, int C, int G, void* blob);
+
+/* GPU re-pack: reference buffers -> stream layout in layer->blob. */
+int cq_layer_prepare(const cq_layer* layer, const uint8_t* qweight, const void* scales_f16,
+                     const void* cherry_weight_f16, const int16_t* cherry_indices,
+                     cq_stream_t stream);
+
+/* Inverse GPU re-pack: stream layout -> reference buffers (byte-identical round trip). */
+int cq_layer_unprepare(const cq_layer* layer, uint8_t* qweight, void* scales_f16,
+                       void* cherry_weight_f16, int16_t* cherry_indices, cq_stream_t stream);
+
+/* Bytes of scratch the matvec needs on a device (cross-CTA partial sums and flags).
+ * The scratch must be zero-filled once before its first use and must not be shared
+ * by launches that can overlap on the GPU. */
+size_t cq_scratch_bytes(void);
+
+/* y (M, N) fp16 = [y +] x (M, K) fp16 . W^T, M >= 1.  ldx / ldy are row strides in
+ * elements.  accumulate != 0 adds to y like the reference's `mul +=`.
+ * status_word: device uint32 that receives CQ_ERR_DEVICE_TIMEOUT bits, may be NULL. */
+int cq_layer_matvec(const cq_layer* layer, const void* x_f16, int ldx, void* y_f16, int ldy,
+                    int M, int accumulate, void* scratch, uint32_t* status_word,
+                    cq_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Drop-in operator entry points (reference: csrc/quant_cuda.cpp:41-69, 26-38).
+ * Dimension arguments are what the reference derives from its tensors
+ * (csrc/quant_cuda_kernel.cu:686-690):
+ *   height = qweight.size(0), width = N = qweight.size(1), batch = vec.size(0),
+ *   vec_height = K = vec.size(1), cherry_size = C.
+ * `mul` is accumulated into (the caller pre-zeroes it, llama/qlinear.py:177).
+ * The re-packed layer is cached inside the library, keyed by the four buffer
+ * addresses, the dimensions and version_tag (pass any value that changes when
+ * the buffers' contents change, e.g. a sum of tensor version counters).
+ * ---------------------------------------------------------------------- */
+int cq_vecquant4matmul_cherryq(const void* vec_f16, const uint8_t* qweight,
+                               const void* cherry_weight_f16, const int16_t* cherry_indices,
+                               const void* scaling_factors_f16, void* mul_f16,
+                               int batch, int vec_height, int height, int width,
+                               int cherry_size, int group_size, uint64_t version_tag,
+                               cq_stream_t stream);
+
+/* fp16 != 0: half x / scales / cherry / mul and int16 indices.
+ * fp16 == 0: float x / scales / cherry / mul and int32 indices
+ * (csrc/quant_cuda_kernel.cu:139-179). */
+int cq_vecquant3matmul_cherryq(const void* vec, const uint8_t* qweight,
+                               const void* cherry_weight, const void* cherry_indices,
+                               const void* scaling_factors, void* mul,
+                               int batch, int vec_height, int height, int width,
+                               int cherry_size, int group_size, int fp16,
+                               uint64_t version_tag, cq_stream_t stream);
+
+/* out[k', n] = (u - (2^(bits-1) - 0.5)) * scaling_factors[k' / group_size, n], fp32,
+ * for the K' = height - cherry_size compacted columns
+ * (csrc/quant_cuda_kernel.cu:838-922 and 925-1010; the 4-bit version implements what
+ * the reference intends, not its block-height slip at :934/:964). */
+int cq_dequantize3_normal(const uint8_t* qweight, const float* scaling_factors, float* out,
+                          int qrows, int width, int height, int cherry_size, int group_size,
+                          cq_stream_t stream);
+int cq_dequantize4_normal(const uint8_t* qweight, const float* scaling_factors, float* out,
+                          int qrows, int width, int height, int cherry_size, int group_size,
+                          cq_stream_t stream);
+
+/* Drop every cached re-packed layer (frees device memory). */
+int cq_cache_clear(void);
+/* Number of cached layers and the bytes they hold. */
+int cq_cache_stats(int* n_layers, uint64_t* bytes);
+
+/* Reads and clears the library's per-device status word (host call, synchronises
+ * the given stream).  Returns CQ_OK or CQ_ERR_DEVICE_TIMEOUT. */
+int cq_poll(cq_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Packing (reference: llama/qlinear.py:67-118) and dense unpacking (:120-162).
+ * ---------------------------------------------------------------------- */
+/* weight: (N, K) row-major, fp16 (weight_is_f32 == 0) or fp32.
+ * cherry_unsorted: int32 (C,) distinct column indices in any order.
+ * Outputs in the reference formats above.  tmp: device scratch of
+ * cq_pack_tmp_bytes(K) bytes. */
+size_t cq_pack_tmp_bytes(int K);
+int cq_pack(const void* weight, int weight_is_f32, const int32_t* cherry_unsorted,
+            int bits, int K, int N, int C, int G,
+            uint8_t* qweight, void* scales_f16, void* cherry_weight_f16,
+            int16_t* cherry_indices, void* tmp, cq_stream_t stream);
+
+/* dense: (N, K) fp16 = what QuantLinear.unpack() returns. */
+int cq_unpack_dense(const uint8_t* qweight, const void* scales_f16,
+                    const void* cherry_weight_f16, const int16_t* cherry_indices,
+                    int bits, int K, int N, int C, int G, void* dense_f16,
+                    cq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHERRYQ_H_ */

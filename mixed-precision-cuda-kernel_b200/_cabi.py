@@ -1,0 +1,76 @@
+"""ctypes view of libcherryq.so: one Python function per symbol of include/cherryq.h.
+
+The tests call the C ABI through this module with raw device pointers taken from
+torch tensors (`tensor.data_ptr()`); nothing here allocates device memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import NativeLibraryMissing, lib_path
+
+SYMBOLS = [
+    "cq_strerror", "cq_last_cuda_error", "cq_abi_version",
+    "cq_layer_init", "cq_layer_prepare", "cq_layer_unprepare", "cq_scratch_bytes", "cq_layer_matvec",
+    "cq_vecquant4matmul_cherryq", "cq_vecquant3matmul_cherryq",
+    "cq_dequantize3_normal", "cq_dequantize4_normal",
+    "cq_cache_clear", "cq_cache_stats", "cq_poll",
+    "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense",
+]
+
+
+class cq_layer(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("bits", "K", "N", "C", "G", "Kc", "Kp", "Cp", "n_gran", "n_sub", "sets", "gran_bytes", "cher_bytes")]
+    _fields_ += [(n, C.c_uint64) for n in ("off_stream", "off_cherry", "off_perm", "off_cidx", "blob_bytes")]
+    _fields_ += [("blob", C.c_void_p)]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not os.path.exists(path):
+        raise NativeLibraryMissing(f"{path} is missing; build it first (there is no CPU fallback)")
+    L = C.CDLL(path)
+    vp, i32, u64 = C.c_void_p, C.c_int, C.c_uint64
+    L.cq_strerror.restype = C.c_char_p
+    L.cq_strerror.argtypes = [i32]
+    L.cq_scratch_bytes.restype = C.c_size_t
+    L.cq_pack_tmp_bytes.restype = C.c_size_t
+    L.cq_pack_tmp_bytes.argtypes = [i32]
+    L.cq_layer_init.argtypes = [C.POINTER(cq_layer), i32, i32, i32, i32, i32, vp]
+    L.cq_layer_prepare.argtypes = [C.POINTER(cq_layer), vp, vp, vp, vp, vp]
+    L.cq_layer_unprepare.argtypes = [C.POINTER(cq_layer), vp, vp, vp, vp, vp]
+    L.cq_layer_matvec.argtypes = [C.POINTER(cq_layer), vp, i32, vp, i32, i32, i32, vp, vp, vp]
+    L.cq_vecquant4matmul_cherryq.argtypes = [vp] * 6 + [i32] * 6 + [u64, vp]
+    L.cq_vecquant3matmul_cherryq.argtypes = [vp] * 6 + [i32] * 7 + [u64, vp]
+    L.cq_dequantize3_normal.argtypes = [vp, vp, vp] + [i32] * 5 + [vp]
+    L.cq_dequantize4_normal.argtypes = [vp, vp, vp] + [i32] * 5 + [vp]
+    L.cq_cache_stats.argtypes = [C.POINTER(C.c_int), C.POINTER(C.c_uint64)]
+    L.cq_poll.argtypes = [vp]
+    L.cq_pack.argtypes = [vp, i32, vp] + [i32] * 5 + [vp] * 6
+    L.cq_unpack_dense.argtypes = [vp] * 4 + [i32] * 5 + [vp, vp]
+    _lib = L
+    return L
+
+
+def strerror(rc: int) -> str:
+    return lib().cq_strerror(rc).decode()
+
+
+def check(rc: int, what: str = "cherryq"):
+    if rc != 0:
+        extra = f" (cudaError {lib().cq_last_cuda_error()})" if rc == 6 else ""
+        raise RuntimeError(f"{what}: {strerror(rc)}{extra}")
+
+
+def layer_init(bits, K, N, Cn, G, blob_ptr=None) -> cq_layer:
+    L = cq_layer()
+    check(lib().cq_layer_init(C.byref(L), bits, K, N, Cn, G, blob_ptr), "cq_layer_init")
+    return L

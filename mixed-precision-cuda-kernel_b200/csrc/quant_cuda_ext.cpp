@@ -1,0 +1,283 @@
+// Python module `quant_cuda`: same name, function names, argument order and dtypes as
+// the reference's extension (csrc/quant_cuda.cpp:41-77 of the reference project), so
+// that llama/qlinear.py and benchmark_speed.py of the reference run against it
+// unchanged.  This file holds no device code: it validates the tensors, picks the
+// current CUDA stream and device, and calls the C ABI declared in include/cherryq.h.
+// Differences from the reference, all deliberate:
+//   * work is enqueued on torch's CURRENT stream (the reference uses the legacy
+//     default stream), so the ops can be captured in CUDA graphs;
+//   * a device guard covers all four ops (the reference guards only the matmuls);
+//   * wrong dtypes / devices / shapes / group sizes raise RuntimeError (the
+//     reference's 3-bit op silently does nothing for an unsupported group size).
+// The first matmul call with a given set of weight tensors re-packs them on the GPU
+// (allocates and synchronises), so it must happen before any stream capture.
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <mutex>
+
+#include "cherryq.h"
+
+namespace {
+
+void check_status(int rc, const char* what) {
+  if (rc == CQ_OK) return;
+  if (rc == CQ_ERR_CUDA) {
+    TORCH_CHECK(false, what, ": CUDA error ", cq_last_cuda_error());
+  }
+  TORCH_CHECK(false, what, ": ", cq_strerror(rc));
+}
+
+void check_tensor(const torch::Tensor& t, const char* name, c10::ScalarType dtype, const torch::Tensor& like) {
+  TORCH_CHECK(t.defined(), name, " is undefined");
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == dtype, name, " must have dtype ", c10::toString(dtype), ", got ",
+              c10::toString(t.scalar_type()));
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+  TORCH_CHECK(t.device() == like.device(), name, " is on ", t.device(), " but vec is on ", like.device());
+}
+
+cq_stream_t current_stream() { return (cq_stream_t)c10::cuda::getCurrentCUDAStream().stream(); }
+
+uint64_t version_tag(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& c,
+                     const torch::Tensor& d) {
+  return (uint64_t)a._version() + ((uint64_t)b._version() << 16) + ((uint64_t)c._version() << 32) +
+         ((uint64_t)d._version() << 48);
+}
+
+void vecquant3matmul_cherryq(torch::Tensor vec, torch::Tensor qweight, torch::Tensor cherry_weight,
+                             torch::Tensor cherry_indices, torch::Tensor scaling_factors, torch::Tensor mul,
+                             int group_size, bool fp16) {
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(vec));
+  const auto ft = fp16 ? torch::kFloat16 : torch::kFloat32;
+  const auto it = fp16 ? torch::kInt16 : torch::kInt32;
+  check_tensor(vec, "vec", ft, vec);
+  check_tensor(qweight, "qweight", torch::kUInt8, vec);
+  check_tensor(cherry_weight, "cherry_weight", ft, vec);
+  check_tensor(cherry_indices, "cherry_indices", it, vec);
+  check_tensor(scaling_factors, "scaling_factors", ft, vec);
+  check_tensor(mul, "mul", ft, vec);
+  TORCH_CHECK(vec.dim() == 2 && qweight.dim() == 2 && mul.dim() == 2, "vec, qweight and mul must be 2-D");
+  TORCH_CHECK(mul.size(0) == vec.size(0) && mul.size(1) == qweight.size(1), "mul must be (batch, width)");
+  TORCH_CHECK(cherry_weight.numel() == cherry_indices.size(0) * qweight.size(1), "cherry_weight must be (C, width)");
+  check_status(cq_vecquant3matmul_cherryq(
+                   vec.data_ptr(), qweight.data_ptr<uint8_t>(), cherry_weight.data_ptr(), cherry_indices.data_ptr(),
+                   scaling_factors.data_ptr(), mul.data_ptr(), (int)vec.size(0), (int)vec.size(1),
+                   (int)qweight.size(0), (int)qweight.size(1), (int)cherry_indices.size(0), group_size, fp16 ? 1 : 0,
+                   version_tag(qweight, cherry_weight, cherry_indices, scaling_factors), current_stream()),
+               "vecquant3matmul_cherryq");
+}
+
+void vecquant4matmul_cherryq(torch::Tensor vec, torch::Tensor qweight, torch::Tensor cherry_weight,
+                             torch::Tensor cherry_indices, torch::Tensor scaling_factors, torch::Tensor mul,
+                             int group_size) {
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(vec));
+  check_tensor(vec, "vec", torch::kFloat16, vec);
+  check_tensor(qweight, "qweight", torch::kUInt8, vec);
+  check_tensor(cherry_weight, "cherry_weight", torch::kFloat16, vec);
+  check_tensor(cherry_indices, "cherry_indices", torch::kInt16, vec);
+  check_tensor(scaling_factors, "scaling_factors", torch::kFloat16, vec);
+  check_tensor(mul, "mul", torch::kFloat16, vec);
+  TORCH_CHECK(vec.dim() == 2 && qweight.dim() == 2 && mul.dim() == 2, "vec, qweight and mul must be 2-D");
+  TORCH_CHECK(mul.size(0) == vec.size(0) && mul.size(1) == qweight.size(1), "mul must be (batch, width)");
+  TORCH_CHECK(cherry_weight.numel() == cherry_indices.size(0) * qweight.size(1), "cherry_weight must be (C, width)");
+  check_status(cq_vecquant4matmul_cherryq(
+                   vec.data_ptr(), qweight.data_ptr<uint8_t>(), cherry_weight.data_ptr(),
+                   (const int16_t*)cherry_indices.data_ptr(), scaling_factors.data_ptr(), mul.data_ptr(),
+                   (int)vec.size(0), (int)vec.size(1), (int)qweight.size(0), (int)qweight.size(1),
+                   (int)cherry_indices.size(0), group_size,
+                   version_tag(qweight, cherry_weight, cherry_indices, scaling_factors), current_stream()),
+               "vecquant4matmul_cherryq");
+}
+
+void dequantize_normal(int bits, torch::Tensor qweight, torch::Tensor scaling_factors, torch::Tensor out, int height,
+                       int cherry_size, int group_size) {
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(qweight));
+  check_tensor(qweight, "qweight", torch::kUInt8, qweight);
+  check_tensor(scaling_factors, "scaling_factors", torch::kFloat32, qweight);
+  check_tensor(out, "out", torch::kFloat32, qweight);
+  TORCH_CHECK(qweight.dim() == 2 && out.dim() == 2 && out.size(1) == qweight.size(1) &&
+                  out.size(0) >= height - cherry_size,
+              "out must be (>= height - cherry_size, width)");
+  auto fn = bits == 3 ? cq_dequantize3_normal : cq_dequantize4_normal;
+  check_status(fn(qweight.data_ptr<uint8_t>(), scaling_factors.data_ptr<float>(), out.data_ptr<float>(),
+                  (int)qweight.size(0), (int)qweight.size(1), height, cherry_size, group_size, current_stream()),
+               bits == 3 ? "Dequantize3Normal" : "Dequantize4Normal");
+}
+
+void Dequantize3Normal(torch::Tensor qweight, torch::Tensor scaling_factors, torch::Tensor out, int height,
+                       int cherry_size, int group_size) {
+  dequantize_normal(3, qweight, scaling_factors, out, height, cherry_size, group_size);
+}
+void Dequantize4Normal(torch::Tensor qweight, torch::Tensor scaling_factors, torch::Tensor out, int height,
+                       int cherry_size, int group_size) {
+  dequantize_normal(4, qweight, scaling_factors, out, height, cherry_size, group_size);
+}
+
+// ------------------------------------------------------------------ additive entry points
+// GPU QuantLinear.pack (llama/qlinear.py:67-118): returns (qweight, scales, cherry_weight, cherry_indices).
+std::vector<torch::Tensor> pack(torch::Tensor weight, torch::Tensor cherry_unsorted, int bits, int group_size) {
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(weight));
+  TORCH_CHECK(weight.is_cuda() && weight.dim() == 2 && weight.is_contiguous(), "weight must be a contiguous 2-D CUDA tensor");
+  TORCH_CHECK(weight.scalar_type() == torch::kFloat16 || weight.scalar_type() == torch::kFloat32,
+              "weight must be float16 or float32");
+  check_tensor(cherry_unsorted, "cherry_indices", torch::kInt32, weight);
+  const int N = (int)weight.size(0), K = (int)weight.size(1), C = (int)cherry_unsorted.numel();
+  const int G = group_size == -1 ? K : group_size;
+  TORCH_CHECK(G > 0, "group_size must be positive or -1");
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0 && C % 8 == 0 && C < K, "in_features, out_features and the cherry count must be multiples of 8");
+  auto u8 = torch::TensorOptions().device(weight.device()).dtype(torch::kUInt8);
+  auto qweight = torch::empty({(K - C) / 8 * bits, N}, u8);
+  auto scales = torch::empty({(K - C + G - 1) / G, N}, u8.dtype(torch::kFloat16));
+  auto cw = torch::empty({C, N}, u8.dtype(torch::kFloat16));
+  auto idx = torch::empty({C}, u8.dtype(torch::kInt16));
+  check_status(cq_pack(weight.data_ptr(), weight.scalar_type() == torch::kFloat32, cherry_unsorted.data_ptr<int32_t>(),
+                       bits, K, N, C, G, qweight.data_ptr<uint8_t>(), scales.data_ptr(), cw.data_ptr(),
+                       (int16_t*)idx.data_ptr(), nullptr, current_stream()),
+               "pack");
+  return {qweight, scales, cw, idx};
+}
+
+// GPU QuantLinear.unpack (llama/qlinear.py:120-162): dense (N, K) fp16.
+torch::Tensor unpack_dense(torch::Tensor qweight, torch::Tensor scales, torch::Tensor cherry_weight,
+                           torch::Tensor cherry_indices, int bits, int in_features, int group_size) {
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(qweight));
+  check_tensor(qweight, "qweight", torch::kUInt8, qweight);
+  check_tensor(scales, "scales", torch::kFloat16, qweight);
+  check_tensor(cherry_weight, "cherry_weight", torch::kFloat16, qweight);
+  check_tensor(cherry_indices, "cherry_indices", torch::kInt16, qweight);
+  const int N = (int)qweight.size(1), C = (int)cherry_indices.numel();
+  auto dense = torch::empty({N, in_features}, scales.options());
+  check_status(cq_unpack_dense(qweight.data_ptr<uint8_t>(), scales.data_ptr(), cherry_weight.data_ptr(),
+                               (const int16_t*)cherry_indices.data_ptr(), bits, in_features, N, C, group_size,
+                               dense.data_ptr(), current_stream()),
+               "unpack_dense");
+  return dense;
+}
+
+std::mutex g_mu;
+std::map<int, torch::Tensor> g_scratch;  // per device: matvec scratch followed by a status word
+
+torch::Tensor scratch_for(const torch::Device& dev) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto it = g_scratch.find(dev.index());
+  if (it == g_scratch.end()) {
+    auto t = torch::zeros({(int64_t)cq_scratch_bytes() + 256}, torch::TensorOptions().device(dev).dtype(torch::kUInt8));
+    it = g_scratch.emplace(dev.index(), t).first;
+  }
+  return it->second;
+}
+
+// A layer re-packed into the stream layout; owns its device blob.
+struct PreparedLayer {
+  cq_layer layer;
+  torch::Tensor blob;
+
+  PreparedLayer(torch::Tensor qweight, torch::Tensor scales, torch::Tensor cherry_weight,
+                torch::Tensor cherry_indices, int bits, int in_features, int group_size) {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(qweight));
+    check_tensor(qweight, "qweight", torch::kUInt8, qweight);
+    check_tensor(scales, "scales", torch::kFloat16, qweight);
+    check_tensor(cherry_weight, "cherry_weight", torch::kFloat16, qweight);
+    check_tensor(cherry_indices, "cherry_indices", torch::kInt16, qweight);
+    const int N = (int)qweight.size(1), C = (int)cherry_indices.numel();
+    check_status(cq_layer_init(&layer, bits, in_features, N, C, group_size, nullptr), "PreparedLayer");
+    TORCH_CHECK(qweight.size(0) == layer.Kc / 8 * bits, "qweight has ", qweight.size(0), " rows, expected ",
+                layer.Kc / 8 * bits);
+    TORCH_CHECK(scales.size(0) == (layer.Kc + layer.G - 1) / layer.G && scales.size(1) == N, "scales must be (ceil(K'/G), N)");
+    blob = torch::empty({(int64_t)layer.blob_bytes}, qweight.options());
+    layer.blob = blob.data_ptr();
+    check_status(cq_layer_prepare(&layer, qweight.data_ptr<uint8_t>(), scales.data_ptr(), cherry_weight.data_ptr(),
+                                  (const int16_t*)cherry_indices.data_ptr(), current_stream()),
+                 "PreparedLayer");
+    // the matvec prefetches weights ahead of stream order: finish the re-pack first
+    c10::cuda::getCurrentCUDAStream().synchronize();
+  }
+
+  // A layer rebuilt around an existing blob (e.g. loaded from a file or sliced from a shard).
+  PreparedLayer(torch::Tensor blob_, int bits, int in_features, int out_features, int num_cherries, int group_size) {
+    TORCH_CHECK(blob_.is_cuda() && blob_.scalar_type() == torch::kUInt8 && blob_.is_contiguous(), "blob must be a contiguous CUDA uint8 tensor");
+    check_status(cq_layer_init(&layer, bits, in_features, out_features, num_cherries, group_size, nullptr), "PreparedLayer");
+    TORCH_CHECK((uint64_t)blob_.numel() == layer.blob_bytes, "blob has ", blob_.numel(), " bytes, expected ", layer.blob_bytes);
+    TORCH_CHECK(((uintptr_t)blob_.data_ptr() & 255) == 0, "blob must be 256-byte aligned");
+    blob = blob_;
+    layer.blob = blob.data_ptr();
+  }
+
+  // out (M, N) fp16 = [out +] x (M, K) fp16 . W^T
+  void matvec(torch::Tensor x, torch::Tensor out, bool accumulate) {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(x));
+    check_tensor(x, "x", torch::kFloat16, blob);
+    check_tensor(out, "out", torch::kFloat16, blob);
+    TORCH_CHECK(x.dim() == 2 && x.size(1) == layer.K, "x must be (M, ", layer.K, ")");
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) == layer.N, "out must be (M, ", layer.N, ")");
+    auto scratch = scratch_for(x.device());
+    uint8_t* sp = scratch.data_ptr<uint8_t>();
+    check_status(cq_layer_matvec(&layer, x.data_ptr(), layer.K, out.data_ptr(), layer.N, (int)x.size(0),
+                                 accumulate ? 1 : 0, sp, (uint32_t*)(sp + cq_scratch_bytes()), current_stream()),
+                 "PreparedLayer.matvec");
+  }
+
+  // Back to the reference's four buffers: (qweight, scales, cherry_weight, cherry_indices).
+  std::vector<torch::Tensor> unprepare() {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(blob));
+    auto o = blob.options();
+    auto qweight = torch::empty({layer.Kc / 8 * layer.bits, layer.N}, o);
+    auto scales = torch::empty({(layer.Kc + layer.G - 1) / layer.G, layer.N}, o.dtype(torch::kFloat16));
+    auto cw = torch::empty({layer.C, layer.N}, o.dtype(torch::kFloat16));
+    auto idx = torch::empty({layer.C}, o.dtype(torch::kInt16));
+    check_status(cq_layer_unprepare(&layer, qweight.data_ptr<uint8_t>(), scales.data_ptr(), cw.data_ptr(),
+                                    (int16_t*)idx.data_ptr(), current_stream()),
+                 "PreparedLayer.unprepare");
+    return {qweight, scales, cw, idx};
+  }
+};
+
+// Reads and clears the status word the PreparedLayer launches report into.
+bool device_timed_out(int device_index) {
+  torch::Tensor t;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_scratch.find(device_index);
+    if (it == g_scratch.end()) return false;
+    t = it->second;
+  }
+  auto word = t.slice(0, (int64_t)cq_scratch_bytes(), (int64_t)cq_scratch_bytes() + 4).cpu();
+  const bool bad = word.view(torch::kInt32).item<int32_t>() != 0;
+  if (bad) t.zero_();
+  return bad;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("vecquant3matmul_cherryq", &vecquant3matmul_cherryq, "a 3-bit version");
+  m.def("vecquant4matmul_cherryq", &vecquant4matmul_cherryq, "a 4-bit version");
+  m.def("Dequantize3Normal", &Dequantize3Normal, "Dequantize3Normal");
+  m.def("Dequantize4Normal", &Dequantize4Normal, "Dequantize4Normal");
+  m.def("pack", &pack, "GPU QuantLinear.pack");
+  m.def("unpack_dense", &unpack_dense, "GPU QuantLinear.unpack");
+  m.def("cache_clear", []() { check_status(cq_cache_clear(), "cache_clear"); });
+  m.def("cache_stats", []() {
+    int n = 0;
+    uint64_t b = 0;
+    cq_cache_stats(&n, &b);
+    return std::make_pair(n, b);
+  });
+  m.def("poll", []() { check_status(cq_poll(current_stream()), "poll"); });
+  m.def("device_timed_out", &device_timed_out);
+  m.def("abi_version", &cq_abi_version);
+  py::class_<PreparedLayer>(m, "PreparedLayer")
+      .def(py::init<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int, int, int>())
+      .def(py::init<torch::Tensor, int, int, int, int, int>())
+      .def("matvec", &PreparedLayer::matvec)
+      .def("unprepare", &PreparedLayer::unprepare)
+      .def_readonly("blob", &PreparedLayer::blob)
+      .def_property_readonly("bits", [](const PreparedLayer& p) { return p.layer.bits; })
+      .def_property_readonly("in_features", [](const PreparedLayer& p) { return p.layer.K; })
+      .def_property_readonly("out_features", [](const PreparedLayer& p) { return p.layer.N; })
+      .def_property_readonly("num_cherries", [](const PreparedLayer& p) { return p.layer.C; })
+      .def_property_readonly("group_size", [](const PreparedLayer& p) { return p.layer.G; });
+}

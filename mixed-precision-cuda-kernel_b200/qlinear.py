@@ -1,0 +1,145 @@
+"""Packed inference CherryQ linear (reference: llama/qlinear.py:13-199).
+
+Same constructor, buffers (`cherry_indices` int16 (C,), `cherry_weight` fp16 (C, N),
+`qweight` uint8 (K'/8*bits, N), `scales` fp16 (ceil(K'/G), N), optional `bias`),
+`pack()`, `unpack()`, `forward()` and class-level `dmode()` switch as the reference,
+so a state dict written by the reference loads into it.  What runs underneath is
+different: pack and unpack are GPU kernels, and forward runs the stream matvec on
+a re-packed copy of the buffers (made on first use; `release_reference_buffers()`
+drops the originals afterwards).  All of it needs a CUDA device.
+"""
+import math
+from contextlib import contextmanager
+
+import torch
+import torch.nn as nn
+
+from . import load_quant_cuda
+
+
+class QuantLinear(nn.Module):
+    _layerwise_dequantize = True
+
+    @classmethod
+    @contextmanager
+    def dmode(cls, layerwise_dequantize=True):
+        mode = cls._layerwise_dequantize
+        cls._layerwise_dequantize = layerwise_dequantize
+        try:
+            yield
+        finally:
+            cls._layerwise_dequantize = mode
+
+    def __init__(self, w_bits, group_size, quantizer, cherry_fraction: float, in_features, out_features,
+                 bias=True, **kwargs):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.w_bits = w_bits
+        self.group_size = group_size if group_size != -1 else in_features
+        self.quantizer = quantizer
+        self.cherry_fraction = cherry_fraction
+        self.num_cherries = math.ceil(in_features * cherry_fraction) // 8 * 8
+        self.num_normal = self.in_features - self.num_cherries
+        assert in_features % 8 == 0
+        assert out_features % 8 == 0
+        self.register_buffer("cherry_indices", torch.zeros(self.num_cherries, dtype=torch.int16))
+        self.register_buffer("cherry_weight", torch.zeros((self.num_cherries, out_features), dtype=torch.float16))
+        self.register_buffer("qweight", torch.zeros((self.num_normal // 8 * w_bits, out_features), dtype=torch.uint8))
+        self.register_buffer("scales", torch.zeros((math.ceil(self.num_normal / self.group_size), out_features),
+                                                   dtype=torch.float16))
+        if bias:
+            self.register_buffer("bias", torch.zeros(out_features, dtype=torch.float16))
+        else:
+            self.bias = None
+        self.dequantized = False
+        self._prepared = None
+        self._prepared_key = None
+
+    # ------------------------------------------------------------------ pack / unpack
+    @torch.inference_mode()
+    def pack(self, linear):
+        """GPU version of llama/qlinear.py:67-118; `linear` is the training-side layer."""
+        qc = load_quant_cuda()
+        if linear.bias is not None:
+            self.bias = linear.bias.half()
+        weight = linear.weight.detach()
+        if not weight.is_cuda:
+            if not torch.cuda.is_available():
+                raise RuntimeError("QuantLinear.pack needs a CUDA device (there is no CPU path)")
+            weight = weight.cuda()
+        weight = weight.contiguous()
+        if weight.dtype not in (torch.float16, torch.float32):
+            weight = weight.float()
+        idx = linear.cherry_indices.to(device=weight.device, dtype=torch.int32).contiguous()
+        gs = linear.group_size if linear.group_size != -1 else self.in_features
+        q, s, cw, ci = qc.pack(weight, idx, self.w_bits, gs)
+        self.qweight, self.scales, self.cherry_weight, self.cherry_indices = q, s, cw, ci
+        self._prepared = None
+
+    @torch.inference_mode()
+    def unpack(self):
+        """GPU version of llama/qlinear.py:120-162: dense (out, in) fp16 weight."""
+        qc = load_quant_cuda()
+        self._require_cuda()
+        return qc.unpack_dense(self.qweight, self.scales, self.cherry_weight, self.cherry_indices,
+                               self.w_bits, self.in_features, self.group_size)
+
+    # ------------------------------------------------------------------ forward
+    def _require_cuda(self):
+        if not self.qweight.is_cuda:
+            raise RuntimeError("QuantLinear buffers must be on a CUDA device (there is no CPU path)")
+
+    def prepared(self):
+        """The stream-layout copy of this layer (built on first use)."""
+        key = (self.qweight.data_ptr(), self.qweight._version, self.scales._version,
+               self.cherry_weight._version, self.cherry_indices._version)
+        if self._prepared is None or self._prepared_key != key:
+            qc = load_quant_cuda()
+            self._require_cuda()
+            self._prepared = qc.PreparedLayer(self.qweight, self.scales, self.cherry_weight, self.cherry_indices,
+                                              self.w_bits, self.in_features, self.group_size)
+            self._prepared_key = key
+        return self._prepared
+
+    def release_reference_buffers(self):
+        """Keeps only the stream-layout copy (halves the weight memory); `restore_reference_buffers`
+        rebuilds the four buffers bit-exactly."""
+        self.prepared()
+        dev = self.qweight.device
+        for name in ("qweight", "scales", "cherry_weight", "cherry_indices"):
+            setattr(self, name, torch.empty(0, dtype=getattr(self, name).dtype, device=dev))
+        self._prepared_key = "released"
+
+    def restore_reference_buffers(self):
+        q, s, cw, ci = self._prepared.unprepare()
+        self.qweight, self.scales, self.cherry_weight, self.cherry_indices = q, s, cw, ci
+        self._prepared_key = (q.data_ptr(), q._version, s._version, cw._version, ci._version)
+
+    @torch.inference_mode()
+    def forward(self, x: torch.Tensor):
+        if self._layerwise_dequantize:
+            if self.w_bits not in (3, 4):
+                raise NotImplementedError(f"{self.w_bits} bit kernel is not implemented yet.")
+            layer = self._prepared if self._prepared_key == "released" else self.prepared()
+            out_shape = x.shape[:-1] + (self.out_features,)
+            x2 = x.reshape(-1, x.shape[-1])
+            if x2.dtype != torch.float16:
+                x2 = x2.half()
+            x2 = x2.contiguous()
+            out = torch.empty(x2.shape[0], self.out_features, dtype=torch.float16, device=x2.device)
+            layer.matvec(x2, out, False)
+            out = out.reshape(out_shape).to(x.dtype)
+        else:
+            if not self.dequantized:
+                self.qweight = self.unpack()
+                del self.cherry_indices
+                del self.cherry_weight
+                del self.scales
+                self._prepared = None
+                torch.cuda.empty_cache()
+                self.dequantized = True
+            out = nn.functional.linear(x, self.qweight)
+        if self.bias is not None:
+            out += self.bias
+        return out
