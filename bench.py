@@ -1,0 +1,370 @@
+#!/usr/bin/env python
+"""Benchmark of the CherryQ quantized-linear hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1], the layer the north-star target is quoted on): one
+LLaMA-7B gate/up projection, 4096 -> 11008, 4-bit, group 128, cherry ratio 1/256 (16 fp16
+columns), fp16 activations ~N(0,1), batch 1.  Weights are synthetic with the configuration's
+distributions (dense ~N(0, 0.02), cherry columns ~N(0, 0.2)), quantised and packed by the GPU
+pack kernel.  A "step" is one matvec of that layer.  To keep the 23.5 MB layer from living in
+the 126 MB L2, consecutive steps walk over enough distinct copies of the layer to exceed 3x L2.
+
+metric  : algorithmic bytes of the reference format (qweight + scales + cherry values + indices
+          + x + y) per second, in GB/s - the number the HBM roofline is judged against.
+value   : inputs resident in HBM, stream matvec through the C ABI, CUDA graph of the copies.
+e2e     : the same metric through the drop-in `quant_cuda.vecquant4matmul_cherryq` call with HOST
+          activations: every step copies x from pinned host memory, zero-fills the output (the
+          operator accumulates, as the reference's forward does), runs the op and reads y back.
+N > 1   : the layer is sharded column-parallel (N/P output rows per GPU), every rank runs its
+          shard and the slices are all-gathered with NCCL: strong scaling of one layer.
+--impl reference : the reference's CPU path (unpack to dense fp16 + F.linear per call, restated
+          in oracle/torch_port.py because the Python reference does not travel) on the host cores.
+"""
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+K_IN, N_OUT, BITS, GROUP = 4096, 11008, 4, 128
+WORKLOAD = "llama7b_gate_proj_4096x11008_4bit_g128_cherry1/256_batch1"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(k, n, bits, group, m, c):
+    kc = k - c
+    return kc // 8 * bits * n + math.ceil(kc / group) * n * 2 + c * n * 2 + c * 2 + m * k * 2 + m * n * 2
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = sorted(int(r[1]) for r in self.rows if len(r) > 2 and r[1].isdigit())
+        mx = [int(r[2]) for r in self.rows if len(r) > 2 and r[2].isdigit()]
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_layer_gpu(qc, torch, k, n, bits, group, seed, device):
+    """Synthetic layer with the configuration's distributions, packed on the GPU."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    c = math.ceil(k / 256) // 8 * 8
+    w = torch.randn(n, k, device=device, generator=g) * 0.02
+    idx = torch.randperm(k, device=device, generator=g)[:c].to(torch.int32)
+    w[:, idx.long()] = torch.randn(n, c, device=device, generator=g) * 0.2
+    q, s, cw, ci = qc.pack(w.half().contiguous(), idx.contiguous(), bits, group)
+    return q, s, cw, ci, c
+
+
+def cpu_baseline(seconds=12.0):
+    """The reference's dequantize-then-matmul CPU path on a bounded sample: repeated calls on the
+    full-size layer for about `seconds`."""
+    import numpy as np
+    import torch
+    from oracle import cherryq_oracle as O
+    from oracle import torch_port as TP
+    torch.manual_seed(0)
+    c = O.num_cherries(K_IN, 1 / 256)
+    kc = K_IN - c
+    # random codes / scales of the right shapes: the CPU path's cost does not depend on the values
+    q = torch.randint(0, 256, (kc // 8 * BITS, N_OUT), dtype=torch.uint8)
+    s = (torch.rand(math.ceil(kc / GROUP), N_OUT) * 0.01 + 0.001).half()
+    cw = (torch.randn(c, N_OUT) * 0.2).half()
+    ci = torch.sort(torch.randperm(K_IN)[:c]).values.to(torch.int16)
+    x = torch.randn(1, K_IN).half()
+    TP.forward_dequantize_then_matmul(x, q, s, cw, ci, BITS, GROUP)
+    calls, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds or calls < 3:
+        TP.forward_dequantize_then_matmul(x, q, s, cw, ci, BITS, GROUP)
+        calls += 1
+    dt = (time.perf_counter() - t0) / calls
+    nbytes = algorithmic_bytes(K_IN, N_OUT, BITS, GROUP, 1, c)
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{calls} calls of unpack()+F.linear on the full 4096x11008 layer, {dt * 1e3:.1f} ms per call",
+            "ms_per_call": dt * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from oracle import cherryq_oracle as O
+    from oracle import torch_port as TP
+    c = O.num_cherries(K_IN, 1 / 256)
+    kc = K_IN - c
+    torch.manual_seed(0)
+    q = torch.randint(0, 256, (kc // 8 * BITS, N_OUT), dtype=torch.uint8)
+    s = (torch.rand(math.ceil(kc / GROUP), N_OUT) * 0.01 + 0.001).half()
+    cw = (torch.randn(c, N_OUT) * 0.2).half()
+    ci = torch.sort(torch.randperm(K_IN)[:c]).values.to(torch.int16)
+    x = torch.randn(1, K_IN).half()
+    for _ in range(max(args.warmup, 1)):
+        TP.forward_dequantize_then_matmul(x, q, s, cw, ci, BITS, GROUP)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        TP.forward_dequantize_then_matmul(x, q, s, cw, ci, BITS, GROUP)
+    dt = (time.perf_counter() - t0) / args.steps
+    nbytes = algorithmic_bytes(K_IN, N_OUT, BITS, GROUP, 1, c)
+    v = nbytes / dt / 1e9
+    print(json.dumps({
+        "impl": "reference", "metric": "matvec_algorithmic_GBps_batch1", "value": v, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "path": "reference CPU path: unpack() to dense fp16 + F.linear per call"},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{args.steps} full-layer calls per run"},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import cherryq_b200
+    from cherryq_b200 import _cabi
+    qc = cherryq_b200.load_quant_cuda()
+    lib = _cabi.lib()
+
+    n_local = N_OUT // world // 16 * 16 if world > 1 else N_OUT
+    if world > 1 and n_local * world != N_OUT:
+        # 11008 = 688 sub-tiles of 16 rows: split whole sub-tiles, the last rank takes the remainder
+        per = (N_OUT // 16) // world * 16
+        n_local = per if rank < world - 1 else N_OUT - per * (world - 1)
+    q, s, cw, ci, c = make_layer_gpu(qc, torch, K_IN, n_local, BITS, GROUP, 1234 + rank, dev)
+    alg = algorithmic_bytes(K_IN, N_OUT, BITS, GROUP, 1, c)          # whole layer, all ranks
+    alg_local = algorithmic_bytes(K_IN, n_local, BITS, GROUP, 1, c)
+
+    def ptr(t):
+        return C.c_void_p(t.data_ptr())
+
+    # distinct copies of the prepared layer: > 3x L2 in total
+    L0 = _cabi.layer_init(BITS, K_IN, n_local, c, GROUP)
+    ncopies = max(2, math.ceil(3 * L2_BYTES / L0.blob_bytes))
+    layers, blobs = [], []
+    for i in range(ncopies):
+        L = _cabi.layer_init(BITS, K_IN, n_local, c, GROUP)
+        b = torch.empty(L.blob_bytes, dtype=torch.uint8, device=dev)
+        L.blob = b.data_ptr()
+        if i == 0:
+            _cabi.check(lib.cq_layer_prepare(C.byref(L), ptr(q), ptr(s), ptr(cw), ptr(ci), None), "prepare")
+            torch.cuda.synchronize()
+        else:
+            b.copy_(blobs[0])
+        layers.append(L)
+        blobs.append(b)
+    torch.cuda.synchronize()
+
+    x = torch.randn(1, K_IN, device=dev).half()
+    y = torch.zeros(1, n_local, dtype=torch.float16, device=dev)
+    y_all = torch.zeros(world, n_local, dtype=torch.float16, device=dev) if world > 1 else None
+    scratch = torch.zeros(lib.cq_scratch_bytes(), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    sp = C.c_void_p(stream.cuda_stream)
+
+    def launch(i):
+        _cabi.check(lib.cq_layer_matvec(C.byref(layers[i % ncopies]), ptr(x), K_IN, ptr(y), n_local, 1, 0,
+                                        ptr(scratch), ptr(status), sp), "matvec")
+        if world > 1:
+            dist.all_gather_into_tensor(y_all, y)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        # warm-up (also builds the kernels' attributes before any capture)
+        for i in range(max(args.warmup, 3)):
+            launch(i)
+        stream.synchronize()
+        graph = None
+        if world == 1:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(ncopies):
+                    launch(i)
+            graph.replay()
+            stream.synchronize()
+        barrier()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        done = 0
+        if graph is not None:
+            while done + ncopies <= args.steps:
+                graph.replay()
+                done += ncopies
+        while done < args.steps:
+            launch(done)
+            done += 1
+        e1.record(stream)
+        stream.synchronize()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if int(status.item()) != 0:
+        raise RuntimeError("a device-side wait timed out during the benchmark")
+    ms_step = ms / args.steps
+    value = alg / (ms_step * 1e-3) / 1e9
+
+    # kernel time alone (N == 1: the graph holds nothing else; N > 1: events around the kernel only)
+    kern_ms = ms_step
+    if world > 1:
+        with torch.cuda.stream(stream):
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record(stream)
+            for i in range(200):
+                _cabi.check(lib.cq_layer_matvec(C.byref(layers[i % ncopies]), ptr(x), K_IN, ptr(y), n_local, 1, 0,
+                                                ptr(scratch), ptr(status), sp), "matvec")
+            k1.record(stream)
+            stream.synchronize()
+        kern_ms = k0.elapsed_time(k1) / 200
+
+    # ---------------------------------------------------------------- end to end through the drop-in op
+    e2e = None
+    xh = torch.randn(1, K_IN).half().pin_memory()
+    yh = torch.empty(1, n_local, dtype=torch.float16).pin_memory()
+    xd = torch.empty(1, K_IN, dtype=torch.float16, device=dev)
+    out = torch.empty(1, n_local, dtype=torch.float16, device=dev)
+    refs = []
+    for i in range(ncopies):                 # the op's own weight buffers (reference format), > 3x L2 in total
+        refs.append((q, cw, ci, s) if i == 0 else tuple(t.clone() for t in (q, cw, ci, s)))
+
+    def e2e_step(i):
+        qq, cc, ii, ss = refs[i % ncopies]
+        xd.copy_(xh, non_blocking=True)
+        out.zero_()
+        qc.vecquant4matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP)
+        yh.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = min(args.steps, 2000)
+    for i in range(ncopies + 3):
+        e2e_step(i)
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    qc.poll()
+    e2e = {"value": alg / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": K_IN * 2,
+           "d2h_bytes_per_step": n_local * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "path": "quant_cuda.vecquant4matmul_cherryq with pinned host x / y per rank"}
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        achieved = alg_local / (kern_ms * 1e-3) / 1e9
+        line = {
+            "metric": "matvec_algorithmic_GBps_batch1", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "bits": BITS, "group": GROUP, "K": K_IN, "N": N_OUT, "batch": 1,
+                       "l2_defeat": f"{ncopies} distinct layer copies ({ncopies * L0.blob_bytes / 1e6:.0f} MB) walked "
+                                    "round-robin, inputs larger than L2",
+                       "parallelism": "single GPU" if world == 1 else f"column-parallel over {world} GPUs + NCCL all-gather",
+                       "launch": "CUDA graph of the copies" if world == 1 else "stream launches"},
+            "pct_of_nominal_8TBps": value / world / 8000.0 * 100.0 if world == 1 else None,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
+                         "kernel": "cq_matvec_kernel<4,1,1,...>", "alg_bytes_per_launch": alg_local,
+                         "launch_us": kern_ms * 1e3},
+            "e2e": e2e, "gpu_launches": args.steps * world, "clocks": clocks,
+        }
+        line["cpu_baseline"] = cpu_baseline() if world == 1 and not args.no_cpu else None
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20000)
+    ap.add_argument("--warmup", type=int, default=100)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps > 200:
+            args.steps = 200        # each step is a full-layer CPU call (tens of ms): keep the run within minutes
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -78,7 +78,7 @@ typedef struct cq_layer {
   int32_t gran_bytes;  /* bytes of one granule: 16 rows x 128 codes + scales             */
   int32_t cher_bytes;  /* bytes of one sub-tile's cherry block                           */
   /* sections of the device blob */
-  uint64_t off_stream, off_cherry, off_perm, off_cidx, blob_bytes;
+  uint64_t off_stream, off_cherry, off_osh, off_cidx, blob_bytes;
   void* blob;          /* device memory, blob_bytes long, 256-byte aligned               */
 } cq_layer;
 
@@ -94,6 +94,15 @@ int cq_layer_prepare(const cq_layer* layer, const uint8_t* qweight, const void* 
 /* Inverse GPU re-pack: stream layout -> reference buffers (byte-identical round trip). */
 int cq_layer_unprepare(const cq_layer* layer, uint8_t* qweight, void* scales_f16,
                        void* cherry_weight_f16, int16_t* cherry_indices, cq_stream_t stream);
+
+/* Tracing hook (no counterpart in the reference, which only has host wall-clock timers,
+ * benchmark_speed.py:8-17): when device_buffer (1024 x 64 uint64, device memory) is not NULL,
+ * each CTA of later cq_layer_matvec launches stores nanosecond %globaltimer stamps of its
+ * phases there: 0 entry, 1 barriers ready, 2 layer constants staged, 3 previous kernel done,
+ * 4 activations staged, 5 first weights landed, 6 last granule done, 7 exit, 8/9 first and
+ * last bulk copy issued, 16+c consumer passed the wait for ring copy c, 40+c copy c issued
+ * (c < 24).  Pass NULL to switch it off. */
+int cq_trace_set_timeline(void* device_buffer);
 
 /* Bytes of scratch the matvec needs on a device (cross-CTA partial sums and flags).
  * The scratch must be zero-filled once before its first use and must not be shared

@@ -29,7 +29,8 @@ class NativeLibraryMissing(RuntimeError):
 
 
 def lib_path() -> str:
-    return os.path.join(_HERE, "libcherryq.so")
+    """libcherryq.so next to this file; CHERRYQ_LIB overrides it (to try another build)."""
+    return os.environ.get("CHERRYQ_LIB") or os.path.join(_HERE, "libcherryq.so")
 
 
 def ext_path() -> str:

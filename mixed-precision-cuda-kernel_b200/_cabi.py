@@ -16,14 +16,14 @@ SYMBOLS = [
     "cq_vecquant4matmul_cherryq", "cq_vecquant3matmul_cherryq",
     "cq_dequantize3_normal", "cq_dequantize4_normal",
     "cq_cache_clear", "cq_cache_stats", "cq_poll",
-    "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense",
+    "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense", "cq_trace_set_timeline",
 ]
 
 
 class cq_layer(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
                 ("bits", "K", "N", "C", "G", "Kc", "Kp", "Cp", "n_gran", "n_sub", "sets", "gran_bytes", "cher_bytes")]
-    _fields_ += [(n, C.c_uint64) for n in ("off_stream", "off_cherry", "off_perm", "off_cidx", "blob_bytes")]
+    _fields_ += [(n, C.c_uint64) for n in ("off_stream", "off_cherry", "off_osh", "off_cidx", "blob_bytes")]
     _fields_ += [("blob", C.c_void_p)]
 
 
@@ -54,6 +54,7 @@ def lib():
     L.cq_dequantize4_normal.argtypes = [vp, vp, vp] + [i32] * 5 + [vp]
     L.cq_cache_stats.argtypes = [C.POINTER(C.c_int), C.POINTER(C.c_uint64)]
     L.cq_poll.argtypes = [vp]
+    L.cq_trace_set_timeline.argtypes = [vp]
     L.cq_pack.argtypes = [vp, i32, vp] + [i32] * 5 + [vp] * 6
     L.cq_unpack_dense.argtypes = [vp] * 4 + [i32] * 5 + [vp, vp]
     _lib = L

@@ -7,7 +7,7 @@
 //   granule   = one sub-tile x 128 consecutive COMPACT columns k' (cherry columns
 //               removed, original order kept) — the unit of work distribution
 //   stream    = n_sub x n_gran granules, sub-tile major, each `gran_bytes` long:
-//                 [codes: 16 rows x 128 codes x bits/8][scales: sets x 16 fp16]
+//                 [codes: 16 rows x 128 codes x bits/8][scales: sets x 8 x (row g, row g+8) fp16]
 //
 // Codes inside a granule are stored in the order a warp consumes them with
 // mma.sync.m16n8k16 (A = 16 rows x 16 k' of weights, B = 16 k' x 8 batch):
@@ -27,7 +27,8 @@
 //
 //   cherry stream = n_sub blocks of (Cp/16) x [lane][16 B] fp16 A-fragments:
 //          a0 = W[c=16j+2t, 2t+1][row g], a1 = same c, row g+8, a2/a3 = c + 8.
-//   perm  = Kp uint16: original column of compact column k' (0xFFFF past K').
+//   osh   = Kp/8 uint32: per octet of compact columns, how far its first | last << 16 column is
+//          shifted in the original row (number of cherry columns before it); ~0 past K'.
 //   cidx  = Cp uint16: sorted cherry columns (0xFFFF past C).
 #pragma once
 

@@ -81,7 +81,7 @@ __global__ void prepare_scales_kernel(LayoutDims d, const __half* __restrict__ s
        id += (long long)gridDim.x * blockDim.x) {
     const long long gran = id / per;
     const int e = (int)(id % per);
-    const int sp = e >> 4, r = e & 15;
+    const int sp = e >> 4, r = ((e & 15) >> 1) + 8 * (e & 1);   // [set][g][row g, row g+8]
     const int sub = (int)(gran / d.n_gran), gi = (int)(gran % d.n_gran);
     const int n = sub * 16 + r;
     const int kc0 = gi * 128 + sp * (128 / d.sets);
@@ -114,22 +114,30 @@ __global__ void prepare_cherry_kernel(LayoutDims d, const __half* __restrict__ c
 }
 
 // ---------------------------------------------------------------- prepare: index maps
-// Compact column kc -> original column: kc + #{m : idx[m] - m <= kc}, the
-// reference kernel's upper-bound search (csrc/quant_cuda_kernel.cu:785-795).
-__global__ void prepare_perm_kernel(LayoutDims d, const int16_t* __restrict__ idx,
-                                    uint16_t* __restrict__ perm, uint16_t* __restrict__ cidx) {
+// Compact column kc sits at original column kc + shift(kc), shift(kc) = #{m : idx[m] - m <= kc},
+// the reference kernel's upper-bound search (csrc/quant_cuda_kernel.cu:785-795).  Stored per
+// octet of compact columns: shift of its first column | shift of its last column << 16
+// (equal unless a cherry column falls inside the octet); 0xFFFFFFFF past K'.
+__global__ void prepare_index_kernel(LayoutDims d, const int16_t* __restrict__ idx,
+                                     uint32_t* __restrict__ osh, uint16_t* __restrict__ cidx) {
   const int id = blockIdx.x * blockDim.x + threadIdx.x;
-  if (id < d.Kp) {
-    uint16_t v = CQ_PAD_COL;
-    if (id < d.Kc) {
-      int low = 0, high = d.C;
-      while (low < high) {
-        const int mid = (low + high) >> 1;
-        if ((int)idx[mid] - mid <= id) low = mid + 1; else high = mid;
+  if (id < d.Kp / 8) {
+    uint32_t v = 0xFFFFFFFFu;
+    const int k0 = 8 * id;
+    if (k0 < d.Kc) {
+      int sh[2];
+      for (int e = 0; e < 2; ++e) {
+        const int k = k0 + 7 * e;
+        int low = 0, high = d.C;
+        while (low < high) {
+          const int mid = (low + high) >> 1;
+          if ((int)idx[mid] - mid <= k) low = mid + 1; else high = mid;
+        }
+        sh[e] = low;
       }
-      v = (uint16_t)(id + low);
+      v = (uint32_t)sh[0] | ((uint32_t)sh[1] << 16);
     }
-    perm[id] = v;
+    osh[id] = v;
   }
   if (id < d.Cp) cidx[id] = (id < d.C) ? (uint16_t)idx[id] : (uint16_t)CQ_PAD_COL;
 }
@@ -180,7 +188,7 @@ __global__ void unprepare_scales_kernel(LayoutDims d, const uint8_t* __restrict_
     const int kc0 = grp * d.G;
     const int gi = kc0 >> 7, sp = (kc0 & 127) / (128 / d.sets);
     const uint8_t* gran = stream + ((size_t)(n >> 4) * d.n_gran + gi) * d.gran_bytes;
-    scales[id] = reinterpret_cast<const __half*>(gran + code_bytes(d))[sp * 16 + (n & 15)];
+    scales[id] = reinterpret_cast<const __half*>(gran + code_bytes(d))[sp * 16 + 2 * (n & 7) + ((n >> 3) & 1)];
   }
 }
 
@@ -233,7 +241,7 @@ extern "C" int cq_layer_init(cq_layer* L, int bits, int K, int N, int C, int G, 
   size_t off = 0;
   L->off_stream = off; off = align256(off + (size_t)L->n_sub * L->n_gran * L->gran_bytes);
   L->off_cherry = off; off = align256(off + (size_t)L->n_sub * L->cher_bytes);
-  L->off_perm = off;   off = align256(off + (size_t)L->Kp * 2);
+  L->off_osh = off;    off = align256(off + (size_t)(L->Kp / 8) * 4);
   L->off_cidx = off;   off = align256(off + (size_t)(L->Cp ? L->Cp : 16) * 2);
   L->blob_bytes = off;
   L->blob = blob;
@@ -256,9 +264,9 @@ extern "C" int cq_layer_prepare(const cq_layer* L, const uint8_t* qweight, const
   if (d.Cp > 0)
     prepare_cherry_kernel<<<blocks_for((long long)d.n_sub * (d.Cp / 16) * 256, T), T, 0, st>>>(
         d, (const __half*)cherry_weight, (__half*)(blob + L->off_cherry));
-  const int m = d.Kp > d.Cp ? d.Kp : d.Cp;
-  prepare_perm_kernel<<<(m + T - 1) / T, T, 0, st>>>(d, cherry_indices, (uint16_t*)(blob + L->off_perm),
-                                                     (uint16_t*)(blob + L->off_cidx));
+  const int m = d.Kp / 8 > d.Cp ? d.Kp / 8 : d.Cp;
+  prepare_index_kernel<<<(m + T - 1) / T, T, 0, st>>>(d, cherry_indices, (uint32_t*)(blob + L->off_osh),
+                                                      (uint16_t*)(blob + L->off_cidx));
   CQ_CUDA_TRY(cudaGetLastError());
   return CQ_OK;
 }

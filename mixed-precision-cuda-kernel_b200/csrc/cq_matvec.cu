@@ -10,46 +10,46 @@
 //    (16 rows x 128 compact columns).  CTA c owns the contiguous granule range
 //    [T*c/grid, T*(c+1)/grid): an equal byte share whatever N and K are.
 //  * A producer warp moves the range into a shared-memory ring with 1-D bulk
-//    async copies (cp.async.bulk + mbarrier transaction counts), up to 8 granules
-//    per copy.  It starts before the kernel waits for the previous kernel in the
-//    stream (programmatic dependent launch): weights never depend on it.
-//  * 8 consumer warps take the granules of a copy round-robin.  A lane reads its
-//    16 (4-bit) or 24 (3-bit) bytes, turns codes into fp16 pairs with one
-//    mask-or per pair (exponent trick) and one HFMA2, and feeds
-//    mma.sync.m16n8k16 with the activations (staged once in shared memory in
-//    compact order) as the B operand.  Group scales are applied per granule in
-//    fp32.
+//    async copies (cp.async.bulk + mbarrier transaction counts), NCW * GPW
+//    granules per copy.  It starts before the kernel waits for the previous kernel
+//    in the stream (programmatic dependent launch): weights never depend on it.
+//  * NCW consumer warps take the granules of a copy round-robin, GPW each.  A lane
+//    reads its 16 (4-bit) or 24 (3-bit) bytes, turns codes into fp16 pairs with one
+//    AND-OR per pair (exponent trick, offsets folded into a per-group correction
+//    computed while the activations are staged), and feeds mma.sync.m16n8k16 with
+//    the activations (staged once in shared memory in compact order) as the B
+//    operand.  Group scales are applied per granule in fp32.
 //  * A range is walked from its last sub-tile to its first.  A sub-tile cut by a
 //    range boundary is finished by the CTA that holds its end: CTAs holding an
 //    earlier part post their fp32 partial to global scratch early in their walk,
 //    the finishing CTA adds the partials in a fixed order late in its walk.  All
 //    sums are therefore deterministic.  Every wait is bounded; running out sets
 //    a bit in the status word instead of hanging.
+#include <cstdlib>
+
 #include "cq_common.cuh"
 
 namespace {
 
-constexpr int NCW = 8;                 // consumer warps
-constexpr int NTHREADS = (NCW + 1) * 32;
-constexpr int NCONS = NCW * 32;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 struct MatvecParams {
   const uint8_t* stream;
   const uint8_t* cstream;
-  const uint16_t* perm;
   const uint16_t* cidx;
+  const uint32_t* osh;
   const __half* x;
   __half* y;
   float* partial;      // [grid][256]
   uint32_t* flag;      // [grid]
   uint32_t* status;    // may be null
+  unsigned long long* timeline;  // may be null: [grid][64] %globaltimer stamps (tracing)
   int M, K, N, C, Cp, Kp, n_gran, n_sub, gran_bytes, cher_bytes;
   int ldx, ldy, accumulate;
   uint32_t T;          // total granules
   int stages, nslot, max_cher;
   // shared-memory offsets
-  int off_ring, off_cher, off_xs, off_xc, off_slot, off_bar;
+  int off_ring, off_cher, off_xs, off_xc, off_cidx, off_osh, off_corr, off_slot, off_pf, off_bar;
   int xs_stride;       // halves per activation row in smem (Kp + 8)
   int xc_stride;       // halves per cherry-activation row (Cp + 8)
 };
@@ -78,8 +78,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: gives up after WAIT_LIMIT polls (or at once when the CTA already
 // gave up somewhere), records the failure and lets the caller carry on.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t* status) {
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            uint32_t* status) {
   const uint32_t limit = *abort_flag ? 1u : WAIT_LIMIT;
   for (uint32_t it = 0; it < limit; ++it)
     if (mbar_try_wait(bar, parity)) return true;
@@ -87,11 +87,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (status) atomicOr(status, 1u);
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status);
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+template <int NCONS>
 __device__ __forceinline__ void bar_consumers() {
   asm volatile("bar.sync 1, %0;" ::"n"(NCONS) : "memory");
 }
@@ -102,11 +108,6 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
 __device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -115,51 +116,199 @@ __device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
 __device__ __forceinline__ void st_release(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-
-// fp16x2 constants
-constexpr uint32_t MAGIC = 0x64006400u;  // (1024, 1024)
-// 4-bit: field at mantissa bit 2 -> 1024 + 4u, at bit 6 -> 1024 + 64u; u - 7.5 in one FMA
-constexpr uint32_t S4_MUL_P2 = 0x34003400u;  // 0.25
-constexpr uint32_t S4_ADD_P2 = 0xDC1EDC1Eu;  // -263.5
-constexpr uint32_t S4_MUL_P6 = 0x24002400u;  // 1/64
-constexpr uint32_t S4_ADD_P6 = 0xCDE0CDE0u;  // -23.5
-// 3-bit: fields at mantissa bits 1, 4, 7; u - 3.5
-constexpr uint32_t S3_MUL_P1 = 0x38003800u;  // 0.5
-constexpr uint32_t S3_ADD_P1 = 0xE007E007u;  // -515.5
-constexpr uint32_t S3_MUL_P4 = 0x2C002C00u;  // 1/16
-constexpr uint32_t S3_ADD_P4 = 0xD438D438u;  // -67.5
-constexpr uint32_t S3_MUL_P7 = 0x20002000u;  // 1/128
-constexpr uint32_t S3_ADD_P7 = 0xC9C0C9C0u;  // -11.5
-
-// One 4-bit stream word -> 4 fp16 pairs (codes (0,1), (2,3), (4,5), (6,7)), each u - 7.5.
-__device__ __forceinline__ void dequant4(uint32_t w, uint32_t* out) {
-  const uint32_t v1 = w << 2, v2 = w >> 6;
-  out[0] = hfma2_u32((v1 & 0x003C003Cu) | MAGIC, S4_MUL_P2, S4_ADD_P2);
-  out[1] = hfma2_u32((v1 & 0x03C003C0u) | MAGIC, S4_MUL_P6, S4_ADD_P6);
-  out[2] = hfma2_u32((v2 & 0x003C003Cu) | MAGIC, S4_MUL_P2, S4_ADD_P2);
-  out[3] = hfma2_u32((v2 & 0x03C003C0u) | MAGIC, S4_MUL_P6, S4_ADD_P6);
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
 
-// Three 3-bit stream words of one row -> 16 fp16 pairs (codes (2q, 2q+1)), each u - 3.5.
-__device__ __forceinline__ void dequant3(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t* out) {
+__device__ __forceinline__ void stamp(const MatvecParams& p, int slot) {
+  if (p.timeline) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.timeline[(size_t)blockIdx.x * 64 + slot] = t;
+  }
+}
+
+// ------------------------------------------------------------------ decode
+// Codes become fp16 values with one AND-OR each: OR-ing a code field that sits at
+// mantissa bit p into the bit pattern of 1024.0 gives the fp16 number 1024 + 2^p * u.
+// No subtraction follows.  Instead the activation that meets this code in the MMA is
+// pre-multiplied by 2^(c-p) when it is staged, so that the product is
+// 2^c * (B + u) * x with B = 2^(10-p), and the excess (B + off) * x, summed per
+// group while staging ("corr"), is removed in fp32 when the group scale is applied:
+//     y += s * (acc * 2^-c - corr).
+// p is a function of the code's position only, so both sides agree by layout.
+constexpr uint32_t MAGIC = 0x64006400u;  // (1024, 1024)
+
+template <int BITS> struct Fold;
+template <> struct Fold<4> {
+  static constexpr int C_EXP = 2;                 // products carry 2^2
+  static constexpr float OFF = 7.5f;
+};
+template <> struct Fold<3> {
+  static constexpr int C_EXP = 1;
+  static constexpr float OFF = 3.5f;
+};
+// Mantissa bit p of the code field of pair q.  4-bit: q = (position >> 1) in the lane's
+// 16 codes of a 64-column half (even -> 2, odd -> 6).  3-bit: q = 0..15 over the row's 32
+// codes of the granule (word slot q % 5 -> 1, 4, 7, 4, 7; pair 15 -> 7).
+template <int BITS>
+__device__ __forceinline__ int fold_p(int q) {
+  if (BITS == 4) return (q & 1) ? 6 : 2;
+  const int r = q % 5;
+  return q == 15 ? 7 : (r == 0 ? 1 : ((r & 1) ? 4 : 7));
+}
+
+// One 4-bit stream word -> 4 fp16 pairs (codes (0,1), (2,3), (4,5), (6,7)): 1024 + 4u, 1024 + 64u, ...
+__device__ __forceinline__ void decode4(uint32_t w, uint32_t* out) {
+  const uint32_t v1 = w << 2, v2 = w >> 6;
+  out[0] = (v1 & 0x003C003Cu) | MAGIC;
+  out[1] = (v1 & 0x03C003C0u) | MAGIC;
+  out[2] = (v2 & 0x003C003Cu) | MAGIC;
+  out[3] = (v2 & 0x03C003C0u) | MAGIC;
+}
+
+// Three 3-bit stream words of one row -> 16 fp16 pairs (codes (2q, 2q+1)).
+__device__ __forceinline__ void decode3(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t* out) {
   const uint32_t w[3] = {w0, w1, w2};
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
-    const uint32_t v = w[i] >> 9;
-    out[5 * i + 0] = hfma2_u32((w[i] & 0x000E000Eu) | MAGIC, S3_MUL_P1, S3_ADD_P1);
-    out[5 * i + 1] = hfma2_u32((w[i] & 0x00700070u) | MAGIC, S3_MUL_P4, S3_ADD_P4);
-    out[5 * i + 2] = hfma2_u32((w[i] & 0x03800380u) | MAGIC, S3_MUL_P7, S3_ADD_P7);
-    out[5 * i + 3] = hfma2_u32((v & 0x000E000Eu) | MAGIC, S3_MUL_P1, S3_ADD_P1);
-    out[5 * i + 4] = hfma2_u32((v & 0x00700070u) | MAGIC, S3_MUL_P4, S3_ADD_P4);
+    const uint32_t v = w[i] >> 6;
+    out[5 * i + 0] = (w[i] & 0x000E000Eu) | MAGIC;   // field at bit 1
+    out[5 * i + 1] = (w[i] & 0x00700070u) | MAGIC;   // field at bit 4
+    out[5 * i + 2] = (w[i] & 0x03800380u) | MAGIC;   // field at bit 7
+    out[5 * i + 3] = (v & 0x00700070u) | MAGIC;      // field at bit 10 -> 4
+    out[5 * i + 4] = (v & 0x03800380u) | MAGIC;      // field at bit 13 -> 7
   }
-  uint32_t r = ((w0 << 1) & 0x00020002u) | MAGIC;
-  r |= (w1 << 2) & 0x00040004u;
-  r |= (w2 << 3) & 0x00080008u;
-  out[15] = hfma2_u32(r, S3_MUL_P1, S3_ADD_P1);
+  uint32_t r = ((w0 << 7) & 0x00800080u) | MAGIC;    // pair 15: one bit from each word, at bits 7..9
+  r |= (w1 << 8) & 0x01000100u;
+  r |= (w2 << 9) & 0x02000200u;
+  out[15] = r;
 }
 
-template <int BITS, int SETS, int MB>
-__global__ void __launch_bounds__(NTHREADS, 1) cq_matvec_kernel(const MatvecParams p) {
+// R granules (16 rows x 128 compact columns each) for one warp, in one straight-line
+// block so that their independent MMA chains interleave: adds s * (sum - corr) to tot.
+//   gran[r]  granule bytes in the ring        xoff[r]  granule's first column (halves)
+//   corr_g[r] the granule's correction row    xrow[b]  lane's activation row pointer
+template <int BITS, int SETS, int MB, int R>
+__device__ __forceinline__ void process_granules(const uint8_t* const* gran, const uint32_t* xoff,
+                                                 const float* const* corr_g, const __half* const* xrow,
+                                                 int lane, float (&tot)[MB][4]
+#ifdef CQ_TRACE_INNER
+                                                 , unsigned long long* itr
+#endif
+                                                 ) {
+#ifdef CQ_TRACE_INNER
+#define ITR(k) do { if (itr) itr[k] = clock64(); } while (0)
+#else
+#define ITR(k) do { } while (0)
+#endif
+  const int g = lane >> 2, t = lane & 3;
+  ITR(0);
+  // scales of rows (g, g+8) sit next to each other: [set][g][2]; corr: [set][8 * MB] floats per
+  // granule, this lane's columns are 8b + 2t, + 1.  Loaded first: they are needed last.
+  float2 s_lo[R], s_hi[R], c_lo[R][MB], c_hi[R][MB];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const __half2* sc = reinterpret_cast<const __half2*>(gran[r] + 256 * BITS);
+    s_lo[r] = __half22float2(sc[g]);
+    s_hi[r] = (SETS == 2) ? __half22float2(sc[8 + g]) : s_lo[r];
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+      c_lo[r][b] = *reinterpret_cast<const float2*>(corr_g[r] + 8 * b + 2 * t);
+      c_hi[r][b] = (SETS == 2) ? *reinterpret_cast<const float2*>(corr_g[r] + 8 * MB + 8 * b + 2 * t) : c_lo[r][b];
+    }
+  }
+  // Two accumulators per (granule, half): the four MMAs of a half alternate between them, so
+  // that no MMA waits for the one issued just before it.
+  float acc[R][2][2][MB][4];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int b = 0; b < MB; ++b)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[r][h][j][b][e] = 0.f;
+
+  uint32_t A0[R][16], A1[R][16];  // fp16 pairs of rows g and g+8 (8 per 64-column half)
+  if (BITS == 3) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint2* wp = reinterpret_cast<const uint2*>(gran[r] + lane * 24);
+      const uint2 u0 = wp[0], u1 = wp[1], u2 = wp[2];
+      decode3(u0.x, u0.y, u1.x, A0[r]);
+      decode3(u1.y, u2.x, u2.y, A1[r]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (BITS == 4) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const uint4 w = *reinterpret_cast<const uint4*>(gran[r] + h * 512 + lane * 16);
+        decode4(w.x, A0[r] + 8 * h);
+        decode4(w.y, A0[r] + 8 * h + 4);
+        decode4(w.z, A1[r] + 8 * h);
+        decode4(w.w, A1[r] + 8 * h + 4);
+      }
+    }
+    ITR(1 + 3 * h);
+    uint32_t X[R][MB][8];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int b = 0; b < MB; ++b) {
+        const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + xoff[r] + h * 64);
+        const uint4 xa = xp[0], xb = xp[1];
+        X[r][b][0] = xa.x; X[r][b][1] = xa.y; X[r][b][2] = xa.z; X[r][b][3] = xa.w;
+        X[r][b][4] = xb.x; X[r][b][5] = xb.y; X[r][b][6] = xb.z; X[r][b][7] = xb.w;
+      }
+    ITR(2 + 3 * h);
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int b = 0; b < MB; ++b)
+          mma16816(acc[r][h][m & 1][b], A0[r][8 * h + 2 * m], A1[r][8 * h + 2 * m], A0[r][8 * h + 2 * m + 1],
+                   A1[r][8 * h + 2 * m + 1], X[r][b][2 * m], X[r][b][2 * m + 1]);
+    ITR(3 + 3 * h);
+  }
+  const float inv = 1.f / (float)(1 << Fold<BITS>::C_EXP);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+      float a0[4], a1[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        a0[e] = acc[r][0][0][b][e] + acc[r][0][1][b][e];
+        a1[e] = acc[r][1][0][b][e] + acc[r][1][1][b][e];
+      }
+      if (SETS == 2) {
+        tot[b][0] += s_lo[r].x * (a0[0] * inv - c_lo[r][b].x) + s_hi[r].x * (a1[0] * inv - c_hi[r][b].x);
+        tot[b][1] += s_lo[r].x * (a0[1] * inv - c_lo[r][b].y) + s_hi[r].x * (a1[1] * inv - c_hi[r][b].y);
+        tot[b][2] += s_lo[r].y * (a0[2] * inv - c_lo[r][b].x) + s_hi[r].y * (a1[2] * inv - c_hi[r][b].x);
+        tot[b][3] += s_lo[r].y * (a0[3] * inv - c_lo[r][b].y) + s_hi[r].y * (a1[3] * inv - c_hi[r][b].y);
+      } else {
+        tot[b][0] += s_lo[r].x * ((a0[0] + a1[0]) * inv - c_lo[r][b].x);
+        tot[b][1] += s_lo[r].x * ((a0[1] + a1[1]) * inv - c_lo[r][b].y);
+        tot[b][2] += s_lo[r].y * ((a0[2] + a1[2]) * inv - c_lo[r][b].x);
+        tot[b][3] += s_lo[r].y * ((a0[3] + a1[3]) * inv - c_lo[r][b].y);
+      }
+    }
+  }
+  ITR(7);
+}
+
+template <int BITS, int SETS, int MB, int NCW, int GPW, int MINB>
+__global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const MatvecParams p) {
+  constexpr int NCONS = NCW * 32;
+  constexpr int CHUNK = NCW * GPW;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_abort;
 
@@ -171,19 +320,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) cq_matvec_kernel(const MatvecPara
   const uint32_t GB = (uint32_t)p.gran_bytes;
 
   const uint32_t bar_base = smem_u32(smem + p.off_bar);
-  const int S = p.stages;
+  const uint32_t S = (uint32_t)p.stages;
   // barriers: full[s] at bar_base + 8 s, empty[s] at bar_base + 8 (S + s), cherry at 8 * 2S
   if (tid == 0) {
+    stamp(p, 0);
+    if (p.timeline) p.timeline[(size_t)blockIdx.x * 64 + 10] = (unsigned long long)clock64();
     s_abort = 0;
-    for (int s = 0; s < S; ++s) {
+    for (uint32_t s = 0; s < S; ++s) {
       mbar_init(bar_base + 8 * s, 1);
       mbar_init(bar_base + 8 * (S + s), NCW);
     }
     mbar_init(bar_base + 16 * S, 1);
+    mbar_init(bar_base + 16 * S + 8, 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
+  if (tid == 0) stamp(p, 1);
   // Let the next kernel in the stream start its own prologue and weight prefetch.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (ga >= gb) return;  // (host launches grid <= T, so this does not happen)
@@ -202,43 +355,202 @@ __global__ void __launch_bounds__(NTHREADS, 1) cq_matvec_kernel(const MatvecPara
         bulk_g2s(smem_u32(smem + p.off_cher), p.cstream + (size_t)jc_lo * p.cher_bytes, bytes,
                  bar_base + 16 * S);
       }
-      uint32_t cc = 0;
+      const uint32_t ring = smem_u32(smem + p.off_ring);
+      uint32_t stage = 0, phase = 1;   // empty barriers: the first pass over the ring needs no wait
+      bool first_pass = true;
+      int nchunk = 0;
+      stamp(p, 8);
       for (int i = 0; i < npieces; ++i) {
         const uint32_t j = j_hi - i;
         const uint32_t start = max(ga, j * NG), end = min(gb, (j + 1) * NG);
-        for (uint32_t q0 = start; q0 < end; q0 += NCW, ++cc) {
-          const uint32_t len = min((uint32_t)NCW, end - q0);
-          const uint32_t s = cc % S;
-          if (cc >= (uint32_t)S) mbar_wait(bar_base + 8 * (S + s), ((cc / S) - 1) & 1, &s_abort, p.status);
-          mbar_expect_tx(bar_base + 8 * s, len * GB);
-          bulk_g2s(smem_u32(smem + p.off_ring) + s * NCW * GB, p.stream + (size_t)q0 * GB, len * GB,
-                   bar_base + 8 * s);
+        for (uint32_t q0 = start; q0 < end; q0 += CHUNK) {
+          const uint32_t len = min((uint32_t)CHUNK, end - q0);
+          if (!first_pass) mbar_wait(bar_base + 8 * (S + stage), phase, &s_abort, p.status);
+          if (nchunk < 24) stamp(p, 40 + nchunk);
+          ++nchunk;
+          mbar_expect_tx(bar_base + 8 * stage, len * GB);
+          bulk_g2s(ring + stage * CHUNK * GB, p.stream + (size_t)q0 * GB, len * GB, bar_base + 8 * stage);
+          if (++stage == S) { stage = 0; phase ^= 1; first_pass = false; }
         }
       }
+      stamp(p, 9);
+    }
+    // The sub-tile at the head of this range may have been started by earlier CTAs, which posted
+    // their partials early in their walk.  Fetch them now (this warp is idle) so that the
+    // consumers find the sum in shared memory when they finish the sub-tile.  The scratch may
+    // still hold the previous launch's flags until that launch has completed: wait for it first.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    {
+      float* pf = reinterpret_cast<float*>(smem + p.off_pf);
+      const uint32_t s0g = j_lo * NG;
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+      if (ga > s0g && gb >= s0g + NG) {
+        const uint32_t c_first = (uint32_t)((((uint64_t)s0g + 1) * grid - 1) / p.T);
+        for (uint32_t c = c_first; c < cta; ++c) {
+          bool ok = false;
+          const uint32_t limit = s_abort ? 1u : WAIT_LIMIT;
+          for (uint32_t it = 0; it < limit; ++it) {
+            if (ld_acquire(p.flag + c) != 0) { ok = true; break; }
+            __nanosleep(64);
+          }
+          if (!ok) {
+            s_abort = 1;
+            if (p.status) atomicOr(p.status, 2u);
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] += __ldcg(p.partial + (size_t)c * 256 + e * 32 + lane);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) pf[e * 32 + lane] = v[e];
+      mbar_arrive(bar_base + 16 * S + 8);   // release: the consumers wait on this barrier
     }
     return;
   }
 
   // ------------------------------------------------------------------ consumers
-  // Everything below may read what the previous kernel in the stream wrote.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-
+  // Layer constants first (they do not depend on the previous kernel): the sorted cherry
+  // columns and, per octet of compact columns, how far its first and last column are shifted
+  // in the original row (see cq_common.cuh).
   __half* xs = reinterpret_cast<__half*>(smem + p.off_xs);
   __half* xc = reinterpret_cast<__half*>(smem + p.off_xc);
-  for (int idx = tid; idx < p.M * p.Kp; idx += NCONS) {
-    const int m = idx / p.Kp, k = idx - m * p.Kp;
-    const uint32_t o = p.perm[k];
-    xs[m * p.xs_stride + k] = (o != CQ_PAD_COL) ? p.x[(size_t)m * p.ldx + o] : __float2half(0.f);
+  float* corr = reinterpret_cast<float*>(smem + p.off_corr);
+  uint16_t* cidx_s = reinterpret_cast<uint16_t*>(smem + p.off_cidx);
+  uint32_t* osh = reinterpret_cast<uint32_t*>(smem + p.off_osh);
+  const int noct = p.Kp >> 3;
+  const int Kc = p.K - p.C;
+  for (int c = tid; c < p.Cp; c += NCONS) cidx_s[c] = p.cidx[c];
+  // corr entries of activation rows that do not exist must read as zero
+  for (int i = tid; i < (int)NG * SETS * 8 * MB; i += NCONS) corr[i] = 0.f;
+  for (int o = tid; o < noct; o += NCONS) osh[o] = p.osh[o];
+  bar_consumers<NCONS>();
+  if (tid == 0) stamp(p, 2);
+
+  // Everything below may read what the previous kernel in the stream wrote.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (tid == 0) stamp(p, 3);
+
+  // Activations of the cherry columns: issue the loads now, store them after the main gather,
+  // so that both cost one trip to L2 together.
+  constexpr int XCU = 2;
+  __half xcv[XCU];
+#pragma unroll
+  for (int u = 0; u < XCU; ++u) {
+    const int idx = tid + u * NCONS;
+    xcv[u] = __float2half(0.f);
+    if (idx < p.M * p.Cp) {
+      const int m = idx / p.Cp, c = idx - m * p.Cp;
+      const uint32_t o = cidx_s[c];
+      if (o != CQ_PAD_COL) xcv[u] = __ldg(p.x + (size_t)m * p.ldx + o);
+    }
   }
-  for (int idx = tid; idx < p.M * p.Cp; idx += NCONS) {
+  {
+    // xs[m][k'] = 2^(c-p(k')) * x[m][orig(k')] for the compact columns, 8 at a time (zero past K'),
+    // and corr[granule][set][m] = sum over the group of (B + off) * x.
+    const int nitem = noct * p.M;
+    constexpr int U = 8;
+    constexpr int CE = Fold<BITS>::C_EXP;
+    for (int base = 0; base < nitem; base += NCONS * U) {
+      uint32_t v[U][4];
+      int dsto[U], mrow[U], oct[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int it = base + u * NCONS + tid;
+        dsto[u] = -1;
+        mrow[u] = 0;
+        oct[u] = 0;
+        v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0u;
+        if (it < nitem) {
+          const int m = (p.M == 1) ? 0 : it / noct;
+          const int o = it - m * noct;
+          const int k0 = 8 * o;
+          dsto[u] = m * p.xs_stride + k0;
+          mrow[u] = m;
+          oct[u] = o;
+          const uint32_t sh = osh[o];
+          if (sh != 0xFFFFFFFFu) {
+            const int Kc_unused = Kc; (void)Kc_unused;
+            const int lo0 = (int)(sh & 0xFFFFu), lo7 = (int)(sh >> 16);
+            const __half* xr = p.x + (size_t)m * p.ldx;
+            if (lo7 == lo0) {
+              const int src = k0 + lo0;
+              if ((src & 1) == 0 && (((uintptr_t)xr) & 3) == 0) {
+                const uint32_t* s32 = reinterpret_cast<const uint32_t*>(xr + src);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[u][i] = __ldg(s32 + i);
+              } else {
+                const unsigned short* s16 = reinterpret_cast<const unsigned short*>(xr + src);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  v[u][i] = (uint32_t)__ldg(s16 + 2 * i) | ((uint32_t)__ldg(s16 + 2 * i + 1) << 16);
+              }
+            } else {
+              unsigned short h[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                int lo = lo0, hi = lo7;
+                while (lo < hi) {
+                  const int mid = (lo + hi) >> 1;
+                  if ((int)cidx_s[mid] - mid <= k0 + i) lo = mid + 1; else hi = mid;
+                }
+                h[i] = __ldg(reinterpret_cast<const unsigned short*>(xr + k0 + i + lo));
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) v[u][i] = (uint32_t)h[2 * i] | ((uint32_t)h[2 * i + 1] << 16);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        // first pair index of this octet among the row's pairs of the granule
+        const int oo = oct[u] & 15;
+        const int q0 = (BITS == 4) ? 0 : 8 * (oo >> 3) + 4 * (oo & 1);
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int pp = fold_p<BITS>(q0 + i);
+          const uint32_t sc16 = (uint32_t)((15 + CE - pp) << 10);                 // fp16 2^(c-p)
+          const uint32_t scaled = hmul2_u32(v[u][i], sc16 | (sc16 << 16));
+          const float coef = __int_as_float((127 + pp - CE) << 23) *              // 2^(p-c) * (B + off)
+                             ((float)(1 << (10 - pp)) + Fold<BITS>::OFF);
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&scaled));
+          part += (f.x + f.y) * coef;
+          v[u][i] = scaled;
+        }
+        // 16 (8 for 64-wide groups) neighbouring lanes hold the octets of one group of one row
+#pragma unroll
+        for (int d = 1; d < 16 / SETS; d <<= 1) part += __shfl_xor_sync(0xffffffffu, part, d);
+        if (dsto[u] >= 0) {
+          *reinterpret_cast<uint4*>(xs + dsto[u]) = make_uint4(v[u][0], v[u][1], v[u][2], v[u][3]);
+          if ((oct[u] & (16 / SETS - 1)) == 0) {
+            const int gi = oct[u] >> 4, sp = (SETS == 2) ? ((oct[u] >> 3) & 1) : 0;
+            corr[(gi * SETS + sp) * 8 * MB + mrow[u]] = part;
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < XCU; ++u) {
+    const int idx = tid + u * NCONS;
+    if (idx < p.M * p.Cp) {
+      const int m = idx / p.Cp, c = idx - m * p.Cp;
+      xc[m * p.xc_stride + c] = xcv[u];
+    }
+  }
+  for (int idx = tid + XCU * NCONS; idx < p.M * p.Cp; idx += NCONS) {
     const int m = idx / p.Cp, c = idx - m * p.Cp;
-    const uint32_t o = p.cidx[c];
+    const uint32_t o = cidx_s[c];
     xc[m * p.xc_stride + c] = (o != CQ_PAD_COL) ? p.x[(size_t)m * p.ldx + o] : __float2half(0.f);
   }
-  bar_consumers();
+  bar_consumers<NCONS>();
+  if (tid == 0) stamp(p, 4);
 
   const int g = lane >> 2, t = lane & 3;
-  float4* slots = reinterpret_cast<float4*>(smem + p.off_slot);
+  float* slots = reinterpret_cast<float*>(smem + p.off_slot);   // [slot][warp][m][16 rows]
   const uint8_t* ring = smem + p.off_ring;
   const uint8_t* cher = smem + p.off_cher;
 
@@ -248,117 +560,107 @@ __global__ void __launch_bounds__(NTHREADS, 1) cq_matvec_kernel(const MatvecPara
 #pragma unroll
     for (int r = 0; r < 4; ++r) tot[b][r] = 0.f;
 
-  bool xrow_ok[MB];
+  // B-operand column g of activation tile b is activation row 8b + g.  Columns past the last
+  // row are never read back from the accumulators, so they may carry any existing row.
   const __half* xrow[MB];
   const __half* xcrow[MB];
 #pragma unroll
   for (int b = 0; b < MB; ++b) {
-    const int m = 8 * b + g;
-    xrow_ok[b] = m < p.M;
-    xrow[b] = xs + (xrow_ok[b] ? m : 0) * p.xs_stride + 16 * t;
-    xcrow[b] = xc + (xrow_ok[b] ? m : 0) * p.xc_stride + 2 * t;
+    const int m = (8 * b + g) % p.M;
+    xrow[b] = xs + m * p.xs_stride + 16 * t;
+    xcrow[b] = xc + m * p.xc_stride + 2 * t;
   }
 
-  uint32_t cc = 0, qrun = 0;
-  int pending = 0;
+  uint32_t stage = 0, phase = 0, qrun = 0;
+  int pending = 0, nchunk = 0;
   bool cher_ready = false;
 
   for (int i = 0; i < npieces; ++i) {
     const uint32_t j = j_hi - i;
     const uint32_t sub0 = j * NG;
     const uint32_t start = max(ga, sub0), end = min(gb, sub0 + NG);
-    for (uint32_t q0 = start; q0 < end; q0 += NCW, ++cc) {
-      const uint32_t len = min((uint32_t)NCW, end - q0);
-      const uint32_t s = cc % S;
-      mbar_wait(bar_base + 8 * s, (cc / S) & 1, &s_abort, p.status);
-      const uint32_t o = ((uint32_t)warp - qrun) & (NCW - 1);
-      qrun += len;
-      if (o < len) {
-        const uint32_t gi = q0 + o - sub0;               // granule inside the sub-tile
-        const uint8_t* gran = ring + (size_t)s * NCW * GB + (size_t)o * GB;
-        const __half* sc = reinterpret_cast<const __half*>(gran + 256 * BITS);
-        float acc[MB][4];
+    for (uint32_t q0 = start; q0 < end; q0 += CHUNK) {
+      const uint32_t len = min((uint32_t)CHUNK, end - q0);
+      const bool trace = p.timeline && lane == 0 && (warp == 0 || warp == 5) && nchunk >= 2 && nchunk < 6;
+      unsigned long long* tr = trace ? p.timeline + (size_t)(512 + blockIdx.x) * 64 + (warp == 5 ? 32 : 0) + (nchunk - 2) * 4 : nullptr;
+      if (trace) tr[0] = clock64();
+      mbar_wait(bar_base + 8 * stage, phase, &s_abort, p.status);
+      if (trace) tr[1] = clock64();
+      if (tid == 0 && i == 0 && q0 == start) stamp(p, 5);
+      if (tid == 0 && nchunk < 24) stamp(p, 16 + nchunk);
+      ++nchunk;
+      const uint32_t rot = ((uint32_t)warp - qrun) & (NCW - 1);
+      qrun = (qrun + len) & (NCW - 1);
+      const uint8_t* sbase = ring + (size_t)stage * CHUNK * GB;
+      const uint32_t gi0 = q0 + rot - sub0;                 // this warp's first granule inside the sub-tile
+      if (len == (uint32_t)CHUNK) {
+        const uint8_t* gp[GPW];
+        uint32_t xo[GPW];
+        const float* cg[GPW];
 #pragma unroll
-        for (int b = 0; b < MB; ++b)
-#pragma unroll
-          for (int r = 0; r < 4; ++r) acc[b][r] = 0.f;
-
-        uint32_t A0[16], A1[16];  // fp16 pairs of rows g and g+8 (8 per 64-column half)
-        if (BITS == 4) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint4 w = *reinterpret_cast<const uint4*>(gran + h * 512 + lane * 16);
-            dequant4(w.x, A0 + 8 * h);
-            dequant4(w.y, A0 + 8 * h + 4);
-            dequant4(w.z, A1 + 8 * h);
-            dequant4(w.w, A1 + 8 * h + 4);
-          }
-        } else {
-          const uint2* wp = reinterpret_cast<const uint2*>(gran + lane * 24);
-          const uint2 u0 = wp[0], u1 = wp[1], u2 = wp[2];
-          dequant3(u0.x, u0.y, u1.x, A0);
-          dequant3(u1.y, u2.x, u2.y, A1);
+        for (int r = 0; r < GPW; ++r) {
+          gp[r] = sbase + (size_t)(rot + NCW * r) * GB;
+          xo[r] = (gi0 + NCW * r) * 128;
+          cg[r] = corr + (gi0 + NCW * r) * SETS * 8 * MB;
         }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-#pragma unroll
-          for (int b = 0; b < MB; ++b) {
-            uint4 xa = make_uint4(0, 0, 0, 0), xb = make_uint4(0, 0, 0, 0);
-            if (xrow_ok[b]) {
-              const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + gi * 128 + h * 64);
-              xa = xp[0];
-              xb = xp[1];
-            }
-            const uint32_t X[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-            for (int m = 0; m < 4; ++m)
-              mma16816(acc[b], A0[8 * h + 2 * m], A1[8 * h + 2 * m], A0[8 * h + 2 * m + 1],
-                       A1[8 * h + 2 * m + 1], X[2 * m], X[2 * m + 1]);
-          }
-          if (SETS == 2 || h == 1) {
-            const int sp = (SETS == 2) ? h : 0;
-            const float s0 = __half2float(sc[sp * 16 + g]), s1 = __half2float(sc[sp * 16 + g + 8]);
-#pragma unroll
-            for (int b = 0; b < MB; ++b) {
-              tot[b][0] += s0 * acc[b][0];
-              tot[b][1] += s0 * acc[b][1];
-              tot[b][2] += s1 * acc[b][2];
-              tot[b][3] += s1 * acc[b][3];
-              acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.f;
-            }
-          }
-        }
-        // The granule that starts a sub-tile also adds the sub-tile's fp16 cherry columns.
-        if (gi == 0 && p.Cp > 0) {
-          if (!cher_ready) {
-            mbar_wait(bar_base + 16 * S, 0, &s_abort, p.status);
-            cher_ready = true;
-          }
-          const uint8_t* blk = cher + (size_t)(j - jc_lo) * p.cher_bytes;
-          for (int jj = 0; jj < p.Cp / 16; ++jj) {
-            const uint4 a = *reinterpret_cast<const uint4*>(blk + jj * 512 + lane * 16);
-#pragma unroll
-            for (int b = 0; b < MB; ++b) {
-              uint32_t b0 = 0, b1 = 0;
-              if (xrow_ok[b]) {
-                b0 = *reinterpret_cast<const uint32_t*>(xcrow[b] + 16 * jj);
-                b1 = *reinterpret_cast<const uint32_t*>(xcrow[b] + 16 * jj + 8);
-              }
-              mma16816(tot[b], a.x, a.y, a.z, a.w, b0, b1);
-            }
+        process_granules<BITS, SETS, MB, GPW>(gp, xo, cg, xrow, lane, tot
+#ifdef CQ_TRACE_INNER
+            , trace ? tr + 8 * 64 * 1024 / 64 * 0 + (size_t)256 * 64 : nullptr
+#endif
+            );
+      } else {
+        for (int r = 0; r < GPW; ++r) {
+          const uint32_t o = rot + NCW * r;
+          if (o < len) {
+            const uint8_t* gp[1] = {sbase + (size_t)o * GB};
+            const uint32_t xo[1] = {(gi0 + NCW * r) * 128};
+            const float* cg[1] = {corr + (gi0 + NCW * r) * SETS * 8 * MB};
+            process_granules<BITS, SETS, MB, 1>(gp, xo, cg, xrow, lane, tot
+#ifdef CQ_TRACE_INNER
+            , nullptr
+#endif
+            );
           }
         }
       }
+      // The granule that starts a sub-tile also adds the sub-tile's fp16 cherry columns.
+      if (q0 == sub0 && rot == 0 && p.Cp > 0) {
+        if (!cher_ready) {
+          mbar_wait(bar_base + 16 * S, 0, &s_abort, p.status);
+          cher_ready = true;
+        }
+        const uint8_t* blk = cher + (size_t)(j - jc_lo) * p.cher_bytes;
+        for (int jj = 0; jj < p.Cp / 16; ++jj) {
+          const uint4 a = *reinterpret_cast<const uint4*>(blk + jj * 512 + lane * 16);
+#pragma unroll
+          for (int b = 0; b < MB; ++b) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xcrow[b] + 16 * jj);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xcrow[b] + 16 * jj + 8);
+            mma16816(tot[b], a.x, a.y, a.z, a.w, b0, b1);
+          }
+        }
+      }
+      if (trace) tr[2] = clock64();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_base + 8 * (S + s));
+      if (lane == 0) mbar_arrive(bar_base + 8 * (S + stage));
+      if (trace) tr[3] = clock64();
+      if (++stage == S) { stage = 0; phase ^= 1; }
     }
 
-    // ---- end of piece i: park this warp's partial
+    // ---- end of piece i: park this warp's partial (the lane's C fragment: rows g, g+8; columns 2t, 2t+1)
     {
-      float4* dst = slots + ((size_t)((i % p.nslot) * NCW + warp) * MB) * 32 + lane;
+      float* dst = slots + ((size_t)((i % p.nslot) * NCW + warp) * p.M) * 16;
 #pragma unroll
       for (int b = 0; b < MB; ++b) {
-        dst[b * 32] = make_float4(tot[b][0], tot[b][1], tot[b][2], tot[b][3]);
+        const int m0 = 8 * b + 2 * t;
+        if (m0 < p.M) {
+          dst[m0 * 16 + g] = tot[b][0];
+          dst[m0 * 16 + g + 8] = tot[b][2];
+        }
+        if (m0 + 1 < p.M) {
+          dst[(m0 + 1) * 16 + g] = tot[b][1];
+          dst[(m0 + 1) * 16 + g + 8] = tot[b][3];
+        }
         tot[b][0] = tot[b][1] = tot[b][2] = tot[b][3] = 0.f;
       }
     }
@@ -367,61 +669,54 @@ __global__ void __launch_bounds__(NTHREADS, 1) cq_matvec_kernel(const MatvecPara
     if (!(post_now || pending == p.nslot || i == npieces - 1)) continue;
 
     // ---- emit the pending pieces
-    bar_consumers();
+    if (tid == 0 && i == npieces - 1) stamp(p, 6);
+    bar_consumers<NCONS>();
     uint32_t reset_lo = 1, reset_hi = 0;    // flags to clear afterwards (finishing CTA only)
     bool posted = false;
-    for (int ii = i - pending + 1; ii <= i; ++ii) {
-      const uint32_t jj = j_hi - ii;
-      const uint32_t s0g = jj * NG;
-      const uint32_t pstart = max(ga, s0g), pend = min(gb, s0g + NG);
-      const int m = tid >> 4, r = tid & 15;
-      float v = 0.f;
-      if (m < p.M) {
-        const int b = m >> 3, col = m & 7;
-        const int ln = (r & 7) * 4 + (col >> 1);
-        const int reg = (r >> 3) * 2 + (col & 1);
-        const float* sl = reinterpret_cast<const float*>(slots + ((size_t)((ii % p.nslot) * NCW) * MB + b) * 32 + ln) + reg;
+    if (tid < 256) {
+      for (int ii = i - pending + 1; ii <= i; ++ii) {
+        const uint32_t jj = j_hi - ii;
+        const uint32_t s0g = jj * NG;
+        const uint32_t pstart = max(ga, s0g), pend = min(gb, s0g + NG);
+        const int m = tid >> 4, r = tid & 15;
+        float v = 0.f;
+        if (m < p.M) {
+          const float* sl = slots + ((size_t)((ii % p.nslot) * NCW) * p.M + m) * 16 + r;
 #pragma unroll
-        for (int w = 0; w < NCW; ++w) v += sl[(size_t)w * MB * 32 * 4];
-      }
-      if (pend < s0g + NG) {
-        // an earlier part of a cut sub-tile: hand the partial to the CTA that holds its end
-        p.partial[(size_t)cta * 256 + tid] = v;
-        posted = true;
-      } else {
-        if (pstart > s0g) {
-          const uint32_t c_first = (uint32_t)((((uint64_t)s0g + 1) * grid - 1) / p.T);
-          reset_lo = c_first;
-          reset_hi = cta - 1;
-          for (uint32_t c = c_first; c < cta; ++c) {
-            bool ok = false;
-            const uint32_t limit = s_abort ? 1u : WAIT_LIMIT;
-            for (uint32_t it = 0; it < limit; ++it) {
-              if (ld_acquire(p.flag + c) != 0) { ok = true; break; }
-              __nanosleep(64);
-            }
-            if (!ok) {
-              s_abort = 1;
-              if (p.status) atomicOr(p.status, 2u);
-            }
-            v += __ldcg(p.partial + (size_t)c * 256 + tid);
-          }
+          for (int w = 0; w < NCW; ++w) v += sl[(size_t)w * p.M * 16];
         }
-        const int n = (int)jj * 16 + r;
-        if (m < p.M && n < p.N) {
-          __half* yp = p.y + (size_t)m * p.ldy + n;
-          if (p.accumulate) v += __half2float(*yp);
-          *yp = __float2half(v);
+        if (pend < s0g + NG) {
+          // an earlier part of a cut sub-tile: hand the partial to the CTA that holds its end
+          p.partial[(size_t)cta * 256 + tid] = v;
+          posted = true;
+        } else {
+          if (pstart > s0g) {
+            const uint32_t c_first = (uint32_t)((((uint64_t)s0g + 1) * grid - 1) / p.T);
+            reset_lo = c_first;
+            reset_hi = cta - 1;
+            mbar_wait(bar_base + 16 * S + 8, 0, &s_abort, p.status);
+            v += reinterpret_cast<const float*>(smem + p.off_pf)[tid];
+          }
+          const int n = (int)jj * 16 + r;
+          if (m < p.M && n < p.N) {
+            __half* yp = p.y + (size_t)m * p.ldy + n;
+            if (p.accumulate) v += __half2float(*yp);
+            *yp = __float2half(v);
+          }
         }
       }
     }
-    bar_consumers();
+    bar_consumers<NCONS>();
     if (tid == 0) {
       if (posted) {
         __threadfence();
         st_release(p.flag + cta, 1u);
       }
       for (uint32_t c = reset_lo; c <= reset_hi && reset_lo <= reset_hi; ++c) p.flag[c] = 0u;
+      if (i == npieces - 1) {
+        stamp(p, 7);
+        if (p.timeline) p.timeline[(size_t)blockIdx.x * 64 + 11] = (unsigned long long)clock64();
+      }
     }
     pending = 0;
   }
@@ -441,7 +736,7 @@ DeviceInfo device_info(int dev) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return DeviceInfo();
     cache[dev].sms = prop.multiProcessorCount;
-    cache[dev].max_smem = (int)prop.sharedMemPerBlockOptin;
+    cache[dev].max_smem = (int)prop.sharedMemPerBlockOptin - 1024;
     cache[dev].ok = true;
   }
   return cache[dev];
@@ -449,43 +744,88 @@ DeviceInfo device_info(int dev) {
 
 typedef void (*KernelFn)(const MatvecParams);
 
-KernelFn pick_kernel(int bits, int sets, int mb) {
+// Kernel shapes: (consumer warps, granules per warp per ring stage).
+struct Shape { int ncw, gpw; };
+constexpr Shape SHAPES[] = {{8, 2}, {16, 1}, {8, 1}, {12, 1}, {16, 1}};
+constexpr int N_SHAPES = sizeof(SHAPES) / sizeof(SHAPES[0]);
+
+template <int NCW, int GPW, int MINB>
+KernelFn pick_bits(int bits, int sets, int mb) {
   if (bits == 4) {
-    if (sets == 1) return mb == 1 ? cq_matvec_kernel<4, 1, 1> : cq_matvec_kernel<4, 1, 2>;
-    return mb == 1 ? cq_matvec_kernel<4, 2, 1> : cq_matvec_kernel<4, 2, 2>;
+    if (sets == 1) return mb == 1 ? cq_matvec_kernel<4, 1, 1, NCW, GPW, MINB> : cq_matvec_kernel<4, 1, 2, NCW, GPW, MINB>;
+    return mb == 1 ? cq_matvec_kernel<4, 2, 1, NCW, GPW, MINB> : cq_matvec_kernel<4, 2, 2, NCW, GPW, MINB>;
   }
-  if (sets == 1) return mb == 1 ? cq_matvec_kernel<3, 1, 1> : cq_matvec_kernel<3, 1, 2>;
-  return mb == 1 ? cq_matvec_kernel<3, 2, 1> : cq_matvec_kernel<3, 2, 2>;
+  if (sets == 1) return mb == 1 ? cq_matvec_kernel<3, 1, 1, NCW, GPW, MINB> : cq_matvec_kernel<3, 1, 2, NCW, GPW, MINB>;
+  return mb == 1 ? cq_matvec_kernel<3, 2, 1, NCW, GPW, MINB> : cq_matvec_kernel<3, 2, 2, NCW, GPW, MINB>;
 }
+
+KernelFn pick_kernel(int shape, int bits, int sets, int mb) {
+  switch (shape) {
+    case 0: return pick_bits<8, 2, 1>(bits, sets, mb);
+    case 1: return pick_bits<16, 1, 2>(bits, sets, mb);   // capped at 56 registers: two CTAs per SM
+    case 2: return pick_bits<8, 1, 1>(bits, sets, mb);
+    case 3: return pick_bits<12, 1, 1>(bits, sets, mb);
+    default: return pick_bits<16, 1, 1>(bits, sets, mb);
+  }
+}
+
+// Tuning knobs read once from the environment (for experiments; defaults are the product):
+//   CQ_SHAPE  index into SHAPES      CQ_SMEM_KB  shared-memory target per CTA
+//   CQ_PDL    0 disables programmatic dependent launch
+struct Knobs { int shape, smem_kb, pdl; };
+Knobs knobs() {
+  static Knobs k = [] {
+    Knobs v{0, 112, 1};
+    if (const char* e = getenv("CQ_SHAPE")) v.shape = atoi(e);
+    if (const char* e = getenv("CQ_SMEM_KB")) v.smem_kb = atoi(e);
+    if (const char* e = getenv("CQ_PDL")) v.pdl = atoi(e);
+    if (v.shape < 0 || v.shape >= N_SHAPES) v.shape = 0;
+    return v;
+  }();
+  return k;
+}
+
+unsigned long long* g_timeline = nullptr;
 
 int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
 // Shared-memory plan for M activation rows; returns total bytes or -1 if it cannot fit.
-int plan_smem(const cq_layer* L, int M, int grid, int max_smem, MatvecParams* p) {
+int plan_smem(const cq_layer* L, int M, int grid, int max_smem, Shape sh, int target_kb, MatvecParams* p) {
   const uint32_t T = (uint32_t)L->n_sub * (uint32_t)L->n_gran;
   const uint32_t per = (T + grid - 1) / grid;
   const int max_pieces = (int)((per + L->n_gran - 1) / L->n_gran) + 1;
   const int mb = (M + 7) / 8;
+  const int chunk_gran = sh.ncw * sh.gpw;
   p->nslot = max_pieces < 8 ? max_pieces : 8;
   p->max_cher = max_pieces;
   p->xs_stride = L->Kp + 8;
   p->xc_stride = L->Cp + 8;
-  const int chunk = NCW * L->gran_bytes;
+  const int chunk = chunk_gran * L->gran_bytes;
   int off = 0;
   p->off_cher = off; off = align_up(off + p->max_cher * L->cher_bytes, 128);
   p->off_xs = off;   off = align_up(off + M * p->xs_stride * 2, 128);
   p->off_xc = off;   off = align_up(off + M * p->xc_stride * 2, 128);
-  p->off_slot = off; off = align_up(off + p->nslot * NCW * mb * 512, 128);
-  p->off_bar = off;  off = align_up(off + (2 * 16 + 1) * 8, 128);
+  p->off_cidx = off; off = align_up(off + (L->Cp + 8) * 2, 128);
+  p->off_corr = off; off = align_up(off + L->n_gran * L->sets * 8 * mb * 4, 128);
+  // the octet-shift table is only needed while activations are staged: it shares the slots' space
+  {
+    const int slot_bytes = p->nslot * sh.ncw * M * 64, osh_bytes = (L->Kp / 8) * 4;
+    p->off_slot = off; p->off_osh = off;
+    off = align_up(off + (slot_bytes > osh_bytes ? slot_bytes : osh_bytes), 128);
+  }
+  p->off_pf = off;   off = align_up(off + 256 * 4, 128);
+  p->off_bar = off;  off = align_up(off + (2 * 16 + 2) * 8, 128);
   p->off_ring = off;
   const int fixed = off;
-  // Ring: aim at <= ~112 KB per CTA so two launches can overlap on one SM, but never
-  // fewer than 3 stages; never more than 16.
-  const int target = 112 * 1024;
-  int stages = (target - fixed) / chunk;
-  if (stages < 3) stages = 3;
+  // Ring: with <= target_kb per CTA two launches overlap on one SM (the next layer prefetches its
+  // weights while this one computes).  That only pays while the ring still holds enough bytes in
+  // flight to cover HBM latency; otherwise take the whole SM.
+  int budget = target_kb * 1024;
+  if (budget - fixed < 64 * 1024) budget = max_smem;
+  int stages = (budget - fixed) / chunk;
+  if (stages < 2) stages = 2;
   if (stages > 16) stages = 16;
-  const uint32_t max_chunks = per / NCW + (uint32_t)max_pieces + 1;
+  const uint32_t max_chunks = per / chunk_gran + (uint32_t)max_pieces + 1;
   if ((uint32_t)stages > max_chunks) stages = (int)max_chunks;
   if (stages < 1) stages = 1;
   while (stages > 1 && fixed + stages * chunk > max_smem) --stages;
@@ -496,13 +836,20 @@ int plan_smem(const cq_layer* L, int M, int grid, int max_smem, MatvecParams* p)
 
 }  // namespace
 
+// Tracing: when a device buffer of 1024 x 16 uint64 is set, every CTA of the following matvec
+// launches stores %globaltimer stamps of its phases there (slot meanings in cq_matvec_kernel).
+extern "C" int cq_trace_set_timeline(void* device_buffer) {
+  g_timeline = (unsigned long long*)device_buffer;
+  return CQ_OK;
+}
+
 extern "C" size_t cq_scratch_bytes(void) {
   // up to 1024 CTAs: 256 floats of partial + one flag each
   return (size_t)1024 * 256 * sizeof(float) + 1024 * sizeof(uint32_t);
 }
 
-// Launches over at most `rows` activation rows at a time; the caller (cq_layer_matvec)
-// splits larger batches.
+// Launches over at most 16 activation rows (fewer when the shared-memory plan needs it);
+// the caller (cq_layer_matvec) walks larger batches.
 static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, int ldy, int M,
                        int accumulate, void* scratch, uint32_t* status, cudaStream_t st,
                        int* rows_done) {
@@ -510,6 +857,8 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   CQ_CUDA_TRY(cudaGetDevice(&dev));
   const DeviceInfo di = device_info(dev);
   if (!di.ok) return CQ_ERR_NO_DEVICE;
+  const Knobs kn = knobs();
+  const Shape sh = SHAPES[kn.shape];
   const uint32_t T = (uint32_t)L->n_sub * (uint32_t)L->n_gran;
   int grid = di.sms < 1024 ? di.sms : 1024;
   if ((uint32_t)grid > T) grid = (int)T;
@@ -518,36 +867,37 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   int rows = M < 16 ? M : 16;
   int smem = -1;
   for (; rows >= 1; --rows) {
-    smem = plan_smem(L, rows, grid, di.max_smem, &p);
+    smem = plan_smem(L, rows, grid, di.max_smem, sh, kn.smem_kb, &p);
     if (smem >= 0) break;
   }
   if (smem < 0) return CQ_ERR_TOO_LARGE;
   const uint8_t* blob = (const uint8_t*)L->blob;
   p.stream = blob + L->off_stream;
   p.cstream = blob + L->off_cherry;
-  p.perm = (const uint16_t*)(blob + L->off_perm);
   p.cidx = (const uint16_t*)(blob + L->off_cidx);
+  p.osh = (const uint32_t*)(blob + L->off_osh);
   p.x = x; p.y = y;
   p.partial = (float*)scratch;
   p.flag = (uint32_t*)((uint8_t*)scratch + (size_t)1024 * 256 * sizeof(float));
   p.status = status;
+  p.timeline = g_timeline;
   p.M = rows; p.K = L->K; p.N = L->N; p.C = L->C; p.Cp = L->Cp; p.Kp = L->Kp;
   p.n_gran = L->n_gran; p.n_sub = L->n_sub; p.gran_bytes = L->gran_bytes; p.cher_bytes = L->cher_bytes;
   p.ldx = ldx; p.ldy = ldy; p.accumulate = accumulate;
   p.T = T;
 
-  KernelFn fn = pick_kernel(L->bits, L->sets, (rows + 7) / 8);
+  KernelFn fn = pick_kernel(kn.shape, L->bits, L->sets, (rows + 7) / 8);
   CQ_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(NTHREADS);
+  cfg.blockDim = dim3((sh.ncw + 1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = kn.pdl ? 1 : 0;
   CQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, fn, p));
   *rows_done = rows;
   return CQ_OK;

@@ -43,8 +43,9 @@ cq_stream_t current_stream() { return (cq_stream_t)c10::cuda::getCurrentCUDAStre
 
 uint64_t version_tag(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& c,
                      const torch::Tensor& d) {
-  return (uint64_t)a._version() + ((uint64_t)b._version() << 16) + ((uint64_t)c._version() << 32) +
-         ((uint64_t)d._version() << 48);
+  // inference tensors (created under torch.inference_mode) keep no version counter
+  auto v = [](const torch::Tensor& t) -> uint64_t { return t.is_inference() ? 0u : (uint64_t)t._version(); };
+  return v(a) + (v(b) << 16) + (v(c) << 32) + (v(d) << 48);
 }
 
 void vecquant3matmul_cherryq(torch::Tensor vec, torch::Tensor qweight, torch::Tensor cherry_weight,

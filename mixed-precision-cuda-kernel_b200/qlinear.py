@@ -90,10 +90,15 @@ class QuantLinear(nn.Module):
         if not self.qweight.is_cuda:
             raise RuntimeError("QuantLinear buffers must be on a CUDA device (there is no CPU path)")
 
+    def _buffer_key(self):
+        def ver(t):   # tensors made under torch.inference_mode keep no version counter
+            return 0 if t.is_inference() else t._version
+        bufs = (self.qweight, self.scales, self.cherry_weight, self.cherry_indices)
+        return tuple(t.data_ptr() for t in bufs) + tuple(ver(t) for t in bufs)
+
     def prepared(self):
         """The stream-layout copy of this layer (built on first use)."""
-        key = (self.qweight.data_ptr(), self.qweight._version, self.scales._version,
-               self.cherry_weight._version, self.cherry_indices._version)
+        key = self._buffer_key()
         if self._prepared is None or self._prepared_key != key:
             qc = load_quant_cuda()
             self._require_cuda()
@@ -114,7 +119,7 @@ class QuantLinear(nn.Module):
     def restore_reference_buffers(self):
         q, s, cw, ci = self._prepared.unprepare()
         self.qweight, self.scales, self.cherry_weight, self.cherry_indices = q, s, cw, ci
-        self._prepared_key = (q.data_ptr(), q._version, s._version, cw._version, ci._version)
+        self._prepared_key = self._buffer_key()
 
     @torch.inference_mode()
     def forward(self, x: torch.Tensor):

@@ -31,8 +31,8 @@ def dims(bits, K, N, C, G):
     off = al(off + d["n_sub"] * n_gran * d["gran_bytes"])
     d["off_cherry"] = off
     off = al(off + d["n_sub"] * d["cher_bytes"])
-    d["off_perm"] = off
-    off = al(off + d["Kp"] * 2)
+    d["off_osh"] = off
+    off = al(off + d["Kp"] // 8 * 4)
     d["off_cidx"] = off
     off = al(off + (d["Cp"] or 16) * 2)
     d["blob_bytes"] = off
@@ -103,7 +103,7 @@ def build_blob(qweight, scales, cherry_weight, cherry_indices, bits, K, G):
                 for r in range(16):
                     n = sub * 16 + r
                     if n < N and kc0 < d["Kc"]:
-                        srow[sp * 16 + r] = sc16[kc0 // G, n]
+                        srow[sp * 16 + 2 * (r & 7) + (r >> 3)] = sc16[kc0 // G, n]
             blob[base + 256 * bits: base + gb] = srow.view(np.uint8)
     cw16 = cherry_weight.view(np.uint16) if C else np.zeros((0, N), np.uint16)
     for sub in range(d["n_sub"]):
@@ -119,12 +119,14 @@ def build_blob(qweight, scales, cherry_weight, cherry_indices, bits, K, G):
                             blk[lane, 2 * reg + e] = cw16[c, n]
             o = d["off_cherry"] + sub * d["cher_bytes"] + j * 512
             blob[o:o + 512] = blk.reshape(-1).view(np.uint8)
-    perm = np.full(d["Kp"], PAD, np.uint16)
     idx = cherry_indices.astype(np.int64)
     mask = np.ones(K, bool)
     mask[idx] = False
-    perm[:d["Kc"]] = np.nonzero(mask)[0]
-    blob[d["off_perm"]:d["off_perm"] + 2 * d["Kp"]] = perm.view(np.uint8)
+    orig = np.nonzero(mask)[0]                        # original column of every compact column
+    osh = np.full(d["Kp"] // 8, 0xFFFFFFFF, np.uint32)
+    for o in range(d["Kc"] // 8):
+        osh[o] = (orig[8 * o] - 8 * o) | ((orig[8 * o + 7] - (8 * o + 7)) << 16)
+    blob[d["off_osh"]:d["off_osh"] + 4 * (d["Kp"] // 8)] = osh.view(np.uint8)
     cidx = np.full(d["Cp"] or 16, PAD, np.uint16)
     cidx[:C] = idx
     if d["Cp"] == 0:
@@ -134,48 +136,79 @@ def build_blob(qweight, scales, cherry_weight, cherry_indices, bits, K, G):
 
 
 # ------------------------------------------------------------------ consumption model
+# The kernel's decode: OR a code field at mantissa bit p into the bits of fp16 1024.0
+# -> 1024 + 2^p u; the activation that meets it is pre-scaled by 2^(c-p), and
+# (B + off) x with B = 2^(10-p) is subtracted per group afterwards.
 MAGIC = 0x64006400
+C_EXP = {4: 2, 3: 1}
+OFF = {4: 7.5, 3: 3.5}
 
 
-def _hfma2(a_u32, mul, add):
-    """fma.rn.f16x2 on a packed pair: result as two float32 (exact for these inputs)."""
-    pair = np.array([a_u32 & 0xFFFF, a_u32 >> 16], np.uint16).view(np.float16).astype(np.float64)
-    r = pair * mul + add
-    return r.astype(np.float16).astype(np.float64)
+def p_of_pair(bits, q):
+    """Mantissa bit of the code field of pair q (4-bit: q = position >> 1 in the lane's 16 codes
+    of a half; 3-bit: q = 0..15 over the row's 32 codes of a granule)."""
+    if bits == 4:
+        return 6 if q & 1 else 2
+    if q == 15:
+        return 7
+    return (1, 4, 7, 4, 7)[q % 5]
 
 
-def dequant4(w):
+def _pair(a_u32):
+    return np.array([a_u32 & 0xFFFF, a_u32 >> 16], np.uint16).view(np.float16).astype(np.float64)
+
+
+def decode4(w):
     v1, v2 = (w << 2) & 0xFFFFFFFF, w >> 6
-    return [
-        _hfma2((v1 & 0x003C003C) | MAGIC, 0.25, -263.5),
-        _hfma2((v1 & 0x03C003C0) | MAGIC, 1 / 64, -23.5),
-        _hfma2((v2 & 0x003C003C) | MAGIC, 0.25, -263.5),
-        _hfma2((v2 & 0x03C003C0) | MAGIC, 1 / 64, -23.5),
-    ]
+    return [_pair((v1 & 0x003C003C) | MAGIC), _pair((v1 & 0x03C003C0) | MAGIC),
+            _pair((v2 & 0x003C003C) | MAGIC), _pair((v2 & 0x03C003C0) | MAGIC)]
 
 
-def dequant3(w0, w1, w2):
+def decode3(w0, w1, w2):
     out = []
     for w in (w0, w1, w2):
-        v = w >> 9
-        out.append(_hfma2((w & 0x000E000E) | MAGIC, 0.5, -515.5))
-        out.append(_hfma2((w & 0x00700070) | MAGIC, 1 / 16, -67.5))
-        out.append(_hfma2((w & 0x03800380) | MAGIC, 1 / 128, -11.5))
-        out.append(_hfma2((v & 0x000E000E) | MAGIC, 0.5, -515.5))
-        out.append(_hfma2((v & 0x00700070) | MAGIC, 1 / 16, -67.5))
-    r = (((w0 << 1) & 0x00020002) | MAGIC) | ((w1 << 2) & 0x00040004) | ((w2 << 3) & 0x00080008)
-    out.append(_hfma2(r, 0.5, -515.5))
+        v = w >> 6
+        out += [_pair((w & 0x000E000E) | MAGIC), _pair((w & 0x00700070) | MAGIC), _pair((w & 0x03800380) | MAGIC),
+                _pair((v & 0x00700070) | MAGIC), _pair((v & 0x03800380) | MAGIC)]
+    r = (((w0 << 7) & 0x00800080) | MAGIC) | ((w1 << 8) & 0x01000100) | ((w2 << 9) & 0x02000200)
+    out.append(_pair(r))
     return out
+
+
+def stage_activations(d, xs):
+    """xs (M, Kp) compact activations -> (pre-scaled fp16 copy as float64, corr (M, n_gran, sets))."""
+    bits, ce = d["bits"], C_EXP[d["bits"]]
+    kpp = np.arange(d["Kp"]) % 128
+    h, i = kpp >> 6, kpp & 15
+    q = (i >> 1) if bits == 4 else 8 * h + (i >> 1)
+    p = np.array([p_of_pair(bits, int(v)) for v in q])
+    xsc = (xs * 2.0 ** (ce - p)).astype(np.float16).astype(np.float64)
+    coef = 2.0 ** (p - ce) * (2.0 ** (10 - p) + OFF[bits])
+    per = 128 // d["sets"]
+    corr = (xsc * coef).reshape(xs.shape[0], d["n_gran"], d["sets"], per).sum(-1)
+    return xsc, corr
 
 
 def consume_blob(blob, d, x):
     """y (M, N) float64 computed the way the kernel walks the stream."""
     bits, N, M = d["bits"], d["N"], x.shape[0]
-    perm = blob[d["off_perm"]:d["off_perm"] + 2 * d["Kp"]].view(np.uint16)
+    osh = blob[d["off_osh"]:d["off_osh"] + 4 * (d["Kp"] // 8)].view(np.uint32)
     cidx = blob[d["off_cidx"]:d["off_cidx"] + 2 * d["Cp"]].view(np.uint16)
     xs = np.zeros((M, d["Kp"]))
-    ok = perm != PAD
-    xs[:, ok] = x[:, perm[ok].astype(np.int64)].astype(np.float64)
+    cher = cidx[cidx != PAD].astype(np.int64)
+    for o, sh in enumerate(osh):
+        if sh == 0xFFFFFFFF:
+            continue
+        lo0, lo7 = int(sh & 0xFFFF), int(sh >> 16)
+        for i in range(8):
+            k = 8 * o + i
+            if lo0 == lo7:
+                s = lo0
+            else:   # a cherry column falls inside the octet: per-column search, as the kernel does
+                s = int(np.sum(cher - np.arange(len(cher)) <= k))
+            xs[:, k] = x[:, k + s].astype(np.float64)
+    xs, corr = stage_activations(d, xs)
+    inv = 2.0 ** -C_EXP[bits]
     xc = np.zeros((M, d["Cp"]))
     okc = cidx != PAD
     xc[:, okc] = x[:, cidx[okc].astype(np.int64)].astype(np.float64)
@@ -192,18 +225,20 @@ def consume_blob(blob, d, x):
                     A = [[], []]
                     for h in range(2):
                         w = words[h * 128 + lane * 4: h * 128 + lane * 4 + 4]
-                        A[0] += dequant4(int(w[0])) + dequant4(int(w[1]))
-                        A[1] += dequant4(int(w[2])) + dequant4(int(w[3]))
+                        A[0] += decode4(int(w[0])) + decode4(int(w[1]))
+                        A[1] += decode4(int(w[2])) + decode4(int(w[3]))
                 else:
                     w = [int(v) for v in words[lane * 6: lane * 6 + 6]]
-                    A = [dequant3(*w[0:3]), dequant3(*w[3:6])]
+                    A = [decode3(*w[0:3]), decode3(*w[3:6])]
                 for h in range(2):
                     sp = h if d["sets"] == 2 else 0
                     kbase = gi * 128 + 64 * h + 16 * t
                     for hi in range(2):
                         row = sub * 16 + g + 8 * hi
                         wv = np.concatenate(A[hi][8 * h: 8 * h + 8])        # 16 codes i = 0..15
-                        y[:, row] += sc[sp * 16 + g + 8 * hi] * (xs[:, kbase:kbase + 16] @ wv)
+                        y[:, row] += sc[sp * 16 + 2 * g + hi] * ((xs[:, kbase:kbase + 16] @ wv) * inv)
+                        if t == 0 and (h == 0 or d["sets"] == 2):
+                            y[:, row] -= sc[sp * 16 + 2 * g + hi] * corr[:, gi, sp]
         for j in range(d["Cp"] // 16):
             o = d["off_cherry"] + sub * d["cher_bytes"] + j * 512
             blk = blob[o:o + 512].view(np.float16).astype(np.float64).reshape(32, 8)

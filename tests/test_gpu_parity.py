@@ -84,7 +84,7 @@ def test_prepare_matches_layout_model_and_roundtrips(cabi, name):
     assert d["blob_bytes"] == p.L.blob_bytes
     for sec, nbytes in (("off_stream", d["n_sub"] * d["n_gran"] * d["gran_bytes"]),
                         ("off_cherry", d["n_sub"] * d["cher_bytes"]),
-                        ("off_perm", 2 * d["Kp"]), ("off_cidx", 2 * d["Cp"])):
+                        ("off_osh", 4 * (d["Kp"] // 8)), ("off_cidx", 2 * d["Cp"])):
         o = d[sec]
         assert np.array_equal(got[o:o + nbytes], model[o:o + nbytes]), sec
     # inverse re-pack: byte-identical reference buffers
@@ -336,7 +336,7 @@ def test_quantlinear_module(qc, name):
     assert y.shape == (1, 5, g["N"])
     assert rel_err(y.reshape(5, -1).cpu().numpy(), g["y"].astype(np.float64)) <= TIGHT_TOL
     # fake-quant (training-side) forward: the second oracle
-    yf = tl(x.reshape(5, -1)).float().cpu().numpy()
+    yf = tl(x.reshape(5, -1)).detach().float().cpu().numpy()
     ref = g["x"].astype(np.float64) @ g["fake"].astype(np.float64).T
     assert rel_err(yf, ref) <= 5e-3
     # keep only the stream copy, then rebuild the reference buffers bit-exactly

@@ -77,3 +77,13 @@ def test_dequantize_normal_matches_dense_normal_columns():
 def test_num_cherries():
     for k, want in [(4096, 16), (11008, 40), (5120, 16), (13824, 48), (8192, 32), (28672, 112), (256, 0)]:
         assert O.num_cherries(k, 1 / 256) == want
+
+
+@pytest.mark.parametrize("name", golden_cases())
+def test_torch_port_unpack_matches_reference(name):
+    import torch
+    from oracle import torch_port as TP
+    g = load_golden(name)
+    dense = TP.unpack(torch.from_numpy(g["qweight"]), torch.from_numpy(g["scales"]), torch.from_numpy(g["cherry_weight"]),
+                      torch.from_numpy(g["cherry_indices"]), g["bits"], g["G"], g["K"])
+    assert np.array_equal(dense.numpy().view(np.uint16), g["dense"].view(np.uint16))
