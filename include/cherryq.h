@@ -117,6 +117,36 @@ int cq_layer_matvec(const cq_layer* layer, const void* x_f16, int ldx, void* y_f
                     cq_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Tile-layout prepared layer: the format of the tcgen05 (UMMA + tensor memory) kernels.
+ * 128-row tiles; a granule is 128 rows x 128 compact columns; cherry columns travel in the same
+ * stream as fp16 items of 16 columns.  Same role as cq_layer above, different kernel family.
+ * ---------------------------------------------------------------------- */
+typedef struct cq_tlayer {
+  int32_t bits, K, N, C, G;
+  int32_t Kc, Kp, Cp;
+  int32_t n_gran;      /* granules per row tile = Kp / 128                               */
+  int32_t n_tile;      /* row tiles = ceil(N / 128)                                      */
+  int32_t n_cher;      /* cherry items per row tile = Cp / 16                            */
+  int32_t sets;        /* scale sets per granule: 1 (G % 128 == 0) or 2 (G == 64)        */
+  int32_t gran_bytes;  /* 2048 * bits + 256 * sets                                       */
+  int32_t tile_bytes;  /* n_cher * 4096 + n_gran * gran_bytes                            */
+  uint64_t off_stream, off_cidx, off_osh, blob_bytes;
+  void* blob;          /* device memory, blob_bytes long, 256-byte aligned               */
+} cq_tlayer;
+
+int cq_tlayer_init(cq_tlayer* layer, int bits, int K, int N, int C, int G, void* blob);
+int cq_tlayer_prepare(const cq_tlayer* layer, const uint8_t* qweight, const void* scales_f16,
+                      const void* cherry_weight_f16, const int16_t* cherry_indices,
+                      cq_stream_t stream);
+int cq_tlayer_unprepare(const cq_tlayer* layer, uint8_t* qweight, void* scales_f16,
+                        void* cherry_weight_f16, int16_t* cherry_indices, cq_stream_t stream);
+/* y (M, N) fp16 = [y +] x (M, K) fp16 . W^T for 1 <= M <= 16 per launch (larger M is walked in
+ * slices of 16).  Same scratch and status conventions as cq_layer_matvec. */
+int cq_tlayer_matvec(const cq_tlayer* layer, const void* x_f16, int ldx, void* y_f16, int ldy,
+                     int M, int accumulate, void* scratch, uint32_t* status_word,
+                     cq_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Drop-in operator entry points (reference: csrc/quant_cuda.cpp:41-69, 26-38).
  * Dimension arguments are what the reference derives from its tensors
  * (csrc/quant_cuda_kernel.cu:686-690):

@@ -19,7 +19,8 @@ CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 
 LIB = os.path.join(HERE, "libcherryq.so")
-CUDA_SOURCES = ["cq_api.cu", "cq_layout.cu", "cq_matvec.cu", "cq_pack.cu", "cq_legacy_f32.cu"]
+CUDA_SOURCES = ["cq_api.cu", "cq_layout.cu", "cq_matvec.cu", "cq_pack.cu", "cq_legacy_f32.cu",
+                "cq_tile_layout.cu", "cq_umma_matvec.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--fmad=true",
@@ -50,7 +51,8 @@ def cuda_sources():
 
 def build_lib(force: bool = False, verbose: bool = False) -> str:
     srcs = cuda_sources()
-    deps = srcs + [os.path.join(CSRC, "cq_common.cuh"), os.path.join(ROOT, "include", "cherryq.h")]
+    deps = srcs + [os.path.join(CSRC, "cq_common.cuh"), os.path.join(CSRC, "cq_tile.cuh"),
+                   os.path.join(ROOT, "include", "cherryq.h")]
     if not force and _newer(LIB, deps):
         return LIB
     cmd = [_nvcc()] + NVCC_FLAGS + ["-o", LIB] + srcs + ["-lcudart"]

@@ -17,6 +17,7 @@ SYMBOLS = [
     "cq_dequantize3_normal", "cq_dequantize4_normal",
     "cq_cache_clear", "cq_cache_stats", "cq_poll",
     "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense", "cq_trace_set_timeline",
+    "cq_tlayer_init", "cq_tlayer_prepare", "cq_tlayer_unprepare", "cq_tlayer_matvec",
 ]
 
 
@@ -24,6 +25,14 @@ class cq_layer(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
                 ("bits", "K", "N", "C", "G", "Kc", "Kp", "Cp", "n_gran", "n_sub", "sets", "gran_bytes", "cher_bytes")]
     _fields_ += [(n, C.c_uint64) for n in ("off_stream", "off_cherry", "off_osh", "off_cidx", "blob_bytes")]
+    _fields_ += [("blob", C.c_void_p)]
+
+
+class cq_tlayer(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("bits", "K", "N", "C", "G", "Kc", "Kp", "Cp", "n_gran", "n_tile", "n_cher", "sets", "gran_bytes",
+                 "tile_bytes")]
+    _fields_ += [(n, C.c_uint64) for n in ("off_stream", "off_cidx", "off_osh", "blob_bytes")]
     _fields_ += [("blob", C.c_void_p)]
 
 
@@ -48,6 +57,10 @@ def lib():
     L.cq_layer_prepare.argtypes = [C.POINTER(cq_layer), vp, vp, vp, vp, vp]
     L.cq_layer_unprepare.argtypes = [C.POINTER(cq_layer), vp, vp, vp, vp, vp]
     L.cq_layer_matvec.argtypes = [C.POINTER(cq_layer), vp, i32, vp, i32, i32, i32, vp, vp, vp]
+    L.cq_tlayer_init.argtypes = [C.POINTER(cq_tlayer), i32, i32, i32, i32, i32, vp]
+    L.cq_tlayer_prepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]
+    L.cq_tlayer_unprepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]
+    L.cq_tlayer_matvec.argtypes = [C.POINTER(cq_tlayer), vp, i32, vp, i32, i32, i32, vp, vp, vp]
     L.cq_vecquant4matmul_cherryq.argtypes = [vp] * 6 + [i32] * 6 + [u64, vp]
     L.cq_vecquant3matmul_cherryq.argtypes = [vp] * 6 + [i32] * 7 + [u64, vp]
     L.cq_dequantize3_normal.argtypes = [vp, vp, vp] + [i32] * 5 + [vp]
@@ -74,4 +87,10 @@ def check(rc: int, what: str = "cherryq"):
 def layer_init(bits, K, N, Cn, G, blob_ptr=None) -> cq_layer:
     L = cq_layer()
     check(lib().cq_layer_init(C.byref(L), bits, K, N, Cn, G, blob_ptr), "cq_layer_init")
+    return L
+
+
+def tlayer_init(bits, K, N, Cn, G, blob_ptr=None) -> cq_tlayer:
+    L = cq_tlayer()
+    check(lib().cq_tlayer_init(C.byref(L), bits, K, N, Cn, G, blob_ptr), "cq_tlayer_init")
     return L

@@ -844,8 +844,9 @@ extern "C" int cq_trace_set_timeline(void* device_buffer) {
 }
 
 extern "C" size_t cq_scratch_bytes(void) {
-  // up to 1024 CTAs: 256 floats of partial + one flag each
-  return (size_t)1024 * 256 * sizeof(float) + 1024 * sizeof(uint32_t);
+  // stream kernel: up to 1024 CTAs x 256 floats of partial, flags behind them at 1 MiB;
+  // tile kernel: up to 256 CTAs x 2048 floats, flags behind them at 2 MiB
+  return (size_t)256 * 2048 * sizeof(float) + 1024 * sizeof(uint32_t);
 }
 
 // Launches over at most 16 activation rows (fewer when the shared-memory plan needs it);

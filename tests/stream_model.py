@@ -249,3 +249,154 @@ def consume_blob(blob, d, x):
                     c0 = 16 * j + 2 * t + 8 * (reg >> 1)
                     y[:, row] += xc[:, c0] * blk[lane, 2 * reg] + xc[:, c0 + 1] * blk[lane, 2 * reg + 1]
     return y[:, :N]
+
+
+# ====================================================================== tile layout (tcgen05 kernels)
+def tile_dims(bits, K, N, C, G):
+    if G == -1:
+        G = K
+    Kc = K - C
+    n_gran = (Kc + 127) // 128
+    d = dict(bits=bits, K=K, N=N, C=C, G=G, Kc=Kc, n_gran=n_gran, Kp=n_gran * 128, Cp=(C + 15) // 16 * 16,
+             n_tile=(N + 127) // 128, sets=2 if G == 64 else 1)
+    d["n_cher"] = d["Cp"] // 16
+    d["gran_bytes"] = 2048 * bits + 256 * d["sets"]
+    d["tile_bytes"] = d["n_cher"] * 4096 + n_gran * d["gran_bytes"]
+
+    def al(x):
+        return (x + 255) & ~255
+    off = 0
+    d["off_stream"] = off
+    off = al(off + d["n_tile"] * d["tile_bytes"])
+    d["off_cidx"] = off
+    off = al(off + (d["Cp"] or 16) * 2)
+    d["off_osh"] = off
+    off = al(off + d["Kp"] // 8 * 4)
+    d["blob_bytes"] = off
+    return d
+
+
+def build_tile_blob(qweight, scales, cherry_weight, cherry_indices, bits, K, G):
+    """Reference buffers -> tile layout, restated from the description in csrc/cq_tile.cuh."""
+    N = qweight.shape[1]
+    C = len(cherry_indices)
+    d = tile_dims(bits, K, N, C, G)
+    G = d["G"]
+    rows = d["n_tile"] * 128
+    u = np.zeros((d["Kp"], rows), np.uint64)
+    u[:d["Kc"], :N] = ref_codes(qweight, bits)
+    blob = np.zeros(d["blob_bytes"], np.uint8)
+    sc16 = np.zeros((scales.shape[0], rows), np.uint16)
+    sc16[:, :N] = scales.view(np.uint16)
+    cw16 = np.zeros((d["Cp"], rows), np.uint16)
+    if C:
+        cw16[:C, :N] = cherry_weight.view(np.uint16)
+    for t in range(d["n_tile"]):
+        r0 = t * 128
+        tb = d["off_stream"] + t * d["tile_bytes"]
+        for j in range(d["n_cher"]):
+            # [q][row][8 halves]
+            blk = cw16[16 * j:16 * j + 16, r0:r0 + 128]              # (16 c, 128 rows)
+            item = blk.reshape(2, 8, 128).transpose(0, 2, 1)          # (q, row, e)
+            blob[tb + j * 4096: tb + (j + 1) * 4096] = np.ascontiguousarray(item).reshape(-1).view(np.uint8)
+        for g in range(d["n_gran"]):
+            gb = tb + d["n_cher"] * 4096 + g * d["gran_bytes"]
+            codes = u[128 * g:128 * g + 128, r0:r0 + 128]             # (128 k, 128 rows)
+            words = np.zeros((4 * bits, 128), np.uint64)              # word index, row
+            if bits == 4:
+                for wi in range(16):
+                    for jj in range(8):
+                        words[wi] |= codes[8 * wi + jj] << np.uint64(s4_shift(jj))
+            else:
+                for tr in range(4):
+                    for e in range(32):
+                        code = codes[32 * tr + e]
+                        if e < 30:
+                            q = e >> 1
+                            words[3 * tr + q // 5] |= code << np.uint64(16 * (e & 1) + 1 + 3 * (q % 5))
+                        else:
+                            for wq in range(3):
+                                words[3 * tr + wq] |= ((code >> np.uint64(wq)) & np.uint64(1)) << np.uint64(16 * (e & 1))
+            # [chunk q][row][4 words]
+            arr = words.astype(np.uint32).reshape(bits, 4, 128).transpose(0, 2, 1)
+            blob[gb: gb + 2048 * bits] = np.ascontiguousarray(arr).reshape(-1).view(np.uint8)
+            srow = np.zeros((d["sets"], 128), np.uint16)
+            for sp in range(d["sets"]):
+                kc0 = 128 * g + sp * (128 // d["sets"])
+                if kc0 < d["Kc"]:
+                    srow[sp] = sc16[kc0 // G, r0:r0 + 128]
+            blob[gb + 2048 * bits: gb + d["gran_bytes"]] = srow.reshape(-1).view(np.uint8)
+    idx = cherry_indices.astype(np.int64)
+    cidx = np.full(d["Cp"], PAD, np.uint16)
+    cidx[:C] = idx
+    blob[d["off_cidx"]:d["off_cidx"] + 2 * d["Cp"]] = cidx.view(np.uint8)
+    mask = np.ones(K, bool)
+    mask[idx] = False
+    orig = np.nonzero(mask)[0]
+    osh = np.full(d["Kp"] // 8, 0xFFFFFFFF, np.uint32)
+    for o in range(d["Kc"] // 8):
+        osh[o] = (orig[8 * o] - 8 * o) | ((orig[8 * o + 7] - (8 * o + 7)) << 16)
+    blob[d["off_osh"]:d["off_osh"] + 4 * (d["Kp"] // 8)] = osh.view(np.uint8)
+    return blob, d
+
+
+def p_of_column(bits, k):
+    """Mantissa bit of the code field of compact column k in the tile layout."""
+    if bits == 4:
+        return 6 if (k >> 1) & 1 else 2
+    return p_of_pair(3, (k % 32) >> 1)
+
+
+def consume_tile_blob(blob, d, x):
+    """y (M, N) float64 the way the tcgen05 kernel forms it: per row, decode the row's words into
+    fp16 values 1024 + 2^p u, multiply with pre-scaled activations, subtract the correction."""
+    bits, N, M = d["bits"], d["N"], x.shape[0]
+    ce, off = C_EXP[bits], OFF[bits]
+    osh = blob[d["off_osh"]:d["off_osh"] + 4 * (d["Kp"] // 8)].view(np.uint32)
+    cidx = blob[d["off_cidx"]:d["off_cidx"] + 2 * d["Cp"]].view(np.uint16)
+    cher = cidx[cidx != PAD].astype(np.int64)
+    xs = np.zeros((M, d["Kp"]))
+    for o, sh in enumerate(osh):
+        if sh == 0xFFFFFFFF:
+            continue
+        lo0, lo7 = int(sh & 0xFFFF), int(sh >> 16)
+        for i in range(8):
+            k = 8 * o + i
+            s = lo0 if lo0 == lo7 else int(np.sum(cher - np.arange(len(cher)) <= k))
+            xs[:, k] = x[:, k + s].astype(np.float64)
+    p = np.array([p_of_column(bits, k) for k in range(d["Kp"])])
+    xsc = (xs * 2.0 ** (ce - p)).astype(np.float16).astype(np.float64)
+    coef = 2.0 ** (p - ce) * (2.0 ** (10 - p) + off)
+    xc = np.zeros((M, d["Cp"]))
+    okc = cidx != PAD
+    xc[:, okc] = x[:, cidx[okc].astype(np.int64)].astype(np.float64)
+    y = np.zeros((M, d["n_tile"] * 128))
+    per = 128 // d["sets"]
+    for t in range(d["n_tile"]):
+        tb = d["off_stream"] + t * d["tile_bytes"]
+        for j in range(d["n_cher"]):
+            item = blob[tb + j * 4096: tb + (j + 1) * 4096].view(np.float16).astype(np.float64).reshape(2, 128, 8)
+            for q in range(2):
+                y[:, t * 128:(t + 1) * 128] += xc[:, 16 * j + 8 * q:16 * j + 8 * q + 8] @ item[q].T
+        for g in range(d["n_gran"]):
+            gb = tb + d["n_cher"] * 4096 + g * d["gran_bytes"]
+            arr = blob[gb: gb + 2048 * bits].view(np.uint32).reshape(bits, 128, 4)
+            sc = blob[gb + 2048 * bits: gb + d["gran_bytes"]].view(np.float16).astype(np.float64).reshape(d["sets"], 128)
+            for row in range(128):
+                words = [int(arr[wi >> 2, row, wi & 3]) for wi in range(4 * bits)]
+                vals = []
+                if bits == 4:
+                    for w in words:
+                        for pr in decode4(w):
+                            vals += [pr[0], pr[1]]
+                else:
+                    for tr in range(4):
+                        for pr in decode3(*words[3 * tr:3 * tr + 3]):
+                            vals += [pr[0], pr[1]]
+                vals = np.array(vals)                                   # 128 fp16 values 1024 + 2^p u
+                for sp in range(d["sets"]):
+                    ks = slice(128 * g + sp * per, 128 * g + (sp + 1) * per)
+                    acc = xsc[:, ks] @ vals[sp * per:(sp + 1) * per]
+                    corr = (xsc[:, ks] * coef[ks]).sum(1)
+                    y[:, t * 128 + row] += sc[sp, row] * (acc * 2.0 ** -ce - corr)
+    return y[:, :N]

@@ -23,3 +23,12 @@ def test_dims_of_target_layer():
     d = SM.dims(3, 8192, 28672, 32, 128)
     assert (d["gran_bytes"], d["n_gran"], d["cher_bytes"]) == (800, 64, 1024)
     assert SM.dims(3, 256, 40, 16, 64)["gran_bytes"] == 832
+
+
+@pytest.mark.parametrize("name", ["k256_n32_b4_g128_f16", "k256_n40_b3_g64_f16", "k384_n16_b4_g256_f16", "k640_n8_b3_g64_f32"])
+def test_walk_of_tile_layout_equals_oracle(name):
+    g = load_golden(name)
+    blob, d = SM.build_tile_blob(g["qweight"], g["scales"], g["cherry_weight"], g["cherry_indices"], g["bits"], g["K"], g["G"])
+    y = SM.consume_tile_blob(blob, d, g["x"])
+    ref = O.kernel_forward(g["x"], g["qweight"], g["cherry_weight"], g["cherry_indices"], g["scales"], g["bits"], g["G"])
+    assert np.abs(y - ref).max() <= 1e-6 * np.abs(ref).max()
