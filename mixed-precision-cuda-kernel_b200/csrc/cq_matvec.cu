@@ -29,6 +29,8 @@
 
 #include "cq_common.cuh"
 
+unsigned long long* cq_g_timeline = nullptr;   // tracing buffer, see cq_trace_set_timeline
+
 namespace {
 
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -187,128 +189,27 @@ __device__ __forceinline__ void decode3(uint32_t w0, uint32_t w1, uint32_t w2, u
   out[15] = r;
 }
 
-// R granules (16 rows x 128 compact columns each) for one warp, in one straight-line
-// block so that their independent MMA chains interleave: adds s * (sum - corr) to tot.
-//   gran[r]  granule bytes in the ring        xoff[r]  granule's first column (halves)
-//   corr_g[r] the granule's correction row    xrow[b]  lane's activation row pointer
-template <int BITS, int SETS, int MB, int R>
-__device__ __forceinline__ void process_granules(const uint8_t* const* gran, const uint32_t* xoff,
-                                                 const float* const* corr_g, const __half* const* xrow,
-                                                 int lane, float (&tot)[MB][4]
-#ifdef CQ_TRACE_INNER
-                                                 , unsigned long long* itr
-#endif
-                                                 ) {
-#ifdef CQ_TRACE_INNER
-#define ITR(k) do { if (itr) itr[k] = clock64(); } while (0)
-#else
-#define ITR(k) do { } while (0)
-#endif
-  const int g = lane >> 2, t = lane & 3;
-  ITR(0);
-  // scales of rows (g, g+8) sit next to each other: [set][g][2]; corr: [set][8 * MB] floats per
-  // granule, this lane's columns are 8b + 2t, + 1.  Loaded first: they are needed last.
-  float2 s_lo[R], s_hi[R], c_lo[R][MB], c_hi[R][MB];
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const __half2* sc = reinterpret_cast<const __half2*>(gran[r] + 256 * BITS);
-    s_lo[r] = __half22float2(sc[g]);
-    s_hi[r] = (SETS == 2) ? __half22float2(sc[8 + g]) : s_lo[r];
-#pragma unroll
-    for (int b = 0; b < MB; ++b) {
-      c_lo[r][b] = *reinterpret_cast<const float2*>(corr_g[r] + 8 * b + 2 * t);
-      c_hi[r][b] = (SETS == 2) ? *reinterpret_cast<const float2*>(corr_g[r] + 8 * MB + 8 * b + 2 * t) : c_lo[r][b];
-    }
-  }
-  // Two accumulators per (granule, half): the four MMAs of a half alternate between them, so
-  // that no MMA waits for the one issued just before it.
-  float acc[R][2][2][MB][4];
-#pragma unroll
-  for (int r = 0; r < R; ++r)
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int b = 0; b < MB; ++b)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) acc[r][h][j][b][e] = 0.f;
-
-  uint32_t A0[R][16], A1[R][16];  // fp16 pairs of rows g and g+8 (8 per 64-column half)
-  if (BITS == 3) {
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const uint2* wp = reinterpret_cast<const uint2*>(gran[r] + lane * 24);
-      const uint2 u0 = wp[0], u1 = wp[1], u2 = wp[2];
-      decode3(u0.x, u0.y, u1.x, A0[r]);
-      decode3(u1.y, u2.x, u2.y, A1[r]);
-    }
-  }
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    if (BITS == 4) {
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const uint4 w = *reinterpret_cast<const uint4*>(gran[r] + h * 512 + lane * 16);
-        decode4(w.x, A0[r] + 8 * h);
-        decode4(w.y, A0[r] + 8 * h + 4);
-        decode4(w.z, A1[r] + 8 * h);
-        decode4(w.w, A1[r] + 8 * h + 4);
-      }
-    }
-    ITR(1 + 3 * h);
-    uint32_t X[R][MB][8];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-      for (int b = 0; b < MB; ++b) {
-        const uint4* xp = reinterpret_cast<const uint4*>(xrow[b] + xoff[r] + h * 64);
-        const uint4 xa = xp[0], xb = xp[1];
-        X[r][b][0] = xa.x; X[r][b][1] = xa.y; X[r][b][2] = xa.z; X[r][b][3] = xa.w;
-        X[r][b][4] = xb.x; X[r][b][5] = xb.y; X[r][b][6] = xb.z; X[r][b][7] = xb.w;
-      }
-    ITR(2 + 3 * h);
-#pragma unroll
-    for (int m = 0; m < 4; ++m)
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int b = 0; b < MB; ++b)
-          mma16816(acc[r][h][m & 1][b], A0[r][8 * h + 2 * m], A1[r][8 * h + 2 * m], A0[r][8 * h + 2 * m + 1],
-                   A1[r][8 * h + 2 * m + 1], X[r][b][2 * m], X[r][b][2 * m + 1]);
-    ITR(3 + 3 * h);
-  }
-  const float inv = 1.f / (float)(1 << Fold<BITS>::C_EXP);
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-#pragma unroll
-    for (int b = 0; b < MB; ++b) {
-      float a0[4], a1[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        a0[e] = acc[r][0][0][b][e] + acc[r][0][1][b][e];
-        a1[e] = acc[r][1][0][b][e] + acc[r][1][1][b][e];
-      }
-      if (SETS == 2) {
-        tot[b][0] += s_lo[r].x * (a0[0] * inv - c_lo[r][b].x) + s_hi[r].x * (a1[0] * inv - c_hi[r][b].x);
-        tot[b][1] += s_lo[r].x * (a0[1] * inv - c_lo[r][b].y) + s_hi[r].x * (a1[1] * inv - c_hi[r][b].y);
-        tot[b][2] += s_lo[r].y * (a0[2] * inv - c_lo[r][b].x) + s_hi[r].y * (a1[2] * inv - c_hi[r][b].x);
-        tot[b][3] += s_lo[r].y * (a0[3] * inv - c_lo[r][b].y) + s_hi[r].y * (a1[3] * inv - c_hi[r][b].y);
-      } else {
-        tot[b][0] += s_lo[r].x * ((a0[0] + a1[0]) * inv - c_lo[r][b].x);
-        tot[b][1] += s_lo[r].x * ((a0[1] + a1[1]) * inv - c_lo[r][b].y);
-        tot[b][2] += s_lo[r].y * ((a0[2] + a1[2]) * inv - c_lo[r][b].x);
-        tot[b][3] += s_lo[r].y * ((a0[3] + a1[3]) * inv - c_lo[r][b].y);
-      }
-    }
-  }
-  ITR(7);
+// Geometry of piece i of a CTA's range (pieces = sub-tiles, walked from the last to the first).
+struct Piece {
+  uint32_t j, sub0, start, end;   // sub-tile, its first granule, first / past-last granule of the piece
+};
+__device__ __forceinline__ Piece piece_of(uint32_t i, uint32_t j_hi, uint32_t NG, uint32_t ga, uint32_t gb) {
+  Piece q;
+  q.j = j_hi - i;
+  q.sub0 = q.j * NG;
+  q.start = max(ga, q.sub0);
+  q.end = min(gb, q.sub0 + NG);
+  return q;
 }
 
-template <int BITS, int SETS, int MB, int NCW, int GPW, int MINB>
+// The packed words of one granule that one lane needs, loaded one ring stage ahead of their use.
+template <int BITS> struct Raw;
+template <> struct Raw<4> { uint4 a, b; uint32_t sc[2]; };
+template <> struct Raw<3> { uint2 a, b, c; uint32_t sc[2]; };
+
+template <int BITS, int SETS, int MB, int NCW, int MINB>
 __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const MatvecParams p) {
   constexpr int NCONS = NCW * 32;
-  constexpr int CHUNK = NCW * GPW;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_abort;
 
@@ -318,10 +219,11 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
   const uint32_t gb = (uint32_t)(((uint64_t)p.T * (cta + 1)) / grid);
   const uint32_t NG = (uint32_t)p.n_gran;
   const uint32_t GB = (uint32_t)p.gran_bytes;
+  const uint32_t total = gb - ga;
 
   const uint32_t bar_base = smem_u32(smem + p.off_bar);
   const uint32_t S = (uint32_t)p.stages;
-  // barriers: full[s] at bar_base + 8 s, empty[s] at bar_base + 8 (S + s), cherry at 8 * 2S
+  // barriers: full[s] at bar_base + 8 s, empty[s] at + 8 (S + s), cherry at + 16 S, partial prefetch at + 16 S + 8
   if (tid == 0) {
     stamp(p, 0);
     if (p.timeline) p.timeline[(size_t)blockIdx.x * 64 + 10] = (unsigned long long)clock64();
@@ -342,11 +244,15 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
   if (ga >= gb) return;  // (host launches grid <= T, so this does not happen)
 
   const uint32_t j_hi = (gb - 1) / NG, j_lo = ga / NG;
-  const int npieces = (int)(j_hi - j_lo + 1);
+  const uint32_t npieces = j_hi - j_lo + 1;
   const uint32_t jc_lo = (ga + NG - 1) / NG;           // first sub-tile whose start is in range
   const int ncher = (p.Cp > 0 && j_hi >= jc_lo) ? (int)(j_hi - jc_lo + 1) : 0;
 
   // ------------------------------------------------------------------ producer
+  // The CTA's granules, in walking order, form a sequence of `total` positions.  Ring stage
+  // (g mod S) holds positions [g * NCW, (g + 1) * NCW): position q sits at slot q mod NCW of it
+  // and belongs to consumer warp q mod NCW.  A stage is filled by one bulk copy per piece it
+  // touches (granules of a piece are contiguous in memory).
   if (warp == NCW) {
     if (lane == 0) {
       if (ncher > 0) {
@@ -358,20 +264,27 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
       const uint32_t ring = smem_u32(smem + p.off_ring);
       uint32_t stage = 0, phase = 1;   // empty barriers: the first pass over the ring needs no wait
       bool first_pass = true;
-      int nchunk = 0;
       stamp(p, 8);
-      for (int i = 0; i < npieces; ++i) {
-        const uint32_t j = j_hi - i;
-        const uint32_t start = max(ga, j * NG), end = min(gb, (j + 1) * NG);
-        for (uint32_t q0 = start; q0 < end; q0 += CHUNK) {
-          const uint32_t len = min((uint32_t)CHUNK, end - q0);
-          if (!first_pass) mbar_wait(bar_base + 8 * (S + stage), phase, &s_abort, p.status);
-          if (nchunk < 24) stamp(p, 40 + nchunk);
-          ++nchunk;
-          mbar_expect_tx(bar_base + 8 * stage, len * GB);
-          bulk_g2s(ring + stage * CHUNK * GB, p.stream + (size_t)q0 * GB, len * GB, bar_base + 8 * stage);
-          if (++stage == S) { stage = 0; phase ^= 1; first_pass = false; }
+      uint32_t pi = 0;
+      Piece pc = piece_of(0, j_hi, NG, ga, gb);
+      uint32_t src = pc.start;           // next granule to copy
+      for (uint32_t q0 = 0; q0 < total; q0 += NCW) {
+        const uint32_t len = min((uint32_t)NCW, total - q0);
+        if (!first_pass) mbar_wait(bar_base + 8 * (S + stage), phase, &s_abort, p.status);
+        mbar_expect_tx(bar_base + 8 * stage, len * GB);
+        uint32_t dst = ring + stage * NCW * GB, left = len;
+        while (left > 0) {
+          if (src == pc.end) {
+            pc = piece_of(++pi, j_hi, NG, ga, gb);
+            src = pc.start;
+          }
+          const uint32_t run = min(left, pc.end - src);
+          bulk_g2s(dst, p.stream + (size_t)src * GB, run * GB, bar_base + 8 * stage);
+          dst += run * GB;
+          src += run;
+          left -= run;
         }
+        if (++stage == S) { stage = 0; phase ^= 1; first_pass = false; }
       }
       stamp(p, 9);
     }
@@ -420,7 +333,6 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
   uint16_t* cidx_s = reinterpret_cast<uint16_t*>(smem + p.off_cidx);
   uint32_t* osh = reinterpret_cast<uint32_t*>(smem + p.off_osh);
   const int noct = p.Kp >> 3;
-  const int Kc = p.K - p.C;
   for (int c = tid; c < p.Cp; c += NCONS) cidx_s[c] = p.cidx[c];
   // corr entries of activation rows that do not exist must read as zero
   for (int i = tid; i < (int)NG * SETS * 8 * MB; i += NCONS) corr[i] = 0.f;
@@ -450,7 +362,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
     // xs[m][k'] = 2^(c-p(k')) * x[m][orig(k')] for the compact columns, 8 at a time (zero past K'),
     // and corr[granule][set][m] = sum over the group of (B + off) * x.
     const int nitem = noct * p.M;
-    constexpr int U = 8;
+    constexpr int U = 4;
     constexpr int CE = Fold<BITS>::C_EXP;
     for (int base = 0; base < nitem; base += NCONS * U) {
       uint32_t v[U][4];
@@ -471,7 +383,6 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
           oct[u] = o;
           const uint32_t sh = osh[o];
           if (sh != 0xFFFFFFFFu) {
-            const int Kc_unused = Kc; (void)Kc_unused;
             const int lo0 = (int)(sh & 0xFFFFu), lo7 = (int)(sh >> 16);
             const __half* xr = p.x + (size_t)m * p.ldx;
             if (lo7 == lo0) {
@@ -551,8 +462,6 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
 
   const int g = lane >> 2, t = lane & 3;
   float* slots = reinterpret_cast<float*>(smem + p.off_slot);   // [slot][warp][m][16 rows]
-  const uint8_t* ring = smem + p.off_ring;
-  const uint8_t* cher = smem + p.off_cher;
 
   float tot[MB][4];
 #pragma unroll
@@ -560,94 +469,107 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
 #pragma unroll
     for (int r = 0; r < 4; ++r) tot[b][r] = 0.f;
 
-  // B-operand column g of activation tile b is activation row 8b + g.  Columns past the last
+  // Shared-memory byte offsets (relative to `smem`) this lane reads in every granule.
+  // B-operand column g of activation tile b is activation row 8b + g; columns past the last
   // row are never read back from the accumulators, so they may carry any existing row.
-  const __half* xrow[MB];
-  const __half* xcrow[MB];
+  uint32_t x_off[MB], xc_off[MB];
 #pragma unroll
   for (int b = 0; b < MB; ++b) {
     const int m = (8 * b + g) % p.M;
-    xrow[b] = xs + m * p.xs_stride + 16 * t;
-    xcrow[b] = xc + m * p.xc_stride + 2 * t;
+    x_off[b] = (uint32_t)p.off_xs + (uint32_t)(m * p.xs_stride + 16 * t) * 2u;
+    xc_off[b] = (uint32_t)p.off_xc + (uint32_t)(m * p.xc_stride + 2 * t) * 2u;
   }
+  const uint32_t corr_off = (uint32_t)p.off_corr + (uint32_t)(2 * t) * 4u;
+  const uint32_t lane_w = (BITS == 4) ? (uint32_t)lane * 16u : (uint32_t)lane * 24u;
+  const uint32_t ring_off = (uint32_t)p.off_ring + (uint32_t)warp * GB;       // this warp's slot in stage 0
 
-  uint32_t stage = 0, phase = 0, qrun = 0;
-  int pending = 0, nchunk = 0;
-  bool cher_ready = false;
-
-  for (int i = 0; i < npieces; ++i) {
-    const uint32_t j = j_hi - i;
-    const uint32_t sub0 = j * NG;
-    const uint32_t start = max(ga, sub0), end = min(gb, sub0 + NG);
-    for (uint32_t q0 = start; q0 < end; q0 += CHUNK) {
-      const uint32_t len = min((uint32_t)CHUNK, end - q0);
-      const bool trace = p.timeline && lane == 0 && (warp == 0 || warp == 5) && nchunk >= 2 && nchunk < 6;
-      unsigned long long* tr = trace ? p.timeline + (size_t)(512 + blockIdx.x) * 64 + (warp == 5 ? 32 : 0) + (nchunk - 2) * 4 : nullptr;
-      if (trace) tr[0] = clock64();
-      mbar_wait(bar_base + 8 * stage, phase, &s_abort, p.status);
-      if (trace) tr[1] = clock64();
-      if (tid == 0 && i == 0 && q0 == start) stamp(p, 5);
-      if (tid == 0 && nchunk < 24) stamp(p, 16 + nchunk);
-      ++nchunk;
-      const uint32_t rot = ((uint32_t)warp - qrun) & (NCW - 1);
-      qrun = (qrun + len) & (NCW - 1);
-      const uint8_t* sbase = ring + (size_t)stage * CHUNK * GB;
-      const uint32_t gi0 = q0 + rot - sub0;                 // this warp's first granule inside the sub-tile
-      if (len == (uint32_t)CHUNK) {
-        const uint8_t* gp[GPW];
-        uint32_t xo[GPW];
-        const float* cg[GPW];
-#pragma unroll
-        for (int r = 0; r < GPW; ++r) {
-          gp[r] = sbase + (size_t)(rot + NCW * r) * GB;
-          xo[r] = (gi0 + NCW * r) * 128;
-          cg[r] = corr + (gi0 + NCW * r) * SETS * 8 * MB;
-        }
-        process_granules<BITS, SETS, MB, GPW>(gp, xo, cg, xrow, lane, tot
-#ifdef CQ_TRACE_INNER
-            , trace ? tr + 8 * 64 * 1024 / 64 * 0 + (size_t)256 * 64 : nullptr
-#endif
-            );
-      } else {
-        for (int r = 0; r < GPW; ++r) {
-          const uint32_t o = rot + NCW * r;
-          if (o < len) {
-            const uint8_t* gp[1] = {sbase + (size_t)o * GB};
-            const uint32_t xo[1] = {(gi0 + NCW * r) * 128};
-            const float* cg[1] = {corr + (gi0 + NCW * r) * SETS * 8 * MB};
-            process_granules<BITS, SETS, MB, 1>(gp, xo, cg, xrow, lane, tot
-#ifdef CQ_TRACE_INNER
-            , nullptr
-#endif
-            );
-          }
-        }
-      }
-      // The granule that starts a sub-tile also adds the sub-tile's fp16 cherry columns.
-      if (q0 == sub0 && rot == 0 && p.Cp > 0) {
-        if (!cher_ready) {
-          mbar_wait(bar_base + 16 * S, 0, &s_abort, p.status);
-          cher_ready = true;
-        }
-        const uint8_t* blk = cher + (size_t)(j - jc_lo) * p.cher_bytes;
-        for (int jj = 0; jj < p.Cp / 16; ++jj) {
-          const uint4 a = *reinterpret_cast<const uint4*>(blk + jj * 512 + lane * 16);
-#pragma unroll
-          for (int b = 0; b < MB; ++b) {
-            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xcrow[b] + 16 * jj);
-            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xcrow[b] + 16 * jj + 8);
-            mma16816(tot[b], a.x, a.y, a.z, a.w, b0, b1);
-          }
-        }
-      }
-      if (trace) tr[2] = clock64();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_base + 8 * (S + stage));
-      if (trace) tr[3] = clock64();
-      if (++stage == S) { stage = 0; phase ^= 1; }
+  auto load_raw = [&](uint32_t stage_off, Raw<BITS>& r) {
+    const uint8_t* gp = smem + stage_off + lane_w;
+    if constexpr (BITS == 4) {
+      r.a = *reinterpret_cast<const uint4*>(gp);
+      r.b = *reinterpret_cast<const uint4*>(gp + 512);
+    } else {
+      r.a = *reinterpret_cast<const uint2*>(gp);
+      r.b = *reinterpret_cast<const uint2*>(gp + 8);
+      r.c = *reinterpret_cast<const uint2*>(gp + 16);
     }
+    // scales of rows (g, g+8) sit next to each other: [set][g][2]
+    const uint8_t* sp = smem + stage_off + 256 * BITS + 4 * g;
+    r.sc[0] = *reinterpret_cast<const uint32_t*>(sp);
+    r.sc[1] = (SETS == 2) ? *reinterpret_cast<const uint32_t*>(sp + 32) : r.sc[0];
+  };
 
-    // ---- end of piece i: park this warp's partial (the lane's C fragment: rows g, g+8; columns 2t, 2t+1)
+  // One granule: 8 MMAs (two accumulators per 64-column half, so that no MMA waits for the one
+  // issued just before it), then the group scales and the correction.
+  auto compute = [&](const Raw<BITS>& r, uint32_t gi) {
+    uint32_t A0[16], A1[16];   // fp16 pairs of rows g and g+8 (8 per 64-column half)
+    if constexpr (BITS == 4) {
+      decode4(r.a.x, A0);      decode4(r.a.y, A0 + 4);  decode4(r.a.z, A1);      decode4(r.a.w, A1 + 4);
+      decode4(r.b.x, A0 + 8);  decode4(r.b.y, A0 + 12); decode4(r.b.z, A1 + 8);  decode4(r.b.w, A1 + 12);
+    } else {
+      decode3(r.a.x, r.a.y, r.b.x, A0);
+      decode3(r.b.y, r.c.x, r.c.y, A1);
+    }
+    float acc[2][2][MB][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int b = 0; b < MB; ++b)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[h][j][b][e] = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t X[MB][8];
+#pragma unroll
+      for (int b = 0; b < MB; ++b) {
+        const uint8_t* xp = smem + x_off[b] + gi * 256u + h * 128;
+        const uint4 xa = *reinterpret_cast<const uint4*>(xp), xb = *reinterpret_cast<const uint4*>(xp + 16);
+        X[b][0] = xa.x; X[b][1] = xa.y; X[b][2] = xa.z; X[b][3] = xa.w;
+        X[b][4] = xb.x; X[b][5] = xb.y; X[b][6] = xb.z; X[b][7] = xb.w;
+      }
+#pragma unroll
+      for (int m = 0; m < 4; ++m)
+#pragma unroll
+        for (int b = 0; b < MB; ++b)
+          mma16816(acc[h][m & 1][b], A0[8 * h + 2 * m], A1[8 * h + 2 * m], A0[8 * h + 2 * m + 1], A1[8 * h + 2 * m + 1],
+                   X[b][2 * m], X[b][2 * m + 1]);
+    }
+    const float inv = 1.f / (float)(1 << Fold<BITS>::C_EXP);
+    const float2 s_lo = __half22float2(*reinterpret_cast<const __half2*>(&r.sc[0]));
+    const float2 s_hi = __half22float2(*reinterpret_cast<const __half2*>(&r.sc[1]));
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+      // corr: [granule][set][8 * MB] floats; this lane's columns are 8b + 2t, + 1
+      const uint8_t* cp = smem + corr_off + (gi * SETS * 8 * MB + 8 * b) * 4u;
+      const float2 c_lo = *reinterpret_cast<const float2*>(cp);
+      float a0[4], a1[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        a0[e] = acc[0][0][b][e] + acc[0][1][b][e];
+        a1[e] = acc[1][0][b][e] + acc[1][1][b][e];
+      }
+      if (SETS == 2) {
+        const float2 c_hi = *reinterpret_cast<const float2*>(cp + 8 * MB * 4);
+        tot[b][0] += s_lo.x * (a0[0] * inv - c_lo.x) + s_hi.x * (a1[0] * inv - c_hi.x);
+        tot[b][1] += s_lo.x * (a0[1] * inv - c_lo.y) + s_hi.x * (a1[1] * inv - c_hi.y);
+        tot[b][2] += s_lo.y * (a0[2] * inv - c_lo.x) + s_hi.y * (a1[2] * inv - c_hi.x);
+        tot[b][3] += s_lo.y * (a0[3] * inv - c_lo.y) + s_hi.y * (a1[3] * inv - c_hi.y);
+      } else {
+        tot[b][0] += s_lo.x * ((a0[0] + a1[0]) * inv - c_lo.x);
+        tot[b][1] += s_lo.x * ((a0[1] + a1[1]) * inv - c_lo.y);
+        tot[b][2] += s_lo.y * ((a0[2] + a1[2]) * inv - c_lo.x);
+        tot[b][3] += s_lo.y * ((a0[3] + a1[3]) * inv - c_lo.y);
+      }
+    }
+  };
+
+  // ---- piece bookkeeping: every warp closes every piece, in order, whether or not it held one of
+  // the piece's granules (partials are parked per warp and summed in warp order)
+  int pending = 0;
+  bool cher_ready = false;
+  auto close_piece = [&](uint32_t i) {
     {
       float* dst = slots + ((size_t)((i % p.nslot) * NCW + warp) * p.M) * 16;
 #pragma unroll
@@ -665,8 +587,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
       }
     }
     ++pending;
-    const bool post_now = (i == 0) && (end < sub0 + NG);   // piece 0 ends before its sub-tile does
-    if (!(post_now || pending == p.nslot || i == npieces - 1)) continue;
+    const Piece pc = piece_of(i, j_hi, NG, ga, gb);
+    const bool post_now = (i == 0) && (pc.end < pc.sub0 + NG);   // piece 0 ends before its sub-tile does
+    if (!(post_now || pending == p.nslot || i == npieces - 1)) return;
 
     // ---- emit the pending pieces
     if (tid == 0 && i == npieces - 1) stamp(p, 6);
@@ -674,10 +597,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
     uint32_t reset_lo = 1, reset_hi = 0;    // flags to clear afterwards (finishing CTA only)
     bool posted = false;
     if (tid < 256) {
-      for (int ii = i - pending + 1; ii <= i; ++ii) {
-        const uint32_t jj = j_hi - ii;
-        const uint32_t s0g = jj * NG;
-        const uint32_t pstart = max(ga, s0g), pend = min(gb, s0g + NG);
+      for (uint32_t ii = i + 1 - pending; ii <= i; ++ii) {
+        const Piece q = piece_of(ii, j_hi, NG, ga, gb);
         const int m = tid >> 4, r = tid & 15;
         float v = 0.f;
         if (m < p.M) {
@@ -685,19 +606,19 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
 #pragma unroll
           for (int w = 0; w < NCW; ++w) v += sl[(size_t)w * p.M * 16];
         }
-        if (pend < s0g + NG) {
+        if (q.end < q.sub0 + NG) {
           // an earlier part of a cut sub-tile: hand the partial to the CTA that holds its end
           p.partial[(size_t)cta * 256 + tid] = v;
           posted = true;
         } else {
-          if (pstart > s0g) {
-            const uint32_t c_first = (uint32_t)((((uint64_t)s0g + 1) * grid - 1) / p.T);
+          if (q.start > q.sub0) {
+            const uint32_t c_first = (uint32_t)((((uint64_t)q.sub0 + 1) * grid - 1) / p.T);
             reset_lo = c_first;
             reset_hi = cta - 1;
             mbar_wait(bar_base + 16 * S + 8, 0, &s_abort, p.status);
             v += reinterpret_cast<const float*>(smem + p.off_pf)[tid];
           }
-          const int n = (int)jj * 16 + r;
+          const int n = (int)q.j * 16 + r;
           if (m < p.M && n < p.N) {
             __half* yp = p.y + (size_t)m * p.ldy + n;
             if (p.accumulate) v += __half2float(*yp);
@@ -719,7 +640,68 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
       }
     }
     pending = 0;
+  };
+
+  // ---- this warp's granules: positions warp, warp + NCW, ... of the CTA's sequence.  While
+  // granule i is computed, the words of granule i+1 are already on their way from shared memory
+  // (its ring slot is released as soon as they are requested) and the barrier of granule i+2's
+  // stage is being probed; the probe's answer is only looked at after the math.
+  uint32_t pi = 0;                         // piece of the current position
+  Piece pc = piece_of(0, j_hi, NG, ga, gb);
+  uint32_t pstart = 0;                     // sequence position where piece pi starts
+  if ((uint32_t)warp < total) {
+    uint32_t pos = (uint32_t)warp, stage = 0, phase = 0;
+    Raw<BITS> cur, nxt;
+    mbar_wait(bar_base, 0, &s_abort, p.status);
+    if (tid == 0) stamp(p, 5);
+    load_raw(ring_off, cur);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_base + 8 * S);
+    if (pos + NCW < total) mbar_wait(bar_base + 8 * (1 % S), (1 / S) & 1, &s_abort, p.status);
+    for (;;) {
+      while (pos >= pstart + (pc.end - pc.start)) {
+        close_piece(pi);
+        pstart += pc.end - pc.start;
+        pc = piece_of(++pi, j_hi, NG, ga, gb);
+      }
+      const uint32_t gi = pc.start - pc.sub0 + (pos - pstart);     // granule inside the sub-tile
+      const bool has_next = pos + NCW < total, has_next2 = pos + 2 * NCW < total;
+      uint32_t nstage = stage + 1, nphase = phase;
+      if (nstage == S) { nstage = 0; nphase ^= 1; }
+      uint32_t n2stage = nstage + 1, n2phase = nphase;
+      if (n2stage == S) { n2stage = 0; n2phase ^= 1; }
+      if (has_next) {                      // its stage is known to have landed
+        load_raw(ring_off + nstage * NCW * GB, nxt);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_base + 8 * (S + nstage));
+      }
+      bool ready2 = false;
+      if (has_next2) ready2 = mbar_try_wait(bar_base + 8 * n2stage, n2phase);
+      compute(cur, gi);
+      // The granule that starts a sub-tile also adds the sub-tile's fp16 cherry columns.
+      if (gi == 0 && p.Cp > 0) {
+        if (!cher_ready) {
+          mbar_wait(bar_base + 16 * S, 0, &s_abort, p.status);
+          cher_ready = true;
+        }
+        const uint8_t* blk = smem + p.off_cher + (size_t)(pc.j - jc_lo) * p.cher_bytes;
+        for (int jj = 0; jj < p.Cp / 16; ++jj) {
+          const uint4 a = *reinterpret_cast<const uint4*>(blk + jj * 512 + lane * 16);
+#pragma unroll
+          for (int b = 0; b < MB; ++b) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(smem + xc_off[b] + 32 * jj);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(smem + xc_off[b] + 32 * jj + 16);
+            mma16816(tot[b], a.x, a.y, a.z, a.w, b0, b1);
+          }
+        }
+      }
+      if (!has_next) break;
+      if (has_next2 && !ready2) mbar_wait_slow(bar_base + 8 * n2stage, n2phase, &s_abort, p.status);
+      cur = nxt;
+      pos += NCW; stage = nstage; phase = nphase;
+    }
   }
+  for (; pi < npieces; ++pi) close_piece(pi);
 }
 
 // ------------------------------------------------------------------ host side
@@ -744,28 +726,26 @@ DeviceInfo device_info(int dev) {
 
 typedef void (*KernelFn)(const MatvecParams);
 
-// Kernel shapes: (consumer warps, granules per warp per ring stage).
+// Kernel shapes: consumer warps (one granule per warp per ring stage).
 struct Shape { int ncw, gpw; };
-constexpr Shape SHAPES[] = {{8, 2}, {16, 1}, {8, 1}, {12, 1}, {16, 1}};
+constexpr Shape SHAPES[] = {{8, 1}, {12, 1}, {16, 1}};
 constexpr int N_SHAPES = sizeof(SHAPES) / sizeof(SHAPES[0]);
 
-template <int NCW, int GPW, int MINB>
+template <int NCW, int MINB>
 KernelFn pick_bits(int bits, int sets, int mb) {
   if (bits == 4) {
-    if (sets == 1) return mb == 1 ? cq_matvec_kernel<4, 1, 1, NCW, GPW, MINB> : cq_matvec_kernel<4, 1, 2, NCW, GPW, MINB>;
-    return mb == 1 ? cq_matvec_kernel<4, 2, 1, NCW, GPW, MINB> : cq_matvec_kernel<4, 2, 2, NCW, GPW, MINB>;
+    if (sets == 1) return mb == 1 ? cq_matvec_kernel<4, 1, 1, NCW, MINB> : cq_matvec_kernel<4, 1, 2, NCW, MINB>;
+    return mb == 1 ? cq_matvec_kernel<4, 2, 1, NCW, MINB> : cq_matvec_kernel<4, 2, 2, NCW, MINB>;
   }
-  if (sets == 1) return mb == 1 ? cq_matvec_kernel<3, 1, 1, NCW, GPW, MINB> : cq_matvec_kernel<3, 1, 2, NCW, GPW, MINB>;
-  return mb == 1 ? cq_matvec_kernel<3, 2, 1, NCW, GPW, MINB> : cq_matvec_kernel<3, 2, 2, NCW, GPW, MINB>;
+  if (sets == 1) return mb == 1 ? cq_matvec_kernel<3, 1, 1, NCW, MINB> : cq_matvec_kernel<3, 1, 2, NCW, MINB>;
+  return mb == 1 ? cq_matvec_kernel<3, 2, 1, NCW, MINB> : cq_matvec_kernel<3, 2, 2, NCW, MINB>;
 }
 
 KernelFn pick_kernel(int shape, int bits, int sets, int mb) {
   switch (shape) {
-    case 0: return pick_bits<8, 2, 1>(bits, sets, mb);
-    case 1: return pick_bits<16, 1, 2>(bits, sets, mb);   // capped at 56 registers: two CTAs per SM
-    case 2: return pick_bits<8, 1, 1>(bits, sets, mb);
-    case 3: return pick_bits<12, 1, 1>(bits, sets, mb);
-    default: return pick_bits<16, 1, 1>(bits, sets, mb);
+    case 0: return pick_bits<8, 1>(bits, sets, mb);
+    case 1: return pick_bits<12, 1>(bits, sets, mb);
+    default: return pick_bits<16, 1>(bits, sets, mb);
   }
 }
 
@@ -784,8 +764,6 @@ Knobs knobs() {
   }();
   return k;
 }
-
-unsigned long long* g_timeline = nullptr;
 
 int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
@@ -839,7 +817,7 @@ int plan_smem(const cq_layer* L, int M, int grid, int max_smem, Shape sh, int ta
 // Tracing: when a device buffer of 1024 x 16 uint64 is set, every CTA of the following matvec
 // launches stores %globaltimer stamps of its phases there (slot meanings in cq_matvec_kernel).
 extern "C" int cq_trace_set_timeline(void* device_buffer) {
-  g_timeline = (unsigned long long*)device_buffer;
+  cq_g_timeline = (unsigned long long*)device_buffer;
   return CQ_OK;
 }
 
@@ -881,7 +859,7 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   p.partial = (float*)scratch;
   p.flag = (uint32_t*)((uint8_t*)scratch + (size_t)1024 * 256 * sizeof(float));
   p.status = status;
-  p.timeline = g_timeline;
+  p.timeline = cq_g_timeline;
   p.M = rows; p.K = L->K; p.N = L->N; p.C = L->C; p.Cp = L->Cp; p.Kp = L->Kp;
   p.n_gran = L->n_gran; p.n_sub = L->n_sub; p.gran_bytes = L->gran_bytes; p.cher_bytes = L->cher_bytes;
   p.ldx = ldx; p.ldy = ldy; p.accumulate = accumulate;

@@ -33,6 +33,8 @@
 
 #include "cq_tile.cuh"
 
+extern unsigned long long* cq_g_timeline;
+
 namespace {
 
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -54,6 +56,7 @@ struct UmmaParams {
   float* partial;      // [grid][16][128]
   uint32_t* flag;      // [grid]
   uint32_t* status;
+  unsigned long long* timeline;   // may be null: [grid][64] %globaltimer stamps (tracing)
   int M, K, N, C, Cp, Kp, n_gran, n_tile, n_cher, gran_bytes, tile_bytes, ipt;
   int ldx, ldy, accumulate;
   uint32_t T;          // total items
@@ -146,6 +149,14 @@ __device__ __forceinline__ void tmem_ld8(uint32_t addr, float* v) {
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tstamp(const UmmaParams& p, int slot) {
+  if (p.timeline) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.timeline[(size_t)blockIdx.x * 64 + slot] = t;
+  }
+}
 
 // ------------------------------------------------------------------ decode
 // OR-ing a code field that sits at mantissa bit p into the bit pattern of 1024.0 gives the fp16
@@ -258,6 +269,7 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
   const uint32_t B_PF = B_XC + 8;
 
   if (tid == 0) {
+    tstamp(p, 0);
     s_abort = 0;
     s_slotcnt[0] = s_slotcnt[1] = 0;
     for (uint32_t s = 0; s < S; ++s) { mbar_init(B_WFULL(s), 1); mbar_init(B_WEMPTY(s), 4); }
@@ -277,6 +289,7 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem;
+  if (tid == 0) tstamp(p, 1);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const bool has_work = ia < ib;
@@ -295,10 +308,12 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
                            (j < NCH ? (size_t)j * CQT_CHER_BYTES : (size_t)NCH * CQT_CHER_BYTES + (size_t)(j - NCH) * p.gran_bytes);
         const uint32_t s = n % S;
         if (n >= S) mbar_wait(B_WEMPTY(s), ((n / S) - 1) & 1, &s_abort, p.status, 1u);
+        if (n == 0) tstamp(p, 12);
         mbar_expect_tx(B_WFULL(s), bytes);
         bulk_g2s(ring + s * (uint32_t)p.stage_bytes, p.stream + off, bytes, B_WFULL(s));
         ++n;
       } while (w.next());
+      tstamp(p, 13);
     }
     // Partial sums of the tile at the head of this range that earlier CTAs started: they were
     // posted early in those CTAs' walks.  The scratch may still hold the previous launch's flags
@@ -345,6 +360,7 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
     for (int i = st; i < NCORR * SETS * 16; i += 64) corr[i] = 0.f;
     named_bar(2, 64);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (st == 0) tstamp(p, 2);
 
     // activations of the cherry columns, unscaled: [item j][half c][row r][8 fp16] (+ row group)
     for (int idx = st; idx < p.M * p.Cp; idx += 64) {
@@ -357,6 +373,7 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
     if (lane == 0) mbar_arrive(B_XC);
+    if (st == 0) tstamp(p, 3);
 
     // Windows of up to WIN_GRAN granules, in the order the MMA warp consumes them.  The two stager
     // warps take alternate windows, so that two windows' trips to L2 overlap; a lane stages the
@@ -461,7 +478,7 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(B_XFULL(xs));
+        if (lane == 0) { mbar_arrive(B_XFULL(xs)); if (wn < 8) tstamp(p, 4 + wn); }
       }
       ++wn;
       for (uint32_t e = 0; e < len && more; ++e) { more = w.next(); ++n; }
@@ -504,6 +521,7 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
         }
         tc_commit(B_AEMPTY(a));
         tc_commit(B_DFULL(d));
+        if (n < 24) tstamp(p, 16 + n);
         ++n;
         more = w.next();
       }
@@ -637,9 +655,14 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
     while (more) {
       last_piece = w.piece;
       if ((int)(n % NGRP) == grp) {
+        const uint32_t kidx = n / NGRP;
+        unsigned long long* ft = (p.timeline && tid == 0 && kidx >= 3 && kidx < 7) ? p.timeline + (size_t)(512 + blockIdx.x) * 64 + (kidx - 3) * 12 : nullptr;
+#define FT(i) do { if (ft) ft[i] = clock64(); } while (0)
+        FT(0);
         const uint32_t j = w.cur - w.tile * IPT;
         const uint32_t s = n % S, a = n % NA;
         mbar_wait(B_WFULL(s), (n / S) & 1, &s_abort, p.status, 1024u);
+        FT(1);
         const uint8_t* item = ring + (size_t)s * p.stage_bytes;
         const bool cherry = j < NCH;
         constexpr int NW = 4 * BITS;
@@ -657,8 +680,10 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(B_WEMPTY(s));
+        FT(2);
         if (n >= NA) mbar_wait(B_AEMPTY(a), ((n / NA) - 1) & 1, &s_abort, p.status, 2048u);
         tc_fence_after();
+        FT(3);
         const uint32_t ta = tmem + lane_addr + a * A_COLS;
         if (cherry) {
           const uint32_t v[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
@@ -683,12 +708,18 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
             }
           }
         }
+        FT(4);
         tmem_wait_st();
+        FT(5);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(B_AFULL(a));
+        FT(6);
+        if (tid == 0 && n / NGRP < 12) tstamp(p, 40 + n / NGRP);
 
         if (pend) epilogue();
+        FT(7);
+        if (tid == 0 && n / NGRP < 12) tstamp(p, 52 + n / NGRP);
         pend = true;
         pend_n = n;
         pend_piece = w.piece;
@@ -700,8 +731,10 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
       ++n;
       more = w.next();
     }
+    if (tid == 0) tstamp(p, 14);
     if (pend) epilogue();
     for (int pc = tot_piece; pc <= last_piece; ++pc) flush_piece(pc);
+    if (tid == (NGRP - 1) * 128) tstamp(p, 15);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -780,6 +813,7 @@ extern "C" int cq_tlayer_matvec(const cq_tlayer* L, const void* x, int ldx, void
     p.partial = (float*)scratch;
     p.flag = (uint32_t*)((uint8_t*)scratch + (size_t)256 * 2048 * sizeof(float));
     p.status = status_word;
+    p.timeline = cq_g_timeline;
     p.M = rows; p.K = L->K; p.N = L->N; p.C = L->C; p.Cp = L->Cp; p.Kp = L->Kp;
     p.n_gran = L->n_gran; p.n_tile = L->n_tile; p.n_cher = L->n_cher;
     p.gran_bytes = L->gran_bytes; p.tile_bytes = L->tile_bytes; p.ipt = L->n_cher + L->n_gran;
