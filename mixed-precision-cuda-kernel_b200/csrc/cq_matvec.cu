@@ -752,13 +752,15 @@ KernelFn pick_kernel(int shape, int bits, int sets, int mb) {
 // Tuning knobs read once from the environment (for experiments; defaults are the product):
 //   CQ_SHAPE  index into SHAPES      CQ_SMEM_KB  shared-memory target per CTA
 //   CQ_PDL    0 disables programmatic dependent launch
-struct Knobs { int shape, smem_kb, pdl; };
+struct Knobs { int shape, smem_kb, pdl, max_stages; };
 Knobs knobs() {
   static Knobs k = [] {
-    Knobs v{0, 112, 1};
+    Knobs v{0, 112, 1, 16};
     if (const char* e = getenv("CQ_SHAPE")) v.shape = atoi(e);
     if (const char* e = getenv("CQ_SMEM_KB")) v.smem_kb = atoi(e);
     if (const char* e = getenv("CQ_PDL")) v.pdl = atoi(e);
+    if (const char* e = getenv("CQ_MAX_STAGES")) v.max_stages = atoi(e);
+    if (v.max_stages < 2) v.max_stages = 2;
     if (v.shape < 0 || v.shape >= N_SHAPES) v.shape = 0;
     return v;
   }();
@@ -768,7 +770,8 @@ Knobs knobs() {
 int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
 // Shared-memory plan for M activation rows; returns total bytes or -1 if it cannot fit.
-int plan_smem(const cq_layer* L, int M, int grid, int max_smem, Shape sh, int target_kb, MatvecParams* p) {
+int plan_smem(const cq_layer* L, int M, int grid, int max_smem, Shape sh, int target_kb, int max_stages,
+              MatvecParams* p) {
   const uint32_t T = (uint32_t)L->n_sub * (uint32_t)L->n_gran;
   const uint32_t per = (T + grid - 1) / grid;
   const int max_pieces = (int)((per + L->n_gran - 1) / L->n_gran) + 1;
@@ -801,12 +804,12 @@ int plan_smem(const cq_layer* L, int M, int grid, int max_smem, Shape sh, int ta
   int budget = target_kb * 1024;
   if (budget - fixed < 64 * 1024) budget = max_smem;
   int stages = (budget - fixed) / chunk;
-  if (stages < 2) stages = 2;
   if (stages > 16) stages = 16;
+  if (stages > max_stages) stages = max_stages;
   const uint32_t max_chunks = per / chunk_gran + (uint32_t)max_pieces + 1;
   if ((uint32_t)stages > max_chunks) stages = (int)max_chunks;
-  if (stages < 1) stages = 1;
-  while (stages > 1 && fixed + stages * chunk > max_smem) --stages;
+  // The consumers run two ring stages ahead of their math: at least two stages are required.
+  if (stages < 2) stages = 2;
   if (fixed + stages * chunk > max_smem) return -1;
   p->stages = stages;
   return fixed + stages * chunk;
@@ -846,7 +849,7 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   int rows = M < 16 ? M : 16;
   int smem = -1;
   for (; rows >= 1; --rows) {
-    smem = plan_smem(L, rows, grid, di.max_smem, sh, kn.smem_kb, &p);
+    smem = plan_smem(L, rows, grid, di.max_smem, sh, kn.smem_kb, kn.max_stages, &p);
     if (smem >= 0) break;
   }
   if (smem < 0) return CQ_ERR_TOO_LARGE;
