@@ -53,7 +53,8 @@ typedef enum cq_status {
   CQ_ERR_CUDA = 6,          /* a CUDA runtime call failed; see cq_last_cuda_error()       */
   CQ_ERR_NO_DEVICE = 7,     /* no CUDA device, or device is not compute capability 10.x   */
   CQ_ERR_DEVICE_TIMEOUT = 8,/* a bounded device-side wait ran out (reported by cq_poll)   */
-  CQ_ERR_UNSUPPORTED = 9    /* valid request that this build has no kernel for            */
+  CQ_ERR_UNSUPPORTED = 9,   /* valid request that this build has no kernel for            */
+  CQ_ERR_STATIC_LIMIT = 10  /* request exceeds the built-in scratch of cq_layer_matvec_static */
 } cq_status;
 
 const char* cq_strerror(int status);
@@ -115,6 +116,24 @@ size_t cq_scratch_bytes(void);
 int cq_layer_matvec(const cq_layer* layer, const void* x_f16, int ldx, void* y_f16, int ldy,
                     int M, int accumulate, void* scratch, uint32_t* status_word,
                     cq_stream_t stream);
+
+/* cq_layer_matvec without a scratch argument and without any allocation (no counterpart in the
+ * reference, whose kernels accumulate with atomicAdd and need no scratch,
+ * csrc/quant_cuda_kernel.cu:672-676).  For callers that have no scratch buffer to hand over and may
+ * not allocate one: runtimes whose device memory is planned up front, plugins living in another
+ * process's memory pool, latency-critical loops where an allocation would stall the device.  The
+ * cross-CTA partial sums and flags live in a fixed array inside the library's device image
+ * (263,168 bytes per device).
+ *   Limits: 1 <= M <= 16 (one launch), a device with at most 256 SMs, and a layer whose M rows fit
+ *   one launch's shared-memory plan; otherwise CQ_ERR_STATIC_LIMIT and nothing is launched.
+ *   Every call on a device shares the array: calls that can overlap on the GPU (other streams,
+ *   other threads) race and must be serialised by the caller.  Each call clears the flags on
+ *   `stream` before its launch.
+ *   The first call on each device also resolves the array's device address; make that call
+ *   before beginning any stream capture on the device.
+ * Results are identical to cq_layer_matvec's for the same arguments. */
+int cq_layer_matvec_static(const cq_layer* layer, const void* x_f16, int ldx, void* y_f16, int ldy,
+                           int M, int accumulate, uint32_t* status_word, cq_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Tile-layout prepared layer: the format of the tcgen05 (UMMA + tensor memory) kernels.

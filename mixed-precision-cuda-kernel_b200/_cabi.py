@@ -18,6 +18,7 @@ SYMBOLS = [
     "cq_cache_clear", "cq_cache_stats", "cq_poll",
     "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense", "cq_trace_set_timeline",
     "cq_tlayer_init", "cq_tlayer_prepare", "cq_tlayer_unprepare", "cq_tlayer_matvec",
+    "cq_layer_matvec_static",
 ]
 
 
@@ -57,6 +58,7 @@ def lib():
     L.cq_layer_prepare.argtypes = [C.POINTER(cq_layer), vp, vp, vp, vp, vp]
     L.cq_layer_unprepare.argtypes = [C.POINTER(cq_layer), vp, vp, vp, vp, vp]
     L.cq_layer_matvec.argtypes = [C.POINTER(cq_layer), vp, i32, vp, i32, i32, i32, vp, vp, vp]
+    L.cq_layer_matvec_static.argtypes = [C.POINTER(cq_layer), vp, i32, vp, i32, i32, i32, vp, vp]
     L.cq_tlayer_init.argtypes = [C.POINTER(cq_tlayer), i32, i32, i32, i32, i32, vp]
     L.cq_tlayer_prepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]
     L.cq_tlayer_unprepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]

@@ -109,6 +109,9 @@ extern "C" const char* cq_strerror(int status) {
     case CQ_ERR_NO_DEVICE: return "no usable CUDA device";
     case CQ_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
     case CQ_ERR_UNSUPPORTED: return "not supported by this build";
+    case CQ_ERR_STATIC_LIMIT:
+      return "request exceeds the built-in scratch of cq_layer_matvec_static (more than 16 rows, more "
+             "than 256 SMs, or a layer whose rows do not fit one launch); use cq_layer_matvec";
     default: return "unknown status";
   }
 }

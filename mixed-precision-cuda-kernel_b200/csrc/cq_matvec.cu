@@ -26,6 +26,7 @@
 //    sums are therefore deterministic.  Every wait is bounded; running out sets
 //    a bit in the status word instead of hanging.
 #include <cstdlib>
+#include <mutex>
 
 #include "cq_common.cuh"
 
@@ -901,5 +902,114 @@ extern "C" int cq_layer_matvec(const cq_layer* L, const void* x, int ldx, void* 
     if (rc != CQ_OK) return rc;
     done += rows;
   }
+  return CQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Variant of cq_layer_matvec for callers that own no device scratch and may not obtain any.
+//
+// Who that is: a host runtime that plans all of its device memory up front and forbids
+// allocation once serving has begun (an inference server with a fixed arena, a plugin loaded
+// into somebody else's process that must not disturb that process's memory pool), and code that
+// runs where an allocation would synchronise the device or fail outright, such as a latency-
+// critical decode loop.  cq_layer_matvec asks such a caller for cq_scratch_bytes() of zeroed
+// memory; this entry point brings its own instead: the array below lives in the library's
+// device image, so it exists on every device as soon as the module is loaded there, and no
+// allocating call (runtime, driver or framework) is made here, ever.
+//
+// Limits (beyond them the call returns CQ_ERR_STATIC_LIMIT and launches nothing):
+//   * at most CQ_STATIC_MAX_ROWS (16) activation rows per call: one kernel launch;
+//   * at most CQ_STATIC_MAX_CTAS (256) CTAs, i.e. a device with at most 256 SMs.
+// Layout of the array: [256 CTAs][256 floats] partial sums | 256 flags | (pad to 256 B).
+//
+// Sharing: every call on a device uses the same array.  Partial sums are written before they are
+// read, the flags must be zero when the kernel starts: each call clears them on the stream ahead of
+// its launch, so a call that follows one that ended in a device time-out still starts clean.  Two
+// calls that can run at the same time on one device (different streams, different host threads)
+// race on the array and give wrong sums: serialise them.
+//
+// Set-up: the first call on each device resolves the array's device address
+// (cudaGetSymbolAddress, with that device current).  That first call should be made before any
+// stream capture is begun on the device.
+static constexpr int CQ_STATIC_MAX_ROWS = 16;
+static constexpr int CQ_STATIC_MAX_CTAS = 256;
+static constexpr size_t CQ_STATIC_PARTIAL_BYTES = (size_t)CQ_STATIC_MAX_CTAS * 256 * sizeof(float);
+static constexpr size_t CQ_STATIC_FLAG_BYTES = (size_t)CQ_STATIC_MAX_CTAS * sizeof(uint32_t);
+static constexpr size_t CQ_STATIC_BYTES = CQ_STATIC_PARTIAL_BYTES + CQ_STATIC_FLAG_BYTES;  // 263,168 B
+
+static __device__ __align__(256) unsigned char cq_static_scratch[CQ_STATIC_BYTES];
+
+namespace {
+constexpr int CQ_STATIC_MAX_DEVICES = 64;
+std::mutex g_static_mu;
+unsigned char* g_static_ptr[CQ_STATIC_MAX_DEVICES] = {};
+
+// Device address of cq_static_scratch on the current device (resolved once per device).
+int static_scratch_ptr(int dev, unsigned char** out) {
+  if (dev < 0 || dev >= CQ_STATIC_MAX_DEVICES) return CQ_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    unsigned char* ptr = nullptr;
+    CQ_CUDA_TRY(cudaGetSymbolAddress((void**)&ptr, cq_static_scratch));
+    if (!ptr || ((uintptr_t)ptr & 255)) return CQ_ERR_CUDA;
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return CQ_OK;
+}
+}  // namespace
+
+extern "C" int cq_layer_matvec_static(const cq_layer* L, const void* x, int ldx, void* y, int ldy,
+                                      int M, int accumulate, uint32_t* status_word,
+                                      cq_stream_t stream) {
+  if (!L || !L->blob || !x || !y) return CQ_ERR_BAD_ARG;
+  if (M < 1 || ldx < L->K || ldy < L->N) return CQ_ERR_BAD_ARG;
+  if (((uintptr_t)x & 1) || ((uintptr_t)y & 1)) return CQ_ERR_BAD_ARG;
+  if (M > CQ_STATIC_MAX_ROWS) return CQ_ERR_STATIC_LIMIT;
+  int dev = 0;
+  CQ_CUDA_TRY(cudaGetDevice(&dev));
+  const DeviceInfo di = device_info(dev);
+  if (!di.ok) return CQ_ERR_NO_DEVICE;
+  if (di.sms > CQ_STATIC_MAX_CTAS) return CQ_ERR_STATIC_LIMIT;
+  const Knobs kn = knobs();
+  const Shape sh = SHAPES[kn.shape];
+  const uint32_t T = (uint32_t)L->n_sub * (uint32_t)L->n_gran;
+  int grid = di.sms;
+  if ((uint32_t)grid > T) grid = (int)T;
+
+  // one launch must take all M rows: the array has room for one launch's partial sums only
+  MatvecParams p;
+  const int smem = plan_smem(L, M, grid, di.max_smem, sh, kn.smem_kb, kn.max_stages, &p);
+  if (smem < 0) return CQ_ERR_STATIC_LIMIT;
+
+  unsigned char* base = nullptr;
+  const int rc = static_scratch_ptr(dev, &base);
+  if (rc != CQ_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  CQ_CUDA_TRY(cudaMemsetAsync(base + CQ_STATIC_PARTIAL_BYTES, 0, CQ_STATIC_FLAG_BYTES, st));
+
+  const uint8_t* blob = (const uint8_t*)L->blob;
+  p.stream = blob + L->off_stream;
+  p.cstream = blob + L->off_cherry;
+  p.cidx = (const uint16_t*)(blob + L->off_cidx);
+  p.osh = (const uint32_t*)(blob + L->off_osh);
+  p.x = (const __half*)x; p.y = (__half*)y;
+  p.partial = (float*)base;
+  p.flag = (uint32_t*)(base + CQ_STATIC_PARTIAL_BYTES);
+  p.status = status_word;
+  p.timeline = nullptr;
+  p.M = M; p.K = L->K; p.N = L->N; p.C = L->C; p.Cp = L->Cp; p.Kp = L->Kp;
+  p.n_gran = L->n_gran; p.n_sub = L->n_sub; p.gran_bytes = L->gran_bytes; p.cher_bytes = L->cher_bytes;
+  p.ldx = ldx; p.ldy = ldy; p.accumulate = accumulate;
+  p.T = T;
+
+  KernelFn fn = pick_kernel(kn.shape, L->bits, L->sets, (M + 7) / 8);
+  CQ_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3((sh.ncw + 1) * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  CQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, fn, p));
   return CQ_OK;
 }
