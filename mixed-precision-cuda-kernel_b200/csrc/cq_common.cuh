@@ -9,21 +9,24 @@
 //   stream    = n_sub x n_gran granules, sub-tile major, each `gran_bytes` long:
 //                 [codes: 16 rows x 128 codes x bits/8][scales: sets x 8 x (row g, row g+8) fp16]
 //
-// Codes inside a granule are stored in the order a warp consumes them with
-// mma.sync.m16n8k16 (A = 16 rows x 16 k' of weights, B = 16 k' x 8 batch):
-// lane = 4*g + t (g = 0..7, t = 0..3) owns rows g and g+8 and, in each 64-column
-// half `h` of the granule, the 16 compact columns k' = 128*gran + 64*h + 16*t + i.
-// MMA m (0..3) of a half uses the lane's columns i = 4m..4m+3, as fragment
-// registers a0/a1 (i = 4m, 4m+1; rows g / g+8) and a2/a3 (i = 4m+2, 4m+3).
+// Codes inside a granule are stored in the order a warp consumes them with the integer
+// tensor-core instruction mma.sync.m16n8k32 (A = 16 rows x 32 k' of unsigned 8-bit codes,
+// B = 32 k' x 8 columns of signed 8-bit activations): lane = 4*g + c (g = 0..7, c = 0..3)
+// owns rows g and g+8.  MMA m (0..3) covers the granule's columns 32m..32m+31; inside it the
+// lane's fragment registers hold, as bytes i = 0..3, the columns
+//     kk = 32*m + 16*b + 4*c + i        b = 0: registers a0 (row g), a1 (row g+8)
+//                                         b = 1: registers a2 (row g), a3 (row g+8).
+// Register j = 2*m + b (0..7) of a row is the unit of packing:
 //
-//   4-bit: [half h][lane][16 B] = words {row g: i=0..7, i=8..15, row g+8: i=0..7, i=8..15};
-//          inside a word code i sits at nibble (i>>1) + 4*(i&1), so that one mask
-//          yields the fp16 pair (i, i+1) in the (low, high) halves of a register.
-//   3-bit: [lane][24 B] = words {row g: w0 w1 w2, row g+8: w0 w1 w2}; a row's 32
-//          codes e (e<16: half 0, i=e; e>=16: half 1, i=e-16) form pairs q = e>>1;
-//          pair q < 15 lives in word q/5 at bit 16*(e&1) + 1 + 3*(q%5); pair 15
-//          (e = 30, 31) is spread over bit 16*(e&1) of w0 (code bit 0), w1 (bit 1),
-//          w2 (bit 2).
+//   4-bit: one 32-bit word per (row, m): byte i = code(j = 2m) | code(j = 2m+1) << 4, so
+//          `w & 0x0F0F0F0F` and `(w >> 4) & 0x0F0F0F0F` are the two registers.
+//          [plane m>>1][lane][16 B] = words {m even: row g, row g+8; m odd: row g, row g+8}.
+//   3-bit: three words A, B, C per row; byte i of
+//            A = code(j=0) | code(j=1) << 3 | (code(j=6) & 3) << 6
+//            B = code(j=2) | code(j=3) << 3 | (code(j=6) >> 2) << 6 | (code(j=7) >> 2) << 7
+//            C = code(j=4) | code(j=5) << 3 | (code(j=7) & 3) << 6
+//          [lane][16 B] = {A, B, C of row g, A of row g+8}, then at byte 512 [lane][8 B] =
+//          {B, C of row g+8}.
 //
 //   cherry stream = n_sub blocks of (Cp/16) x [lane][16 B] fp16 A-fragments:
 //          a0 = W[c=16j+2t, 2t+1][row g], a1 = same c, row g+8, a2/a3 = c + 8.
@@ -79,3 +82,19 @@ __host__ __device__ inline void cq_s3_pos(int e, int* word, int* bit) {
   *word = q / 5;
   *bit = 16 * (e & 1) + 1 + 3 * (q % 5);
 }
+
+// ---- stream layout: where code (row rl = 0..15, column kk = 0..127) of a granule sits.
+// 4-bit: byte offset of its 32-bit word inside the granule and the shift of the nibble.
+__host__ __device__ inline void cq_sl4_pos(int rl, int kk, int* word_off, int* shift) {
+  const int m = kk >> 5, b = (kk >> 4) & 1, c = (kk >> 2) & 3, i = kk & 3;
+  const int lane = 4 * (rl & 7) + c, r = rl >> 3;
+  *word_off = (m >> 1) * 512 + lane * 16 + ((m & 1) * 2 + r) * 4;
+  *shift = 8 * i + 4 * b;
+}
+// 3-bit: byte offset of word w (0 = A, 1 = B, 2 = C) of row rl for the lane that owns column kk.
+__host__ __device__ inline int cq_sl3_word_off(int rl, int c, int w) {
+  const int lane = 4 * (rl & 7) + c;
+  if ((rl >> 3) == 0) return lane * 16 + 4 * w;
+  return w == 0 ? lane * 16 + 12 : 512 + lane * 8 + 4 * (w - 1);
+}
+

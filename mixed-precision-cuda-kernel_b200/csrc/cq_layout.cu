@@ -32,38 +32,42 @@ __global__ void prepare_codes_kernel(LayoutDims d, const uint8_t* __restrict__ q
     const int w = (int)(id % wpg);
     const int sub = (int)(gran / d.n_gran), gi = (int)(gran % d.n_gran);
     uint32_t word = 0;
-    int lane, row_local;
+    // which (lane, row half r, word) this 32-bit word is: the inverse of cq_sl4_pos / cq_sl3_word_off
     if (d.bits == 4) {
-      const int h = w >> 7;
-      lane = (w & 127) >> 2;
-      const int wq = w & 3;
-      row_local = (lane >> 2) + 8 * (wq >> 1);
-      const int n = sub * 16 + row_local;
-      const int kbase = gi * 128 + h * 64 + 16 * (lane & 3) + 8 * (wq & 1);
+      const int plane = w >> 7, lane = (w & 127) >> 2, wq = w & 3;
+      const int m = 2 * plane + (wq >> 1), r = wq & 1;
+      const int n = sub * 16 + (lane >> 2) + 8 * r, c = lane & 3;
       if (n < d.N) {
-        for (int i = 0; i < 8; ++i) {
-          const int kc = kbase + i;
-          if (kc < d.Kc) word |= cq_ref_code(q, 4, kc, n, d.N) << cq_s4_shift(i);
-        }
+        for (int b = 0; b < 2; ++b)
+          for (int i = 0; i < 4; ++i) {
+            const int kc = gi * 128 + 32 * m + 16 * b + 4 * c + i;
+            if (kc < d.Kc) word |= cq_ref_code(q, 4, kc, n, d.N) << (8 * i + 4 * b);
+          }
       }
     } else {
-      lane = w / 6;
-      const int wq = w % 6;
-      row_local = (lane >> 2) + 8 * (wq / 3);
-      const int wi = wq % 3;
-      const int n = sub * 16 + row_local;
-      const int kbase = gi * 128 + 16 * (lane & 3);
+      int lane, r, wi;
+      if (w < 128) {
+        lane = w >> 2;
+        r = ((w & 3) == 3) ? 1 : 0;
+        wi = r ? 0 : (w & 3);
+      } else {
+        lane = (w - 128) >> 1;
+        r = 1;
+        wi = 1 + ((w - 128) & 1);
+      }
+      const int n = sub * 16 + (lane >> 2) + 8 * r, c = lane & 3;
       if (n < d.N) {
-        for (int p = 0; p < 5; ++p) {
-          for (int hh = 0; hh < 2; ++hh) {
-            const int e = 2 * (5 * wi + p) + hh;
-            const int kc = kbase + ((e < 16) ? e : 64 + (e - 16));
-            if (kc < d.Kc) word |= cq_ref_code(q, 3, kc, n, d.N) << (16 * hh + 1 + 3 * p);
-          }
-        }
-        for (int hh = 0; hh < 2; ++hh) {  // pair 15: codes e = 30, 31 -> column 64 + 14 + hh
-          const int kc = kbase + 64 + 14 + hh;
-          if (kc < d.Kc) word |= ((cq_ref_code(q, 3, kc, n, d.N) >> wi) & 1u) << (16 * hh);
+        // code of fragment register j (0..7), byte i
+        auto code = [&](int j, int i) -> uint32_t {
+          const int kc = gi * 128 + 32 * (j >> 1) + 16 * (j & 1) + 4 * c + i;
+          return kc < d.Kc ? cq_ref_code(q, 3, kc, n, d.N) : 0u;
+        };
+        for (int i = 0; i < 4; ++i) {
+          uint32_t byte;
+          if (wi == 0) byte = code(0, i) | (code(1, i) << 3) | ((code(6, i) & 3u) << 6);
+          else if (wi == 1) byte = code(2, i) | (code(3, i) << 3) | ((code(6, i) >> 2) << 6) | ((code(7, i) >> 2) << 7);
+          else byte = code(4, i) | (code(5, i) << 3) | ((code(7, i) & 3u) << 6);
+          word |= byte << (8 * i);
         }
       }
     }
@@ -144,23 +148,21 @@ __global__ void prepare_index_kernel(LayoutDims d, const int16_t* __restrict__ i
 
 // ---------------------------------------------------------------- stream readers
 __device__ __forceinline__ uint32_t stream_code(const LayoutDims& d, const uint8_t* stream, int kc, int n) {
-  const int sub = n >> 4, rl = n & 15, g = rl & 7, hi = rl >> 3;
-  const int gi = kc >> 7, kk = kc & 127, h = kk >> 6, t = (kk & 63) >> 4, i = kk & 15;
-  const int lane = 4 * g + t;
+  const int sub = n >> 4, rl = n & 15;
+  const int gi = kc >> 7, kk = kc & 127;
   const uint8_t* gran = stream + ((size_t)sub * d.n_gran + gi) * d.gran_bytes;
   if (d.bits == 4) {
-    const uint32_t w = *reinterpret_cast<const uint32_t*>(gran + h * 512 + lane * 16 + 4 * (2 * hi + (i >> 3)));
-    return (w >> cq_s4_shift(i & 7)) & 0xFu;
+    int off, shift;
+    cq_sl4_pos(rl, kk, &off, &shift);
+    return (*reinterpret_cast<const uint32_t*>(gran + off) >> shift) & 0xFu;
   }
-  const uint32_t* w = reinterpret_cast<const uint32_t*>(gran + lane * 24 + 12 * hi);
-  const int e = 16 * h + i;
-  if (e < 30) {
-    int word, bit;
-    cq_s3_pos(e, &word, &bit);
-    return (w[word] >> bit) & 0x7u;
-  }
-  const int b = 16 * (e & 1);
-  return ((w[0] >> b) & 1u) | (((w[1] >> b) & 1u) << 1) | (((w[2] >> b) & 1u) << 2);
+  const int j = 2 * (kk >> 5) + ((kk >> 4) & 1), c = (kk >> 2) & 3, i = kk & 3;
+  auto byte_of = [&](int w) -> uint32_t {
+    return (*reinterpret_cast<const uint32_t*>(gran + cq_sl3_word_off(rl, c, w)) >> (8 * i)) & 0xFFu;
+  };
+  if (j < 6) return (byte_of(j >> 1) >> (3 * (j & 1))) & 0x7u;
+  if (j == 6) return (byte_of(0) >> 6) | (((byte_of(1) >> 6) & 1u) << 2);
+  return (byte_of(2) >> 6) | ((byte_of(1) >> 7) << 2);
 }
 
 // ---------------------------------------------------------------- unprepare

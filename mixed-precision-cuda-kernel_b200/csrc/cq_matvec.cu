@@ -10,15 +10,20 @@
 //    (16 rows x 128 compact columns).  CTA c owns the contiguous granule range
 //    [T*c/grid, T*(c+1)/grid): an equal byte share whatever N and K are.
 //  * A producer warp moves the range into a shared-memory ring with 1-D bulk
-//    async copies (cp.async.bulk + mbarrier transaction counts), NCW * GPW
+//    async copies (cp.async.bulk + mbarrier transaction counts), 2 * NCW
 //    granules per copy.  It starts before the kernel waits for the previous kernel
 //    in the stream (programmatic dependent launch): weights never depend on it.
-//  * NCW consumer warps take the granules of a copy round-robin, GPW each.  A lane
-//    reads its 16 (4-bit) or 24 (3-bit) bytes, turns codes into fp16 pairs with one
-//    AND-OR per pair (exponent trick, offsets folded into a per-group correction
-//    computed while the activations are staged), and feeds mma.sync.m16n8k16 with
-//    the activations (staged once in shared memory in compact order) as the B
-//    operand.  Group scales are applied per granule in fp32.
+//  * NCW consumer warps take the granules of a copy two each.  A lane reads
+//    its 32 (4-bit) or 24 (3-bit) bytes and turns them into the A fragments of the integer
+//    tensor-core instruction mma.sync.m16n8k32 (u8 x s8 -> s32) with one or two logic
+//    operations per four codes (byte masks; no conversion, no arithmetic per weight).
+//    The activations are the B operand: while they are staged (once per launch, in compact
+//    column order) every granule's 128 values of a row are scaled to 15-bit integers
+//    q = 128 hi + lo and stored as two signed bytes, which occupy two of the MMA's eight B
+//    columns, so one MMA yields sum(u hi) and sum(u lo) exactly.  Per granule and group:
+//        y += s * (sx * (128 sum(u hi) + sum(u lo)) - off * sx * sum(q))
+//    with sx the activation step of that granule; the last term is prepared while staging.
+//    The cherry columns stay fp16 x fp16 on mma.sync.m16n8k16.
 //  * A range is walked from its last sub-tile to its first.  A sub-tile cut by a
 //    range boundary is finished by the CTA that holds its end: CTAs holding an
 //    earlier part post their fp32 partial to global scratch early in their walk,
@@ -52,8 +57,8 @@ struct MatvecParams {
   uint32_t T;          // total granules
   int stages, nslot, max_cher;
   // shared-memory offsets
-  int off_ring, off_cher, off_xs, off_xc, off_cidx, off_osh, off_corr, off_slot, off_pf, off_bar;
-  int xs_stride;       // halves per activation row in smem (Kp + 8)
+  int off_ring, off_cher, off_zero, off_sched, off_xb, off_xq, off_xc, off_cidx, off_osh, off_slot, off_pf, off_bar;
+  int xb_gran;         // bytes of quantised activations per granule: 2 planes x 2M columns x 64 B
   int xc_stride;       // halves per cherry-activation row (Cp + 8)
 };
 
@@ -119,10 +124,13 @@ __device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
 __device__ __forceinline__ void st_release(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
+// D = A (16 x 32 unsigned bytes) . B (32 x 8 signed bytes) + C, 32-bit integers
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
 }
 
 __device__ __forceinline__ void stamp(const MatvecParams& p, int slot) {
@@ -134,60 +142,28 @@ __device__ __forceinline__ void stamp(const MatvecParams& p, int slot) {
 }
 
 // ------------------------------------------------------------------ decode
-// Codes become fp16 values with one AND-OR each: OR-ing a code field that sits at
-// mantissa bit p into the bit pattern of 1024.0 gives the fp16 number 1024 + 2^p * u.
-// No subtraction follows.  Instead the activation that meets this code in the MMA is
-// pre-multiplied by 2^(c-p) when it is staged, so that the product is
-// 2^c * (B + u) * x with B = 2^(10-p), and the excess (B + off) * x, summed per
-// group while staging ("corr"), is removed in fp32 when the group scale is applied:
-//     y += s * (acc * 2^-c - corr).
-// p is a function of the code's position only, so both sides agree by layout.
-constexpr uint32_t MAGIC = 0x64006400u;  // (1024, 1024)
+// Activations are quantised per granule to integers |q| <= QMAX = 127 * 128 and split as
+// q = 128 hi + lo with hi in [-127, 127], lo in [-64, 63].
+constexpr float QMAX = 16256.f;
+template <int BITS> struct CodeOffset;
+template <> struct CodeOffset<4> { static constexpr float OFF = 7.5f; };
+template <> struct CodeOffset<3> { static constexpr float OFF = 3.5f; };
 
-template <int BITS> struct Fold;
-template <> struct Fold<4> {
-  static constexpr int C_EXP = 2;                 // products carry 2^2
-  static constexpr float OFF = 7.5f;
-};
-template <> struct Fold<3> {
-  static constexpr int C_EXP = 1;
-  static constexpr float OFF = 3.5f;
-};
-// Mantissa bit p of the code field of pair q.  4-bit: q = (position >> 1) in the lane's
-// 16 codes of a 64-column half (even -> 2, odd -> 6).  3-bit: q = 0..15 over the row's 32
-// codes of the granule (word slot q % 5 -> 1, 4, 7, 4, 7; pair 15 -> 7).
-template <int BITS>
-__device__ __forceinline__ int fold_p(int q) {
-  if (BITS == 4) return (q & 1) ? 6 : 2;
-  const int r = q % 5;
-  return q == 15 ? 7 : (r == 0 ? 1 : ((r & 1) ? 4 : 7));
+// Fragment registers j = 0..7 of one row (four codes each, one per byte) from the row's words.
+__device__ __forceinline__ void regs4(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t* R) {
+  constexpr uint32_t M4 = 0x0F0F0F0Fu;
+  R[0] = w0 & M4; R[1] = (w0 >> 4) & M4;
+  R[2] = w1 & M4; R[3] = (w1 >> 4) & M4;
+  R[4] = w2 & M4; R[5] = (w2 >> 4) & M4;
+  R[6] = w3 & M4; R[7] = (w3 >> 4) & M4;
 }
-
-// One 4-bit stream word -> 4 fp16 pairs (codes (0,1), (2,3), (4,5), (6,7)): 1024 + 4u, 1024 + 64u, ...
-__device__ __forceinline__ void decode4(uint32_t w, uint32_t* out) {
-  const uint32_t v1 = w << 2, v2 = w >> 6;
-  out[0] = (v1 & 0x003C003Cu) | MAGIC;
-  out[1] = (v1 & 0x03C003C0u) | MAGIC;
-  out[2] = (v2 & 0x003C003Cu) | MAGIC;
-  out[3] = (v2 & 0x03C003C0u) | MAGIC;
-}
-
-// Three 3-bit stream words of one row -> 16 fp16 pairs (codes (2q, 2q+1)).
-__device__ __forceinline__ void decode3(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t* out) {
-  const uint32_t w[3] = {w0, w1, w2};
-#pragma unroll
-  for (int i = 0; i < 3; ++i) {
-    const uint32_t v = w[i] >> 6;
-    out[5 * i + 0] = (w[i] & 0x000E000Eu) | MAGIC;   // field at bit 1
-    out[5 * i + 1] = (w[i] & 0x00700070u) | MAGIC;   // field at bit 4
-    out[5 * i + 2] = (w[i] & 0x03800380u) | MAGIC;   // field at bit 7
-    out[5 * i + 3] = (v & 0x00700070u) | MAGIC;      // field at bit 10 -> 4
-    out[5 * i + 4] = (v & 0x03800380u) | MAGIC;      // field at bit 13 -> 7
-  }
-  uint32_t r = ((w0 << 7) & 0x00800080u) | MAGIC;    // pair 15: one bit from each word, at bits 7..9
-  r |= (w1 << 8) & 0x01000100u;
-  r |= (w2 << 9) & 0x02000200u;
-  out[15] = r;
+__device__ __forceinline__ void regs3(uint32_t a, uint32_t b, uint32_t c, uint32_t* R) {
+  constexpr uint32_t M3 = 0x07070707u;
+  R[0] = a & M3; R[1] = (a >> 3) & M3;
+  R[2] = b & M3; R[3] = (b >> 3) & M3;
+  R[4] = c & M3; R[5] = (c >> 3) & M3;
+  R[6] = ((a >> 6) & 0x03030303u) | ((b >> 4) & 0x04040404u);
+  R[7] = ((c >> 6) & 0x03030303u) | ((b >> 5) & 0x04040404u);
 }
 
 // Geometry of piece i of a CTA's range (pieces = sub-tiles, walked from the last to the first).
@@ -204,13 +180,17 @@ __device__ __forceinline__ Piece piece_of(uint32_t i, uint32_t j_hi, uint32_t NG
 }
 
 // The packed words of one granule that one lane needs, loaded one ring stage ahead of their use.
-template <int BITS> struct Raw;
-template <> struct Raw<4> { uint4 a, b; uint32_t sc[2]; };
-template <> struct Raw<3> { uint2 a, b, c; uint32_t sc[2]; };
+template <int BITS, int SETS> struct Raw;
+template <int SETS> struct Raw<4, SETS> { uint4 a, b; uint32_t sc[SETS]; };
+template <int SETS> struct Raw<3, SETS> { uint4 a; uint2 b; uint32_t sc[SETS]; };
 
-template <int BITS, int SETS, int MB, int NCW, int MINB>
-__global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const MatvecParams p) {
+// MB = activation tiles of four rows (two B columns per row); MAXR = register cap per thread
+// (see SHAPES on the host side).
+template <int BITS, int SETS, int MB, int NCW, int MAXR>
+__global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_kernel(const MatvecParams p) {
   constexpr int NCONS = NCW * 32;
+  constexpr uint32_t CH = 2 * NCW;        // granules per ring stage: a pair per consumer warp
+  constexpr int MBH = (MB + 1) / 2;       // fp16 MMA tiles of eight activation rows (cherry columns)
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_abort;
 
@@ -227,7 +207,6 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
   // barriers: full[s] at bar_base + 8 s, empty[s] at + 8 (S + s), cherry at + 16 S, partial prefetch at + 16 S + 8
   if (tid == 0) {
     stamp(p, 0);
-    if (p.timeline) p.timeline[(size_t)blockIdx.x * 64 + 10] = (unsigned long long)clock64();
     s_abort = 0;
     for (uint32_t s = 0; s < S; ++s) {
       mbar_init(bar_base + 8 * s, 1);
@@ -251,8 +230,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
 
   // ------------------------------------------------------------------ producer
   // The CTA's granules, in walking order, form a sequence of `total` positions.  Ring stage
-  // (g mod S) holds positions [g * NCW, (g + 1) * NCW): position q sits at slot q mod NCW of it
-  // and belongs to consumer warp q mod NCW.  A stage is filled by one bulk copy per piece it
+  // (i mod S) holds positions [i * CH, (i + 1) * CH): position q sits at slot q mod CH of it
+  // and belongs to consumer warp (q mod CH) / 2.  A stage is filled by one bulk copy per piece it
   // touches (granules of a piece are contiguous in memory).
   if (warp == NCW) {
     if (lane == 0) {
@@ -269,11 +248,11 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
       uint32_t pi = 0;
       Piece pc = piece_of(0, j_hi, NG, ga, gb);
       uint32_t src = pc.start;           // next granule to copy
-      for (uint32_t q0 = 0; q0 < total; q0 += NCW) {
-        const uint32_t len = min((uint32_t)NCW, total - q0);
+      for (uint32_t q0 = 0; q0 < total; q0 += CH) {
+        const uint32_t len = min(CH, total - q0);
         if (!first_pass) mbar_wait(bar_base + 8 * (S + stage), phase, &s_abort, p.status);
         mbar_expect_tx(bar_base + 8 * stage, len * GB);
-        uint32_t dst = ring + stage * NCW * GB, left = len;
+        uint32_t dst = ring + stage * CH * GB, left = len;
         while (left > 0) {
           if (src == pc.end) {
             pc = piece_of(++pi, j_hi, NG, ga, gb);
@@ -328,16 +307,38 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
   // Layer constants first (they do not depend on the previous kernel): the sorted cherry
   // columns and, per octet of compact columns, how far its first and last column are shifted
   // in the original row (see cq_common.cuh).
-  __half* xs = reinterpret_cast<__half*>(smem + p.off_xs);
   __half* xc = reinterpret_cast<__half*>(smem + p.off_xc);
-  float* corr = reinterpret_cast<float*>(smem + p.off_corr);
   uint16_t* cidx_s = reinterpret_cast<uint16_t*>(smem + p.off_cidx);
   uint32_t* osh = reinterpret_cast<uint32_t*>(smem + p.off_osh);
   const int noct = p.Kp >> 3;
   for (int c = tid; c < p.Cp; c += NCONS) cidx_s[c] = p.cidx[c];
-  // corr entries of activation rows that do not exist must read as zero
-  for (int i = tid; i < (int)NG * SETS * 8 * MB; i += NCONS) corr[i] = 0.f;
+  // {step, offset terms} of activation rows that do not exist must read as zero
+  for (int i = tid; i < (int)NG * 4 * MB * 4; i += NCONS) reinterpret_cast<float*>(smem + p.off_xq)[i] = 0.f;
   for (int o = tid; o < noct; o += NCONS) osh[o] = p.osh[o];
+  {
+    // Schedule: for every position of the CTA's sequence, which granule of its sub-tile it is (low 10
+    // bits) and which piece it belongs to.  Piece 0 is the tail of the range (possibly a cut
+    // sub-tile), the pieces after it are whole sub-tiles, the last one may be cut at its start.
+    uint32_t* sched = reinterpret_cast<uint32_t*>(smem + p.off_sched);
+    const Piece p0 = piece_of(0, j_hi, NG, ga, gb);
+    const uint32_t len0 = p0.end - p0.start;
+    const uint32_t padded = (total + CH - 1) / CH * CH;
+    for (uint32_t q = (uint32_t)tid; q < padded; q += NCONS) {
+      const uint32_t qq = q < total ? q : total - 1;
+      uint32_t pi, gi;
+      if (qq < len0) {
+        pi = 0;
+        gi = p0.start - p0.sub0 + qq;
+      } else {
+        const uint32_t rest = qq - len0;
+        pi = 1 + rest / NG;
+        const Piece pq = piece_of(pi, j_hi, NG, ga, gb);
+        gi = pq.start - pq.sub0 + (rest - (pi - 1) * NG);
+      }
+      sched[q] = gi | (pi << 10);
+    }
+  }
+  if (tid < 4) reinterpret_cast<uint32_t*>(smem + p.off_zero)[tid] = 0u;
   bar_consumers<NCONS>();
   if (tid == 0) stamp(p, 2);
 
@@ -360,26 +361,24 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
     }
   }
   {
-    // xs[m][k'] = 2^(c-p(k')) * x[m][orig(k')] for the compact columns, 8 at a time (zero past K'),
-    // and corr[granule][set][m] = sum over the group of (B + off) * x.
+    // Compact columns, 8 at a time (zero past K').  The 16 octets of one granule of one row sit
+    // in 16 neighbouring lanes: they agree on the granule's largest magnitude, quantise, and
+    // add up the integers per group.
     const int nitem = noct * p.M;
-    constexpr int U = 4;
-    constexpr int CE = Fold<BITS>::C_EXP;
+    constexpr int U = 2;
     for (int base = 0; base < nitem; base += NCONS * U) {
       uint32_t v[U][4];
-      int dsto[U], mrow[U], oct[U];
+      int mrow[U], oct[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int it = base + u * NCONS + tid;
-        dsto[u] = -1;
-        mrow[u] = 0;
+        mrow[u] = -1;
         oct[u] = 0;
         v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0u;
         if (it < nitem) {
           const int m = (p.M == 1) ? 0 : it / noct;
           const int o = it - m * noct;
           const int k0 = 8 * o;
-          dsto[u] = m * p.xs_stride + k0;
           mrow[u] = m;
           oct[u] = o;
           const uint32_t sh = osh[o];
@@ -399,15 +398,13 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
                   v[u][i] = (uint32_t)__ldg(s16 + 2 * i) | ((uint32_t)__ldg(s16 + 2 * i + 1) << 16);
               }
             } else {
+              // cherry columns fall inside this octet: the shift grows from lo0 to lo7 along it
               unsigned short h[8];
+              int sft = lo0;
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                int lo = lo0, hi = lo7;
-                while (lo < hi) {
-                  const int mid = (lo + hi) >> 1;
-                  if ((int)cidx_s[mid] - mid <= k0 + i) lo = mid + 1; else hi = mid;
-                }
-                h[i] = __ldg(reinterpret_cast<const unsigned short*>(xr + k0 + i + lo));
+                while (sft < lo7 && (int)cidx_s[sft] - sft <= k0 + i) ++sft;
+                h[i] = __ldg(reinterpret_cast<const unsigned short*>(xr + k0 + i + sft));
               }
 #pragma unroll
               for (int i = 0; i < 4; ++i) v[u][i] = (uint32_t)h[2 * i] | ((uint32_t)h[2 * i + 1] << 16);
@@ -417,29 +414,52 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        // first pair index of this octet among the row's pairs of the granule
-        const int oo = oct[u] & 15;
-        const int q0 = (BITS == 4) ? 0 : 8 * (oo >> 3) + 4 * (oo & 1);
-        float part = 0.f;
+        float f[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int pp = fold_p<BITS>(q0 + i);
-          const uint32_t sc16 = (uint32_t)((15 + CE - pp) << 10);                 // fp16 2^(c-p)
-          const uint32_t scaled = hmul2_u32(v[u][i], sc16 | (sc16 << 16));
-          const float coef = __int_as_float((127 + pp - CE) << 23) *              // 2^(p-c) * (B + off)
-                             ((float)(1 << (10 - pp)) + Fold<BITS>::OFF);
-          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&scaled));
-          part += (f.x + f.y) * coef;
-          v[u][i] = scaled;
+          const float2 t2 = __half22float2(*reinterpret_cast<const __half2*>(&v[u][i]));
+          f[2 * i] = t2.x;
+          f[2 * i + 1] = t2.y;
         }
-        // 16 (8 for 64-wide groups) neighbouring lanes hold the octets of one group of one row
+        float amax = 0.f;
 #pragma unroll
-        for (int d = 1; d < 16 / SETS; d <<= 1) part += __shfl_xor_sync(0xffffffffu, part, d);
-        if (dsto[u] >= 0) {
-          *reinterpret_cast<uint4*>(xs + dsto[u]) = make_uint4(v[u][0], v[u][1], v[u][2], v[u][3]);
-          if ((oct[u] & (16 / SETS - 1)) == 0) {
-            const int gi = oct[u] >> 4, sp = (SETS == 2) ? ((oct[u] >> 3) & 1) : 0;
-            corr[(gi * SETS + sp) * 8 * MB + mrow[u]] = part;
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+        for (int d = 1; d < 16; d <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+        // (an infinite or NaN activation makes the step infinite or NaN: the outputs of the rows it
+        // feeds come out NaN, as they do in the reference)
+        const float inv = amax > 0.f ? QMAX / amax : 0.f;
+        const float sx = amax / QMAX;
+        int q[8], qsum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          q[i] = __float2int_rn(f[i] * inv);
+          qsum += q[i];
+        }
+#pragma unroll
+        for (int d = 1; d < 16 / SETS; d <<= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, d);
+        if (mrow[u] >= 0) {
+          uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int hi = (q[i] + 64) >> 7;
+            const int lo = q[i] - (hi << 7);
+            hw[i >> 2] |= ((uint32_t)hi & 0xFFu) << (8 * (i & 3));
+            lw[i >> 2] |= ((uint32_t)lo & 0xFFu) << (8 * (i & 3));
+          }
+          // columns kk = 8 oo .. 8 oo + 7 of the granule: plane kk >> 6, lane column c = (kk >> 2) & 3
+          // (two of them), bytes ((kk >> 4) & 3) * 4 + i of the lane's 16
+          const int gi = oct[u] >> 4, oo = oct[u] & 15;
+          uint8_t* dst = smem + p.off_xb + (size_t)gi * p.xb_gran + (oo >> 3) * (p.M * 128) +
+                         (2 * mrow[u]) * 64 + (2 * (oo & 1)) * 16 + ((oo >> 1) & 3) * 4;
+          *reinterpret_cast<uint32_t*>(dst) = hw[0];
+          *reinterpret_cast<uint32_t*>(dst + 16) = hw[1];
+          *reinterpret_cast<uint32_t*>(dst + 64) = lw[0];
+          *reinterpret_cast<uint32_t*>(dst + 80) = lw[1];
+          if ((oo & (16 / SETS - 1)) == 0) {
+            float* xq = reinterpret_cast<float*>(smem + p.off_xq) + ((size_t)gi * 4 * MB + mrow[u]) * 4;
+            const float nc = (-CodeOffset<BITS>::OFF * (float)qsum) * sx;
+            if (oo == 0) { xq[0] = sx; xq[1] = nc; } else { xq[2] = nc; }
           }
         }
       }
@@ -464,104 +484,113 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
   const int g = lane >> 2, t = lane & 3;
   float* slots = reinterpret_cast<float*>(smem + p.off_slot);   // [slot][warp][m][16 rows]
 
-  float tot[MB][4];
+  // integer path: tot[b][0] = (row g, activation row 4b + t), tot[b][1] = (row g + 8, same)
+  float tot[MB][2];
 #pragma unroll
-  for (int b = 0; b < MB; ++b)
+  for (int b = 0; b < MB; ++b) tot[b][0] = tot[b][1] = 0.f;
+  // cherry path (fp16 MMA fragment order): ctot[b][0..3] = (row g, activation rows 8b + 2t, + 1), (row g + 8, same)
+  float ctot[MBH][4];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) tot[b][r] = 0.f;
+  for (int b = 0; b < MBH; ++b) ctot[b][0] = ctot[b][1] = ctot[b][2] = ctot[b][3] = 0.f;
+  bool did_cher = false;
 
   // Shared-memory byte offsets (relative to `smem`) this lane reads in every granule.
-  // B-operand column g of activation tile b is activation row 8b + g; columns past the last
-  // row are never read back from the accumulators, so they may carry any existing row.
-  uint32_t x_off[MB], xc_off[MB];
+  // B column n = lane >> 2 of activation tile b is byte plane (n & 1: hi, lo) of activation row
+  // 4b + (n >> 1); columns of rows that do not exist are fed zeros.
+  const uint32_t xb_off = (uint32_t)p.off_xb + (uint32_t)lane * 16u;
+  const uint32_t xb_plane = (uint32_t)p.M * 128u;
+  const uint32_t xq_off = (uint32_t)p.off_xq + (uint32_t)t * 16u;
+  uint32_t xc_off[MBH];
 #pragma unroll
-  for (int b = 0; b < MB; ++b) {
+  for (int b = 0; b < MBH; ++b) {
     const int m = (8 * b + g) % p.M;
-    x_off[b] = (uint32_t)p.off_xs + (uint32_t)(m * p.xs_stride + 16 * t) * 2u;
     xc_off[b] = (uint32_t)p.off_xc + (uint32_t)(m * p.xc_stride + 2 * t) * 2u;
   }
-  const uint32_t corr_off = (uint32_t)p.off_corr + (uint32_t)(2 * t) * 4u;
-  const uint32_t lane_w = (BITS == 4) ? (uint32_t)lane * 16u : (uint32_t)lane * 24u;
-  const uint32_t ring_off = (uint32_t)p.off_ring + (uint32_t)warp * GB;       // this warp's slot in stage 0
+  const uint32_t ring_off = (uint32_t)p.off_ring + 2u * (uint32_t)warp * GB;  // this warp's pair of slots in stage 0
+  // B column lane >> 2 of tile b: where this lane's 16 bytes of plane 0 are, how far plane 1 and the
+  // next granule are; a column past the last activation row reads the zero block with strides 0
+  uint32_t xcol_off[MB], xcol_gran[MB], xcol_plane[MB];
+#pragma unroll
+  for (int b = 0; b < MB; ++b) {
+    const bool has = 8 * b + g < 2 * p.M;
+    xcol_off[b] = has ? xb_off + b * 512 : (uint32_t)p.off_zero;
+    xcol_gran[b] = has ? (uint32_t)p.xb_gran : 0u;
+    xcol_plane[b] = has ? xb_plane : 0u;
+  }
 
-  auto load_raw = [&](uint32_t stage_off, Raw<BITS>& r) {
-    const uint8_t* gp = smem + stage_off + lane_w;
-    if constexpr (BITS == 4) {
-      r.a = *reinterpret_cast<const uint4*>(gp);
-      r.b = *reinterpret_cast<const uint4*>(gp + 512);
-    } else {
-      r.a = *reinterpret_cast<const uint2*>(gp);
-      r.b = *reinterpret_cast<const uint2*>(gp + 8);
-      r.c = *reinterpret_cast<const uint2*>(gp + 16);
-    }
+  auto load_raw = [&](uint32_t stage_off, Raw<BITS, SETS>& r) {
+    const uint8_t* gp = smem + stage_off;
+    r.a = *reinterpret_cast<const uint4*>(gp + lane * 16);
+    if constexpr (BITS == 4) r.b = *reinterpret_cast<const uint4*>(gp + 512 + lane * 16);
+    else r.b = *reinterpret_cast<const uint2*>(gp + 512 + lane * 8);
     // scales of rows (g, g+8) sit next to each other: [set][g][2]
-    const uint8_t* sp = smem + stage_off + 256 * BITS + 4 * g;
-    r.sc[0] = *reinterpret_cast<const uint32_t*>(sp);
-    r.sc[1] = (SETS == 2) ? *reinterpret_cast<const uint32_t*>(sp + 32) : r.sc[0];
+#pragma unroll
+    for (int sp = 0; sp < SETS; ++sp) r.sc[sp] = *reinterpret_cast<const uint32_t*>(gp + 256 * BITS + 32 * sp + 4 * g);
   };
 
-  // One granule: 8 MMAs (two accumulators per 64-column half, so that no MMA waits for the one
-  // issued just before it), then the group scales and the correction.
-  auto compute = [&](const Raw<BITS>& r, uint32_t gi) {
-    uint32_t A0[16], A1[16];   // fp16 pairs of rows g and g+8 (8 per 64-column half)
-    if constexpr (BITS == 4) {
-      decode4(r.a.x, A0);      decode4(r.a.y, A0 + 4);  decode4(r.a.z, A1);      decode4(r.a.w, A1 + 4);
-      decode4(r.b.x, A0 + 8);  decode4(r.b.y, A0 + 12); decode4(r.b.z, A1 + 8);  decode4(r.b.w, A1 + 12);
-    } else {
-      decode3(r.a.x, r.a.y, r.b.x, A0);
-      decode3(r.b.y, r.c.x, r.c.y, A1);
-    }
-    float acc[2][2][MB][4];
+  // Two granules at once: their bytes become the A fragments of four integer MMAs each (two per
+  // group when groups are 64 wide), issued alternately so that neither chain waits for itself;
+  // per activation tile, the two sums of each row are joined, scaled by the activation step and
+  // the group scale, and the offset term is added.  out[e][b][0 / 1] = rows g / g + 8.
+  auto compute_pair = [&](const Raw<BITS, SETS> (&r)[2], const uint32_t (&gi)[2], float (&out)[2][MB][2]) {
+    uint32_t R0[2][8], R1[2][8];     // fragment registers of rows g and g + 8
+    float2 sc[2][SETS];
 #pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int b = 0; b < MB; ++b)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) acc[h][j][b][e] = 0.f;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      uint32_t X[MB][8];
-#pragma unroll
-      for (int b = 0; b < MB; ++b) {
-        const uint8_t* xp = smem + x_off[b] + gi * 256u + h * 128;
-        const uint4 xa = *reinterpret_cast<const uint4*>(xp), xb = *reinterpret_cast<const uint4*>(xp + 16);
-        X[b][0] = xa.x; X[b][1] = xa.y; X[b][2] = xa.z; X[b][3] = xa.w;
-        X[b][4] = xb.x; X[b][5] = xb.y; X[b][6] = xb.z; X[b][7] = xb.w;
+    for (int e = 0; e < 2; ++e) {
+      if constexpr (BITS == 4) {
+        regs4(r[e].a.x, r[e].a.z, r[e].b.x, r[e].b.z, R0[e]);
+        regs4(r[e].a.y, r[e].a.w, r[e].b.y, r[e].b.w, R1[e]);
+      } else {
+        regs3(r[e].a.x, r[e].a.y, r[e].a.z, R0[e]);
+        regs3(r[e].a.w, r[e].b.x, r[e].b.y, R1[e]);
       }
 #pragma unroll
-      for (int m = 0; m < 4; ++m)
-#pragma unroll
-        for (int b = 0; b < MB; ++b)
-          mma16816(acc[h][m & 1][b], A0[8 * h + 2 * m], A1[8 * h + 2 * m], A0[8 * h + 2 * m + 1], A1[8 * h + 2 * m + 1],
-                   X[b][2 * m], X[b][2 * m + 1]);
+      for (int sp = 0; sp < SETS; ++sp) sc[e][sp] = __half22float2(*reinterpret_cast<const __half2*>(&r[e].sc[sp]));
     }
-    const float inv = 1.f / (float)(1 << Fold<BITS>::C_EXP);
-    const float2 s_lo = __half22float2(*reinterpret_cast<const __half2*>(&r.sc[0]));
-    const float2 s_hi = __half22float2(*reinterpret_cast<const __half2*>(&r.sc[1]));
+    constexpr int MPS = 4 / SETS;     // MMAs per group
 #pragma unroll
     for (int b = 0; b < MB; ++b) {
-      // corr: [granule][set][8 * MB] floats; this lane's columns are 8b + 2t, + 1
-      const uint8_t* cp = smem + corr_off + (gi * SETS * 8 * MB + 8 * b) * 4u;
-      const float2 c_lo = *reinterpret_cast<const float2*>(cp);
-      float a0[4], a1[4];
+      uint32_t X[2][8];
+      float sx[2], nc[2][2];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        a0[e] = acc[0][0][b][e] + acc[0][1][b][e];
-        a1[e] = acc[1][0][b][e] + acc[1][1][b][e];
+      for (int e = 0; e < 2; ++e) {
+        {
+          // lanes whose B column does not exist read a block of zeros instead (stride 0)
+          const uint8_t* xp = smem + xcol_off[b] + gi[e] * xcol_gran[b];
+          const uint4 xa = *reinterpret_cast<const uint4*>(xp), xb = *reinterpret_cast<const uint4*>(xp + xcol_plane[b]);
+          X[e][0] = xa.x; X[e][1] = xa.y; X[e][2] = xa.z; X[e][3] = xa.w;
+          X[e][4] = xb.x; X[e][5] = xb.y; X[e][6] = xb.z; X[e][7] = xb.w;
+        }
+        const uint8_t* qp = smem + xq_off + (gi[e] * 4 * MB + 4 * b) * 16u;
+        if constexpr (SETS == 2) {
+          const float4 qv = *reinterpret_cast<const float4*>(qp);
+          sx[e] = qv.x; nc[e][0] = qv.y; nc[e][1] = qv.z;
+        } else {
+          const float2 qv = *reinterpret_cast<const float2*>(qp);
+          sx[e] = qv.x; nc[e][0] = qv.y; nc[e][1] = 0.f;
+        }
+        out[e][b][0] = out[e][b][1] = 0.f;
       }
-      if (SETS == 2) {
-        const float2 c_hi = *reinterpret_cast<const float2*>(cp + 8 * MB * 4);
-        tot[b][0] += s_lo.x * (a0[0] * inv - c_lo.x) + s_hi.x * (a1[0] * inv - c_hi.x);
-        tot[b][1] += s_lo.x * (a0[1] * inv - c_lo.y) + s_hi.x * (a1[1] * inv - c_hi.y);
-        tot[b][2] += s_lo.y * (a0[2] * inv - c_lo.x) + s_hi.y * (a1[2] * inv - c_hi.x);
-        tot[b][3] += s_lo.y * (a0[3] * inv - c_lo.y) + s_hi.y * (a1[3] * inv - c_hi.y);
-      } else {
-        tot[b][0] += s_lo.x * ((a0[0] + a1[0]) * inv - c_lo.x);
-        tot[b][1] += s_lo.x * ((a0[1] + a1[1]) * inv - c_lo.y);
-        tot[b][2] += s_lo.y * ((a0[2] + a1[2]) * inv - c_lo.x);
-        tot[b][3] += s_lo.y * ((a0[3] + a1[3]) * inv - c_lo.y);
+#pragma unroll
+      for (int sp = 0; sp < SETS; ++sp) {
+        int acc[2][4];
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          imma16832(acc[e], R0[e][2 * MPS * sp], R1[e][2 * MPS * sp], R0[e][2 * MPS * sp + 1], R1[e][2 * MPS * sp + 1],
+                    X[e][2 * MPS * sp], X[e][2 * MPS * sp + 1], 0, 0, 0, 0);
+#pragma unroll
+        for (int m = MPS * sp + 1; m < MPS * (sp + 1); ++m)
+#pragma unroll
+          for (int e = 0; e < 2; ++e)
+            imma16832(acc[e], R0[e][2 * m], R1[e][2 * m], R0[e][2 * m + 1], R1[e][2 * m + 1], X[e][2 * m], X[e][2 * m + 1],
+                      acc[e][0], acc[e][1], acc[e][2], acc[e][3]);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float v0 = fmaf((float)(acc[e][0] * 128 + acc[e][1]), sx[e], nc[e][sp]);
+          const float v1 = fmaf((float)(acc[e][2] * 128 + acc[e][3]), sx[e], nc[e][sp]);
+          out[e][b][0] = fmaf(sc[e][sp].x, v0, out[e][b][0]);
+          out[e][b][1] = fmaf(sc[e][sp].y, v1, out[e][b][1]);
+        }
       }
     }
   };
@@ -575,16 +604,29 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
       float* dst = slots + ((size_t)((i % p.nslot) * NCW + warp) * p.M) * 16;
 #pragma unroll
       for (int b = 0; b < MB; ++b) {
-        const int m0 = 8 * b + 2 * t;
-        if (m0 < p.M) {
-          dst[m0 * 16 + g] = tot[b][0];
-          dst[m0 * 16 + g + 8] = tot[b][2];
+        const int m = 4 * b + t;
+        if (m < p.M) {
+          dst[m * 16 + g] = tot[b][0];
+          dst[m * 16 + g + 8] = tot[b][1];
         }
-        if (m0 + 1 < p.M) {
-          dst[(m0 + 1) * 16 + g] = tot[b][1];
-          dst[(m0 + 1) * 16 + g + 8] = tot[b][3];
+        tot[b][0] = tot[b][1] = 0.f;
+      }
+      if (did_cher) {           // warp-uniform: this warp held the sub-tile's first granule
+        __syncwarp();
+#pragma unroll
+        for (int b = 0; b < MBH; ++b) {
+          const int m0 = 8 * b + 2 * t;
+          if (m0 < p.M) {
+            dst[m0 * 16 + g] += ctot[b][0];
+            dst[m0 * 16 + g + 8] += ctot[b][2];
+          }
+          if (m0 + 1 < p.M) {
+            dst[(m0 + 1) * 16 + g] += ctot[b][1];
+            dst[(m0 + 1) * 16 + g + 8] += ctot[b][3];
+          }
+          ctot[b][0] = ctot[b][1] = ctot[b][2] = ctot[b][3] = 0.f;
         }
-        tot[b][0] = tot[b][1] = tot[b][2] = tot[b][3] = 0.f;
+        did_cher = false;
       }
     }
     ++pending;
@@ -635,74 +677,69 @@ __global__ void __launch_bounds__((NCW + 1) * 32, MINB) cq_matvec_kernel(const M
         st_release(p.flag + cta, 1u);
       }
       for (uint32_t c = reset_lo; c <= reset_hi && reset_lo <= reset_hi; ++c) p.flag[c] = 0u;
-      if (i == npieces - 1) {
-        stamp(p, 7);
-        if (p.timeline) p.timeline[(size_t)blockIdx.x * 64 + 11] = (unsigned long long)clock64();
-      }
+      if (i == npieces - 1) stamp(p, 7);
     }
     pending = 0;
   };
 
-  // ---- this warp's granules: positions warp, warp + NCW, ... of the CTA's sequence.  While
-  // granule i is computed, the words of granule i+1 are already on their way from shared memory
-  // (its ring slot is released as soon as they are requested) and the barrier of granule i+2's
-  // stage is being probed; the probe's answer is only looked at after the math.
-  uint32_t pi = 0;                         // piece of the current position
-  Piece pc = piece_of(0, j_hi, NG, ga, gb);
-  uint32_t pstart = 0;                     // sequence position where piece pi starts
-  if ((uint32_t)warp < total) {
-    uint32_t pos = (uint32_t)warp, stage = 0, phase = 0;
-    Raw<BITS> cur, nxt;
-    mbar_wait(bar_base, 0, &s_abort, p.status);
-    if (tid == 0) stamp(p, 5);
-    load_raw(ring_off, cur);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_base + 8 * S);
-    if (pos + NCW < total) mbar_wait(bar_base + 8 * (1 % S), (1 / S) & 1, &s_abort, p.status);
-    for (;;) {
-      while (pos >= pstart + (pc.end - pc.start)) {
-        close_piece(pi);
-        pstart += pc.end - pc.start;
-        pc = piece_of(++pi, j_hi, NG, ga, gb);
-      }
-      const uint32_t gi = pc.start - pc.sub0 + (pos - pstart);     // granule inside the sub-tile
-      const bool has_next = pos + NCW < total, has_next2 = pos + 2 * NCW < total;
-      uint32_t nstage = stage + 1, nphase = phase;
-      if (nstage == S) { nstage = 0; nphase ^= 1; }
-      uint32_t n2stage = nstage + 1, n2phase = nphase;
-      if (n2stage == S) { n2stage = 0; n2phase ^= 1; }
-      if (has_next) {                      // its stage is known to have landed
-        load_raw(ring_off + nstage * NCW * GB, nxt);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_base + 8 * (S + nstage));
-      }
-      bool ready2 = false;
-      if (has_next2) ready2 = mbar_try_wait(bar_base + 8 * n2stage, n2phase);
-      compute(cur, gi);
-      // The granule that starts a sub-tile also adds the sub-tile's fp16 cherry columns.
-      if (gi == 0 && p.Cp > 0) {
-        if (!cher_ready) {
-          mbar_wait(bar_base + 16 * S, 0, &s_abort, p.status);
-          cher_ready = true;
-        }
-        const uint8_t* blk = smem + p.off_cher + (size_t)(pc.j - jc_lo) * p.cher_bytes;
-        for (int jj = 0; jj < p.Cp / 16; ++jj) {
-          const uint4 a = *reinterpret_cast<const uint4*>(blk + jj * 512 + lane * 16);
+  // ---- this warp's granules.  Ring stage (it mod S) holds positions [it * CH, (it + 1) * CH) of the
+  // CTA's sequence, CH = 2 * NCW; warp w owns the pair at 2w of every stage.  Per stage a warp
+  // waits for the copy, pulls its two granules into registers, hands the slot back, and only then
+  // does the math.  Which granule of which piece a position is comes from the schedule table.
+  // The granule that starts a sub-tile also adds the sub-tile's fp16 cherry columns.
+  auto add_cherries = [&](uint32_t piece) {
+    if (!cher_ready) {
+      mbar_wait(bar_base + 16 * S, 0, &s_abort, p.status);
+      cher_ready = true;
+    }
+    did_cher = true;
+    const uint8_t* blk = smem + p.off_cher + (size_t)(j_hi - piece - jc_lo) * p.cher_bytes;
+    for (int jj = 0; jj < p.Cp / 16; ++jj) {
+      const uint4 a = *reinterpret_cast<const uint4*>(blk + jj * 512 + lane * 16);
 #pragma unroll
-          for (int b = 0; b < MB; ++b) {
-            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(smem + xc_off[b] + 32 * jj);
-            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(smem + xc_off[b] + 32 * jj + 16);
-            mma16816(tot[b], a.x, a.y, a.z, a.w, b0, b1);
-          }
-        }
+      for (int b = 0; b < MBH; ++b) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(smem + xc_off[b] + 32 * jj);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(smem + xc_off[b] + 32 * jj + 16);
+        mma16816(ctot[b], a.x, a.y, a.z, a.w, b0, b1);
       }
-      if (!has_next) break;
-      if (has_next2 && !ready2) mbar_wait_slow(bar_base + 8 * n2stage, n2phase, &s_abort, p.status);
-      cur = nxt;
-      pos += NCW; stage = nstage; phase = nphase;
+    }
+  };
+
+  uint32_t nclosed = 0;
+  {
+    const uint32_t n_iters = (total + CH - 1) / CH;
+    const uint32_t sched_off = (uint32_t)p.off_sched + 8u * (uint32_t)warp;
+    uint32_t stage = 0, phase = 0;
+    uint32_t pa = 2u * (uint32_t)warp;
+    for (uint32_t it = 0; it < n_iters; ++it, pa += CH) {
+      mbar_wait(bar_base + 8 * stage, phase, &s_abort, p.status);
+      if (it == 0 && tid == 0) stamp(p, 5);
+      const bool va = pa < total, vb = pa + 1 < total;     // warp-uniform
+      Raw<BITS, SETS> r[2];
+      const uint32_t soff = ring_off + stage * CH * GB;
+      load_raw(va ? soff : ring_off, r[0]);                 // (a stale slot is harmless: its result is dropped)
+      load_raw(vb ? soff + GB : ring_off, r[1]);
+      const uint2 se = *reinterpret_cast<const uint2*>(smem + sched_off + it * (CH * 4));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_base + 8 * (S + stage));
+      if (++stage == S) { stage = 0; phase ^= 1; }
+      if (!va) continue;
+      const uint32_t gi[2] = {se.x & 1023u, se.y & 1023u};
+      float out[2][MB][2];
+      compute_pair(r, gi, out);
+      while (nclosed < (se.x >> 10)) close_piece(nclosed++);
+#pragma unroll
+      for (int b = 0; b < MB; ++b) { tot[b][0] += out[0][b][0]; tot[b][1] += out[0][b][1]; }
+      if (gi[0] == 0 && p.Cp > 0) add_cherries(se.x >> 10);
+      if (vb) {
+        while (nclosed < (se.y >> 10)) close_piece(nclosed++);
+#pragma unroll
+        for (int b = 0; b < MB; ++b) { tot[b][0] += out[1][b][0]; tot[b][1] += out[1][b][1]; }
+        if (gi[1] == 0 && p.Cp > 0) add_cherries(se.y >> 10);
+      }
     }
   }
-  for (; pi < npieces; ++pi) close_piece(pi);
+  for (; nclosed < npieces; ++nclosed) close_piece(nclosed);
 }
 
 // ------------------------------------------------------------------ host side
@@ -727,27 +764,42 @@ DeviceInfo device_info(int dev) {
 
 typedef void (*KernelFn)(const MatvecParams);
 
-// Kernel shapes: consumer warps (one granule per warp per ring stage).
-struct Shape { int ncw, gpw; };
-constexpr Shape SHAPES[] = {{8, 1}, {12, 1}, {16, 1}};
+// Kernel shapes: consumer warps (a pair of granules per warp per ring stage) and the register cap.
+// Shape 0 is the product: 19 consumer warps with the whole SM to themselves measured fastest on the
+// LLaMA-7B layers (more warps hide more of the per-instruction latency of the unpack code than
+// sharing the SM with the next launch's prefetch gains).  Shapes 1..3 are capped so that two CTAs
+// fit one SM (registers are split over four sub-partitions, so ceil(warps / 4) warps of each CTA
+// land on one of them: 2 * ceil(warps / 4) * 32 * regs <= 16384); they need CQ_SMEM_KB <= 111.
+// Launches of more than four activation rows use one shape and the whole register file.
+struct Shape { int ncw; };
+constexpr Shape SHAPES[] = {{19}, {11}, {8}, {15}, {23}};
 constexpr int N_SHAPES = sizeof(SHAPES) / sizeof(SHAPES[0]);
 
-template <int NCW, int MINB>
-KernelFn pick_bits(int bits, int sets, int mb) {
-  if (bits == 4) {
-    if (sets == 1) return mb == 1 ? cq_matvec_kernel<4, 1, 1, NCW, MINB> : cq_matvec_kernel<4, 1, 2, NCW, MINB>;
-    return mb == 1 ? cq_matvec_kernel<4, 2, 1, NCW, MINB> : cq_matvec_kernel<4, 2, 2, NCW, MINB>;
-  }
-  if (sets == 1) return mb == 1 ? cq_matvec_kernel<3, 1, 1, NCW, MINB> : cq_matvec_kernel<3, 1, 2, NCW, MINB>;
-  return mb == 1 ? cq_matvec_kernel<3, 2, 1, NCW, MINB> : cq_matvec_kernel<3, 2, 2, NCW, MINB>;
+template <int NCW, int MAXR>
+KernelFn pick_small(int bits, int sets) {
+  if (bits == 4) return sets == 1 ? cq_matvec_kernel<4, 1, 1, NCW, MAXR> : cq_matvec_kernel<4, 2, 1, NCW, MAXR>;
+  return sets == 1 ? cq_matvec_kernel<3, 1, 1, NCW, MAXR> : cq_matvec_kernel<3, 2, 1, NCW, MAXR>;
+}
+template <int MB>
+KernelFn pick_large(int bits, int sets) {
+  if (bits == 4) return sets == 1 ? cq_matvec_kernel<4, 1, MB, 11, 128> : cq_matvec_kernel<4, 2, MB, 11, 128>;
+  return sets == 1 ? cq_matvec_kernel<3, 1, MB, 11, 128> : cq_matvec_kernel<3, 2, MB, 11, 128>;
 }
 
-KernelFn pick_kernel(int shape, int bits, int sets, int mb) {
-  switch (shape) {
-    case 0: return pick_bits<8, 1>(bits, sets, mb);
-    case 1: return pick_bits<12, 1>(bits, sets, mb);
-    default: return pick_bits<16, 1>(bits, sets, mb);
+// mb = activation tiles of four rows: 1, 2 or 4.  Returns the kernel and its consumer warp count.
+KernelFn pick_kernel(int shape, int bits, int sets, int mb, int* ncw) {
+  if (mb == 1) {
+    *ncw = SHAPES[shape].ncw;
+    switch (shape) {
+      case 0: return pick_small<19, 96>(bits, sets);
+      case 1: return pick_small<11, 80>(bits, sets);
+      case 2: return pick_small<8, 80>(bits, sets);
+      case 3: return pick_small<15, 64>(bits, sets);
+      default: return pick_small<23, 80>(bits, sets);
+    }
   }
+  *ncw = 11;
+  return mb == 2 ? pick_large<2>(bits, sets) : pick_large<4>(bits, sets);
 }
 
 // Tuning knobs read once from the environment (for experiments; defaults are the product):
@@ -756,7 +808,7 @@ KernelFn pick_kernel(int shape, int bits, int sets, int mb) {
 struct Knobs { int shape, smem_kb, pdl, max_stages; };
 Knobs knobs() {
   static Knobs k = [] {
-    Knobs v{0, 112, 1, 16};
+    Knobs v{0, 220, 1, 16};
     if (const char* e = getenv("CQ_SHAPE")) v.shape = atoi(e);
     if (const char* e = getenv("CQ_SMEM_KB")) v.smem_kb = atoi(e);
     if (const char* e = getenv("CQ_PDL")) v.pdl = atoi(e);
@@ -770,28 +822,32 @@ Knobs knobs() {
 
 int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
-// Shared-memory plan for M activation rows; returns total bytes or -1 if it cannot fit.
-int plan_smem(const cq_layer* L, int M, int grid, int max_smem, Shape sh, int target_kb, int max_stages,
-              MatvecParams* p) {
+int tiles_of(int M) { return M <= 4 ? 1 : (M <= 8 ? 2 : 4); }
+
+// Shared-memory plan for M activation rows with `nslot` parking slots for finished pieces;
+// returns total bytes or -1 if it cannot fit.
+int plan_smem_slots(const cq_layer* L, int M, int grid, int max_smem, int ncw, int target_kb, int max_stages,
+                    int nslot, MatvecParams* p) {
   const uint32_t T = (uint32_t)L->n_sub * (uint32_t)L->n_gran;
   const uint32_t per = (T + grid - 1) / grid;
   const int max_pieces = (int)((per + L->n_gran - 1) / L->n_gran) + 1;
-  const int mb = (M + 7) / 8;
-  const int chunk_gran = sh.ncw * sh.gpw;
-  p->nslot = max_pieces < 8 ? max_pieces : 8;
+  const int mb = tiles_of(M);
+  p->nslot = max_pieces < nslot ? max_pieces : nslot;
   p->max_cher = max_pieces;
-  p->xs_stride = L->Kp + 8;
+  p->xb_gran = 256 * M;
   p->xc_stride = L->Cp + 8;
-  const int chunk = chunk_gran * L->gran_bytes;
+  const int chunk = 2 * ncw * L->gran_bytes;
   int off = 0;
   p->off_cher = off; off = align_up(off + p->max_cher * L->cher_bytes, 128);
-  p->off_xs = off;   off = align_up(off + M * p->xs_stride * 2, 128);
+  p->off_zero = off; off = align_up(off + 16, 128);
+  p->off_sched = off; off = align_up(off + ((int)per + 2 * ncw) * 4, 128);
+  p->off_xb = off;   off = align_up(off + L->n_gran * p->xb_gran, 128);
+  p->off_xq = off;   off = align_up(off + L->n_gran * 4 * mb * 16, 128);
   p->off_xc = off;   off = align_up(off + M * p->xc_stride * 2, 128);
   p->off_cidx = off; off = align_up(off + (L->Cp + 8) * 2, 128);
-  p->off_corr = off; off = align_up(off + L->n_gran * L->sets * 8 * mb * 4, 128);
   // the octet-shift table is only needed while activations are staged: it shares the slots' space
   {
-    const int slot_bytes = p->nslot * sh.ncw * M * 64, osh_bytes = (L->Kp / 8) * 4;
+    const int slot_bytes = p->nslot * ncw * M * 64, osh_bytes = (L->Kp / 8) * 4;
     p->off_slot = off; p->off_osh = off;
     off = align_up(off + (slot_bytes > osh_bytes ? slot_bytes : osh_bytes), 128);
   }
@@ -799,21 +855,39 @@ int plan_smem(const cq_layer* L, int M, int grid, int max_smem, Shape sh, int ta
   p->off_bar = off;  off = align_up(off + (2 * 16 + 2) * 8, 128);
   p->off_ring = off;
   const int fixed = off;
-  // Ring: with <= target_kb per CTA two launches overlap on one SM (the next layer prefetches its
-  // weights while this one computes).  That only pays while the ring still holds enough bytes in
-  // flight to cover HBM latency; otherwise take the whole SM.
+  // Ring: target_kb per CTA (the default takes the whole SM; <= 111 lets two launches share an
+  // SM, which only pays while the ring still holds enough bytes in flight to cover HBM latency).
   int budget = target_kb * 1024;
-  if (budget - fixed < 64 * 1024) budget = max_smem;
+  if (budget > max_smem) budget = max_smem;
+  if (budget - fixed < 48 * 1024) budget = max_smem;
   int stages = (budget - fixed) / chunk;
   if (stages > 16) stages = 16;
   if (stages > max_stages) stages = max_stages;
-  const uint32_t max_chunks = per / chunk_gran + (uint32_t)max_pieces + 1;
+  const uint32_t max_chunks = per / (2 * ncw) + 2;
   if ((uint32_t)stages > max_chunks) stages = (int)max_chunks;
-  // The consumers run two ring stages ahead of their math: at least two stages are required.
+  // One stage is being refilled while another is read: at least two stages are required.
   if (stages < 2) stages = 2;
   if (fixed + stages * chunk > max_smem) return -1;
   p->stages = stages;
   return fixed + stages * chunk;
+}
+
+// Fewer parking slots (more, smaller output rounds) when many activation rows make them large.
+int plan_smem(const cq_layer* L, int M, int grid, int max_smem, int ncw, int target_kb, int max_stages,
+              MatvecParams* p) {
+  for (int nslot = 8; nslot >= 1; nslot >>= 1) {
+    const int smem = plan_smem_slots(L, M, grid, max_smem, ncw, target_kb, max_stages, nslot, p);
+    if (smem >= 0) return smem;
+  }
+  return -1;
+}
+
+// Opt in to the dynamic shared memory the plan needs, and ask for the largest shared-memory
+// carve-out so that a second CTA (the next launch in the stream) fits beside this one.
+cudaError_t prepare_kernel(KernelFn fn, int smem) {
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
 }  // namespace
@@ -841,16 +915,17 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   const DeviceInfo di = device_info(dev);
   if (!di.ok) return CQ_ERR_NO_DEVICE;
   const Knobs kn = knobs();
-  const Shape sh = SHAPES[kn.shape];
   const uint32_t T = (uint32_t)L->n_sub * (uint32_t)L->n_gran;
   int grid = di.sms < 1024 ? di.sms : 1024;
   if ((uint32_t)grid > T) grid = (int)T;
 
   MatvecParams p;
   int rows = M < 16 ? M : 16;
-  int smem = -1;
+  int smem = -1, ncw = 0;
+  KernelFn fn = nullptr;
   for (; rows >= 1; --rows) {
-    smem = plan_smem(L, rows, grid, di.max_smem, sh, kn.smem_kb, kn.max_stages, &p);
+    fn = pick_kernel(kn.shape, L->bits, L->sets, tiles_of(rows), &ncw);
+    smem = plan_smem(L, rows, grid, di.max_smem, ncw, kn.smem_kb, kn.max_stages, &p);
     if (smem >= 0) break;
   }
   if (smem < 0) return CQ_ERR_TOO_LARGE;
@@ -869,11 +944,10 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   p.ldx = ldx; p.ldy = ldy; p.accumulate = accumulate;
   p.T = T;
 
-  KernelFn fn = pick_kernel(kn.shape, L->bits, L->sets, (rows + 7) / 8);
-  CQ_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  CQ_CUDA_TRY(prepare_kernel(fn, smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3((sh.ncw + 1) * 32);
+  cfg.blockDim = dim3((ncw + 1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -972,14 +1046,15 @@ extern "C" int cq_layer_matvec_static(const cq_layer* L, const void* x, int ldx,
   if (!di.ok) return CQ_ERR_NO_DEVICE;
   if (di.sms > CQ_STATIC_MAX_CTAS) return CQ_ERR_STATIC_LIMIT;
   const Knobs kn = knobs();
-  const Shape sh = SHAPES[kn.shape];
   const uint32_t T = (uint32_t)L->n_sub * (uint32_t)L->n_gran;
   int grid = di.sms;
   if ((uint32_t)grid > T) grid = (int)T;
 
   // one launch must take all M rows: the array has room for one launch's partial sums only
   MatvecParams p;
-  const int smem = plan_smem(L, M, grid, di.max_smem, sh, kn.smem_kb, kn.max_stages, &p);
+  int ncw = 0;
+  KernelFn fn = pick_kernel(kn.shape, L->bits, L->sets, tiles_of(M), &ncw);
+  const int smem = plan_smem(L, M, grid, di.max_smem, ncw, kn.smem_kb, kn.max_stages, &p);
   if (smem < 0) return CQ_ERR_STATIC_LIMIT;
 
   unsigned char* base = nullptr;
@@ -1003,11 +1078,10 @@ extern "C" int cq_layer_matvec_static(const cq_layer* L, const void* x, int ldx,
   p.ldx = ldx; p.ldy = ldy; p.accumulate = accumulate;
   p.T = T;
 
-  KernelFn fn = pick_kernel(kn.shape, L->bits, L->sets, (M + 7) / 8);
-  CQ_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  CQ_CUDA_TRY(prepare_kernel(fn, smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3((sh.ncw + 1) * 32);
+  cfg.blockDim = dim3((ncw + 1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   CQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, fn, p));

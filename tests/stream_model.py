@@ -3,9 +3,11 @@
 Test infrastructure: an independent restatement (from the layout description in
 csrc/cq_common.cuh) of
   * the re-pack reference buffers -> stream (`build_blob`), and
-  * the decode + mma.sync.m16n8k16 fragment walk of the matvec kernel
-    (`consume_blob`), including the fp16 exponent-trick decode with the same masks
-    and constants as the CUDA code.
+  * the walk of the stream by the matvec kernel (`consume_blob`): byte-mask decode
+    into the A fragments of the integer mma.sync.m16n8k32, activations quantised per
+    granule into two signed bytes, integer sums, scale and offset applied per group.
+The second half of the file models the tile layout of the tcgen05 kernels the same way
+(fp16 exponent-trick decode with the same masks and constants as the CUDA code).
 CPU tests check model(build) against the oracle; GPU tests check the CUDA re-pack
 against `build_blob` byte for byte.
 """
@@ -72,30 +74,29 @@ def build_blob(qweight, scales, cherry_weight, cherry_indices, bits, K, G):
             base = d["off_stream"] + (sub * d["n_gran"] + gi) * gb
             words = np.zeros(64 * bits, np.uint32)
             for lane in range(32):
-                g, t = lane >> 2, lane & 3
-                for hi in range(2):
-                    n = sub * 16 + g + 8 * hi
+                g, c = lane >> 2, lane & 3
+                for r in range(2):
+                    n = sub * 16 + g + 8 * r
+
+                    def code(j, i):      # fragment register j = 2 m + b, byte i
+                        return int(u[gi * 128 + 32 * (j >> 1) + 16 * (j & 1) + 4 * c + i, n])
                     if bits == 4:
-                        for h in range(2):
-                            for half in range(2):
-                                w = 0
-                                for i in range(8):
-                                    kc = gi * 128 + 64 * h + 16 * t + 8 * half + i
-                                    w |= int(u[kc, n]) << s4_shift(i)
-                                words[(h * 128 + lane * 4) + 2 * hi + half] = w
+                        for m in range(4):
+                            w = 0
+                            for i in range(4):
+                                w |= (code(2 * m, i) | (code(2 * m + 1, i) << 4)) << (8 * i)
+                            words[(m >> 1) * 128 + lane * 4 + (m & 1) * 2 + r] = w
                     else:
-                        ws = [0, 0, 0]
-                        for e in range(32):
-                            kc = gi * 128 + 16 * t + (e if e < 16 else 64 + e - 16)
-                            code = int(u[kc, n])
-                            if e < 30:
-                                q = e >> 1
-                                ws[q // 5] |= code << (16 * (e & 1) + 1 + 3 * (q % 5))
-                            else:
-                                for wi in range(3):
-                                    ws[wi] |= ((code >> wi) & 1) << (16 * (e & 1))
-                        for wi in range(3):
-                            words[lane * 6 + 3 * hi + wi] = ws[wi]
+                        wa = wb = wc = 0
+                        for i in range(4):
+                            wa |= (code(0, i) | (code(1, i) << 3) | ((code(6, i) & 3) << 6)) << (8 * i)
+                            wb |= (code(2, i) | (code(3, i) << 3) | ((code(6, i) >> 2) << 6) | ((code(7, i) >> 2) << 7)) << (8 * i)
+                            wc |= (code(4, i) | (code(5, i) << 3) | ((code(7, i) & 3) << 6)) << (8 * i)
+                        if r == 0:
+                            words[lane * 4: lane * 4 + 3] = (wa, wb, wc)
+                        else:
+                            words[lane * 4 + 3] = wa
+                            words[128 + lane * 2: 128 + lane * 2 + 2] = (wb, wc)
             blob[base:base + 256 * bits] = words.view(np.uint8)
             srow = np.zeros(d["sets"] * 16, np.uint16)
             for sp in range(d["sets"]):
@@ -136,17 +137,123 @@ def build_blob(qweight, scales, cherry_weight, cherry_indices, bits, K, G):
 
 
 # ------------------------------------------------------------------ consumption model
-# The kernel's decode: OR a code field at mantissa bit p into the bits of fp16 1024.0
-# -> 1024 + 2^p u; the activation that meets it is pre-scaled by 2^(c-p), and
+OFF = {4: 7.5, 3: 3.5}
+QMAX = 16256           # 127 * 128: the quantised activation splits into two signed bytes
+
+
+def quantise_activations(d, xs):
+    """xs (M, Kp) compact fp16 activations (as float32) -> what the kernel stages per granule and row:
+    hi / lo signed bytes (q = 128 hi + lo), the step sx, and per set nc = -off * sum(q) * sx.
+    All arithmetic in float32, operation for operation as in the kernel."""
+    M = xs.shape[0]
+    x4 = xs.astype(np.float32).reshape(M, d["n_gran"], 128)
+    amax = np.abs(x4).max(-1)                                                  # (M, n_gran)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        inv = np.where(amax > 0, np.float32(QMAX) / amax, np.float32(0)).astype(np.float32)
+    sx = (amax / np.float32(QMAX)).astype(np.float32)
+    q = np.rint(x4 * inv[..., None]).astype(np.int64)                          # float32 product, half-to-even
+    hi = (q + 64) >> 7
+    lo = q - 128 * hi
+    assert hi.min() >= -128 and hi.max() <= 127 and lo.min() >= -64 and lo.max() <= 63
+    per = 128 // d["sets"]
+    qs = q.reshape(M, d["n_gran"], d["sets"], per).sum(-1)
+    nc = ((np.float32(-OFF[d["bits"]]) * qs.astype(np.float32)) * sx[..., None]).astype(np.float32)
+    return hi, lo, sx, nc
+
+
+def decode_regs(bits, w):
+    """The eight fragment registers (4 codes each, bytes i = 0..3) of one row from its words."""
+    if bits == 4:
+        regs = []
+        for m in range(4):
+            regs += [w[m] & 0x0F0F0F0F, (w[m] >> 4) & 0x0F0F0F0F]
+        return regs
+    a, b, c = w
+    m3 = 0x07070707
+    return [a & m3, (a >> 3) & m3, b & m3, (b >> 3) & m3, c & m3, (c >> 3) & m3,
+            ((a >> 6) & 0x03030303) | ((b >> 4) & 0x04040404),
+            ((c >> 6) & 0x03030303) | ((b >> 5) & 0x04040404)]
+
+
+def consume_blob(blob, d, x):
+    """y (M, N) float64 computed the way the kernel walks the stream."""
+    bits, N, M = d["bits"], d["N"], x.shape[0]
+    osh = blob[d["off_osh"]:d["off_osh"] + 4 * (d["Kp"] // 8)].view(np.uint32)
+    cidx = blob[d["off_cidx"]:d["off_cidx"] + 2 * d["Cp"]].view(np.uint16)
+    xs = np.zeros((M, d["Kp"]), np.float32)
+    cher = cidx[cidx != PAD].astype(np.int64)
+    for o, sh in enumerate(osh):
+        if sh == 0xFFFFFFFF:
+            continue
+        lo0, lo7 = int(sh & 0xFFFF), int(sh >> 16)
+        for i in range(8):
+            k = 8 * o + i
+            if lo0 == lo7:
+                s = lo0
+            else:   # a cherry column falls inside the octet: per-column search, as the kernel does
+                s = int(np.sum(cher - np.arange(len(cher)) <= k))
+            xs[:, k] = x[:, k + s].astype(np.float32)
+    hi, lo, sx, nc = quantise_activations(d, xs)
+    xc = np.zeros((M, d["Cp"]))
+    okc = cidx != PAD
+    xc[:, okc] = x[:, cidx[okc].astype(np.int64)].astype(np.float64)
+    y = np.zeros((M, d["n_sub"] * 16))
+    gb = d["gran_bytes"]
+    for sub in range(d["n_sub"]):
+        for gi in range(d["n_gran"]):
+            base = d["off_stream"] + (sub * d["n_gran"] + gi) * gb
+            words = blob[base:base + 256 * bits].view(np.uint32)
+            sc = blob[base + 256 * bits:base + gb].view(np.float16).astype(np.float64)
+            for lane in range(32):
+                g, c = lane >> 2, lane & 3
+                for r in range(2):
+                    row = sub * 16 + g + 8 * r
+                    if bits == 4:
+                        w = [int(words[(m >> 1) * 128 + lane * 4 + (m & 1) * 2 + r]) for m in range(4)]
+                    elif r == 0:
+                        w = [int(v) for v in words[lane * 4: lane * 4 + 3]]
+                    else:
+                        w = [int(words[lane * 4 + 3]), int(words[128 + lane * 2]), int(words[128 + lane * 2 + 1])]
+                    regs = decode_regs(bits, w)
+                    for sp in range(d["sets"]):
+                        ms = range(4) if d["sets"] == 1 else range(2 * sp, 2 * sp + 2)
+                        acc_h = np.zeros(M, np.int64)
+                        acc_l = np.zeros(M, np.int64)
+                        for m in ms:
+                            for b in range(2):
+                                for i in range(4):
+                                    code = (regs[2 * m + b] >> (8 * i)) & 0xFF
+                                    kk = 32 * m + 16 * b + 4 * c + i
+                                    acc_h += code * hi[:, gi, kk]
+                                    acc_l += code * lo[:, gi, kk]
+                        v = (128 * acc_h + acc_l).astype(np.float64)
+                        # the lanes c = 0..3 of a row split its columns; the offset term goes in once
+                        y[:, row] += sc[sp * 16 + 2 * g + r] * v * sx[:, gi]
+                        if c == 0:
+                            y[:, row] += sc[sp * 16 + 2 * g + r] * nc[:, gi, sp]
+        for j in range(d["Cp"] // 16):
+            o = d["off_cherry"] + sub * d["cher_bytes"] + j * 512
+            blk = blob[o:o + 512].view(np.float16).astype(np.float64).reshape(32, 8)
+            for lane in range(32):
+                g, t = lane >> 2, lane & 3
+                for reg in range(4):
+                    row = sub * 16 + g + 8 * (reg & 1)
+                    c0 = 16 * j + 2 * t + 8 * (reg >> 1)
+                    y[:, row] += xc[:, c0] * blk[lane, 2 * reg] + xc[:, c0 + 1] * blk[lane, 2 * reg + 1]
+    return y[:, :N]
+
+
+# ====================================================================== tile layout (tcgen05 kernels)
+# The tile kernels decode with the fp16 exponent trick: OR a code field at mantissa bit p into the
+# bits of fp16 1024.0 -> 1024 + 2^p u; the activation that meets it is pre-scaled by 2^(c-p), and
 # (B + off) x with B = 2^(10-p) is subtracted per group afterwards.
 MAGIC = 0x64006400
 C_EXP = {4: 2, 3: 1}
-OFF = {4: 7.5, 3: 3.5}
 
 
 def p_of_pair(bits, q):
-    """Mantissa bit of the code field of pair q (4-bit: q = position >> 1 in the lane's 16 codes
-    of a half; 3-bit: q = 0..15 over the row's 32 codes of a granule)."""
+    """Mantissa bit of the code field of pair q (4-bit: q = position >> 1; 3-bit: q = 0..15 over a
+    row's 32 codes)."""
     if bits == 4:
         return 6 if q & 1 else 2
     if q == 15:
@@ -175,83 +282,6 @@ def decode3(w0, w1, w2):
     return out
 
 
-def stage_activations(d, xs):
-    """xs (M, Kp) compact activations -> (pre-scaled fp16 copy as float64, corr (M, n_gran, sets))."""
-    bits, ce = d["bits"], C_EXP[d["bits"]]
-    kpp = np.arange(d["Kp"]) % 128
-    h, i = kpp >> 6, kpp & 15
-    q = (i >> 1) if bits == 4 else 8 * h + (i >> 1)
-    p = np.array([p_of_pair(bits, int(v)) for v in q])
-    xsc = (xs * 2.0 ** (ce - p)).astype(np.float16).astype(np.float64)
-    coef = 2.0 ** (p - ce) * (2.0 ** (10 - p) + OFF[bits])
-    per = 128 // d["sets"]
-    corr = (xsc * coef).reshape(xs.shape[0], d["n_gran"], d["sets"], per).sum(-1)
-    return xsc, corr
-
-
-def consume_blob(blob, d, x):
-    """y (M, N) float64 computed the way the kernel walks the stream."""
-    bits, N, M = d["bits"], d["N"], x.shape[0]
-    osh = blob[d["off_osh"]:d["off_osh"] + 4 * (d["Kp"] // 8)].view(np.uint32)
-    cidx = blob[d["off_cidx"]:d["off_cidx"] + 2 * d["Cp"]].view(np.uint16)
-    xs = np.zeros((M, d["Kp"]))
-    cher = cidx[cidx != PAD].astype(np.int64)
-    for o, sh in enumerate(osh):
-        if sh == 0xFFFFFFFF:
-            continue
-        lo0, lo7 = int(sh & 0xFFFF), int(sh >> 16)
-        for i in range(8):
-            k = 8 * o + i
-            if lo0 == lo7:
-                s = lo0
-            else:   # a cherry column falls inside the octet: per-column search, as the kernel does
-                s = int(np.sum(cher - np.arange(len(cher)) <= k))
-            xs[:, k] = x[:, k + s].astype(np.float64)
-    xs, corr = stage_activations(d, xs)
-    inv = 2.0 ** -C_EXP[bits]
-    xc = np.zeros((M, d["Cp"]))
-    okc = cidx != PAD
-    xc[:, okc] = x[:, cidx[okc].astype(np.int64)].astype(np.float64)
-    y = np.zeros((M, d["n_sub"] * 16))
-    gb = d["gran_bytes"]
-    for sub in range(d["n_sub"]):
-        for gi in range(d["n_gran"]):
-            base = d["off_stream"] + (sub * d["n_gran"] + gi) * gb
-            words = blob[base:base + 256 * bits].view(np.uint32)
-            sc = blob[base + 256 * bits:base + gb].view(np.float16).astype(np.float64)
-            for lane in range(32):
-                g, t = lane >> 2, lane & 3
-                if bits == 4:
-                    A = [[], []]
-                    for h in range(2):
-                        w = words[h * 128 + lane * 4: h * 128 + lane * 4 + 4]
-                        A[0] += decode4(int(w[0])) + decode4(int(w[1]))
-                        A[1] += decode4(int(w[2])) + decode4(int(w[3]))
-                else:
-                    w = [int(v) for v in words[lane * 6: lane * 6 + 6]]
-                    A = [decode3(*w[0:3]), decode3(*w[3:6])]
-                for h in range(2):
-                    sp = h if d["sets"] == 2 else 0
-                    kbase = gi * 128 + 64 * h + 16 * t
-                    for hi in range(2):
-                        row = sub * 16 + g + 8 * hi
-                        wv = np.concatenate(A[hi][8 * h: 8 * h + 8])        # 16 codes i = 0..15
-                        y[:, row] += sc[sp * 16 + 2 * g + hi] * ((xs[:, kbase:kbase + 16] @ wv) * inv)
-                        if t == 0 and (h == 0 or d["sets"] == 2):
-                            y[:, row] -= sc[sp * 16 + 2 * g + hi] * corr[:, gi, sp]
-        for j in range(d["Cp"] // 16):
-            o = d["off_cherry"] + sub * d["cher_bytes"] + j * 512
-            blk = blob[o:o + 512].view(np.float16).astype(np.float64).reshape(32, 8)
-            for lane in range(32):
-                g, t = lane >> 2, lane & 3
-                for reg in range(4):
-                    row = sub * 16 + g + 8 * (reg & 1)
-                    c0 = 16 * j + 2 * t + 8 * (reg >> 1)
-                    y[:, row] += xc[:, c0] * blk[lane, 2 * reg] + xc[:, c0 + 1] * blk[lane, 2 * reg + 1]
-    return y[:, :N]
-
-
-# ====================================================================== tile layout (tcgen05 kernels)
 def tile_dims(bits, K, N, C, G):
     if G == -1:
         G = K

@@ -13,8 +13,9 @@ def test_walk_of_stream_equals_oracle(name):
     blob, d = SM.build_blob(g["qweight"], g["scales"], g["cherry_weight"], g["cherry_indices"], g["bits"], g["K"], g["G"])
     y = SM.consume_blob(blob, d, g["x"])
     ref = O.kernel_forward(g["x"], g["qweight"], g["cherry_weight"], g["cherry_indices"], g["scales"], g["bits"], g["G"])
-    # pre-scaled activations that fall below the fp16 normal range are rounded (|x| < 2^-8)
-    assert np.abs(y - ref).max() <= 1e-6 * np.abs(ref).max()
+    # activations enter as 15-bit integers per granule (step = max|x| / 16256): each product is off
+    # by at most 3.1e-5 of the granule's largest activation
+    assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
 
 
 def test_dims_of_target_layer():
