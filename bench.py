@@ -165,6 +165,41 @@ def run_reference(args):
     }))
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one cq_matvec_kernel launch on this workload, from the
+# ncu capture summarised in profiles/stream_matvec_4096x11008_4bit_batch1_ncu.md (23,679,744 + 256 bytes)
+NCU_DRAM_BYTES_PER_LAUNCH = 23_680_000
+
+
+def phase_timeline(torch, lib, _cabi, layers, ncopies, x, y, n_local, scratch, status, dev):
+    """Per-phase nanosecond stamps (%globaltimer, written by every CTA through the library's tracing
+    hook cq_trace_set_timeline) of back-to-back launches; printed to stderr as a small table."""
+    def ptr(t):
+        return C.c_void_p(t.data_ptr())
+    n = min(ncopies, 8)
+    bufs = [torch.zeros(1024 * 64, dtype=torch.int64, device=dev) for _ in range(n)]
+    for _ in range(3):
+        for i in range(n):
+            lib.cq_trace_set_timeline(ptr(bufs[i]))
+            _cabi.check(lib.cq_layer_matvec(C.byref(layers[i]), ptr(x), K_IN, ptr(y), n_local, 1, 0,
+                                            ptr(scratch), ptr(status), None), "matvec")
+    torch.cuda.synchronize()
+    lib.cq_trace_set_timeline(None)
+    import numpy as np
+    grid = torch.cuda.get_device_properties(dev).multi_processor_count
+    t = np.stack([b.cpu().numpy().reshape(1024, 64)[:grid] for b in bufs]).astype(np.float64)
+    names = ["CTA entry", "barriers ready", "layer constants staged", "previous kernel done (wait returned)",
+             "activations staged", "first weights landed", "last granule done", "exit",
+             "first bulk copy issued", "last bulk copy issued"]
+    print("phase timeline, ns after the previous launch's last CTA exit (min / median / max over CTAs), "
+          "launch %d of a chain:" % (n - 2), file=sys.stderr)
+    li = n - 2
+    t0 = t[li - 1][:, 7].max()
+    for si, nm in enumerate(names):
+        col = t[li][:, si] - t0
+        print(f"  {nm:38s} {col.min():8.0f} {np.median(col):8.0f} {col.max():8.0f}", file=sys.stderr)
+    print(f"  period (exit to exit)                  {t[li][:, 7].max() - t0:8.0f}", file=sys.stderr)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -325,6 +360,9 @@ def run_ours(args):
            "d2h_bytes_per_step": n_local * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
            "path": "quant_cuda.vecquant4matmul_cherryq with pinned host x / y per rank"}
 
+    if args.timeline and rank == 0:
+        phase_timeline(torch, lib, _cabi, layers, ncopies, x, y, n_local, scratch, status, dev)
+
     if rank == 0:
         peak, peak_kind = measured_peak()
         achieved = alg_local / (kern_ms * 1e-3) / 1e9
@@ -339,7 +377,7 @@ def run_ours(args):
                        "launch": "CUDA graph of the copies" if world == 1 else "stream launches"},
             "pct_of_nominal_8TBps": value / world / 8000.0 * 100.0 if world == 1 else None,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH * alg_local / alg, "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
                          "kernel": "cq_matvec_kernel<4,1,1,...>", "alg_bytes_per_launch": alg_local,
                          "launch_us": kern_ms * 1e3},
             "e2e": e2e, "gpu_launches": args.steps * world, "clocks": clocks,
@@ -357,6 +395,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=100)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--timeline", action="store_true",
+                    help="also print the kernel's per-phase device timeline to stderr (after the timed region)")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 200:
