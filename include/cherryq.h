@@ -165,6 +165,17 @@ int cq_tlayer_matvec(const cq_tlayer* layer, const void* x_f16, int ldx, void* y
                      int M, int accumulate, void* scratch, uint32_t* status_word,
                      cq_stream_t stream);
 
+/* Prefill GEMM: y (M, N) fp16 = [y +] x (M, K) fp16 . W^T for many activation rows, on the tcgen05
+ * tensor cores (weights dequantised to fp16 on the fly into tensor memory, fp32 accumulation).
+ * Replaces the reference's dense mode, QuantLinear.unpack() followed by F.linear
+ * (llama/qlinear.py:183-195), and its batched kernels for large batches
+ * (csrc/quant_cuda_kernel.cu:718-835).  `workspace` is device memory of at least
+ * cq_tlayer_gemm_workspace_bytes(layer, M) bytes, 128-byte aligned, for the staged activations;
+ * launches that can overlap on the GPU need separate workspaces. */
+size_t cq_tlayer_gemm_workspace_bytes(const cq_tlayer* layer, int M);
+int cq_tlayer_gemm(const cq_tlayer* layer, const void* x_f16, int ldx, void* y_f16, int ldy, int M,
+                   int accumulate, void* workspace, uint32_t* status_word, cq_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Drop-in operator entry points (reference: csrc/quant_cuda.cpp:41-69, 26-38).
  * Dimension arguments are what the reference derives from its tensors

@@ -18,7 +18,7 @@ SYMBOLS = [
     "cq_cache_clear", "cq_cache_stats", "cq_poll",
     "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense", "cq_trace_set_timeline",
     "cq_tlayer_init", "cq_tlayer_prepare", "cq_tlayer_unprepare", "cq_tlayer_matvec",
-    "cq_layer_matvec_static",
+    "cq_layer_matvec_static", "cq_tlayer_gemm_workspace_bytes", "cq_tlayer_gemm",
 ]
 
 
@@ -63,6 +63,9 @@ def lib():
     L.cq_tlayer_prepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]
     L.cq_tlayer_unprepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]
     L.cq_tlayer_matvec.argtypes = [C.POINTER(cq_tlayer), vp, i32, vp, i32, i32, i32, vp, vp, vp]
+    L.cq_tlayer_gemm.argtypes = [C.POINTER(cq_tlayer), vp, i32, vp, i32, i32, i32, vp, vp, vp]
+    L.cq_tlayer_gemm_workspace_bytes.argtypes = [C.POINTER(cq_tlayer), i32]
+    L.cq_tlayer_gemm_workspace_bytes.restype = C.c_size_t
     L.cq_vecquant4matmul_cherryq.argtypes = [vp] * 6 + [i32] * 6 + [u64, vp]
     L.cq_vecquant3matmul_cherryq.argtypes = [vp] * 6 + [i32] * 7 + [u64, vp]
     L.cq_dequantize3_normal.argtypes = [vp, vp, vp] + [i32] * 5 + [vp]

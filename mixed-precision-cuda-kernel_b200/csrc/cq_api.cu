@@ -2,7 +2,8 @@
 // (csrc/quant_cuda.cpp:41-69 of the reference project) on top of the prepared
 // layer interface: the first call with a given set of reference buffers re-packs
 // them on the GPU into the stream layout and caches the result; every call then
-// runs the stream matvec.
+// runs the stream matvec.  Calls with 32 or more activation rows (prefill) take the tensor-core
+// GEMM on a second cached copy in the tile layout.
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -31,10 +32,16 @@ struct CacheKey {
 struct DeviceState {
   void* scratch = nullptr;
   uint32_t* status = nullptr;
+  void* gemm_ws = nullptr;        // staged activations of the prefill GEMM (grow-only)
+  size_t gemm_ws_bytes = 0;
 };
+
+constexpr int PREFILL_MIN_ROWS = 32;      // from here on the tensor-core GEMM is used
+constexpr int PREFILL_CHUNK_ROWS = 4096;  // rows per GEMM call (bounds the workspace)
 
 std::mutex g_mu;
 std::map<CacheKey, cq_layer> g_cache;
+std::map<CacheKey, cq_tlayer> g_tcache;
 std::map<int, DeviceState> g_dev;
 
 int device_state(int dev, DeviceState* out) {
@@ -48,6 +55,50 @@ int device_state(int dev, DeviceState* out) {
     it = g_dev.emplace(dev, ds).first;
   }
   *out = it->second;
+  return CQ_OK;
+}
+
+// Prefill: y += x . W^T through the tile-layout copy of the layer and the tcgen05 GEMM.
+int legacy_gemm(const CacheKey& key, int dev, const void* vec, const uint8_t* qweight, const void* cherry_weight,
+                const int16_t* cherry_indices, const void* scales, void* mul, int batch, uint32_t* status,
+                cudaStream_t st) {
+  auto it = g_tcache.find(key);
+  if (it == g_tcache.end()) {
+    cq_tlayer L;
+    int rc = cq_tlayer_init(&L, key.bits, key.K, key.N, key.C, key.G, nullptr);
+    if (rc) return rc;
+    void* blob = nullptr;
+    CQ_CUDA_TRY(cudaMalloc(&blob, L.blob_bytes));
+    L.blob = blob;
+    rc = cq_tlayer_prepare(&L, qweight, scales, cherry_weight, cherry_indices, st);
+    if (rc) {
+      cudaFree(blob);
+      return rc;
+    }
+    it = g_tcache.emplace(key, L).first;
+  }
+  const cq_tlayer& L = it->second;
+  DeviceState& ds = g_dev[dev];
+  const int chunk = batch < PREFILL_CHUNK_ROWS ? batch : PREFILL_CHUNK_ROWS;
+  const size_t need = cq_tlayer_gemm_workspace_bytes(&L, chunk);
+  if (need > ds.gemm_ws_bytes) {
+    if (ds.gemm_ws) {
+      CQ_CUDA_TRY(cudaStreamSynchronize(st));   // earlier GEMMs may still read the old buffer
+      CQ_CUDA_TRY(cudaFree(ds.gemm_ws));
+      ds.gemm_ws = nullptr;
+      ds.gemm_ws_bytes = 0;
+    }
+    CQ_CUDA_TRY(cudaMalloc(&ds.gemm_ws, need));
+    ds.gemm_ws_bytes = need;
+  }
+  const __half* xp = (const __half*)vec;
+  __half* yp = (__half*)mul;
+  for (int m0 = 0; m0 < batch; m0 += PREFILL_CHUNK_ROWS) {
+    const int rows = batch - m0 < PREFILL_CHUNK_ROWS ? batch - m0 : PREFILL_CHUNK_ROWS;
+    const int rc = cq_tlayer_gemm(&L, xp + (size_t)m0 * key.K, key.K, yp + (size_t)m0 * key.N, key.N, rows,
+                                  /*accumulate=*/1, ds.gemm_ws, status, st);
+    if (rc) return rc;
+  }
   return CQ_OK;
 }
 
@@ -68,6 +119,8 @@ int legacy_matmul(int bits, const void* vec, const uint8_t* qweight, const void*
   if (rc) return rc;
   const CacheKey key{dev, qweight, scales, cherry_weight, cherry_indices, bits, vec_height, width,
                      cherry_size, group_size, tag};
+  if (batch >= PREFILL_MIN_ROWS)
+    return legacy_gemm(key, dev, vec, qweight, cherry_weight, cherry_indices, scales, mul, batch, ds.status, st);
   auto it = g_cache.find(key);
   if (it == g_cache.end()) {
     cq_layer L;
@@ -160,6 +213,14 @@ extern "C" int cq_cache_clear(void) {
     if (cur != kv.first.dev) cudaSetDevice(cur);
   }
   g_cache.clear();
+  for (auto& kv : g_tcache) {
+    int cur = 0;
+    cudaGetDevice(&cur);
+    if (cur != kv.first.dev) cudaSetDevice(kv.first.dev);
+    cudaFree(kv.second.blob);
+    if (cur != kv.first.dev) cudaSetDevice(cur);
+  }
+  g_tcache.clear();
   return CQ_OK;
 }
 
@@ -167,7 +228,8 @@ extern "C" int cq_cache_stats(int* n_layers, uint64_t* bytes) {
   std::lock_guard<std::mutex> lock(g_mu);
   uint64_t b = 0;
   for (auto& kv : g_cache) b += kv.second.blob_bytes;
-  if (n_layers) *n_layers = (int)g_cache.size();
+  for (auto& kv : g_tcache) b += kv.second.blob_bytes;
+  if (n_layers) *n_layers = (int)(g_cache.size() + g_tcache.size());
   if (bytes) *bytes = b;
   return CQ_OK;
 }
