@@ -168,6 +168,7 @@ def run_reference(args):
 # dram__bytes_read.sum + dram__bytes_write.sum of one cq_matvec_kernel launch on this workload, from the
 # ncu capture summarised in profiles/stream_matvec_4096x11008_4bit_batch1_ncu.md (23,679,744 + 256 bytes)
 NCU_DRAM_BYTES_PER_LAUNCH = 23_680_000
+PREFILL_TOKENS = 2048
 
 
 def phase_timeline(torch, lib, _cabi, layers, ncopies, x, y, n_local, scratch, status, dev):
@@ -388,6 +389,160 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def measured_tensor_peak():
+    """Dense 16-bit tensor TFLOP/s measured on this pool (burst figure: the kernel is timed alone)."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
+def run_prefill(args):
+    """Prefill of PREFILL_TOKENS tokens through one layer: the tensor-core GEMM of the path.  Same layer
+    as the decode workload; the line reports dense TFLOP/s against the measured 16-bit tensor peak."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import cherryq_b200
+    from cherryq_b200 import _cabi
+    qc = cherryq_b200.load_quant_cuda()
+    lib = _cabi.lib()
+    M = PREFILL_TOKENS
+    n_local = N_OUT
+    if world > 1:
+        # equal shards of whole 128-row tiles (the last tiles of the last rank are padding rows)
+        n_local = math.ceil(N_OUT / 128 / world) * 128
+    q, s, cw, ci, c = make_layer_gpu(qc, torch, K_IN, n_local, BITS, GROUP, 1234 + rank, dev)
+
+    def ptr(t):
+        return C.c_void_p(t.data_ptr())
+
+    ncopies = 6                                      # 6 x 23 MB of weights + 62 MB of x / y per step > L2
+    layers, blobs = [], []
+    for i in range(ncopies):
+        L = _cabi.tlayer_init(BITS, K_IN, n_local, c, GROUP)
+        b = torch.empty(L.blob_bytes, dtype=torch.uint8, device=dev)
+        L.blob = b.data_ptr()
+        if i == 0:
+            _cabi.check(lib.cq_tlayer_prepare(C.byref(L), ptr(q), ptr(s), ptr(cw), ptr(ci), None), "prepare")
+            torch.cuda.synchronize()
+        else:
+            b.copy_(blobs[0])
+        layers.append(L)
+        blobs.append(b)
+    x = torch.randn(M, K_IN, device=dev).half()
+    y = torch.zeros(M, n_local, dtype=torch.float16, device=dev)
+    ws = torch.empty(lib.cq_tlayer_gemm_workspace_bytes(C.byref(layers[0]), M), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    sp = C.c_void_p(stream.cuda_stream)
+    y_all = torch.empty(world, M, n_local, dtype=torch.float16, device=dev) if world > 1 else None
+
+    def launch(i):
+        _cabi.check(lib.cq_tlayer_gemm(C.byref(layers[i % ncopies]), ptr(x), K_IN, ptr(y), n_local, M, 0, ptr(ws),
+                                       ptr(status), sp), "gemm")
+        if world > 1:
+            dist.all_gather_into_tensor(y_all, y)
+
+    steps = min(args.steps, 200)
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 3)):
+            launch(i)
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            launch(i)
+        e1.record(stream)
+        stream.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if int(status.item()) != 0:
+        raise RuntimeError("a device-side wait timed out during the benchmark")
+    ms_step = ms / steps
+    flops = 2.0 * M * K_IN * N_OUT
+    value = flops / (ms_step * 1e-3) / 1e12
+
+    # end to end through the drop-in op: host activations in, host outputs back
+    xh = torch.randn(M, K_IN).half().pin_memory()
+    yh = torch.empty(M, n_local, dtype=torch.float16).pin_memory()
+    xd = torch.empty(M, K_IN, dtype=torch.float16, device=dev)
+    out = torch.empty(M, n_local, dtype=torch.float16, device=dev)
+
+    def e2e_step():
+        xd.copy_(xh, non_blocking=True)
+        out.zero_()
+        qc.vecquant4matmul_cherryq(xd, q, cw, ci, s, out, GROUP)
+        yh.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    e2e_steps = min(steps, 30)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    qc.poll()
+    if rank == 0:
+        peak, kind = measured_tensor_peak()
+        achieved = flops / world / (ms_step * 1e-3) / 1e12
+        line = {
+            "metric": "prefill_dense_TFLOPs", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"llama7b_gate_proj_4096x11008_4bit_g128_cherry1/256_prefill{M}", "bits": BITS,
+                       "group": GROUP, "K": K_IN, "N": N_OUT, "tokens": M,
+                       "l2_defeat": f"{ncopies} distinct layer copies + x, y, staged activations per step "
+                                    f"({(ncopies * layers[0].blob_bytes + x.numel() * 2 + y.numel() * 2 + ws.numel()) / 1e6:.0f} MB) "
+                                    "larger than L2",
+                       "parallelism": "single GPU" if world == 1 else f"column-parallel over {world} GPUs + NCCL all-gather",
+                       "launch": "stream launches (activation pre-pass + GEMM kernel per step)"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": kind + " cuBLAS bf16 burst (MEASURED_PEAKS.json)",
+                         "kernel": "cq_prefill_kernel<4,1> (+ prefill_stage_x_kernel, inside the timed step)",
+                         "flops_per_launch": flops / world, "launch_us": ms_step * 1e3},
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K_IN * 2,
+                    "d2h_bytes_per_step": M * n_local * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "path": "quant_cuda.vecquant4matmul_cherryq with pinned host x / y per rank"},
+            "gpu_launches": 2 * steps * world, "clocks": clocks, "cpu_baseline": None,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -395,6 +550,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=100)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: batch-1 matvec (the headline line); prefill: 2048-token GEMM of the same layer")
     ap.add_argument("--timeline", action="store_true",
                     help="also print the kernel's per-phase device timeline to stderr (after the timed region)")
     args = ap.parse_args()
@@ -402,6 +559,8 @@ def main():
         if args.steps > 200:
             args.steps = 200        # each step is a full-layer CPU call (tens of ms): keep the run within minutes
         run_reference(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_ours(args)
 

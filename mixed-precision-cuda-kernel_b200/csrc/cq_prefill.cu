@@ -11,18 +11,21 @@
 //     memory with tcgen05.st: exponent-trick unpack (AND-OR into the bits of 1024.0), one exact
 //     subtraction and one multiplication by the group scale per fp16 pair, which reproduces
 //     unpack()'s fp16 values bit for bit;
-//   * B operand = 128 tokens of activations per CTA tile, prepared once per call by a small
-//     pre-pass kernel (gather into compact column order, canonical K-major UMMA layout) so that
-//     the main kernel moves them with plain bulk async copies;
-//   * D = 128 rows x 128 tokens fp32 in tensor memory, accumulated over the whole K by
-//     tcgen05.mma.cta_group::1.kind::f16 (A from TMEM, M = 128, N = 128, K = 16 per instruction),
-//     double-buffered so that the fp16 store of one tile overlaps the MMAs of the next.
+//   * B operand = NT tokens of activations per CTA tile (NT = 256, or 128 for calls of at most 128
+//     rows), prepared once per call by a small pre-pass kernel (gather into compact column
+//     order, canonical K-major UMMA layout) so that the main kernel moves them with plain bulk
+//     async copies;
+//   * D = 128 rows x NT tokens fp32 in tensor memory, accumulated over the whole K by
+//     tcgen05.mma.cta_group::1.kind::f16 (A from TMEM, M = 128, N = NT, K = 16 per instruction);
+//     with NT = 128 there are two accumulator buffers, so that the fp16 store of one tile overlaps
+//     the MMAs of the next.
 //
-// Warp roles (448 threads, one CTA per SM, persistent over (token block, row tile) units):
-//   warps 0-7   two decode groups (items alternate between them), thread r of a group = row r
-//   warp 8      MMA issuer (one lane); owns the tensor-memory allocation
-//   warp 9      producer (one lane): bulk copies of weight items and activation tiles
-//   warps 10-13 epilogue: tcgen05.ld of a finished tile, fp16 store to y
+// Warp roles (704 threads, one CTA per SM, persistent over (token block, row tile) units):
+//   warps 0-15  four decode groups (items go round-robin), thread r of a group = row r; a group
+//               needs about twice the time the tensor core spends on an item, hence four of them
+//   warp 16     MMA issuer (one lane); owns the tensor-memory allocation
+//   warp 17     producer (one lane): bulk copies of weight items and activation tiles
+//   warps 18-21 epilogue: tcgen05.ld of a finished tile, fp16 store to y
 // Every wait is bounded and reports into the status word instead of hanging.
 #include <cstdlib>
 
@@ -31,18 +34,19 @@
 namespace {
 
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
-constexpr int NT = 128;                 // tokens per tile = UMMA N
-constexpr int NA = 3;                   // A slots in tensor memory (64 columns each)
+// NT = tokens per tile = UMMA N: 256 (one accumulator buffer; the MMA runs at its full rate) or 128
+// (two accumulator buffers; less padding for few tokens).
+constexpr int NGRP = 4;                 // decode groups of four warps
+constexpr int NA = 4;                   // A slots in tensor memory (64 columns each), one per decode group
 constexpr int A_COLS = 64;
-constexpr int ND = 2;                   // accumulator buffers (NT columns each)
 constexpr int D_BASE = NA * A_COLS;
 constexpr int TMEM_COLS = 512;
 constexpr int SW = 4;                   // weight ring stages
-constexpr int SB = 4;                   // activation ring stages
-constexpr int B_KSTEP_BYTES = NT * 32;  // one K = 16 step: [token group][k half][8 tokens][16 B]
-constexpr int B_GRAN_BYTES = 8 * B_KSTEP_BYTES;
-constexpr int B_CHER_BYTES = B_KSTEP_BYTES;
-constexpr int NTHREADS = 448;
+constexpr int NTHREADS = (NGRP * 4 + 6) * 32;
+// one K = 16 step of the B operand: [token group of 8][k half][8 tokens][16 B] = NT * 32 bytes;
+// a granule is 8 steps, a cherry item one
+__host__ __device__ constexpr int b_kstep_bytes(int nt) { return nt * 32; }
+__host__ __device__ constexpr int b_gran_bytes(int nt) { return nt * 256; }
 
 struct PrefillParams {
   const uint8_t* stream;     // tile-layout weight stream
@@ -52,7 +56,7 @@ struct PrefillParams {
   int M, N, n_gran, n_tile, n_cher, gran_bytes, tile_bytes, ldy, accumulate;
   uint32_t n_units;          // token blocks x row tiles
   unsigned long long xb_blk_bytes;
-  int wstage_bytes, off_wring, off_bring, off_bar;
+  int wstage_bytes, sb, off_wring, off_bring, off_bar;   // sb = activation ring stages
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -194,9 +198,10 @@ __device__ __forceinline__ void dequant3(uint32_t w0, uint32_t w1, uint32_t w2, 
 // the granules (128 compact columns = 8 steps).  Tokens past M are zeros.
 __global__ void prefill_stage_x_kernel(const __half* __restrict__ x, int ldx, int M, const uint32_t* __restrict__ osh,
                                        const uint16_t* __restrict__ cidx, int C, int Kc, int n_gran, int n_cher,
-                                       uint8_t* __restrict__ xb, unsigned long long blk_bytes, int n_mblk) {
+                                       uint8_t* __restrict__ xb, unsigned long long blk_bytes, int n_mblk, int NT) {
   const int per_tok = 2 * n_cher + 16 * n_gran;            // octets per token
   const long long total = (long long)n_mblk * NT * per_tok;
+  const int B_KSTEP_BYTES = b_kstep_bytes(NT), B_GRAN_BYTES = b_gran_bytes(NT), B_CHER_BYTES = B_KSTEP_BYTES;
   for (long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x; id < total;
        id += (long long)gridDim.x * blockDim.x) {
     const int m = (int)(id / per_tok), oi = (int)(id % per_tok);
@@ -222,12 +227,23 @@ __global__ void prefill_stage_x_kernel(const __half* __restrict__ x, int ldx, in
       const uint32_t sh = osh[o];
       if (m < M && sh != 0xFFFFFFFFu) {
         const int lo0 = (int)(sh & 0xFFFFu), lo7 = (int)(sh >> 16);
-        int sft = lo0;
+        if (lo0 == lo7 && ((k0 + lo0) & 1) == 0 && (((uintptr_t)xr) & 3) == 0) {
+          // eight consecutive columns at a 4-byte aligned address (K' is a multiple of 8: all exist)
+          const uint32_t* s32 = reinterpret_cast<const uint32_t*>(xr + k0 + lo0);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          // cherry columns inside the octet: the shift grows from lo0 to lo7 along it
-          while (sft < lo7 && (int)cidx[sft] - sft <= k0 + e) ++sft;
-          if (k0 + e < Kc) h[e] = __ldg(xr + k0 + e + sft);
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t w = __ldg(s32 + i);
+            h[2 * i] = (unsigned short)(w & 0xFFFFu);
+            h[2 * i + 1] = (unsigned short)(w >> 16);
+          }
+        } else {
+          int sft = lo0;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            // cherry columns inside the octet: the shift grows from lo0 to lo7 along it
+            while (sft < lo7 && (int)cidx[sft] - sft <= k0 + e) ++sft;
+            if (k0 + e < Kc) h[e] = __ldg(xr + k0 + e + sft);
+          }
         }
       }
       dst = xb + (size_t)mb * blk_bytes + (size_t)n_cher * B_CHER_BYTES + (size_t)g * B_GRAN_BYTES +
@@ -243,9 +259,14 @@ __global__ void prefill_stage_x_kernel(const __half* __restrict__ x, int ldx, in
 }
 
 // ------------------------------------------------------------------ main kernel
-template <int BITS, int SETS>
+// RT = row tiles of 128 rows per unit: with two, one staged activation tile feeds two weight tiles,
+// which halves the activation bytes an SM has to pull from L2 per flop.
+template <int BITS, int SETS, int NT, int RT>
 __global__ void __launch_bounds__(NTHREADS, 1) cq_prefill_kernel(const PrefillParams p) {
-  constexpr int W_MMA = 8, W_PROD = 9, W_EPI = 10;
+  constexpr int W_MMA = NGRP * 4, W_PROD = NGRP * 4 + 1;
+  constexpr int ND = (NT * RT == 128) ? 2 : 1;            // accumulator buffers (RT * NT columns each)
+  constexpr int SBMAX = 4;
+  constexpr int B_KSTEP_BYTES = b_kstep_bytes(NT), B_GRAN_BYTES = b_gran_bytes(NT), B_CHER_BYTES = B_KSTEP_BYTES;
   // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = NT, M = 128
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | (8u << 24);
   extern __shared__ __align__(128) uint8_t smem[];
@@ -256,16 +277,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) cq_prefill_kernel(const PrefillPa
   const uint32_t grid = gridDim.x, cta = blockIdx.x;
   const uint32_t NCH = (uint32_t)p.n_cher, IPT = NCH + (uint32_t)p.n_gran;
   const uint32_t NTILE = (uint32_t)p.n_tile;
+  const uint32_t NPAIR = (NTILE + RT - 1) / RT;          // units per token block
+  const uint32_t SB = (uint32_t)p.sb;
 
   const uint32_t bar0 = smem_u32(smem + p.off_bar);
   auto B_WFULL = [&](uint32_t s) { return bar0 + 8 * s; };
   auto B_WEMPTY = [&](uint32_t s) { return bar0 + 8 * (SW + s); };
   auto B_BFULL = [&](uint32_t s) { return bar0 + 8 * (2 * SW + s); };
-  auto B_BEMPTY = [&](uint32_t s) { return bar0 + 8 * (2 * SW + SB + s); };
-  auto B_AFULL = [&](uint32_t a) { return bar0 + 8 * (2 * SW + 2 * SB + a); };
-  auto B_AEMPTY = [&](uint32_t a) { return bar0 + 8 * (2 * SW + 2 * SB + NA + a); };
-  auto B_DFULL = [&](uint32_t d) { return bar0 + 8 * (2 * SW + 2 * SB + 2 * NA + d); };
-  auto B_DEMPTY = [&](uint32_t d) { return bar0 + 8 * (2 * SW + 2 * SB + 2 * NA + ND + d); };
+  auto B_BEMPTY = [&](uint32_t s) { return bar0 + 8 * (2 * SW + SBMAX + s); };
+  auto B_AFULL = [&](uint32_t a) { return bar0 + 8 * (2 * SW + 2 * SBMAX + a); };
+  auto B_AEMPTY = [&](uint32_t a) { return bar0 + 8 * (2 * SW + 2 * SBMAX + NA + a); };
+  auto B_DFULL = [&](uint32_t d) { return bar0 + 8 * (2 * SW + 2 * SBMAX + 2 * NA + d); };
+  auto B_DEMPTY = [&](uint32_t d) { return bar0 + 8 * (2 * SW + 2 * SBMAX + 2 * NA + 2 + d); };
 
   if (tid == 0) {
     s_abort = 0;
@@ -292,23 +315,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) cq_prefill_kernel(const PrefillPa
       // the staged activations are written by the kernel launched just before this one
       asm volatile("griddepcontrol.wait;" ::: "memory");
       const uint32_t wring = smem_u32(smem + p.off_wring), bring = smem_u32(smem + p.off_bring);
-      uint32_t n = 0;
+      uint32_t n = 0, nb = 0;      // weight items and activation tiles issued so far
       for (uint32_t u = cta; u < p.n_units; u += grid) {
-        const uint32_t mb = u / NTILE, t = u - mb * NTILE;
-        const uint8_t* wsrc = p.stream + (size_t)t * p.tile_bytes;
+        const uint32_t mb = u / NPAIR, t0 = (u - mb * NPAIR) * RT;
+        const uint32_t ntr = min((uint32_t)RT, NTILE - t0);
         const uint8_t* bsrc = p.xb + (size_t)mb * p.xb_blk_bytes;
-        for (uint32_t j = 0; j < IPT; ++j, ++n) {
+        size_t woff = 0;             // offset of item j inside a row tile's block
+        for (uint32_t j = 0; j < IPT; ++j, ++nb) {
           const bool cherry = j < NCH;
-          const uint32_t sw = n % SW, sb = n % SB;
+          const uint32_t sb = nb % SB;
           const uint32_t wbytes = cherry ? (uint32_t)CQT_CHER_BYTES : (uint32_t)p.gran_bytes;
           const uint32_t bbytes = cherry ? (uint32_t)B_CHER_BYTES : (uint32_t)B_GRAN_BYTES;
-          if (n >= SW) mbar_wait(B_WEMPTY(sw), ((n / SW) - 1) & 1, &s_abort, p.status, 1u);
-          mbar_expect_tx(B_WFULL(sw), wbytes);
-          bulk_g2s(wring + sw * (uint32_t)p.wstage_bytes, wsrc, wbytes, B_WFULL(sw));
-          if (n >= SB) mbar_wait(B_BEMPTY(sb), ((n / SB) - 1) & 1, &s_abort, p.status, 2u);
+          for (uint32_t rt = 0; rt < ntr; ++rt, ++n) {
+            const uint32_t sw = n % SW;
+            if (n >= SW) mbar_wait(B_WEMPTY(sw), ((n / SW) - 1) & 1, &s_abort, p.status, 1u);
+            mbar_expect_tx(B_WFULL(sw), wbytes);
+            bulk_g2s(wring + sw * (uint32_t)p.wstage_bytes, p.stream + (size_t)(t0 + rt) * p.tile_bytes + woff, wbytes,
+                     B_WFULL(sw));
+          }
+          if (nb >= SB) mbar_wait(B_BEMPTY(sb), ((nb / SB) - 1) & 1, &s_abort, p.status, 2u);
           mbar_expect_tx(B_BFULL(sb), bbytes);
           bulk_g2s(bring + sb * (uint32_t)B_GRAN_BYTES, bsrc, bbytes, B_BFULL(sb));
-          wsrc += wbytes;
+          woff += wbytes;
           bsrc += bbytes;
         }
       }
@@ -317,25 +345,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) cq_prefill_kernel(const PrefillPa
     // ================================================================ MMA issuer
     if (lane == 0) {
       const uint32_t bring = smem_u32(smem + p.off_bring);
-      uint32_t n = 0, lu = 0;
+      uint32_t n = 0, nb = 0, lu = 0;
       for (uint32_t u = cta; u < p.n_units; u += grid, ++lu) {
+        const uint32_t mb = u / NPAIR, t0 = (u - mb * NPAIR) * RT;
+        const uint32_t ntr = min((uint32_t)RT, NTILE - t0);
         const uint32_t dbuf = lu % ND;
         if (lu >= ND) mbar_wait(B_DEMPTY(dbuf), ((lu / ND) - 1) & 1, &s_abort, p.status, 4u);
-        const uint32_t td = tmem + D_BASE + dbuf * NT;
-        for (uint32_t j = 0; j < IPT; ++j, ++n) {
-          const uint32_t a = n % NA, sb = n % SB;
-          mbar_wait(B_AFULL(a), (n / NA) & 1, &s_abort, p.status, 8u);
-          mbar_wait(B_BFULL(sb), (n / SB) & 1, &s_abort, p.status, 16u);
-          tc_fence_after();
-          const uint32_t ta = tmem + a * A_COLS, bbase = bring + sb * (uint32_t)B_GRAN_BYTES;
-          if (j < NCH) {
-            umma_ts(td, ta, smem_desc(bbase, 8, 16), IDESC, j != 0);
-          } else {
+        for (uint32_t j = 0; j < IPT; ++j, ++nb) {
+          const uint32_t sb = nb % SB;
+          mbar_wait(B_BFULL(sb), (nb / SB) & 1, &s_abort, p.status, 16u);
+          const uint32_t bbase = bring + sb * (uint32_t)B_GRAN_BYTES;
+          for (uint32_t rt = 0; rt < ntr; ++rt, ++n) {
+            const uint32_t a = n % NA;
+            const uint32_t td = tmem + D_BASE + (dbuf * RT + rt) * NT;
+            mbar_wait(B_AFULL(a), (n / NA) & 1, &s_abort, p.status, 8u);
+            tc_fence_after();
+            const uint32_t ta = tmem + a * A_COLS;
+            if (j < NCH) {
+              umma_ts(td, ta, smem_desc(bbase, 8, 16), IDESC, j != 0);
+            } else {
 #pragma unroll
-            for (uint32_t ks = 0; ks < 8; ++ks)
-              umma_ts(td, ta + ks * 8, smem_desc(bbase + ks * B_KSTEP_BYTES, 8, 16), IDESC, (j != 0 || ks != 0));
+              for (uint32_t ks = 0; ks < 8; ++ks)
+                umma_ts(td, ta + ks * 8, smem_desc(bbase + ks * B_KSTEP_BYTES, 8, 16), IDESC, (j != 0 || ks != 0));
+            }
+            tc_commit(B_AEMPTY(a));
           }
-          tc_commit(B_AEMPTY(a));
           tc_commit(B_BEMPTY(sb));
         }
         tc_commit(B_DFULL(dbuf));
@@ -349,8 +383,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) cq_prefill_kernel(const PrefillPa
     const uint8_t* wring = smem + p.off_wring;
     uint32_t n = 0;
     for (uint32_t u = cta; u < p.n_units; u += grid) {
-      for (uint32_t j = 0; j < IPT; ++j, ++n) {
-        if ((int)(n & 1) != grp) continue;
+      const uint32_t mbu = u / NPAIR, t0 = (u - mbu * NPAIR) * RT;
+      const uint32_t ntr = min((uint32_t)RT, NTILE - t0);
+      for (uint32_t jj = 0; jj < IPT * ntr; ++jj, ++n) {
+        const uint32_t j = jj / ntr;               // items of the unit: (item j, row tile 0), (j, 1), ...
+        if ((int)(n % NGRP) != grp) continue;
         const uint32_t sw = n % SW, a = n % NA;
         mbar_wait(B_WFULL(sw), (n / SW) & 1, &s_abort, p.status, 32u);
         const uint8_t* item = wring + (size_t)sw * p.wstage_bytes;
@@ -406,33 +443,36 @@ __global__ void __launch_bounds__(NTHREADS, 1) cq_prefill_kernel(const PrefillPa
       }
     }
   } else {
-    // ================================================================ epilogue (warps 10..13)
+    // ================================================================ epilogue (last four warps)
     const int quad = warp & 3;                              // the tensor-memory lanes this warp may read
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     uint32_t lu = 0;
     for (uint32_t u = cta; u < p.n_units; u += grid, ++lu) {
-      const uint32_t mb = u / NTILE, t = u - mb * NTILE;
+      const uint32_t mb = u / NPAIR, t0 = (u - mb * NPAIR) * RT;
+      const uint32_t ntr = min((uint32_t)RT, NTILE - t0);
       const uint32_t dbuf = lu % ND;
       mbar_wait(B_DFULL(dbuf), (lu / ND) & 1, &s_abort, p.status, 128u);
       tc_fence_after();
-      const int n_row = (int)t * 128 + row;
       const int tok0 = (int)mb * NT;
+      for (uint32_t rt = 0; rt < ntr; ++rt) {
+        const int n_row = (int)(t0 + rt) * 128 + row;
 #pragma unroll 1
-      for (int c = 0; c < NT / 16; ++c) {
-        float v[16];
-        tmem_ld16(tmem + lane_addr + D_BASE + dbuf * NT + c * 16, v);
-        tmem_wait_ld();
-        if (n_row < p.N) {
+        for (int c = 0; c < NT / 16; ++c) {
+          float v[16];
+          tmem_ld16(tmem + lane_addr + D_BASE + (dbuf * RT + rt) * NT + c * 16, v);
+          tmem_wait_ld();
+          if (n_row < p.N) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int tok = tok0 + c * 16 + e;
-            if (tok < p.M) {
-              __half* yp = p.y + (size_t)tok * p.ldy + n_row;
-              float val = v[e];
-              if (p.accumulate) val += __half2float(*yp);
-              *yp = __float2half(val);
+            for (int e = 0; e < 16; ++e) {
+              const int tok = tok0 + c * 16 + e;
+              if (tok < p.M) {
+                __half* yp = p.y + (size_t)tok * p.ldy + n_row;
+                float val = v[e];
+                if (p.accumulate) val += __half2float(*yp);
+                *yp = __float2half(val);
+              }
             }
           }
         }
@@ -469,21 +509,34 @@ PDeviceInfo pdevice_info(int dev) {
 int palign_up(int v, int a) { return (v + a - 1) / a * a; }
 
 typedef void (*PKernelFn)(const PrefillParams);
+template <int NT, int RT>
 PKernelFn ppick(int bits, int sets) {
-  if (bits == 4) return sets == 1 ? cq_prefill_kernel<4, 1> : cq_prefill_kernel<4, 2>;
-  return sets == 1 ? cq_prefill_kernel<3, 1> : cq_prefill_kernel<3, 2>;
+  if (bits == 4) return sets == 1 ? cq_prefill_kernel<4, 1, NT, RT> : cq_prefill_kernel<4, 2, NT, RT>;
+  return sets == 1 ? cq_prefill_kernel<3, 1, NT, RT> : cq_prefill_kernel<3, 2, NT, RT>;
 }
 
-unsigned long long xb_block_bytes(const cq_tlayer* L) {
-  return (unsigned long long)L->n_cher * B_CHER_BYTES + (unsigned long long)L->n_gran * B_GRAN_BYTES;
+// Tile shape for a call of M rows: 0 = 128 rows x 128 tokens (two accumulator buffers), 1 = 128 x 256,
+// 2 = 256 x 128.  CQ_PREFILL_SHAPE overrides, for experiments.
+int tile_shape(int M, int n_tile) {
+  static int forced = [] { const char* e = getenv("CQ_PREFILL_SHAPE"); return e ? atoi(e) : -1; }();
+  if (forced >= 0 && forced <= 2) return forced;
+  (void)n_tile;
+  // measured on 4096 -> 11008, 2048 tokens: 128 x 256 tiles 938 TFLOP/s, 128 x 128 673, 256 x 128 613: the
+  // tensor-memory MMA only reaches its rate at N = 256
+  return M > 128 ? 1 : 0;
+}
+
+unsigned long long xb_block_bytes(const cq_tlayer* L, int nt) {
+  return (unsigned long long)L->n_cher * b_kstep_bytes(nt) + (unsigned long long)L->n_gran * b_gran_bytes(nt);
 }
 
 }  // namespace
 
 extern "C" size_t cq_tlayer_gemm_workspace_bytes(const cq_tlayer* L, int M) {
   if (!L || M < 1) return 0;
-  const size_t n_mblk = ((size_t)M + NT - 1) / NT;
-  return n_mblk * (size_t)xb_block_bytes(L);
+  // (both tile widths stage the same bytes per token; round up to the wider one)
+  const size_t n_mblk = ((size_t)M + 255) / 256;
+  return n_mblk * (size_t)xb_block_bytes(L, 256);
 }
 
 extern "C" int cq_tlayer_gemm(const cq_tlayer* L, const void* x, int ldx, void* y, int ldy, int M, int accumulate,
@@ -497,8 +550,10 @@ extern "C" int cq_tlayer_gemm(const cq_tlayer* L, const void* x, int ldx, void* 
   if (!di.ok) return CQ_ERR_NO_DEVICE;
   cudaStream_t st = (cudaStream_t)stream;
   const uint8_t* blob = (const uint8_t*)L->blob;
+  const int shape = tile_shape(M, L->n_tile);
+  const int NT = shape == 1 ? 256 : 128, RT = shape == 2 ? 2 : 1;
   const int n_mblk = (M + NT - 1) / NT;
-  const unsigned long long blk = xb_block_bytes(L);
+  const unsigned long long blk = xb_block_bytes(L, NT);
 
   {
     const long long total = (long long)n_mblk * NT * (2 * L->n_cher + 16 * L->n_gran);
@@ -506,7 +561,7 @@ extern "C" int cq_tlayer_gemm(const cq_tlayer* L, const void* x, int ldx, void* 
     if (blocks > 148 * 32) blocks = 148 * 32;
     prefill_stage_x_kernel<<<(int)blocks, 256, 0, st>>>(
         (const __half*)x, ldx, M, (const uint32_t*)(blob + L->off_osh), (const uint16_t*)(blob + L->off_cidx), L->C,
-        L->Kc, L->n_gran, L->n_cher, (uint8_t*)workspace, blk, n_mblk);
+        L->Kc, L->n_gran, L->n_cher, (uint8_t*)workspace, blk, n_mblk, NT);
     CQ_CUDA_TRY(cudaGetLastError());
   }
 
@@ -517,19 +572,22 @@ extern "C" int cq_tlayer_gemm(const cq_tlayer* L, const void* x, int ldx, void* 
   p.status = status_word;
   p.M = M; p.N = L->N; p.n_gran = L->n_gran; p.n_tile = L->n_tile; p.n_cher = L->n_cher;
   p.gran_bytes = L->gran_bytes; p.tile_bytes = L->tile_bytes; p.ldy = ldy; p.accumulate = accumulate;
-  p.n_units = (uint32_t)n_mblk * (uint32_t)L->n_tile;
+  p.n_units = (uint32_t)n_mblk * (uint32_t)((L->n_tile + RT - 1) / RT);
   p.xb_blk_bytes = blk;
   p.wstage_bytes = palign_up(L->gran_bytes > CQT_CHER_BYTES ? L->gran_bytes : CQT_CHER_BYTES, 128);
   int off = 0;
-  p.off_bar = off;   off = palign_up(off + (2 * SW + 2 * SB + 2 * NA + 2 * ND) * 8, 128);
+  p.off_bar = off;   off = palign_up(off + (2 * SW + 2 * 4 + 2 * NA + 4) * 8, 128);
   p.off_wring = off; off = palign_up(off + SW * p.wstage_bytes, 128);
-  p.off_bring = off; off = palign_up(off + SB * B_GRAN_BYTES, 128);
-  const int smem = off;
-  if (smem > di.max_smem) return CQ_ERR_TOO_LARGE;
+  p.off_bring = off;
+  p.sb = (di.max_smem - off) / b_gran_bytes(NT);
+  if (p.sb > 4) p.sb = 4;
+  if (p.sb < 2) return CQ_ERR_TOO_LARGE;
+  const int smem = off + p.sb * b_gran_bytes(NT);
   int grid = di.sms;
   if ((uint32_t)grid > p.n_units) grid = (int)p.n_units;
 
-  PKernelFn fn = ppick(L->bits, L->sets);
+  PKernelFn fn = shape == 1 ? ppick<256, 1>(L->bits, L->sets)
+                            : (shape == 2 ? ppick<128, 2>(L->bits, L->sets) : ppick<128, 1>(L->bits, L->sets));
   CQ_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
