@@ -364,6 +364,13 @@ def run_ours(args):
     if args.timeline and rank == 0:
         phase_timeline(torch, lib, _cabi, layers, ncopies, x, y, n_local, scratch, status, dev)
 
+    # the other half of the path, same layer: the 2048-token prefill GEMM (single-GPU runs only)
+    prefill = None
+    if world == 1 and not args.no_cpu:
+        del layers, blobs, refs
+        torch.cuda.empty_cache()
+        prefill = prefill_measure(torch, dist, dev, world, rank, local, 60, 5)
+
     if rank == 0:
         peak, peak_kind = measured_peak()
         achieved = alg_local / (kern_ms * 1e-3) / 1e9
@@ -384,6 +391,9 @@ def run_ours(args):
             "e2e": e2e, "gpu_launches": args.steps * world, "clocks": clocks,
         }
         line["cpu_baseline"] = cpu_baseline() if world == 1 and not args.no_cpu else None
+        if prefill is not None:
+            line["prefill"] = {k: prefill[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "roofline", "e2e")}
+            line["prefill"]["workload"] = prefill["config"]["workload"]
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -414,6 +424,14 @@ def run_prefill(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    line = prefill_measure(torch, dist, dev, world, rank, local, args.steps, args.warmup)
+    if rank == 0:
+        return line
+    return None
+
+
+def prefill_measure(torch, dist, dev, world, rank, local, steps_arg, warmup_arg):
+    """Times the prefill GEMM (and its end-to-end leg) and returns the JSON line as a dict (rank 0)."""
     import cherryq_b200
     from cherryq_b200 import _cabi
     qc = cherryq_b200.load_quant_cuda()
@@ -455,9 +473,9 @@ def run_prefill(args):
         if world > 1:
             dist.all_gather_into_tensor(y_all, y)
 
-    steps = min(args.steps, 200)
+    steps = min(steps_arg, 200)
     with torch.cuda.stream(stream):
-        for i in range(max(args.warmup, 3)):
+        for i in range(max(warmup_arg, 3)):
             launch(i)
         stream.synchronize()
         if world > 1:
@@ -520,7 +538,7 @@ def run_prefill(args):
         achieved = flops / world / (ms_step * 1e-3) / 1e12
         line = {
             "metric": "prefill_dense_TFLOPs", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "warmup": max(warmup_arg, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"llama7b_gate_proj_4096x11008_4bit_g128_cherry1/256_prefill{M}", "bits": BITS,
                        "group": GROUP, "K": K_IN, "N": N_OUT, "tokens": M,
@@ -538,9 +556,8 @@ def run_prefill(args):
                     "path": "quant_cuda.vecquant4matmul_cherryq with pinned host x / y per rank"},
             "gpu_launches": 2 * steps * world, "clocks": clocks, "cpu_baseline": None,
         }
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+        return line
+    return None
 
 
 def main():
