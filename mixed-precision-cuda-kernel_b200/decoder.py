@@ -1,0 +1,227 @@
+"""Minimal LLaMA-architecture decode harness around the CherryQ quantized linear.
+
+The reference evaluates its kernels inside a vendored Hugging Face LLaMA
+(llama/modeling_llama_quant.py:724-785 decoder layer, :251 MLP, :371-419 attention of the
+reference project; protocol of benchmark_perplexity.py:92-113).  This module keeps only what
+a decode benchmark needs: RMSNorm, rotary embeddings (HF "rotate half" convention), an fp16
+KV cache, SwiGLU, an unquantised fp16 lm_head, greedy sampling, and the seven quantized
+projections per layer as `QuantLinear` modules (q, k, v, o, gate, up, down - separate, as in
+the reference, each with its own cherry columns).  Weights are random (no checkpoint can be
+loaded offline): dense ~ N(0, 0.02), cherry columns ~ N(0, 0.2), packed on the GPU layer by
+layer so that the fp16 model never exists in memory.
+
+One decode step (embedding lookup -> layers -> logits -> argmax -> cache / position update)
+touches only device tensors, so it is captured once in a CUDA graph and replayed.
+Attention uses torch's scaled_dot_product_attention over the whole cache with a boolean mask
+(static shapes for the graph); it is plumbing here, not the measured path.
+
+`dense=True` builds the parity twin: the same packed buffers, every projection computed as
+F.linear(x, unpack()) the way the reference's dense mode does (llama/qlinear.py:183-195).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from types import SimpleNamespace
+
+import torch
+import torch.nn.functional as F
+
+from .qlinear import QuantLinear
+
+
+@dataclass
+class DecoderConfig:
+    n_layers: int = 32
+    hidden: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 32
+    ffn: int = 11008
+    vocab: int = 32000
+    bits: int = 4
+    group: int = 128
+    cherry_fraction: float = 1 / 256
+    max_seq: int = 512
+    rope_theta: float = 10000.0
+    eps: float = 1e-5
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.n_heads
+
+
+LLAMA2_7B = DecoderConfig()
+LLAMA2_13B = DecoderConfig(n_layers=40, hidden=5120, n_heads=40, n_kv_heads=40, ffn=13824, bits=3)
+LLAMA2_70B = DecoderConfig(n_layers=80, hidden=8192, n_heads=64, n_kv_heads=8, ffn=28672, bits=3)
+
+
+def linear_algorithmic_bytes(k: int, n: int, bits: int, group: int, fraction: float, m: int = 1) -> int:
+    """Bytes one call of a quantized linear has to move (reference-format sizes)."""
+    c = math.ceil(k * fraction) // 8 * 8
+    kc = k - c
+    return kc // 8 * bits * n + math.ceil(kc / group) * n * 2 + c * n * 2 + c * 2 + m * k * 2 + m * n * 2
+
+
+class CherryDecoder:
+    PROJ = ("q", "k", "v", "o", "gate", "up", "down")
+
+    def __init__(self, cfg: DecoderConfig, device="cuda", seed: int = 0, dense: bool = False,
+                 release_reference_buffers: bool = False):
+        if not torch.cuda.is_available():
+            raise RuntimeError("CherryDecoder needs a CUDA device (there is no CPU path)")
+        self.cfg, self.dev, self.dense = cfg, torch.device(device), dense
+        g = torch.Generator(device=self.dev).manual_seed(seed)
+        hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+        shapes = {"q": (cfg.hidden, h * hd), "k": (cfg.hidden, kv * hd), "v": (cfg.hidden, kv * hd),
+                  "o": (h * hd, cfg.hidden), "gate": (cfg.hidden, cfg.ffn), "up": (cfg.hidden, cfg.ffn),
+                  "down": (cfg.ffn, cfg.hidden)}
+        self.shapes = shapes
+        self.layers = []
+        for _ in range(cfg.n_layers):
+            lay = {name: self._make_linear(k, n, g) for name, (k, n) in shapes.items()}
+            lay["norm1"] = torch.ones(cfg.hidden, dtype=torch.float16, device=self.dev)
+            lay["norm2"] = torch.ones(cfg.hidden, dtype=torch.float16, device=self.dev)
+            if release_reference_buffers and not dense:
+                for name in self.PROJ:
+                    lay[name].release_reference_buffers()
+            self.layers.append(lay)
+        self.embed = (torch.randn(cfg.vocab, cfg.hidden, device=self.dev, generator=g) * 0.02).half()
+        self.lm_head = (torch.randn(cfg.vocab, cfg.hidden, device=self.dev, generator=g) * 0.02).half()
+        self.final_norm = torch.ones(cfg.hidden, dtype=torch.float16, device=self.dev)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=self.dev, dtype=torch.float32) / hd))
+        ang = torch.outer(torch.arange(cfg.max_seq, device=self.dev, dtype=torch.float32), inv)
+        self.cos, self.sin = ang.cos(), ang.sin()                      # (max_seq, hd / 2)
+        self.k_cache = torch.zeros(cfg.n_layers, cfg.max_seq, kv, hd, dtype=torch.float16, device=self.dev)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        # state of the decode loop, all on the device
+        self.tok = torch.zeros(1, dtype=torch.long, device=self.dev)
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.dev)
+        self.mask = torch.zeros(1, 1, 1, cfg.max_seq, dtype=torch.bool, device=self.dev)
+        self.graph = None
+
+    # ------------------------------------------------------------------ construction
+    def _make_linear(self, k: int, n: int, g: torch.Generator) -> QuantLinear:
+        cfg = self.cfg
+        w = (torch.randn(n, k, device=self.dev, generator=g) * 0.02).half()
+        c = math.ceil(k * cfg.cherry_fraction) // 8 * 8
+        idx = torch.randperm(k, device=self.dev, generator=g)[:c].to(torch.int32)
+        if c:
+            w[:, idx.long()] = (torch.randn(n, c, device=self.dev, generator=g) * 0.2).half()
+        ql = QuantLinear(cfg.bits, cfg.group, None, cfg.cherry_fraction, k, n, bias=False).to(self.dev)
+        ql.pack(SimpleNamespace(weight=w, bias=None, cherry_indices=idx, group_size=cfg.group))
+        if self.dense:
+            ql.dense_weight = ql.unpack()
+        return ql
+
+    def quantized_bytes_per_token(self) -> int:
+        cfg = self.cfg
+        per_layer = sum(linear_algorithmic_bytes(k, n, cfg.bits, cfg.group, cfg.cherry_fraction)
+                        for k, n in self.shapes.values())
+        return per_layer * cfg.n_layers
+
+    def lm_head_bytes(self) -> int:
+        return self.cfg.vocab * self.cfg.hidden * 2
+
+    # ------------------------------------------------------------------ building blocks
+    def _lin(self, ql: QuantLinear, x: torch.Tensor) -> torch.Tensor:
+        if self.dense:
+            return F.linear(x, ql.dense_weight)
+        return ql(x)
+
+    def _norm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.cfg.eps)).half() * w
+
+    def _rope(self, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """x (T, heads, hd), pos (T,) long: HF LLaMA convention (halves rotated against each other)."""
+        cos, sin = self.cos[pos][:, None, :], self.sin[pos][:, None, :]
+        x1, x2 = x[..., : x.shape[-1] // 2].float(), x[..., x.shape[-1] // 2:].float()
+        return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).half()
+
+    def _layer(self, li: int, x: torch.Tensor, pos: torch.Tensor, decode: bool) -> torch.Tensor:
+        cfg, lay = self.cfg, self.layers[li]
+        t, h, kv, hd = x.shape[0], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        xn = self._norm(x, lay["norm1"])
+        q = self._rope(self._lin(lay["q"], xn).view(t, h, hd), pos)
+        k = self._rope(self._lin(lay["k"], xn).view(t, kv, hd), pos)
+        v = self._lin(lay["v"], xn).view(t, kv, hd)
+        self.k_cache[li].index_copy_(0, pos, k)
+        self.v_cache[li].index_copy_(0, pos, v)
+        if decode:
+            kk = self.k_cache[li].transpose(0, 1)[None]                 # (1, kv, max_seq, hd)
+            vv = self.v_cache[li].transpose(0, 1)[None]
+            a = F.scaled_dot_product_attention(q.transpose(0, 1)[None], kk, vv, attn_mask=self.mask,
+                                               enable_gqa=(kv != h))
+        else:
+            a = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
+                                               v.transpose(0, 1)[None], is_causal=True, enable_gqa=(kv != h))
+        a = a[0].transpose(0, 1).reshape(t, h * hd)
+        x = x + self._lin(lay["o"], a)
+        xn = self._norm(x, lay["norm2"])
+        act = F.silu(self._lin(lay["gate"], xn)) * self._lin(lay["up"], xn)
+        return x + self._lin(lay["down"], act)
+
+    def _logits(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(self._norm(x, self.final_norm), self.lm_head)
+
+    # ------------------------------------------------------------------ prefill / decode
+    @torch.inference_mode()
+    def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Runs the prompt (T,) through the model, fills the cache, returns the last position's logits."""
+        t = tokens.shape[0]
+        assert 0 < t < self.cfg.max_seq
+        pos = torch.arange(t, device=self.dev)
+        x = self.embed[tokens]
+        for li in range(self.cfg.n_layers):
+            x = self._layer(li, x, pos, decode=False)
+        logits = self._logits(x[-1:])
+        self.mask.zero_()
+        self.mask[..., :t] = True
+        self.pos.fill_(t)
+        self.tok.copy_(logits.argmax(-1))
+        return logits
+
+    @torch.inference_mode()
+    def _step(self) -> torch.Tensor:
+        """One greedy decode step on the device-side state; returns the logits (1, vocab)."""
+        self.mask.index_fill_(3, self.pos, True)
+        x = self.embed[self.tok]
+        for li in range(self.cfg.n_layers):
+            x = self._layer(li, x, self.pos, decode=True)
+        logits = self._logits(x)
+        self.tok.copy_(logits.argmax(-1))
+        self.pos.add_(1)
+        return logits
+
+    @torch.inference_mode()
+    def capture(self):
+        """Captures one decode step in a CUDA graph (the state tensors are saved and restored)."""
+        saved = (self.tok.clone(), self.pos.clone(), self.mask.clone(), self.k_cache.clone(), self.v_cache.clone())
+        s = torch.cuda.Stream(device=self.dev)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):          # warm-up: first-use re-packs and allocations happen here
+                self._step()
+            s.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=s):
+                self.graph_logits = self._step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        for dst, src in zip((self.tok, self.pos, self.mask, self.k_cache, self.v_cache), saved):
+            dst.copy_(src)
+
+    @torch.inference_mode()
+    def generate(self, n_tokens: int, use_graph: bool = True) -> torch.Tensor:
+        """Greedy continuation after `prefill`: returns the n_tokens generated ids (the first one is
+        the prefill's argmax)."""
+        out = torch.empty(n_tokens, dtype=torch.long, device=self.dev)
+        if use_graph and self.graph is None:
+            self.capture()
+        for i in range(n_tokens):
+            out[i:i + 1].copy_(self.tok)
+            if use_graph:
+                self.graph.replay()
+            else:
+                self._step()
+        return out

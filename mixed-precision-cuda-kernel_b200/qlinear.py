@@ -132,8 +132,19 @@ class QuantLinear(nn.Module):
             if x2.dtype != torch.float16:
                 x2 = x2.half()
             x2 = x2.contiguous()
-            out = torch.empty(x2.shape[0], self.out_features, dtype=torch.float16, device=x2.device)
-            layer.matvec(x2, out, False)
+            if x2.shape[0] >= 32 and self._prepared_key != "released":
+                # prefill-sized batches: the drop-in op routes them to the tensor-core GEMM
+                qc = load_quant_cuda()
+                out = torch.zeros(x2.shape[0], self.out_features, dtype=torch.float16, device=x2.device)
+                if self.w_bits == 4:
+                    qc.vecquant4matmul_cherryq(x2, self.qweight, self.cherry_weight, self.cherry_indices,
+                                               self.scales, out, self.group_size)
+                else:
+                    qc.vecquant3matmul_cherryq(x2, self.qweight, self.cherry_weight, self.cherry_indices,
+                                               self.scales, out, self.group_size, True)
+            else:
+                out = torch.empty(x2.shape[0], self.out_features, dtype=torch.float16, device=x2.device)
+                layer.matvec(x2, out, False)
             out = out.reshape(out_shape).to(x.dtype)
         else:
             if not self.dequantized:
