@@ -136,6 +136,31 @@ int cq_layer_matvec_static(const cq_layer* layer, const void* x_f16, int ldx, vo
                            int M, int accumulate, uint32_t* status_word, cq_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Element-wise kernels of the decode harness around the quantized linear (fp16 in / out, fp32
+ * arithmetic).  In the reference they are PyTorch ops of its vendored LLaMA
+ * (llama/modeling_llama_quant.py: LlamaRMSNorm, apply_rotary_pos_emb, LlamaMLP.forward).
+ * ---------------------------------------------------------------------- */
+/* h = x (+ residual); y = h * rsqrt(mean(h^2) + eps) * weight; h is stored to h_out when not NULL. */
+int cq_rmsnorm(const void* x_f16, const void* residual_f16, const void* weight_f16, void* y_f16,
+               void* h_out_f16, int rows, int hidden, float eps, cq_stream_t stream);
+/* Rotary embedding ("rotate half" convention) of q (T, H, D) and k (T, KV, D) in place at
+ * positions[t] (device int64), tables (max_seq, D/2) fp32; k and v rows are written to the caches
+ * (max_seq, KV, D) at the same positions. */
+int cq_rope_cache(void* q_f16, void* k_f16, const void* v_f16, const float* cos_table,
+                  const float* sin_table, const long long* positions, void* k_cache_f16,
+                  void* v_cache_f16, int T, int n_heads, int n_kv_heads, int head_dim,
+                  cq_stream_t stream);
+/* Single-query attention over the caches (max_seq, KV, D): out (H, D) = softmax(q . K^T * scale) . V
+ * over positions 0..position[0] (device int64), grouped-query heads allowed; head_dim divides 256,
+ * max_seq <= 8192 (the reference calls PyTorch's attention, llama/modeling_llama_quant.py:371-419). */
+int cq_attn_decode(const void* q_f16, const void* k_cache_f16, const void* v_cache_f16,
+                   const long long* position, void* out_f16, int n_heads, int n_kv_heads, int head_dim,
+                   int max_seq, float scale, cq_stream_t stream);
+/* out = silu(gate) * up, n elements. */
+int cq_silu_mul(const void* gate_f16, const void* up_f16, void* out_f16, long long n,
+                cq_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Tile-layout prepared layer: the format of the tcgen05 (UMMA + tensor memory) kernels.
  * 128-row tiles; a granule is 128 rows x 128 compact columns; cherry columns travel in the same
  * stream as fp16 items of 16 columns.  Same role as cq_layer above, different kernel family.

@@ -14,6 +14,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
+#include <cmath>
 
 #include <map>
 #include <mutex>
@@ -253,6 +254,84 @@ bool device_timed_out(int device_index) {
 
 }  // namespace
 
+// ---- element-wise kernels of the decode harness
+std::vector<torch::Tensor> rmsnorm(torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor weight,
+                                   double eps, bool return_sum) {
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(x));
+  check_tensor(x, "x", torch::kFloat16, x);
+  check_tensor(weight, "weight", torch::kFloat16, x);
+  TORCH_CHECK(x.dim() == 2 && weight.numel() == x.size(1), "x must be (rows, hidden) and weight (hidden,)");
+  const void* res = nullptr;
+  if (residual.has_value()) {
+    check_tensor(*residual, "residual", torch::kFloat16, x);
+    TORCH_CHECK(residual->sizes() == x.sizes(), "residual must have the shape of x");
+    res = residual->data_ptr();
+  }
+  auto y = torch::empty_like(x);
+  torch::Tensor h;
+  if (return_sum) h = torch::empty_like(x);
+  check_status(cq_rmsnorm(x.data_ptr(), res, weight.data_ptr(), y.data_ptr(), return_sum ? h.data_ptr() : nullptr,
+                          (int)x.size(0), (int)x.size(1), (float)eps, current_stream()),
+               "rmsnorm");
+  if (return_sum) return {y, h};
+  return {y};
+}
+
+void rope_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor cos_table, torch::Tensor sin_table,
+                torch::Tensor positions, torch::Tensor k_cache, torch::Tensor v_cache) {
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(q));
+  check_tensor(q, "q", torch::kFloat16, q);
+  check_tensor(k, "k", torch::kFloat16, q);
+  check_tensor(v, "v", torch::kFloat16, q);
+  check_tensor(cos_table, "cos", torch::kFloat32, q);
+  check_tensor(sin_table, "sin", torch::kFloat32, q);
+  check_tensor(positions, "positions", torch::kInt64, q);
+  check_tensor(k_cache, "k_cache", torch::kFloat16, q);
+  check_tensor(v_cache, "v_cache", torch::kFloat16, q);
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.sizes() == k.sizes() && q.size(0) == k.size(0) && q.size(2) == k.size(2),
+              "q must be (T, H, D), k and v (T, KV, D)");
+  const int T = (int)q.size(0), H = (int)q.size(1), KV = (int)k.size(1), D = (int)q.size(2);
+  TORCH_CHECK(positions.numel() == T, "positions must have T entries");
+  TORCH_CHECK(cos_table.dim() == 2 && cos_table.size(1) == D / 2 && sin_table.sizes() == cos_table.sizes(),
+              "cos / sin tables must be (max_seq, D / 2)");
+  TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(1) == KV && k_cache.size(2) == D && v_cache.sizes() == k_cache.sizes() &&
+                  k_cache.size(0) <= cos_table.size(0),
+              "caches must be (max_seq, KV, D) with max_seq within the rotary tables");
+  check_status(cq_rope_cache(q.data_ptr(), k.data_ptr(), v.data_ptr(), cos_table.data_ptr<float>(),
+                             sin_table.data_ptr<float>(), (const long long*)positions.data_ptr(), k_cache.data_ptr(),
+                             v_cache.data_ptr(), T, H, KV, D, current_stream()),
+               "rope_cache");
+}
+
+torch::Tensor silu_mul(torch::Tensor gate, torch::Tensor up) {
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(gate));
+  check_tensor(gate, "gate", torch::kFloat16, gate);
+  check_tensor(up, "up", torch::kFloat16, gate);
+  TORCH_CHECK(gate.sizes() == up.sizes(), "gate and up must have the same shape");
+  auto out = torch::empty_like(gate);
+  check_status(cq_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), (long long)gate.numel(), current_stream()),
+               "silu_mul");
+  return out;
+}
+
+
+torch::Tensor attn_decode(torch::Tensor q, torch::Tensor k_cache, torch::Tensor v_cache, torch::Tensor position) {
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(q));
+  check_tensor(q, "q", torch::kFloat16, q);
+  check_tensor(k_cache, "k_cache", torch::kFloat16, q);
+  check_tensor(v_cache, "v_cache", torch::kFloat16, q);
+  check_tensor(position, "position", torch::kInt64, q);
+  TORCH_CHECK(q.dim() == 3 && q.size(0) == 1, "q must be (1, H, D)");
+  TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(2) == q.size(2) && v_cache.sizes() == k_cache.sizes(),
+              "caches must be (max_seq, KV, D)");
+  auto out = torch::empty_like(q);
+  check_status(cq_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), (const long long*)position.data_ptr(),
+                              out.data_ptr(), (int)q.size(1), (int)k_cache.size(1), (int)q.size(2), (int)k_cache.size(0),
+                              1.0f / std::sqrt((float)q.size(2)), current_stream()),
+               "attn_decode");
+  return out;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("vecquant3matmul_cherryq", &vecquant3matmul_cherryq, "a 3-bit version");
   m.def("vecquant4matmul_cherryq", &vecquant4matmul_cherryq, "a 4-bit version");
@@ -267,6 +346,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     cq_cache_stats(&n, &b);
     return std::make_pair(n, b);
   });
+  m.def("rmsnorm", &rmsnorm, "RMSNorm with optional residual add");
+  m.def("rope_cache", &rope_cache, "rotary embedding in place + KV cache write");
+  m.def("silu_mul", &silu_mul, "silu(gate) * up");
+  m.def("attn_decode", &attn_decode, "single-query attention over the KV cache");
   m.def("poll", []() { check_status(cq_poll(current_stream()), "poll"); });
   m.def("device_timed_out", &device_timed_out);
   m.def("abi_version", &cq_abi_version);

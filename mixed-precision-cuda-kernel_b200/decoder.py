@@ -3,8 +3,9 @@
 The reference evaluates its kernels inside a vendored Hugging Face LLaMA
 (llama/modeling_llama_quant.py:724-785 decoder layer, :251 MLP, :371-419 attention of the
 reference project; protocol of benchmark_perplexity.py:92-113).  This module keeps only what
-a decode benchmark needs: RMSNorm, rotary embeddings (HF "rotate half" convention), an fp16
-KV cache, SwiGLU, an unquantised fp16 lm_head, greedy sampling, and the seven quantized
+a decode benchmark needs: RMSNorm fused with the residual add, rotary embeddings (HF "rotate
+half" convention) fused with the KV-cache write, SwiGLU (three small CUDA kernels of the
+library), an fp16 KV cache, an unquantised fp16 lm_head, greedy sampling, and the seven quantized
 projections per layer as `QuantLinear` modules (q, k, v, o, gate, up, down - separate, as in
 the reference, each with its own cherry columns).  Weights are random (no checkpoint can be
 loaded offline): dense ~ N(0, 0.02), cherry columns ~ N(0, 0.2), packed on the GPU layer by
@@ -12,8 +13,9 @@ layer so that the fp16 model never exists in memory.
 
 One decode step (embedding lookup -> layers -> logits -> argmax -> cache / position update)
 touches only device tensors, so it is captured once in a CUDA graph and replayed.
-Attention uses torch's scaled_dot_product_attention over the whole cache with a boolean mask
-(static shapes for the graph); it is plumbing here, not the measured path.
+Decode attention is a single-query kernel of the library that reads the current position on the
+device (so the captured graph serves every step); prefill attention is torch's
+scaled_dot_product_attention.  Both are plumbing here, not the measured path.
 
 `dense=True` builds the parity twin: the same packed buffers, every projection computed as
 F.linear(x, unpack()) the way the reference's dense mode does (llama/qlinear.py:183-195).
@@ -27,6 +29,7 @@ from types import SimpleNamespace
 import torch
 import torch.nn.functional as F
 
+from . import load_quant_cuda
 from .qlinear import QuantLinear
 
 
@@ -70,6 +73,7 @@ class CherryDecoder:
         if not torch.cuda.is_available():
             raise RuntimeError("CherryDecoder needs a CUDA device (there is no CPU path)")
         self.cfg, self.dev, self.dense = cfg, torch.device(device), dense
+        self.qc = load_quant_cuda()
         g = torch.Generator(device=self.dev).manual_seed(seed)
         hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
         shapes = {"q": (cfg.hidden, h * hd), "k": (cfg.hidden, kv * hd), "v": (cfg.hidden, kv * hd),
@@ -96,7 +100,6 @@ class CherryDecoder:
         # state of the decode loop, all on the device
         self.tok = torch.zeros(1, dtype=torch.long, device=self.dev)
         self.pos = torch.zeros(1, dtype=torch.long, device=self.dev)
-        self.mask = torch.zeros(1, 1, 1, cfg.max_seq, dtype=torch.bool, device=self.dev)
         self.graph = None
 
     # ------------------------------------------------------------------ construction
@@ -128,41 +131,35 @@ class CherryDecoder:
             return F.linear(x, ql.dense_weight)
         return ql(x)
 
-    def _norm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.cfg.eps)).half() * w
+    def _norm(self, h: torch.Tensor, delta, w: torch.Tensor):
+        """(rmsnorm(h + delta) * w, h + delta): the residual add rides in the norm kernel."""
+        if delta is None:
+            return self.qc.rmsnorm(h, None, w, self.cfg.eps, False)[0], h
+        y, hs = self.qc.rmsnorm(h, delta, w, self.cfg.eps, True)
+        return y, hs
 
-    def _rope(self, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
-        """x (T, heads, hd), pos (T,) long: HF LLaMA convention (halves rotated against each other)."""
-        cos, sin = self.cos[pos][:, None, :], self.sin[pos][:, None, :]
-        x1, x2 = x[..., : x.shape[-1] // 2].float(), x[..., x.shape[-1] // 2:].float()
-        return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).half()
-
-    def _layer(self, li: int, x: torch.Tensor, pos: torch.Tensor, decode: bool) -> torch.Tensor:
+    def _layer(self, li: int, h: torch.Tensor, delta, pos: torch.Tensor, decode: bool):
+        """One decoder layer on the residual stream h with the previous layer's MLP output `delta`
+        still to be added; returns (h, delta) in the same form."""
         cfg, lay = self.cfg, self.layers[li]
-        t, h, kv, hd = x.shape[0], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
-        xn = self._norm(x, lay["norm1"])
-        q = self._rope(self._lin(lay["q"], xn).view(t, h, hd), pos)
-        k = self._rope(self._lin(lay["k"], xn).view(t, kv, hd), pos)
+        t, nh, kv, hd = h.shape[0], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        xn, h = self._norm(h, delta, lay["norm1"])
+        q = self._lin(lay["q"], xn).view(t, nh, hd)
+        k = self._lin(lay["k"], xn).view(t, kv, hd)
         v = self._lin(lay["v"], xn).view(t, kv, hd)
-        self.k_cache[li].index_copy_(0, pos, k)
-        self.v_cache[li].index_copy_(0, pos, v)
+        self.qc.rope_cache(q, k, v, self.cos, self.sin, pos, self.k_cache[li], self.v_cache[li])
         if decode:
-            kk = self.k_cache[li].transpose(0, 1)[None]                 # (1, kv, max_seq, hd)
-            vv = self.v_cache[li].transpose(0, 1)[None]
-            a = F.scaled_dot_product_attention(q.transpose(0, 1)[None], kk, vv, attn_mask=self.mask,
-                                               enable_gqa=(kv != h))
+            a = self.qc.attn_decode(q, self.k_cache[li], self.v_cache[li], pos).view(t, nh * hd)
         else:
             a = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
-                                               v.transpose(0, 1)[None], is_causal=True, enable_gqa=(kv != h))
-        a = a[0].transpose(0, 1).reshape(t, h * hd)
-        x = x + self._lin(lay["o"], a)
-        xn = self._norm(x, lay["norm2"])
-        act = F.silu(self._lin(lay["gate"], xn)) * self._lin(lay["up"], xn)
-        return x + self._lin(lay["down"], act)
+                                               v.transpose(0, 1)[None], is_causal=True, enable_gqa=(kv != nh))
+            a = a[0].transpose(0, 1).reshape(t, nh * hd)
+        xn, h = self._norm(h, self._lin(lay["o"], a), lay["norm2"])
+        act = self.qc.silu_mul(self._lin(lay["gate"], xn), self._lin(lay["up"], xn))
+        return h, self._lin(lay["down"], act)
 
-    def _logits(self, x: torch.Tensor) -> torch.Tensor:
-        return F.linear(self._norm(x, self.final_norm), self.lm_head)
+    def _logits(self, h: torch.Tensor, delta) -> torch.Tensor:
+        return F.linear(self._norm(h, delta, self.final_norm)[0], self.lm_head)
 
     # ------------------------------------------------------------------ prefill / decode
     @torch.inference_mode()
@@ -171,12 +168,10 @@ class CherryDecoder:
         t = tokens.shape[0]
         assert 0 < t < self.cfg.max_seq
         pos = torch.arange(t, device=self.dev)
-        x = self.embed[tokens]
+        h, delta = self.embed[tokens], None
         for li in range(self.cfg.n_layers):
-            x = self._layer(li, x, pos, decode=False)
-        logits = self._logits(x[-1:])
-        self.mask.zero_()
-        self.mask[..., :t] = True
+            h, delta = self._layer(li, h, delta, pos, decode=False)
+        logits = self._logits(h[-1:].contiguous(), delta[-1:].contiguous())
         self.pos.fill_(t)
         self.tok.copy_(logits.argmax(-1))
         return logits
@@ -184,11 +179,10 @@ class CherryDecoder:
     @torch.inference_mode()
     def _step(self) -> torch.Tensor:
         """One greedy decode step on the device-side state; returns the logits (1, vocab)."""
-        self.mask.index_fill_(3, self.pos, True)
-        x = self.embed[self.tok]
+        h, delta = self.embed[self.tok], None
         for li in range(self.cfg.n_layers):
-            x = self._layer(li, x, self.pos, decode=True)
-        logits = self._logits(x)
+            h, delta = self._layer(li, h, delta, self.pos, decode=True)
+        logits = self._logits(h, delta)
         self.tok.copy_(logits.argmax(-1))
         self.pos.add_(1)
         return logits
@@ -196,7 +190,7 @@ class CherryDecoder:
     @torch.inference_mode()
     def capture(self):
         """Captures one decode step in a CUDA graph (the state tensors are saved and restored)."""
-        saved = (self.tok.clone(), self.pos.clone(), self.mask.clone(), self.k_cache.clone(), self.v_cache.clone())
+        saved = (self.tok.clone(), self.pos.clone(), self.k_cache.clone(), self.v_cache.clone())
         s = torch.cuda.Stream(device=self.dev)
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -208,7 +202,7 @@ class CherryDecoder:
                 self.graph_logits = self._step()
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
-        for dst, src in zip((self.tok, self.pos, self.mask, self.k_cache, self.v_cache), saved):
+        for dst, src in zip((self.tok, self.pos, self.k_cache, self.v_cache), saved):
             dst.copy_(src)
 
     @torch.inference_mode()

@@ -59,3 +59,63 @@ def test_bytes_accounting(dec):
     # per-call bytes of the 7B projections incl. batch-1 activations: 4 x 8,765,472 + 2 x 23,543,328 + 23,524,944
     assert per_layer == 4 * 8_765_472 + 2 * 23_543_328 + 23_524_944
     assert abs(per_layer * cfg.n_layers - 3.38e9) < 5e6          # ~3.38 GB of quantized weights per decoded token
+
+
+def test_fused_elementwise_ops_match_torch(dec):
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(5, 512, device="cuda", generator=g).half()
+    r = torch.randn(5, 512, device="cuda", generator=g).half()
+    w = (1 + 0.1 * torch.randn(512, device="cuda", generator=g)).half()
+    y, h = qc.rmsnorm(x, r, w, 1e-5, True)
+    hs = (x + r)
+    ref = (hs.float() * torch.rsqrt(hs.float().pow(2).mean(-1, keepdim=True) + 1e-5)).half() * w
+    assert torch.equal(h, hs)
+    assert float((y.float() - ref.float()).abs().max()) <= 2e-3 * float(ref.float().abs().max())
+    y0 = qc.rmsnorm(x, None, w, 1e-5, False)[0]
+    ref0 = (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5)).half() * w
+    assert float((y0.float() - ref0.float()).abs().max()) <= 2e-3 * float(ref0.float().abs().max())
+
+    a, b = torch.randn(3, 1000, device="cuda", generator=g).half(), torch.randn(3, 1000, device="cuda", generator=g).half()
+    assert float((qc.silu_mul(a, b).float() - (torch.nn.functional.silu(a) * b).float()).abs().max()) <= 4e-3
+
+    T, H, KV, D, S = 6, 4, 2, 64, 32
+    q = torch.randn(T, H, D, device="cuda", generator=g).half()
+    k = torch.randn(T, KV, D, device="cuda", generator=g).half()
+    v = torch.randn(T, KV, D, device="cuda", generator=g).half()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda", dtype=torch.float32) / D))
+    ang = torch.outer(torch.arange(S, device="cuda", dtype=torch.float32), inv)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([3, 4, 5, 9, 10, 31], device="cuda")
+
+    def rope(t):
+        c, s = cos[pos][:, None, :], sin[pos][:, None, :]
+        t1, t2 = t[..., : D // 2].float(), t[..., D // 2:].float()
+        return torch.cat((t1 * c - t2 * s, t2 * c + t1 * s), -1).half()
+    rq, rk = rope(q), rope(k)
+    kc = torch.zeros(S, KV, D, dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    qc.rope_cache(q, k, v, cos, sin, pos, kc, vc)
+    assert float((q.float() - rq.float()).abs().max()) <= 2e-3 and float((k.float() - rk.float()).abs().max()) <= 2e-3
+    assert torch.equal(kc[pos], k) and torch.equal(vc[pos], v)
+    untouched = torch.ones(S, dtype=torch.bool, device="cuda")
+    untouched[pos] = False
+    assert not bool(kc[untouched].any()) and not bool(vc[untouched].any())
+
+
+@pytest.mark.parametrize("H,KV,D,S,P", [(8, 8, 128, 512, 300), (8, 2, 64, 128, 0), (4, 4, 128, 2048, 2047)])
+def test_attention_decode_matches_torch(dec, H, KV, D, S, P):
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    g = torch.Generator(device="cuda").manual_seed(H + P)
+    q = torch.randn(1, H, D, device="cuda", generator=g).half()
+    kc = torch.randn(S, KV, D, device="cuda", generator=g).half()
+    vc = torch.randn(S, KV, D, device="cuda", generator=g).half()
+    pos = torch.tensor([P], device="cuda")
+    out = qc.attn_decode(q, kc, vc, pos)
+    k = kc[:P + 1].float().repeat_interleave(H // KV, dim=1)          # (P+1, H, D)
+    v = vc[:P + 1].float().repeat_interleave(H // KV, dim=1)
+    w = torch.softmax(torch.einsum("hd,phd->hp", q[0].float(), k) / D ** 0.5, dim=-1)
+    ref = torch.einsum("hp,phd->hd", w, v)
+    assert float((out[0].float() - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))
