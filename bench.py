@@ -571,7 +571,8 @@ def run_model(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     from cherryq_b200 import decoder as D
-    cfg = D.DecoderConfig(**{**D.LLAMA2_7B.__dict__, "max_seq": 512})
+    base = {"7b": D.LLAMA2_7B, "13b": D.LLAMA2_13B, "70b": D.LLAMA2_70B}[args.model]
+    cfg = D.DecoderConfig(**{**base.__dict__, "max_seq": 512})
     prompt_len, gen = 128, 256
     t_build = time.time()
     model = D.CherryDecoder(cfg, device=dev, seed=1234)
@@ -630,10 +631,13 @@ def run_model(args):
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": gen, "warmup": 8,
         "ms_per_step": ms_tok, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": "llama2_7b_arch_4bit_g128_cherry1/256_prompt128_greedy256_batch1", "layers": cfg.n_layers,
+        "config": {"workload": f"llama2_{args.model}_arch_{cfg.bits}bit_g128_cherry1/256_prompt128_greedy256_batch1",
+                   "layers": cfg.n_layers, "kv_heads": cfg.n_kv_heads,
                    "hidden": cfg.hidden, "ffn": cfg.ffn, "vocab": cfg.vocab, "bits": cfg.bits,
-                   "l2_defeat": "3.4 GB of quantized weights + 262 MB lm_head per token, far larger than L2",
-                   "launch": "one CUDA graph per decode step (224 quantized projections, attention, norms, lm_head, argmax)"},
+                   "l2_defeat": f"{qbytes / 1e9:.1f} GB of quantized weights + {hbytes / 1e6:.0f} MB lm_head per token, "
+                                "far larger than L2",
+                   "launch": f"one CUDA graph per decode step ({cfg.n_layers * 7} quantized projections, attention, "
+                             "norms, lm_head, argmax)"},
         "roofline": {"bound": "hbm", "achieved": (qbytes + hbytes) / (ms_tok * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": (qbytes + hbytes) / (ms_tok * 1e-3) / 1e9 / peak, "traffic": None,
                      "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
@@ -660,6 +664,8 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model"],
                     help="decode: batch-1 matvec (the headline line); prefill: 2048-token GEMM of the same layer; "
                          "model: LLaMA-2-7B-architecture greedy decode, tokens/s")
+    ap.add_argument("--model", default="7b", choices=["7b", "13b", "70b"],
+                    help="architecture of the model workload: LLaMA-2 7B (4-bit), 13B (3-bit) or 70B (3-bit, GQA)")
     ap.add_argument("--timeline", action="store_true",
                     help="also print the kernel's per-phase device timeline to stderr (after the timed region)")
     args = ap.parse_args()

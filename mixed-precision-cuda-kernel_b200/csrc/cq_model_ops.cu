@@ -9,18 +9,39 @@
 namespace {
 
 // One CTA per row: h = x (+ residual); y = h * rsqrt(mean(h^2) + eps) * w; optionally h is stored.
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ residual,
-                                                      const __half* __restrict__ w, __half* __restrict__ y,
-                                                      __half* __restrict__ h_out, int hidden, float eps) {
-  __shared__ float red[8];
+// A thread keeps its (up to 16) values in registers between the two passes; 16-byte accesses.
+// hidden is a multiple of 8 and at most 16 * 1024.
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ residual,
+                                                       const __half* __restrict__ w, __half* __restrict__ y,
+                                                       __half* __restrict__ h_out, int hidden, float eps) {
+  __shared__ float red[32];
   const size_t row = blockIdx.x;
-  const __half* xr = x + row * hidden;
-  const __half* rr = residual ? residual + row * hidden : nullptr;
+  const int nvec = hidden >> 3;                       // 16-byte vectors per row
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * hidden);
+  const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + row * hidden) : nullptr;
+  uint4 hv[2];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = __half2float(xr[i]);
-    if (rr) v = __half2float(__float2half(v + __half2float(rr[i])));   // the sum is an fp16 tensor
-    ss += v * v;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int i = threadIdx.x + c * blockDim.x;
+    hv[c] = make_uint4(0, 0, 0, 0);
+    if (i < nvec) {
+      uint4 v = xr[i];
+      if (rr) {
+        const uint4 r = rr[i];
+        __half2* a = reinterpret_cast<__half2*>(&v);
+        const __half2* b = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a[e] = __hadd2(a[e], b[e]);            // the sum is an fp16 tensor
+      }
+      hv[c] = v;
+      const __half2* a = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(a[e]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
   }
   for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -28,11 +49,24 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __half* __restrict__
   float tot = 0.f;
   for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
   const float inv = rsqrtf(tot / (float)hidden + eps);
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = __half2float(xr[i]);
-    if (rr) v = __half2float(__float2half(v + __half2float(rr[i])));
-    if (h_out) h_out[row * hidden + i] = __float2half(v);
-    y[row * hidden + i] = __hmul(__float2half(v * inv), w[i]);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < nvec) {
+      if (h_out) reinterpret_cast<uint4*>(h_out + row * hidden)[i] = hv[c];
+      const uint4 wv = wr[i];
+      uint4 o;
+      const __half2* a = reinterpret_cast<const __half2*>(&hv[c]);
+      const __half2* ww = reinterpret_cast<const __half2*>(&wv);
+      __half2* oo = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(a[e]);
+        oo[e] = __hmul2(__floats2half2_rn(f.x * inv, f.y * inv), ww[e]);
+      }
+      reinterpret_cast<uint4*>(y + row * hidden)[i] = o;
+    }
   }
 }
 
@@ -97,32 +131,34 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
   const int n_pos = (int)pos[0] + 1;
   float* red = sc + n_pos;
   const __half* qh = q + (size_t)head * D;
-  // scores: a warp per position (two positions in flight per warp), lanes over the head dimension
+  // scores: a warp per position, four positions in flight per warp, lanes over the head dimension
   float lmax = -INFINITY;
-  for (int p0 = warp; p0 < n_pos; p0 += 2 * ATT_WARPS) {
-    const int p1 = p0 + ATT_WARPS;
-    const bool two = p1 < n_pos;
-    const __half* k0 = k_cache + ((size_t)p0 * KV + kvh) * D;
-    const __half* k1 = k_cache + ((size_t)(two ? p1 : p0) * KV + kvh) * D;
-    float a0 = 0.f, a1 = 0.f;
+  for (int p0 = warp; p0 < n_pos; p0 += 4 * ATT_WARPS) {
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    const __half* kr[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int p = p0 + u * ATT_WARPS;
+      kr[u] = k_cache + ((size_t)(p < n_pos ? p : p0) * KV + kvh) * D;
+    }
     for (int d = 2 * lane; d < D; d += 64) {
-      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(qh + d));
-      const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(k0 + d));
-      const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(k1 + d));
-      a0 += a.x * b0.x + a.y * b0.y;
-      a1 += a.x * b1.x + a.y * b1.y;
+      const float2 qv = __half22float2(*reinterpret_cast<const __half2*>(qh + d));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 kv2 = __half22float2(*reinterpret_cast<const __half2*>(kr[u] + d));
+        a[u] += qv.x * kv2.x + qv.y * kv2.y;
+      }
     }
-    for (int o = 16; o > 0; o >>= 1) {
-      a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-      a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      for (int o = 16; o > 0; o >>= 1) a[u] += __shfl_xor_sync(0xffffffffu, a[u], o);
+      a[u] *= scale;
+      const int p = p0 + u * ATT_WARPS;
+      if (p < n_pos) {
+        if (lane == 0) sc[p] = a[u];
+        lmax = fmaxf(lmax, a[u]);
+      }
     }
-    a0 *= scale;
-    a1 *= scale;
-    if (lane == 0) {
-      sc[p0] = a0;
-      if (two) sc[p1] = a1;
-    }
-    lmax = fmaxf(lmax, two ? fmaxf(a0, a1) : a0);
   }
   if (lane == 0) red[warp] = lmax;
   __syncthreads();
@@ -146,12 +182,22 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
   const int parts = ATT_THREADS / D;
   const int d = tid % D, part = tid / D;
   float acc0 = 0.f, acc1 = 0.f;
-  int p = part;
-  for (; p + parts < n_pos; p += 2 * parts) {
-    acc0 += sc[p] * __half2float(v_cache[((size_t)p * KV + kvh) * D + d]);
-    acc1 += sc[p + parts] * __half2float(v_cache[((size_t)(p + parts) * KV + kvh) * D + d]);
+  {
+    const __half* vb = v_cache + (size_t)kvh * D + d;
+    const size_t vstride = (size_t)KV * D;
+    int p = part;
+    for (; p + 7 * parts < n_pos; p += 8 * parts) {       // eight loads in flight
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __half2float(vb[(size_t)(p + u * parts) * vstride]);
+#pragma unroll
+      for (int u = 0; u < 8; u += 2) {
+        acc0 += sc[p + u * parts] * v[u];
+        acc1 += sc[p + (u + 1) * parts] * v[u + 1];
+      }
+    }
+    for (; p < n_pos; p += parts) acc0 += sc[p] * __half2float(vb[(size_t)p * vstride]);
   }
-  if (p < n_pos) acc0 += sc[p] * __half2float(v_cache[((size_t)p * KV + kvh) * D + d]);
   red[tid] = acc0 + acc1;
   __syncthreads();
   if (tid < D) {
@@ -172,9 +218,15 @@ int blocks_for(long long total, int threads, int cap) {
 
 extern "C" int cq_rmsnorm(const void* x, const void* residual, const void* weight, void* y, void* h_out, int rows,
                           int hidden, float eps, cq_stream_t stream) {
-  if (!x || !weight || !y || rows < 1 || hidden < 1) return CQ_ERR_BAD_ARG;
-  rmsnorm_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((const __half*)x, (const __half*)residual,
-                                                           (const __half*)weight, (__half*)y, (__half*)h_out, hidden, eps);
+  if (!x || !weight || !y || rows < 1 || hidden < 8) return CQ_ERR_BAD_ARG;
+  if ((hidden & 7) || hidden > 16 * 1024) return CQ_ERR_BAD_SHAPE;
+  if (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)y | (uintptr_t)residual | (uintptr_t)h_out) & 15) return CQ_ERR_BAD_ARG;
+  int threads = ((hidden >> 3) + 1) / 2;                 // two 16-byte vectors per thread
+  threads = (threads + 31) / 32 * 32;
+  if (threads > 1024) threads = 1024;
+  if (threads < 32) threads = 32;
+  rmsnorm_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>((const __half*)x, (const __half*)residual,
+                                                               (const __half*)weight, (__half*)y, (__half*)h_out, hidden, eps);
   CQ_CUDA_TRY(cudaGetLastError());
   return CQ_OK;
 }
