@@ -14,6 +14,9 @@ namespace {
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ residual,
                                                        const __half* __restrict__ w, __half* __restrict__ y,
                                                        __half* __restrict__ h_out, int hidden, float eps) {
+  // programmatic dependent launch: let the next kernel start its prologue, then wait for our inputs
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float red[32];
   const size_t row = blockIdx.x;
   const int nvec = hidden >> 3;                       // 16-byte vectors per row
@@ -76,6 +79,9 @@ __global__ void rope_cache_kernel(__half* __restrict__ q, __half* __restrict__ k
                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                   const long long* __restrict__ pos, __half* __restrict__ k_cache,
                                   __half* __restrict__ v_cache, int T, int H, int KV, int D) {
+  // programmatic dependent launch: let the next kernel start its prologue, then wait for our inputs
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int half = D / 2;
   const long long total = (long long)T * (H + 2 * KV) * half;
   for (long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x; id < total;
@@ -108,6 +114,9 @@ __global__ void rope_cache_kernel(__half* __restrict__ q, __half* __restrict__ k
 
 __global__ void silu_mul_kernel(const __half* __restrict__ gate, const __half* __restrict__ up,
                                 __half* __restrict__ out, long long n) {
+  // programmatic dependent launch: let the next kernel start its prologue, then wait for our inputs
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const float g = __half2float(gate[i]);
     const __half act = __float2half(g / (1.f + __expf(-g)));          // silu result is an fp16 tensor
@@ -125,6 +134,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
                                                                   const long long* __restrict__ pos,
                                                                   __half* __restrict__ out, int H, int KV, int D,
                                                                   float scale) {
+  // programmatic dependent launch: let the next kernel start its prologue, then wait for our inputs
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   extern __shared__ float sc[];              // [n_pos] scores, then [ATT_THREADS] reduction scratch
   const int head = blockIdx.x, kvh = head / (H / KV);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -214,6 +226,23 @@ int blocks_for(long long total, int threads, int cap) {
   return (int)b;
 }
 
+// All kernels here are launched with the programmatic-serialization attribute (they wait for their
+// inputs with griddepcontrol.wait), so that in a chain of small kernels the launch latencies overlap.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace
 
 extern "C" int cq_rmsnorm(const void* x, const void* residual, const void* weight, void* y, void* h_out, int rows,
@@ -225,9 +254,8 @@ extern "C" int cq_rmsnorm(const void* x, const void* residual, const void* weigh
   threads = (threads + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;
   if (threads < 32) threads = 32;
-  rmsnorm_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>((const __half*)x, (const __half*)residual,
-                                                               (const __half*)weight, (__half*)y, (__half*)h_out, hidden, eps);
-  CQ_CUDA_TRY(cudaGetLastError());
+  CQ_CUDA_TRY(launch_pdl(rmsnorm_kernel, dim3(rows), dim3(threads), 0, (cudaStream_t)stream, (const __half*)x,
+                         (const __half*)residual, (const __half*)weight, (__half*)y, (__half*)h_out, hidden, eps));
   return CQ_OK;
 }
 
@@ -237,18 +265,16 @@ extern "C" int cq_rope_cache(void* q, void* k, const void* v, const float* cos_t
   if (!q || !k || !v || !cos_table || !sin_table || !positions || !k_cache || !v_cache) return CQ_ERR_BAD_ARG;
   if (T < 1 || n_heads < 1 || n_kv_heads < 1 || head_dim < 2 || (head_dim & 1)) return CQ_ERR_BAD_ARG;
   const long long total = (long long)T * (n_heads + 2 * n_kv_heads) * (head_dim / 2);
-  rope_cache_kernel<<<blocks_for(total, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
-      (__half*)q, (__half*)k, (const __half*)v, cos_table, sin_table, positions, (__half*)k_cache, (__half*)v_cache, T,
-      n_heads, n_kv_heads, head_dim);
-  CQ_CUDA_TRY(cudaGetLastError());
+  CQ_CUDA_TRY(launch_pdl(rope_cache_kernel, dim3(blocks_for(total, 256, 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
+                         (__half*)q, (__half*)k, (const __half*)v, cos_table, sin_table, positions, (__half*)k_cache,
+                         (__half*)v_cache, T, n_heads, n_kv_heads, head_dim));
   return CQ_OK;
 }
 
 extern "C" int cq_silu_mul(const void* gate, const void* up, void* out, long long n, cq_stream_t stream) {
   if (!gate || !up || !out || n < 1) return CQ_ERR_BAD_ARG;
-  silu_mul_kernel<<<blocks_for(n, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>((const __half*)gate, (const __half*)up,
-                                                                                 (__half*)out, n);
-  CQ_CUDA_TRY(cudaGetLastError());
+  CQ_CUDA_TRY(launch_pdl(silu_mul_kernel, dim3(blocks_for(n, 256, 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
+                         (const __half*)gate, (const __half*)up, (__half*)out, n));
   return CQ_OK;
 }
 
@@ -260,9 +286,8 @@ extern "C" int cq_attn_decode(const void* q, const void* k_cache, const void* v_
       256 % head_dim || max_seq < 1 || max_seq > 8192)
     return CQ_ERR_BAD_SHAPE;
   const int smem = (max_seq + ATT_THREADS) * (int)sizeof(float);
-  attn_decode_kernel<<<n_heads, ATT_THREADS, smem, (cudaStream_t)stream>>>((const __half*)q, (const __half*)k_cache,
-                                                                   (const __half*)v_cache, position, (__half*)out,
-                                                                   n_heads, n_kv_heads, head_dim, scale);
-  CQ_CUDA_TRY(cudaGetLastError());
+  CQ_CUDA_TRY(launch_pdl(attn_decode_kernel, dim3(n_heads), dim3(ATT_THREADS), (size_t)smem, (cudaStream_t)stream,
+                         (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, position, (__half*)out, n_heads,
+                         n_kv_heads, head_dim, scale));
   return CQ_OK;
 }
