@@ -364,6 +364,32 @@ def run_ours(args):
     if args.timeline and rank == 0:
         phase_timeline(torch, lib, _cabi, layers, ncopies, x, y, n_local, scratch, status, dev)
 
+    # the reference project's own CUDA kernel on the same layer copies (built by oracle/build_ref.py;
+    # information only: batch 1, device-resident inputs, CUDA events)
+    ref_gpu = None
+    if world == 1 and rank == 0:
+        try:
+            from oracle import build_ref
+            rmod = build_ref.load()
+        except Exception:
+            rmod = None
+        if rmod is not None:
+            rsteps = 10 * ncopies
+            for i in range(ncopies):
+                qq, cc, ii, ss = refs[i]
+                rmod.vecquant4matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP)
+            torch.cuda.synchronize()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record()
+            for i in range(rsteps):
+                qq, cc, ii, ss = refs[i % ncopies]
+                rmod.vecquant4matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP)
+            r1.record()
+            torch.cuda.synchronize()
+            rms = r0.elapsed_time(r1) / rsteps
+            ref_gpu = {"kernel": "VecQuant4MatMulKernelCherryQBatchedHalf (reference csrc/quant_cuda_kernel.cu, unmodified, sm_100a)",
+                       "us_per_call": rms * 1e3, "GBps": alg / (rms * 1e-3) / 1e9, "steps": rsteps}
+
     # the other half of the path, same layer: the 2048-token prefill GEMM (single-GPU runs only)
     prefill = None
     if world == 1 and not args.no_cpu:
@@ -391,6 +417,9 @@ def run_ours(args):
             "e2e": e2e, "gpu_launches": args.steps * world, "clocks": clocks,
         }
         line["cpu_baseline"] = cpu_baseline() if world == 1 and not args.no_cpu else None
+        line["reference_gpu_kernel"] = ref_gpu
+        if ref_gpu is not None:
+            line["speedup_vs_reference_gpu_kernel"] = ref_gpu["us_per_call"] / (ms_step * 1e3)
         if prefill is not None:
             line["prefill"] = {k: prefill[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "roofline", "e2e")}
             line["prefill"]["workload"] = prefill["config"]["workload"]
