@@ -57,7 +57,7 @@ struct MatvecParams {
   uint32_t T;          // total granules
   int stages, nslot, max_cher;
   // shared-memory offsets
-  int off_ring, off_cher, off_zero, off_sched, off_xb, off_xq, off_xc, off_cidx, off_osh, off_slot, off_pf, off_bar;
+  int off_ring, off_cher, off_zero, off_sched, off_xb, off_xq, off_xc, off_slot, off_pf, off_bar;
   int xb_gran;         // bytes of quantised activations per granule: 2 planes x 2M columns x 64 B
   int xc_stride;       // halves per cherry-activation row (Cp + 8)
 };
@@ -304,17 +304,30 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
   }
 
   // ------------------------------------------------------------------ consumers
-  // Layer constants first (they do not depend on the previous kernel): the sorted cherry
-  // columns and, per octet of compact columns, how far its first and last column are shifted
-  // in the original row (see cq_common.cuh).
+  // Layer constants first (they do not depend on the previous kernel).  The index tables (sorted
+  // cherry columns; per octet of compact columns, how far its first and last column are shifted in
+  // the original row, see cq_common.cuh) are read straight from global memory into registers: the
+  // entries of a thread's first items are requested here, so that they are at hand when the
+  // dependency wait returns and the activation loads can be issued at once.
   __half* xc = reinterpret_cast<__half*>(smem + p.off_xc);
-  uint16_t* cidx_s = reinterpret_cast<uint16_t*>(smem + p.off_cidx);
-  uint32_t* osh = reinterpret_cast<uint32_t*>(smem + p.off_osh);
   const int noct = p.Kp >> 3;
-  for (int c = tid; c < p.Cp; c += NCONS) cidx_s[c] = p.cidx[c];
+  constexpr int XCU = 2;      // cherry activations a thread fetches ahead
+  constexpr int U = 2;        // octets of compact columns a thread stages per round
+  const int nitem = noct * p.M;
+  uint32_t sh_first[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int it = u * NCONS + tid;
+    sh_first[u] = it < nitem ? __ldg(p.osh + (p.M == 1 ? it : it % noct)) : 0xFFFFFFFFu;
+  }
+  uint32_t cher_col[XCU];
+#pragma unroll
+  for (int u = 0; u < XCU; ++u) {
+    const int idx = tid + u * NCONS;
+    cher_col[u] = idx < p.M * p.Cp ? (uint32_t)__ldg(p.cidx + idx % p.Cp) : (uint32_t)CQ_PAD_COL;
+  }
   // {step, offset terms} of activation rows that do not exist must read as zero
   for (int i = tid; i < (int)NG * 4 * MB * 4; i += NCONS) reinterpret_cast<float*>(smem + p.off_xq)[i] = 0.f;
-  for (int o = tid; o < noct; o += NCONS) osh[o] = p.osh[o];
   {
     // Schedule: for every position of the CTA's sequence, which granule of its sub-tile it is (low 10
     // bits) and which piece it belongs to.  Piece 0 is the tail of the range (possibly a cut
@@ -339,7 +352,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
     }
   }
   if (tid < 4) reinterpret_cast<uint32_t*>(smem + p.off_zero)[tid] = 0u;
-  bar_consumers<NCONS>();
+  bar_consumers<NCONS>();       // (the zero fill above must not overtake the staging stores below)
   if (tid == 0) stamp(p, 2);
 
   // Everything below may read what the previous kernel in the stream wrote.
@@ -348,24 +361,17 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
 
   // Activations of the cherry columns: issue the loads now, store them after the main gather,
   // so that both cost one trip to L2 together.
-  constexpr int XCU = 2;
   __half xcv[XCU];
 #pragma unroll
   for (int u = 0; u < XCU; ++u) {
     const int idx = tid + u * NCONS;
     xcv[u] = __float2half(0.f);
-    if (idx < p.M * p.Cp) {
-      const int m = idx / p.Cp, c = idx - m * p.Cp;
-      const uint32_t o = cidx_s[c];
-      if (o != CQ_PAD_COL) xcv[u] = __ldg(p.x + (size_t)m * p.ldx + o);
-    }
+    if (cher_col[u] != CQ_PAD_COL) xcv[u] = __ldg(p.x + (size_t)(idx / p.Cp) * p.ldx + cher_col[u]);
   }
   {
     // Compact columns, 8 at a time (zero past K').  The 16 octets of one granule of one row sit
     // in 16 neighbouring lanes: they agree on the granule's largest magnitude, quantise, and
     // add up the integers per group.
-    const int nitem = noct * p.M;
-    constexpr int U = 2;
     for (int base = 0; base < nitem; base += NCONS * U) {
       uint32_t v[U][4];
       int mrow[U], oct[U];
@@ -381,7 +387,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
           const int k0 = 8 * o;
           mrow[u] = m;
           oct[u] = o;
-          const uint32_t sh = osh[o];
+          const uint32_t sh = (base == 0) ? sh_first[u] : __ldg(p.osh + o);
           if (sh != 0xFFFFFFFFu) {
             const int lo0 = (int)(sh & 0xFFFFu), lo7 = (int)(sh >> 16);
             const __half* xr = p.x + (size_t)m * p.ldx;
@@ -403,7 +409,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
               int sft = lo0;
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                while (sft < lo7 && (int)cidx_s[sft] - sft <= k0 + i) ++sft;
+                while (sft < lo7 && (int)__ldg(p.cidx + sft) - sft <= k0 + i) ++sft;
                 h[i] = __ldg(reinterpret_cast<const unsigned short*>(xr + k0 + i + sft));
               }
 #pragma unroll
@@ -475,7 +481,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
   }
   for (int idx = tid + XCU * NCONS; idx < p.M * p.Cp; idx += NCONS) {
     const int m = idx / p.Cp, c = idx - m * p.Cp;
-    const uint32_t o = cidx_s[c];
+    const uint32_t o = __ldg(p.cidx + c);
     xc[m * p.xc_stride + c] = (o != CQ_PAD_COL) ? p.x[(size_t)m * p.ldx + o] : __float2half(0.f);
   }
   bar_consumers<NCONS>();
@@ -844,13 +850,7 @@ int plan_smem_slots(const cq_layer* L, int M, int grid, int max_smem, int ncw, i
   p->off_xb = off;   off = align_up(off + L->n_gran * p->xb_gran, 128);
   p->off_xq = off;   off = align_up(off + L->n_gran * 4 * mb * 16, 128);
   p->off_xc = off;   off = align_up(off + M * p->xc_stride * 2, 128);
-  p->off_cidx = off; off = align_up(off + (L->Cp + 8) * 2, 128);
-  // the octet-shift table is only needed while activations are staged: it shares the slots' space
-  {
-    const int slot_bytes = p->nslot * ncw * M * 64, osh_bytes = (L->Kp / 8) * 4;
-    p->off_slot = off; p->off_osh = off;
-    off = align_up(off + (slot_bytes > osh_bytes ? slot_bytes : osh_bytes), 128);
-  }
+  p->off_slot = off; off = align_up(off + p->nslot * ncw * M * 64, 128);
   p->off_pf = off;   off = align_up(off + 256 * 4, 128);
   p->off_bar = off;  off = align_up(off + (2 * 16 + 2) * 8, 128);
   p->off_ring = off;

@@ -655,14 +655,9 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
     while (more) {
       last_piece = w.piece;
       if ((int)(n % NGRP) == grp) {
-        const uint32_t kidx = n / NGRP;
-        unsigned long long* ft = (p.timeline && tid == 0 && kidx >= 3 && kidx < 7) ? p.timeline + (size_t)(512 + blockIdx.x) * 64 + (kidx - 3) * 12 : nullptr;
-#define FT(i) do { if (ft) ft[i] = clock64(); } while (0)
-        FT(0);
         const uint32_t j = w.cur - w.tile * IPT;
         const uint32_t s = n % S, a = n % NA;
         mbar_wait(B_WFULL(s), (n / S) & 1, &s_abort, p.status, 1024u);
-        FT(1);
         const uint8_t* item = ring + (size_t)s * p.stage_bytes;
         const bool cherry = j < NCH;
         constexpr int NW = 4 * BITS;
@@ -680,10 +675,8 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(B_WEMPTY(s));
-        FT(2);
         if (n >= NA) mbar_wait(B_AEMPTY(a), ((n / NA) - 1) & 1, &s_abort, p.status, 2048u);
         tc_fence_after();
-        FT(3);
         const uint32_t ta = tmem + lane_addr + a * A_COLS;
         if (cherry) {
           const uint32_t v[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
@@ -708,17 +701,13 @@ __global__ void __launch_bounds__((NGRP * 4 + 4) * 32, 1) cq_umma_matvec_kernel(
             }
           }
         }
-        FT(4);
         tmem_wait_st();
-        FT(5);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(B_AFULL(a));
-        FT(6);
         if (tid == 0 && n / NGRP < 12) tstamp(p, 40 + n / NGRP);
 
         if (pend) epilogue();
-        FT(7);
         if (tid == 0 && n / NGRP < 12) tstamp(p, 52 + n / NGRP);
         pend = true;
         pend_n = n;
