@@ -117,6 +117,11 @@ int cq_layer_matvec(const cq_layer* layer, const void* x_f16, int ldx, void* y_f
                     int M, int accumulate, void* scratch, uint32_t* status_word,
                     cq_stream_t stream);
 
+/* Self-test of the bounded device-side waits (no counterpart in the reference, whose kernels do
+ * not wait on one another): a one-warp kernel waits on a barrier that is never completed, gives
+ * up after about one second, sets bit 0 of *status_word (device memory) and returns normally. */
+int cq_selftest_bounded_wait(uint32_t* status_word, cq_stream_t stream);
+
 /* cq_layer_matvec without a scratch argument and without any allocation (no counterpart in the
  * reference, whose kernels accumulate with atomicAdd and need no scratch,
  * csrc/quant_cuda_kernel.cu:672-676).  For callers that have no scratch buffer to hand over and may

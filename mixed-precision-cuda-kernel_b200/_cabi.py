@@ -19,7 +19,7 @@ SYMBOLS = [
     "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense", "cq_trace_set_timeline",
     "cq_tlayer_init", "cq_tlayer_prepare", "cq_tlayer_unprepare", "cq_tlayer_matvec",
     "cq_layer_matvec_static", "cq_tlayer_gemm_workspace_bytes", "cq_tlayer_gemm",
-    "cq_rmsnorm", "cq_rope_cache", "cq_silu_mul", "cq_attn_decode",
+    "cq_selftest_bounded_wait", "cq_rmsnorm", "cq_rope_cache", "cq_silu_mul", "cq_attn_decode",
 ]
 
 

@@ -55,7 +55,7 @@ struct MatvecParams {
   int M, K, N, C, Cp, Kp, n_gran, n_sub, gran_bytes, cher_bytes;
   int ldx, ldy, accumulate;
   uint32_t T;          // total granules
-  int stages, nslot, max_cher;
+  int stages, nslot, max_cher, inflight;
   // shared-memory offsets
   int off_ring, off_cher, off_zero, off_sched, off_xb, off_xq, off_xc, off_slot, off_pf, off_bar;
   int xb_gran;         // bytes of quantised activations per granule: 2 planes x 2M columns x 64 B
@@ -88,9 +88,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // gave up somewhere), records the failure and lets the caller carry on.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             uint32_t* status) {
+  // bounded in polls and in time (about one second of the device's nanosecond timer)
   const uint32_t limit = *abort_flag ? 1u : WAIT_LIMIT;
-  for (uint32_t it = 0; it < limit; ++it)
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 63u) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 1000000000ull) break;
+    }
+  }
   *abort_flag = 1;
   if (status) atomicOr(status, 1u);
   return false;
@@ -248,9 +257,16 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
       uint32_t pi = 0;
       Piece pc = piece_of(0, j_hi, NG, ga, gb);
       uint32_t src = pc.start;           // next granule to copy
-      for (uint32_t q0 = 0; q0 < total; q0 += CH) {
+      const uint32_t INFL = (uint32_t)p.inflight;
+      uint32_t k = 0;                    // stage counter
+      for (uint32_t q0 = 0; q0 < total; q0 += CH, ++k) {
         const uint32_t len = min(CH, total - q0);
         if (!first_pass) mbar_wait(bar_base + 8 * (S + stage), phase, &s_abort, p.status);
+        // Pace the copies: at most INFL stages are outstanding, so that stages land in order and the
+        // first one is usable early (the memory system interleaves everything that is in flight).
+        // (only while the ring is deeper than that: otherwise the slot wait above paces already, and the
+        // barrier of stage k - INFL may have been re-armed)
+        if (INFL < S && k >= INFL) mbar_wait(bar_base + 8 * ((k - INFL) % S), ((k - INFL) / S) & 1, &s_abort, p.status);
         mbar_expect_tx(bar_base + 8 * stage, len * GB);
         uint32_t dst = ring + stage * CH * GB, left = len;
         while (left > 0) {
@@ -810,15 +826,17 @@ KernelFn pick_kernel(int shape, int bits, int sets, int mb, int* ncw) {
 
 // Tuning knobs read once from the environment (for experiments; defaults are the product):
 //   CQ_SHAPE  index into SHAPES      CQ_SMEM_KB  shared-memory target per CTA
-//   CQ_PDL    0 disables programmatic dependent launch
-struct Knobs { int shape, smem_kb, pdl, max_stages; };
+//   CQ_PDL    0 disables programmatic dependent launch   CQ_INFLIGHT  ring stages outstanding at a time
+struct Knobs { int shape, smem_kb, pdl, max_stages, inflight; };
 Knobs knobs() {
   static Knobs k = [] {
-    Knobs v{0, 220, 1, 16};
+    Knobs v{0, 220, 1, 16, 2};
     if (const char* e = getenv("CQ_SHAPE")) v.shape = atoi(e);
     if (const char* e = getenv("CQ_SMEM_KB")) v.smem_kb = atoi(e);
     if (const char* e = getenv("CQ_PDL")) v.pdl = atoi(e);
     if (const char* e = getenv("CQ_MAX_STAGES")) v.max_stages = atoi(e);
+    if (const char* e = getenv("CQ_INFLIGHT")) v.inflight = atoi(e);
+    if (v.inflight < 1) v.inflight = 1;
     if (v.max_stages < 2) v.max_stages = 2;
     if (v.shape < 0 || v.shape >= N_SHAPES) v.shape = 0;
     return v;
@@ -943,6 +961,7 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   p.n_gran = L->n_gran; p.n_sub = L->n_sub; p.gran_bytes = L->gran_bytes; p.cher_bytes = L->cher_bytes;
   p.ldx = ldx; p.ldy = ldy; p.accumulate = accumulate;
   p.T = T;
+  p.inflight = kn.inflight;
 
   CQ_CUDA_TRY(prepare_kernel(fn, smem));
   cudaLaunchConfig_t cfg = {};
@@ -976,6 +995,31 @@ extern "C" int cq_layer_matvec(const cq_layer* L, const void* x, int ldx, void* 
     if (rc != CQ_OK) return rc;
     done += rows;
   }
+  return CQ_OK;
+}
+
+// Self-test of the bounded waits: one warp waits on a barrier that nothing ever completes.  The
+// wait gives up after about a second, sets bit 0 of the status word and the kernel returns normally,
+// which is what every wait of the matvec kernels does when its partner never shows up.
+namespace {
+__global__ void bounded_wait_selftest_kernel(uint32_t* status) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  mbar_wait(b, 0, &abort_flag, status);
+}
+}  // namespace
+
+extern "C" int cq_selftest_bounded_wait(uint32_t* status_word, cq_stream_t stream) {
+  if (!status_word) return CQ_ERR_BAD_ARG;
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status_word);
+  CQ_CUDA_TRY(cudaGetLastError());
   return CQ_OK;
 }
 
@@ -1077,6 +1121,7 @@ extern "C" int cq_layer_matvec_static(const cq_layer* L, const void* x, int ldx,
   p.n_gran = L->n_gran; p.n_sub = L->n_sub; p.gran_bytes = L->gran_bytes; p.cher_bytes = L->cher_bytes;
   p.ldx = ldx; p.ldy = ldy; p.accumulate = accumulate;
   p.T = T;
+  p.inflight = kn.inflight;
 
   CQ_CUDA_TRY(prepare_kernel(fn, smem));
   cudaLaunchConfig_t cfg = {};

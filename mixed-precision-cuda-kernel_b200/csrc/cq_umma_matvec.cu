@@ -84,11 +84,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status,
-                                            uint32_t code) {
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            uint32_t* status, uint32_t code) {
+  // bounded in polls and in time (about one second of the device's nanosecond timer)
   const uint32_t limit = *abort_flag ? 1u : WAIT_LIMIT;
-  for (uint32_t it = 0; it < limit; ++it)
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 63u) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 1000000000ull) break;
+    }
+  }
   *abort_flag = 1;
   if (status) atomicOr(status, code);
   return false;

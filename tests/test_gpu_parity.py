@@ -350,3 +350,16 @@ def test_quantlinear_module(qc, name):
     with QuantLinear.dmode(layerwise_dequantize=False):
         y3 = ql(x)
     assert rel_err(y3.reshape(5, -1).float().cpu().numpy(), g["y"].astype(np.float64)) <= 5e-3
+
+
+def test_a_wait_that_nothing_satisfies_gives_up_and_reports(cabi):
+    """Failure detection without a fault: the bounded wait runs out (about one second), the kernel
+    returns, the status word carries the time-out bit, and the context keeps working."""
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cabi.check(cabi.lib().cq_selftest_bounded_wait(ptr(status), None), "selftest")
+    torch.cuda.synchronize()
+    assert int(status.item()) & 1
+    g = load_golden("k256_n32_b4_g128_f16")
+    p = Prepared(cabi, g["qweight"], g["scales"], g["cherry_weight"], g["cherry_indices"], 4, g["K"], g["G"])
+    y = p.matvec(g["x"][:1]).cpu().numpy()
+    assert rel_err(y, g["y"][:1].astype(np.float64)) <= TIGHT_TOL
