@@ -395,6 +395,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
       for (int u = 0; u < U; ++u) {
         const int it = base + u * NCONS + tid;
         mrow[u] = -1;
+        if (base + u * NCONS + (tid & ~31) >= nitem) continue;   // the whole warp is past the last item
         oct[u] = 0;
         v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0u;
         if (it < nitem) {
@@ -436,6 +437,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
+        if (base + u * NCONS + (tid & ~31) >= nitem) continue;   // (warp-uniform: the shuffles below stay whole)
         float f[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
