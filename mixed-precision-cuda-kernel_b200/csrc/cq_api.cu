@@ -2,7 +2,7 @@
 // (csrc/quant_cuda.cpp:41-69 of the reference project) on top of the prepared
 // layer interface: the first call with a given set of reference buffers re-packs
 // them on the GPU into the stream layout and caches the result; every call then
-// runs the stream matvec.  Calls with 32 or more activation rows (prefill) take the tensor-core
+// runs the stream matvec.  Calls with 12 or more activation rows (large decode batches, prefill) take the tensor-core
 // GEMM on a second cached copy in the tile layout.
 #include <map>
 #include <mutex>
@@ -36,7 +36,9 @@ struct DeviceState {
   size_t gemm_ws_bytes = 0;
 };
 
-constexpr int PREFILL_MIN_ROWS = 32;      // from here on the tensor-core GEMM is used
+// From here on the tensor-core GEMM is used: measured on 4096 -> 11008 4-bit, 16 rows take 51 us on the
+// stream matvec (whose per-row activation staging grows with the batch) and 37 us on the GEMM.
+constexpr int PREFILL_MIN_ROWS = 12;
 constexpr int PREFILL_CHUNK_ROWS = 4096;  // rows per GEMM call (bounds the workspace)
 
 std::mutex g_mu;
