@@ -661,36 +661,48 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
     // ---- emit the pending pieces
     if (tid == 0 && i == npieces - 1) stamp(p, 6);
     bar_consumers<NCONS>();
-    uint32_t reset_lo = 1, reset_hi = 0;    // flags to clear afterwards (finishing CTA only)
-    bool posted = false;
-    if (tid < 256) {
-      for (uint32_t ii = i + 1 - pending; ii <= i; ++ii) {
-        const Piece q = piece_of(ii, j_hi, NG, ga, gb);
-        const int m = tid >> 4, r = tid & 15;
-        float v = 0.f;
-        if (m < p.M) {
-          const float* sl = slots + ((size_t)((ii % p.nslot) * NCW) * p.M + m) * 16 + r;
+    // one thread per (pending piece, activation row, weight row): all pieces are emitted at once
+    const uint32_t first = i + 1 - pending;
+    const uint32_t n_out = (uint32_t)pending * (uint32_t)p.M * 16u;
+    for (uint32_t e = (uint32_t)tid; e < n_out; e += NCONS) {
+      const uint32_t pl = e / ((uint32_t)p.M * 16u), mr = e - pl * (uint32_t)p.M * 16u;
+      const uint32_t ii = first + pl;
+      const int m = (int)(mr >> 4), r = (int)(mr & 15u);
+      const Piece q = piece_of(ii, j_hi, NG, ga, gb);
+      float v = 0.f;
+      {
+        const float* sl = slots + ((size_t)((ii % p.nslot) * NCW) * p.M + m) * 16 + r;
 #pragma unroll
-          for (int w = 0; w < NCW; ++w) v += sl[(size_t)w * p.M * 16];
+        for (int w = 0; w < NCW; ++w) v += sl[(size_t)w * p.M * 16];
+      }
+      if (q.end < q.sub0 + NG) {
+        // an earlier part of a cut sub-tile: hand the partial to the CTA that holds its end
+        p.partial[(size_t)cta * 256 + mr] = v;
+      } else {
+        if (q.start > q.sub0) {
+          mbar_wait(bar_base + 16 * S + 8, 0, &s_abort, p.status);
+          v += reinterpret_cast<const float*>(smem + p.off_pf)[mr];
         }
+        const int n = (int)q.j * 16 + r;
+        if (n < p.N) {
+          __half* yp = p.y + (size_t)m * p.ldy + n;
+          if (p.accumulate) v += __half2float(*yp);
+          *yp = __float2half(v);
+        }
+      }
+    }
+    // what thread 0 has to publish afterwards: did a pending piece post a partial, and which flags
+    // of earlier CTAs the finished head sub-tile consumed
+    uint32_t reset_lo = 1, reset_hi = 0;
+    bool posted = false;
+    if (tid == 0) {
+      for (uint32_t ii = first; ii <= i; ++ii) {
+        const Piece q = piece_of(ii, j_hi, NG, ga, gb);
         if (q.end < q.sub0 + NG) {
-          // an earlier part of a cut sub-tile: hand the partial to the CTA that holds its end
-          p.partial[(size_t)cta * 256 + tid] = v;
           posted = true;
-        } else {
-          if (q.start > q.sub0) {
-            const uint32_t c_first = (uint32_t)((((uint64_t)q.sub0 + 1) * grid - 1) / p.T);
-            reset_lo = c_first;
-            reset_hi = cta - 1;
-            mbar_wait(bar_base + 16 * S + 8, 0, &s_abort, p.status);
-            v += reinterpret_cast<const float*>(smem + p.off_pf)[tid];
-          }
-          const int n = (int)q.j * 16 + r;
-          if (m < p.M && n < p.N) {
-            __half* yp = p.y + (size_t)m * p.ldy + n;
-            if (p.accumulate) v += __half2float(*yp);
-            *yp = __float2half(v);
-          }
+        } else if (q.start > q.sub0) {
+          reset_lo = (uint32_t)((((uint64_t)q.sub0 + 1) * grid - 1) / p.T);
+          reset_hi = cta - 1;
         }
       }
     }
