@@ -452,8 +452,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_ke
         for (int d = 1; d < 16; d <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
         // (an infinite or NaN activation makes the step infinite or NaN: the outputs of the rows it
         // feeds come out NaN, as they do in the reference)
-        const float inv = amax > 0.f ? QMAX / amax : 0.f;
-        const float sx = amax / QMAX;
+        // (reciprocal and products instead of two divisions: each is one correctly rounded operation)
+        const float inv = amax > 0.f ? QMAX * __frcp_rn(amax) : 0.f;
+        const float sx = amax * (1.f / QMAX);
         int q[8], qsum = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {

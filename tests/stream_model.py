@@ -149,8 +149,9 @@ def quantise_activations(d, xs):
     x4 = xs.astype(np.float32).reshape(M, d["n_gran"], 128)
     amax = np.abs(x4).max(-1)                                                  # (M, n_gran)
     with np.errstate(divide="ignore", invalid="ignore"):
-        inv = np.where(amax > 0, np.float32(QMAX) / amax, np.float32(0)).astype(np.float32)
-    sx = (amax / np.float32(QMAX)).astype(np.float32)
+        rcp = (np.float32(1) / amax).astype(np.float32)                       # correctly rounded reciprocal
+        inv = np.where(amax > 0, np.float32(QMAX) * rcp, np.float32(0)).astype(np.float32)
+    sx = (amax * np.float32(1.0 / QMAX)).astype(np.float32)
     q = np.rint(x4 * inv[..., None]).astype(np.int64)                          # float32 product, half-to-even
     hi = (q + 64) >> 7
     lo = q - 128 * hi
