@@ -166,8 +166,8 @@ def run_reference(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one cq_matvec_kernel launch on this workload, from the
-# ncu capture summarised in profiles/stream_matvec_4096x11008_4bit_batch1_ncu.md (23,679,744 + 256 bytes)
-NCU_DRAM_BYTES_PER_LAUNCH = 23_680_000
+# ncu capture summarised in profiles/stream_matvec_4096x11008_4bit_batch1_ncu.md (23,815,424 + 256 bytes)
+NCU_DRAM_BYTES_PER_LAUNCH = 23_815_680
 PREFILL_TOKENS = 2048
 
 
