@@ -595,16 +595,20 @@ def run_model(args):
     import torch
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
-    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
-        raise RuntimeError("the model workload is single-GPU in this version")
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     from cherryq_b200 import decoder as D
     base = {"7b": D.LLAMA2_7B, "13b": D.LLAMA2_13B, "70b": D.LLAMA2_70B}[args.model]
     cfg = D.DecoderConfig(**{**base.__dict__, "max_seq": 512})
     prompt_len, gen = 128, 256
     t_build = time.time()
-    model = D.CherryDecoder(cfg, device=dev, seed=1234)
+    model = D.CherryDecoder(cfg, device=dev, seed=1234, tp_group=dist.group.WORLD if world > 1 else None)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
     prompt = torch.randint(0, cfg.vocab, (prompt_len,), device=dev, generator=torch.Generator(device=dev).manual_seed(0))
@@ -623,10 +627,22 @@ def run_model(args):
     model.prefill(prompt)
     model.generate(8)                           # warm the graph
     model.prefill(prompt)
-    sampler = ClockSampler(0)
-    sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     gen_ms, toks = timed(lambda: model.generate(gen))
-    clocks = sampler.stop()
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        tt = torch.tensor([gen_ms, prefill_ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        gen_ms, prefill_ms = float(tt[0]), float(tt[1])
+        same = toks.clone()
+        dist.broadcast(same, src=0)
+        if not torch.equal(same, toks):
+            raise RuntimeError("the ranks generated different tokens")
     tok_s = gen / (gen_ms * 1e-3)
 
     # the quantized projections alone, same call sequence, captured the same way
@@ -653,22 +669,38 @@ def run_model(args):
         head_ms, _ = timed(lambda: [torch.nn.functional.linear(h, model.lm_head) for _ in range(50)])
     head_ms /= 50
 
-    qbytes, hbytes = model.quantized_bytes_per_token(), model.lm_head_bytes()
+    qbytes, hbytes = model.quantized_bytes_per_token() * world, model.lm_head_bytes()
+
+    def leave():
+        # Captured graphs hold NCCL kernels; tearing the communicator down under them has hung.  All
+        # ranks meet once more, drop their graphs and leave the process without the teardown.
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+    if rank != 0:
+        leave()
     peak, peak_kind = measured_peak()
     ms_tok = gen_ms / gen
     line = {
-        "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": gen, "warmup": 8,
-        "ms_per_step": ms_tok, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": gen, "warmup": 8,
+        "ms_per_step": ms_tok, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
         "config": {"workload": f"llama2_{args.model}_arch_{cfg.bits}bit_g128_cherry1/256_prompt128_greedy256_batch1",
                    "layers": cfg.n_layers, "kv_heads": cfg.n_kv_heads,
                    "hidden": cfg.hidden, "ffn": cfg.ffn, "vocab": cfg.vocab, "bits": cfg.bits,
                    "l2_defeat": f"{qbytes / 1e9:.1f} GB of quantized weights + {hbytes / 1e6:.0f} MB lm_head per token, "
                                 "far larger than L2",
+                   "parallelism": "single GPU" if world == 1 else
+                                  f"column-parallel over {world} GPUs, 4 NCCL all-gathers per layer inside the graph",
                    "launch": f"one CUDA graph per decode step ({cfg.n_layers * 7} quantized projections, attention, "
                              "norms, lm_head, argmax)"},
         "roofline": {"bound": "hbm", "achieved": (qbytes + hbytes) / (ms_tok * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": (qbytes + hbytes) / (ms_tok * 1e-3) / 1e9 / peak, "traffic": None,
+                     "frac": (qbytes + hbytes * world) / world / (ms_tok * 1e-3) / 1e9 / peak, "traffic": None,
                      "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
                      "bytes_per_token": qbytes + hbytes},
         "split": {"quantized_linears_ms": lin_ms, "lm_head_ms": head_ms, "rest_ms": ms_tok - lin_ms - head_ms,
@@ -677,10 +709,12 @@ def run_model(args):
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                 "note": "the decode loop lives on the device (token ids are read back once at the end: "
                         f"{gen * 8} bytes); prompt upload {prompt_len * 8} bytes once"},
-        "gpu_launches": gen * (cfg.n_layers * 7), "clocks": clocks, "cpu_baseline": None,
+        "gpu_launches": gen * (cfg.n_layers * 7) * world, "clocks": clocks, "cpu_baseline": None,
         "build_s": t_build, "first_tokens": [int(t) for t in toks[:8].tolist()],
     }
     print(json.dumps(line))
+    if world > 1:
+        leave()
 
 
 def main():

@@ -17,6 +17,13 @@ Decode attention is a single-query kernel of the library that reads the current 
 device (so the captured graph serves every step); prefill attention is torch's
 scaled_dot_product_attention.  Both are plumbing here, not the measured path.
 
+`tp_group` shards every projection along its output rows over the ranks of a process group
+(column parallel: heads for q / k / v, output features for o / gate / up / down) and gathers the
+slices with an NCCL all-gather where the next op needs the whole vector (attention output, o,
+SwiGLU output, down): four collectives per layer.  Every output element is still computed by
+exactly the single-GPU arithmetic, so the tokens are identical for every group size; all ranks
+draw the full random weight and pack only their rows.
+
 `dense=True` builds the parity twin: the same packed buffers, every projection computed as
 F.linear(x, unpack()) the way the reference's dense mode does (llama/qlinear.py:183-195).
 """
@@ -69,20 +76,30 @@ class CherryDecoder:
     PROJ = ("q", "k", "v", "o", "gate", "up", "down")
 
     def __init__(self, cfg: DecoderConfig, device="cuda", seed: int = 0, dense: bool = False,
-                 release_reference_buffers: bool = False):
+                 release_reference_buffers: bool = False, tp_group=None):
         if not torch.cuda.is_available():
             raise RuntimeError("CherryDecoder needs a CUDA device (there is no CPU path)")
         self.cfg, self.dev, self.dense = cfg, torch.device(device), dense
         self.qc = load_quant_cuda()
+        self.group = tp_group
+        if tp_group is not None:
+            import torch.distributed as dist
+            self.tp, self.rank = dist.get_world_size(tp_group), dist.get_rank(tp_group)
+        else:
+            self.tp, self.rank = 1, 0
         g = torch.Generator(device=self.dev).manual_seed(seed)
         hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
         shapes = {"q": (cfg.hidden, h * hd), "k": (cfg.hidden, kv * hd), "v": (cfg.hidden, kv * hd),
                   "o": (h * hd, cfg.hidden), "gate": (cfg.hidden, cfg.ffn), "up": (cfg.hidden, cfg.ffn),
                   "down": (cfg.ffn, cfg.hidden)}
-        self.shapes = shapes
+        if h % self.tp or kv % self.tp or any(n % (8 * self.tp) for _, n in shapes.values()):
+            raise ValueError(f"{self.tp} ranks do not divide the heads / output features of this configuration")
+        self.full_shapes = shapes
+        self.shapes = {name: (k, n // self.tp) for name, (k, n) in shapes.items()}    # this rank's shards
+        self.h_local, self.kv_local = h // self.tp, kv // self.tp
         self.layers = []
         for _ in range(cfg.n_layers):
-            lay = {name: self._make_linear(k, n, g) for name, (k, n) in shapes.items()}
+            lay = {name: self._make_linear(k, n, g) for name, (k, n) in self.full_shapes.items()}
             lay["norm1"] = torch.ones(cfg.hidden, dtype=torch.float16, device=self.dev)
             lay["norm2"] = torch.ones(cfg.hidden, dtype=torch.float16, device=self.dev)
             if release_reference_buffers and not dense:
@@ -95,7 +112,7 @@ class CherryDecoder:
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=self.dev, dtype=torch.float32) / hd))
         ang = torch.outer(torch.arange(cfg.max_seq, device=self.dev, dtype=torch.float32), inv)
         self.cos, self.sin = ang.cos(), ang.sin()                      # (max_seq, hd / 2)
-        self.k_cache = torch.zeros(cfg.n_layers, cfg.max_seq, kv, hd, dtype=torch.float16, device=self.dev)
+        self.k_cache = torch.zeros(cfg.n_layers, cfg.max_seq, self.kv_local, hd, dtype=torch.float16, device=self.dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         # state of the decode loop, all on the device
         self.tok = torch.zeros(1, dtype=torch.long, device=self.dev)
@@ -110,6 +127,9 @@ class CherryDecoder:
         idx = torch.randperm(k, device=self.dev, generator=g)[:c].to(torch.int32)
         if c:
             w[:, idx.long()] = (torch.randn(n, c, device=self.dev, generator=g) * 0.2).half()
+        if self.tp > 1:            # this rank's output rows of the same full matrix
+            n = n // self.tp
+            w = w[self.rank * n:(self.rank + 1) * n].contiguous()
         ql = QuantLinear(cfg.bits, cfg.group, None, cfg.cherry_fraction, k, n, bias=False).to(self.dev)
         ql.pack(SimpleNamespace(weight=w, bias=None, cherry_indices=idx, group_size=cfg.group))
         if self.dense:
@@ -131,6 +151,16 @@ class CherryDecoder:
             return F.linear(x, ql.dense_weight)
         return ql(x)
 
+    def _gather(self, x: torch.Tensor) -> torch.Tensor:
+        """(t, n_local) slices of all ranks -> (t, tp * n_local), in rank order."""
+        if self.tp == 1:
+            return x
+        import torch.distributed as dist
+        t, nl = x.shape
+        out = torch.empty(self.tp, t, nl, dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        return out.view(1, self.tp * nl) if t == 1 else out.permute(1, 0, 2).reshape(t, self.tp * nl)
+
     def _norm(self, h: torch.Tensor, delta, w: torch.Tensor):
         """(rmsnorm(h + delta) * w, h + delta): the residual add rides in the norm kernel."""
         if delta is None:
@@ -142,7 +172,7 @@ class CherryDecoder:
         """One decoder layer on the residual stream h with the previous layer's MLP output `delta`
         still to be added; returns (h, delta) in the same form."""
         cfg, lay = self.cfg, self.layers[li]
-        t, nh, kv, hd = h.shape[0], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        t, nh, kv, hd = h.shape[0], self.h_local, self.kv_local, cfg.head_dim
         xn, h = self._norm(h, delta, lay["norm1"])
         q = self._lin(lay["q"], xn).view(t, nh, hd)
         k = self._lin(lay["k"], xn).view(t, kv, hd)
@@ -154,9 +184,9 @@ class CherryDecoder:
             a = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
                                                v.transpose(0, 1)[None], is_causal=True, enable_gqa=(kv != nh))
             a = a[0].transpose(0, 1).reshape(t, nh * hd)
-        xn, h = self._norm(h, self._lin(lay["o"], a), lay["norm2"])
+        xn, h = self._norm(h, self._gather(self._lin(lay["o"], self._gather(a))), lay["norm2"])
         act = self.qc.silu_mul(self._lin(lay["gate"], xn), self._lin(lay["up"], xn))
-        return h, self._lin(lay["down"], act)
+        return h, self._gather(self._lin(lay["down"], self._gather(act)))
 
     def _logits(self, h: torch.Tensor, delta) -> torch.Tensor:
         return F.linear(self._norm(h, delta, self.final_norm)[0], self.lm_head)
