@@ -80,4 +80,5 @@ def load():
 
 
 if __name__ == "__main__":
-    build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", verbose=True)
+    default_root = os.environ.get("CHERRYQ_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+    build(sys.argv[1] if len(sys.argv) > 1 else default_root, verbose=True)
