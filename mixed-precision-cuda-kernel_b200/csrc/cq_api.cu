@@ -2,7 +2,7 @@
 // (csrc/quant_cuda.cpp:41-69 of the reference project) on top of the prepared
 // layer interface: the first call with a given set of reference buffers re-packs
 // them on the GPU into the stream layout and caches the result; every call then
-// runs the stream matvec.  Calls with 12 or more activation rows (large decode batches, prefill) take the tensor-core
+// runs the stream matvec.  Calls with 8 or more activation rows (large decode batches, prefill) take the tensor-core
 // GEMM on a second cached copy in the tile layout.
 #include <map>
 #include <mutex>
@@ -37,8 +37,9 @@ struct DeviceState {
 };
 
 // From here on the tensor-core GEMM is used: measured on 4096 -> 11008 4-bit, 16 rows take 51 us on the
-// stream matvec (whose per-row activation staging grows with the batch) and 37 us on the GEMM.
-constexpr int PREFILL_MIN_ROWS = 12;
+// stream matvec (whose per-row activation staging grows with the batch) and 34 us on the GEMM with
+// split-K; at 8 rows 30 us against 33 us there, but 4096 -> 4096 and 11008 -> 4096 are well ahead on the GEMM.
+constexpr int PREFILL_MIN_ROWS = 8;
 constexpr int PREFILL_CHUNK_ROWS = 4096;  // rows per GEMM call (bounds the workspace)
 
 std::mutex g_mu;

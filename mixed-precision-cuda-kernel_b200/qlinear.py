@@ -132,8 +132,8 @@ class QuantLinear(nn.Module):
             if x2.dtype != torch.float16:
                 x2 = x2.half()
             x2 = x2.contiguous()
-            if x2.shape[0] >= 12 and self._prepared_key != "released":
-                # 12 rows or more: the drop-in op routes them to the tensor-core GEMM (faster from there on)
+            if x2.shape[0] >= 8 and self._prepared_key != "released":
+                # 8 rows or more: the drop-in op routes them to the tensor-core GEMM (faster from there on)
                 qc = load_quant_cuda()
                 out = torch.zeros(x2.shape[0], self.out_features, dtype=torch.float16, device=x2.device)
                 if self.w_bits == 4:
