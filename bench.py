@@ -256,10 +256,26 @@ def run_ours(args):
     stream = torch.cuda.Stream(device=dev)
     sp = C.c_void_p(stream.cuda_stream)
 
+    # the exchange step of the column-parallel layer: this library's peer-memory kernel, or NCCL when
+    # asked for (--gather nccl) or when the peers' memory cannot be mapped (recorded in the line)
+    peer, gather_kind = None, "none"
+    if world > 1:
+        gather_kind = "NCCL all-gather"
+        if args.gather == "peer" and n_local * world == N_OUT:
+            from cherryq_b200.parallel import PeerAllGather
+            try:
+                peer = PeerAllGather(dist.group.WORLD, dev, capacity_bytes=1 << 20)
+                gather_kind = "peer-memory all-gather kernel (cq_peer_allgather)"
+            except RuntimeError as exc:
+                if rank == 0:
+                    print(f"peer memory unavailable, using NCCL: {exc}", file=sys.stderr)
+
     def launch(i):
         _cabi.check(lib.cq_layer_matvec(C.byref(layers[i % ncopies]), ptr(x), K_IN, ptr(y), n_local, 1, 0,
                                         ptr(scratch), ptr(status), sp), "matvec")
-        if world > 1:
+        if peer is not None:
+            peer.gather_into(y, y_all, stream)
+        elif world > 1:
             dist.all_gather_into_tensor(y_all, y)
 
     def barrier():
@@ -274,7 +290,7 @@ def run_ours(args):
             launch(i)
         stream.synchronize()
         graph = None
-        if world == 1:
+        if world == 1 or peer is not None:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 for i in range(ncopies):
@@ -304,7 +320,7 @@ def run_ours(args):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    if int(status.item()) != 0:
+    if int(status.item()) != 0 or (peer is not None and int(peer.status.item()) != 0):
         raise RuntimeError("a device-side wait timed out during the benchmark")
     ms_step = ms / args.steps
     value = alg / (ms_step * 1e-3) / 1e9
@@ -407,14 +423,14 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "bits": BITS, "group": GROUP, "K": K_IN, "N": N_OUT, "batch": 1,
                        "l2_defeat": f"{ncopies} distinct layer copies ({ncopies * L0.blob_bytes / 1e6:.0f} MB) walked "
                                     "round-robin, inputs larger than L2",
-                       "parallelism": "single GPU" if world == 1 else f"column-parallel over {world} GPUs + NCCL all-gather",
-                       "launch": "CUDA graph of the copies" if world == 1 else "stream launches"},
+                       "parallelism": "single GPU" if world == 1 else f"column-parallel over {world} GPUs + {gather_kind}",
+                       "launch": "CUDA graph of the copies" if graph is not None else "stream launches"},
             "pct_of_nominal_8TBps": value / world / 8000.0 * 100.0 if world == 1 else None,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_DRAM_BYTES_PER_LAUNCH * alg_local / alg, "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
                          "kernel": "cq_matvec_kernel<4,1,1,...>", "alg_bytes_per_launch": alg_local,
                          "launch_us": kern_ms * 1e3},
-            "e2e": e2e, "gpu_launches": args.steps * world, "clocks": clocks,
+            "e2e": e2e, "gpu_launches": args.steps * world * (2 if peer is not None else 1), "clocks": clocks,
         }
         line["cpu_baseline"] = cpu_baseline() if world == 1 and not args.no_cpu else None
         line["reference_gpu_kernel"] = ref_gpu
@@ -528,7 +544,7 @@ def prefill_measure(torch, dist, dev, world, rank, local, steps_arg, warmup_arg)
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    if int(status.item()) != 0:
+    if int(status.item()) != 0 or (peer is not None and int(peer.status.item()) != 0):
         raise RuntimeError("a device-side wait timed out during the benchmark")
     ms_step = ms / steps
     flops = 2.0 * M * K_IN * N_OUT
@@ -608,7 +624,8 @@ def run_model(args):
     cfg = D.DecoderConfig(**{**base.__dict__, "max_seq": 512})
     prompt_len, gen = 128, 256
     t_build = time.time()
-    model = D.CherryDecoder(cfg, device=dev, seed=1234, tp_group=dist.group.WORLD if world > 1 else None)
+    model = D.CherryDecoder(cfg, device=dev, seed=1234, tp_group=dist.group.WORLD if world > 1 else None,
+                            tp_gather=args.gather)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
     prompt = torch.randint(0, cfg.vocab, (prompt_len,), device=dev, generator=torch.Generator(device=dev).manual_seed(0))
@@ -696,7 +713,8 @@ def run_model(args):
                    "l2_defeat": f"{qbytes / 1e9:.1f} GB of quantized weights + {hbytes / 1e6:.0f} MB lm_head per token, "
                                 "far larger than L2",
                    "parallelism": "single GPU" if world == 1 else
-                                  f"column-parallel over {world} GPUs, 4 NCCL all-gathers per layer inside the graph",
+                                  f"column-parallel over {world} GPUs, 4 all-gathers per layer inside the graph "
+                                  f"({'peer-memory kernel cq_peer_allgather' if model.peer is not None else 'NCCL'})",
                    "launch": f"one CUDA graph per decode step ({cfg.n_layers * 7} quantized projections, attention, "
                              "norms, lm_head, argmax)"},
         "roofline": {"bound": "hbm", "achieved": (qbytes + hbytes) / (ms_tok * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
@@ -729,6 +747,8 @@ def main():
                          "model: LLaMA-2-7B-architecture greedy decode, tokens/s")
     ap.add_argument("--model", default="7b", choices=["7b", "13b", "70b"],
                     help="architecture of the model workload: LLaMA-2 7B (4-bit), 13B (3-bit) or 70B (3-bit, GQA)")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="exchange step at N > 1: this library's peer-memory kernel (default) or NCCL")
     ap.add_argument("--timeline", action="store_true",
                     help="also print the kernel's per-phase device timeline to stderr (after the timed region)")
     args = ap.parse_args()

@@ -273,6 +273,32 @@ int cq_unpack_dense(const uint8_t* qweight, const void* scales_f16,
                     int bits, int K, int N, int C, int G, void* dense_f16,
                     cq_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Exchange step of the column-parallel layer over peer memory (no counterpart in the reference,
+ * which runs on one GPU: its llama/qlinear.py:164-199 forward produces the whole output vector).
+ * Every rank holds N / P output columns; one small kernel per rank stores its (rows, cols_local)
+ * fp16 slice into a landing area of every rank with plain peer stores, raises a flag there, waits
+ * (bounded by timeout_ms, then CQ_ERR_DEVICE_TIMEOUT bits in *status_word and the output is left
+ * untouched) for the flags of all ranks and writes the gathered (rows, P * cols_local) fp16 matrix.
+ * One rank per GPU: ranks never share a device.  Every rank makes the same sequence of calls.
+ *
+ * A region is cq_peer_region_bytes(capacity) bytes of device memory, zeroed at creation;
+ * capacity (a multiple of 16) bounds rows * cols_local * 2 * P of one call.  Peers map it through
+ * the 64-byte CUDA IPC handle.  regions[] holds P device pointers, regions[rank] the own one.
+ * Creation, export, open, close and destroy are host calls that synchronise; the gather itself
+ * is one launch on the given stream and can be captured.
+ * ---------------------------------------------------------------------- */
+#define CQ_PEER_MAX_RANKS 8
+size_t cq_peer_region_bytes(size_t capacity);
+int cq_peer_region_create(size_t capacity, void** region);
+int cq_peer_region_destroy(void* region);
+int cq_peer_region_export(const void* region, unsigned char handle[64]);
+int cq_peer_region_open(const unsigned char handle[64], void** region);
+int cq_peer_region_close(void* region);
+int cq_peer_allgather(void* const* regions, int world, int rank, size_t capacity, const void* x_f16,
+                      void* out_f16, int rows, int cols_local, int timeout_ms,
+                      uint32_t* status_word, cq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

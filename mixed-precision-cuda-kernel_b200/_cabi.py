@@ -20,6 +20,8 @@ SYMBOLS = [
     "cq_tlayer_init", "cq_tlayer_prepare", "cq_tlayer_unprepare", "cq_tlayer_matvec",
     "cq_layer_matvec_static", "cq_tlayer_gemm_workspace_bytes", "cq_tlayer_gemm",
     "cq_selftest_bounded_wait", "cq_rmsnorm", "cq_rope_cache", "cq_silu_mul", "cq_attn_decode",
+    "cq_peer_region_bytes", "cq_peer_region_create", "cq_peer_region_destroy", "cq_peer_region_export",
+    "cq_peer_region_open", "cq_peer_region_close", "cq_peer_allgather",
 ]
 
 
@@ -76,6 +78,14 @@ def lib():
     L.cq_trace_set_timeline.argtypes = [vp]
     L.cq_pack.argtypes = [vp, i32, vp] + [i32] * 5 + [vp] * 6
     L.cq_unpack_dense.argtypes = [vp] * 4 + [i32] * 5 + [vp, vp]
+    L.cq_peer_region_bytes.argtypes = [C.c_size_t]
+    L.cq_peer_region_bytes.restype = C.c_size_t
+    L.cq_peer_region_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
+    L.cq_peer_region_destroy.argtypes = [vp]
+    L.cq_peer_region_export.argtypes = [vp, C.c_char_p]
+    L.cq_peer_region_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    L.cq_peer_region_close.argtypes = [vp]
+    L.cq_peer_allgather.argtypes = [C.POINTER(C.c_void_p), i32, i32, C.c_size_t, vp, vp, i32, i32, i32, vp, vp]
     _lib = L
     return L
 

@@ -76,7 +76,7 @@ class CherryDecoder:
     PROJ = ("q", "k", "v", "o", "gate", "up", "down")
 
     def __init__(self, cfg: DecoderConfig, device="cuda", seed: int = 0, dense: bool = False,
-                 release_reference_buffers: bool = False, tp_group=None):
+                 release_reference_buffers: bool = False, tp_group=None, tp_gather: str = "peer"):
         if not torch.cuda.is_available():
             raise RuntimeError("CherryDecoder needs a CUDA device (there is no CPU path)")
         self.cfg, self.dev, self.dense = cfg, torch.device(device), dense
@@ -87,6 +87,14 @@ class CherryDecoder:
             self.tp, self.rank = dist.get_world_size(tp_group), dist.get_rank(tp_group)
         else:
             self.tp, self.rank = 1, 0
+        # exchange step of the sharded projections: "peer" = this library's peer-memory kernel for
+        # slices that fit its landing area (decode batches), NCCL for the rest (prefill); "nccl" = NCCL only
+        self.peer = None
+        if self.tp > 1 and tp_gather == "peer":
+            from .parallel import PeerAllGather
+            self.peer = PeerAllGather(tp_group, self.dev)
+        elif tp_gather not in ("peer", "nccl"):
+            raise ValueError("tp_gather is 'peer' or 'nccl'")
         g = torch.Generator(device=self.dev).manual_seed(seed)
         hd, h, kv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
         shapes = {"q": (cfg.hidden, h * hd), "k": (cfg.hidden, kv * hd), "v": (cfg.hidden, kv * hd),
@@ -157,6 +165,8 @@ class CherryDecoder:
             return x
         import torch.distributed as dist
         t, nl = x.shape
+        if self.peer is not None and x.dtype == torch.float16 and self.peer.fits(t, nl):
+            return self.peer(x.contiguous())
         out = torch.empty(self.tp, t, nl, dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
         return out.view(1, self.tp * nl) if t == 1 else out.permute(1, 0, 2).reshape(t, self.tp * nl)

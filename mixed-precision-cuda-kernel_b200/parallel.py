@@ -101,3 +101,106 @@ class ColumnParallelQuantLinear(torch.nn.Module):
         dist.all_gather_into_tensor(flat, pad.reshape(-1), group=self.group)
         out = flat.view(self.world, *pad.shape)
         return torch.cat([out[r][..., :sizes[r]] for r in range(self.world)], dim=-1)
+
+
+class PeerAllGather:
+    """All-gather of equal (rows, cols_local) fp16 slices through mapped peer memory: one small
+    kernel of this library per call and rank (`cq_peer_allgather`) instead of a library collective.
+
+    Set-up is collective over `group`: every rank creates its region, the 64-byte IPC handles
+    travel through `all_gather_object`, every rank maps the others' regions.  If any rank fails to
+    map a peer (no peer access between the devices, IPC closed in the container) all ranks raise
+    together.  `__call__` enqueues one launch on the current stream and can be captured in a CUDA
+    graph; every rank must make the same sequence of calls.  A peer that never delivers shows up
+    as a timeout bit in `status` (a device word), read with `check()`; the output of that call is
+    then left untouched.  One rank per GPU.
+    """
+
+    def __init__(self, group, device, capacity_bytes: int = 4 << 20, timeout_ms: int = 2000):
+        import ctypes as C
+
+        from . import _cabi
+        self._C, self._cabi, self.lib = C, _cabi, _cabi.lib()
+        self.group, self.device = group, torch.device(device)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        self.capacity, self.timeout_ms = int(capacity_bytes) // 16 * 16, int(timeout_ms)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._opened = []
+        self.own = None
+        with torch.cuda.device(self.device):
+            own = C.c_void_p()
+            rc = self.lib.cq_peer_region_create(self.capacity, C.byref(own))
+            handle = C.create_string_buffer(64)
+            if rc == 0:
+                self.own = own.value
+                rc = self.lib.cq_peer_region_export(own, handle)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, (rc, handle.raw), group=group)
+            ptrs, failed = [], any(h[0] != 0 for h in handles)
+            if not failed:
+                for r, (_, raw) in enumerate(handles):
+                    if r == self.rank:
+                        ptrs.append(self.own)
+                        continue
+                    p = C.c_void_p()
+                    rc = self.lib.cq_peer_region_open(raw, C.byref(p))
+                    if rc != 0:
+                        failed = True
+                        break
+                    self._opened.append(p.value)
+                    ptrs.append(p.value)
+            oks = [None] * self.world
+            dist.all_gather_object(oks, not failed, group=group)
+            if not all(oks):
+                self.close()
+                raise RuntimeError("peer memory could not be mapped on every rank "
+                                   f"(per-rank success: {oks}); use the NCCL all-gather instead")
+            self.regions = (C.c_void_p * self.world)(*ptrs)
+        dist.barrier(group=group)          # every region is zeroed and mapped before the first launch
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dim() != 2:
+            raise ValueError("x must be a (rows, cols_local) fp16 CUDA tensor")
+        out = torch.empty(x.shape[0], self.world * x.shape[1], dtype=torch.float16, device=x.device)
+        return self.gather_into(x, out)
+
+    def gather_into(self, x: torch.Tensor, out: torch.Tensor, stream=None) -> torch.Tensor:
+        """out (rows, world * cols_local) <- the slices x (rows, cols_local) of all ranks, in rank order."""
+        if x.dim() != 2 or x.dtype != torch.float16 or not x.is_cuda or not x.is_contiguous():
+            raise ValueError("x must be a contiguous (rows, cols_local) fp16 CUDA tensor")
+        rows, cols = x.shape
+        if out.dtype != torch.float16 or not out.is_contiguous() or out.numel() != rows * cols * self.world:
+            raise ValueError("out must be a contiguous fp16 tensor of rows * world * cols_local elements")
+        stream = stream if stream is not None else torch.cuda.current_stream(x.device)
+        cv = self._C.c_void_p
+        self._cabi.check(self.lib.cq_peer_allgather(self.regions, self.world, self.rank, self.capacity,
+                                                    cv(x.data_ptr()), cv(out.data_ptr()), rows, cols, self.timeout_ms,
+                                                    cv(self.status.data_ptr()), cv(stream.cuda_stream)), "peer all-gather")
+        return out
+
+    def fits(self, rows: int, cols_local: int) -> bool:
+        return cols_local % 8 == 0 and rows * cols_local * 2 * self.world <= self.capacity
+
+    def check(self) -> None:
+        """Host read of the status word (synchronises): raises if a wait for a peer ran out."""
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            raise RuntimeError("a peer did not deliver its slice within the time limit")
+
+    def close(self) -> None:
+        """Unmap the peers' regions and free the own one.  Call on every rank, with no gather in flight."""
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                self.lib.cq_peer_region_close(self._C.c_void_p(p))
+            self._opened = []
+            if self.own is not None:
+                if dist.is_initialized():
+                    try:
+                        dist.barrier(group=self.group)     # nobody still has this region mapped
+                    except Exception:
+                        pass
+                self.lib.cq_peer_region_destroy(self._C.c_void_p(self.own))
+                self.own = None
