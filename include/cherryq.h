@@ -277,14 +277,16 @@ int cq_unpack_dense(const uint8_t* qweight, const void* scales_f16,
  * Exchange step of the column-parallel layer over peer memory (no counterpart in the reference,
  * which runs on one GPU: its llama/qlinear.py:164-199 forward produces the whole output vector).
  * Every rank holds N / P output columns; one small kernel per rank stores its (rows, cols_local)
- * fp16 slice into a landing area of every rank with plain peer stores, raises a flag there, waits
- * (bounded by timeout_ms, then CQ_ERR_DEVICE_TIMEOUT bits in *status_word and the output is left
- * untouched) for the flags of all ranks and writes the gathered (rows, P * cols_local) fp16 matrix.
+ * fp16 slice into a landing area of every rank with plain peer stores, each 8-byte word carrying
+ * 4 payload bytes and the call's sequence number, polls its own landing area until every word
+ * carries that number (bounded by timeout_ms, then CQ_ERR_DEVICE_TIMEOUT bits in *status_word and
+ * the output is left untouched) and writes the gathered (rows, P * cols_local) fp16 matrix.
  * One rank per GPU: ranks never share a device.  Every rank makes the same sequence of calls.
  *
  * A region is cq_peer_region_bytes(capacity) bytes of device memory, zeroed at creation;
- * capacity (a multiple of 16) bounds rows * cols_local * 2 * P of one call.  Peers map it through
- * the 64-byte CUDA IPC handle.  regions[] holds P device pointers, regions[rank] the own one.
+ * capacity (a multiple of 16) bounds 4 * rows * cols_local * P of one call (twice the payload).
+ * Peers map it through the 64-byte CUDA IPC handle.  regions[] holds P device pointers,
+ * regions[rank] the own one.
  * Creation, export, open, close and destroy are host calls that synchronise; the gather itself
  * is one launch on the given stream and can be captured.
  * ---------------------------------------------------------------------- */

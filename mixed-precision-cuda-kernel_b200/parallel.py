@@ -181,7 +181,7 @@ class PeerAllGather:
         return out
 
     def fits(self, rows: int, cols_local: int) -> bool:
-        return cols_local % 8 == 0 and rows * cols_local * 2 * self.world <= self.capacity
+        return cols_local % 8 == 0 and rows * cols_local * 4 * self.world <= self.capacity    # twice the payload
 
     def check(self) -> None:
         """Host read of the status word (synchronises): raises if a wait for a peer ran out."""

@@ -51,7 +51,7 @@ def test_argument_checks(region):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     x = torch.zeros(1, 12, dtype=torch.float16, device="cuda")
     assert _gather(lib, regions, 1, 0, x, x.clone(), status) == 4            # cols_local not a multiple of 8
-    big = torch.zeros(64, 16384, dtype=torch.float16, device="cuda")          # 2 MB > capacity
+    big = torch.zeros(64, 16384, dtype=torch.float16, device="cuda")          # 2 MB, 4 MB on the wire > capacity
     assert _gather(lib, regions, 1, 0, big, big.clone(), status) == 5
     ok = torch.zeros(1, 16, dtype=torch.float16, device="cuda")
     assert _gather(lib, regions, 1, 1, ok, ok.clone(), status) == 1           # rank outside the world
