@@ -3,7 +3,8 @@
 The layer shards along N (output rows): every output element is an independent dot product, so a
 rank that holds `qweight[:, n0:n1]`, `scales[:, n0:n1]`, `cherry_weight[:, n0:n1]` and the full
 `cherry_indices` computes `y[:, n0:n1]` with exactly the single-GPU arithmetic.  The only
-exchange is one all-gather of the (M, N/P) fp16 slices (NCCL over NVLink).  The reference has no
+exchange is one all-gather of the (M, N/P) fp16 slices: `PeerAllGather` (one kernel of this library
+over mapped peer memory) or NCCL.  The reference has no
 multi-GPU path (its `utils.simple_dispatch_model`, utils.py:28-55, only places whole layers).
 
 Host-side safety net (tested on CPU with gloo): before any GPU work the ranks compare the layer's
@@ -165,6 +166,8 @@ class PeerAllGather:
             raise ValueError("x must be a (rows, cols_local) fp16 CUDA tensor")
         out = torch.empty(x.shape[0], self.world * x.shape[1], dtype=torch.float16, device=x.device)
         return self.gather_into(x, out)
+
+    gather = __call__
 
     def gather_into(self, x: torch.Tensor, out: torch.Tensor, stream=None) -> torch.Tensor:
         """out (rows, world * cols_local) <- the slices x (rows, cols_local) of all ranks, in rank order."""
