@@ -199,11 +199,11 @@ class PeerAllGather:
             for p in self._opened:
                 self.lib.cq_peer_region_close(self._C.c_void_p(p))
             self._opened = []
+            if dist.is_initialized():
+                try:
+                    dist.barrier(group=self.group)     # nobody still has a peer's region mapped
+                except Exception:
+                    pass
             if self.own is not None:
-                if dist.is_initialized():
-                    try:
-                        dist.barrier(group=self.group)     # nobody still has this region mapped
-                    except Exception:
-                        pass
                 self.lib.cq_peer_region_destroy(self._C.c_void_p(self.own))
                 self.own = None

@@ -54,6 +54,7 @@ def main():
             s.synchronize()
             ok &= torch.equal(out, nccl_gather(x, world))
     peer.check()
+    peer.close()                      # collective: unmap the peers, meet, free the own region
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     torch.cuda.synchronize()
