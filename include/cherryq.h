@@ -141,6 +141,53 @@ int cq_layer_matvec_static(const cq_layer* layer, const void* x_f16, int ldx, vo
                            int M, int accumulate, uint32_t* status_word, cq_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Row-layout prepared layer: the format of the ONE-activation-row decode matvec (the batch-1 case
+ * of csrc/quant_cuda_kernel.cu:718-835 and :558-672, :316-438 of the reference).  Every output row
+ * is stored contiguously; within a row the compact columns are cut into K slices of at most 32
+ * groups of 128 columns; a warp works on one (row, slice), its lane l on group l:
+ * One record per output row, rec_bytes long, records back to back:
+ *   codes   [slice][chunk j < bits][lane][16 B]   the lane's 128 codes = bits x 4 words
+ *             4-bit: word w = columns 8w..8w+7, low nibble of byte b = column 8w+b, high = 8w+4+b
+ *             3-bit: words A,B,C of a 32-column set: bits 0-2 / 4-6 of byte b of A,B,C = column
+ *                    4f+b of fields f = 0..5; bit 3 (bit 7) of byte b of A,B,C = code bits 0,1,2
+ *                    of column 24+b (28+b)
+ *   scales  [group][set] fp16 (set = 64-column half, only for 64-wide groups), padded to 16 bytes
+ *   cherry  [C] fp16
+ * followed by
+ *   perm    [groups x 128] uint16: original column of each compact column, K past K'
+ *   cidx    [C] uint16 sorted cherry columns
+ * Same role as cq_layer; no scratch.
+ * ---------------------------------------------------------------------- */
+typedef struct cq_rlayer {
+  int32_t bits, K, N, C, G;
+  int32_t Kc;          /* K - C                                                          */
+  int32_t NG;          /* 128-column groups per row = ceil(Kc / 128)                     */
+  int32_t sets;        /* scale sets per group: 1 (G % 128 == 0) or 2 (G == 64)          */
+  int32_t nsl;         /* K slices = ceil(NG / 32)                                       */
+  int32_t gps;         /* groups per slice = ceil(NG / nsl)                              */
+  int32_t cps;         /* cherry columns per slice = ceil(C / nsl), at most 32           */
+  int32_t row_bytes;   /* code bytes of a record = NG * 16 * bits                        */
+  int32_t srow_bytes;  /* scale bytes of a record, padded to 16                          */
+  int32_t rec_bytes;   /* row_bytes + srow_bytes + 2 C                                   */
+  uint64_t off_rows, off_perm, off_cidx, blob_bytes;
+  void* blob;          /* device memory, blob_bytes long, 256-byte aligned               */
+} cq_rlayer;
+
+/* CQ_ERR_UNSUPPORTED when the layer has more than 32 cherry columns per K slice. */
+int cq_rlayer_init(cq_rlayer* layer, int bits, int K, int N, int C, int G, void* blob);
+int cq_rlayer_prepare(const cq_rlayer* layer, const uint8_t* qweight, const void* scales_f16,
+                      const void* cherry_weight_f16, const int16_t* cherry_indices,
+                      cq_stream_t stream);
+/* Inverse re-pack (byte-identical round trip). */
+int cq_rlayer_unprepare(const cq_rlayer* layer, uint8_t* qweight, void* scales_f16,
+                        void* cherry_weight_f16, int16_t* cherry_indices, cq_stream_t stream);
+/* y (N) fp16 = [y +] x (K) fp16 . W^T, one activation row; allocates nothing, needs no scratch.
+ * status_word: device uint32 that receives CQ_ERR_DEVICE_TIMEOUT bits if a bounded wait on the
+ * kernel's own bulk copies ever runs out; may be NULL. */
+int cq_rlayer_matvec(const cq_rlayer* layer, const void* x_f16, void* y_f16, int accumulate,
+                     uint32_t* status_word, cq_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Element-wise kernels of the decode harness around the quantized linear (fp16 in / out, fp32
  * arithmetic).  In the reference they are PyTorch ops of its vendored LLaMA
  * (llama/modeling_llama_quant.py: LlamaRMSNorm, apply_rotary_pos_emb, LlamaMLP.forward).
