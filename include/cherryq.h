@@ -141,21 +141,23 @@ int cq_layer_matvec_static(const cq_layer* layer, const void* x_f16, int ldx, vo
                            int M, int accumulate, uint32_t* status_word, cq_stream_t stream);
 
 /* ------------------------------------------------------------------------
- * Row-layout prepared layer: the format of the ONE-activation-row decode matvec (the batch-1 case
- * of csrc/quant_cuda_kernel.cu:718-835 and :558-672, :316-438 of the reference).  Every output row
- * is stored contiguously; within a row the compact columns are cut into K slices of at most 32
- * groups of 128 columns; a warp works on one (row, slice), its lane l on group l:
- * One record per output row, rec_bytes long, records back to back:
- *   codes   [slice][chunk j < bits][lane][16 B]   the lane's 128 codes = bits x 4 words
- *             4-bit: word w = columns 8w..8w+7, low nibble of byte b = column 8w+b, high = 8w+4+b
- *             3-bit: words A,B,C of a 32-column set: bits 0-2 / 4-6 of byte b of A,B,C = column
- *                    4f+b of fields f = 0..5; bit 3 (bit 7) of byte b of A,B,C = code bits 0,1,2
- *                    of column 24+b (28+b)
- *   scales  [group][set] fp16 (set = 64-column half, only for 64-wide groups), padded to 16 bytes
- *   cherry  [C] fp16
+ * Row-tile prepared layer: the format of the ONE-activation-row decode matvec (the batch-1 case
+ * of csrc/quant_cuda_kernel.cu:718-835 and :558-672, :316-438 of the reference).  Tiles of 16
+ * consecutive output rows, one contiguous record per tile, records back to back:
+ *   groups  [group of 128 compact columns][256 x bits bytes]: the 16 x 128 codes as A fragments of
+ *             mma.sync.m16n8k32 (u8).  Lane 4 g8 + t; register j of a 32-column chunk = row
+ *             g8 + 8 (j & 1), columns 16 (j >> 1) + 4 t + b in byte b.
+ *             4-bit: [load l = 0, 1][lane][16 B]; word j = register j of chunk 2 l (low nibbles)
+ *                    and of chunk 2 l + 1 (high nibbles).
+ *             3-bit: per 64-column half s words A, B, C: [lane][16 B] = A0 B0 C0 A1, then
+ *                    [lane][8 B] = B1 C1.  Word wi: register wi of chunk 2 s in bits 0-2 and of chunk
+ *                    2 s + 1 in bits 4-6 of its bytes; register 3 as bit planes: code bit wi of chunk
+ *                    2 s (2 s + 1) in bit 3 (bit 7) of word wi.
+ *   scales  [group][set][g8][row g8, row g8 + 8] fp16 (set = 64-column half, only for 64-wide groups)
+ *   cherry  [block of 16 cherry columns][lane][16 B]: A fragments of mma.sync.m16n8k16 (fp16)
  * followed by
  *   perm    [groups x 128] uint16: original column of each compact column, K past K'
- *   cidx    [C] uint16 sorted cherry columns
+ *   cidx    [Cp] uint16 sorted cherry columns, K past C
  * Same role as cq_layer; no scratch.
  * ---------------------------------------------------------------------- */
 typedef struct cq_rlayer {
@@ -163,17 +165,13 @@ typedef struct cq_rlayer {
   int32_t Kc;          /* K - C                                                          */
   int32_t NG;          /* 128-column groups per row = ceil(Kc / 128)                     */
   int32_t sets;        /* scale sets per group: 1 (G % 128 == 0) or 2 (G == 64)          */
-  int32_t nsl;         /* K slices = ceil(NG / 32)                                       */
-  int32_t gps;         /* groups per slice = ceil(NG / nsl)                              */
-  int32_t cps;         /* cherry columns per slice = ceil(C / nsl), at most 32           */
-  int32_t row_bytes;   /* code bytes of a record = NG * 16 * bits                        */
-  int32_t srow_bytes;  /* scale bytes of a record, padded to 16                          */
-  int32_t rec_bytes;   /* row_bytes + srow_bytes + 2 C                                   */
-  uint64_t off_rows, off_perm, off_cidx, blob_bytes;
+  int32_t Cp;          /* C rounded up to 16                                             */
+  int32_t NT;          /* 16-row tiles = ceil(N / 16)                                    */
+  int32_t tile_bytes;  /* NG * 256 * bits + NG * sets * 32 + Cp / 16 * 512               */
+  uint64_t off_tiles, off_perm, off_cidx, blob_bytes;
   void* blob;          /* device memory, blob_bytes long, 256-byte aligned               */
 } cq_rlayer;
 
-/* CQ_ERR_UNSUPPORTED when the layer has more than 32 cherry columns per K slice. */
 int cq_rlayer_init(cq_rlayer* layer, int bits, int K, int N, int C, int G, void* blob);
 int cq_rlayer_prepare(const cq_rlayer* layer, const uint8_t* qweight, const void* scales_f16,
                       const void* cherry_weight_f16, const int16_t* cherry_indices,
@@ -181,7 +179,13 @@ int cq_rlayer_prepare(const cq_rlayer* layer, const uint8_t* qweight, const void
 /* Inverse re-pack (byte-identical round trip). */
 int cq_rlayer_unprepare(const cq_rlayer* layer, uint8_t* qweight, void* scales_f16,
                         void* cherry_weight_f16, int16_t* cherry_indices, cq_stream_t stream);
+/* CQ_OK if cq_rlayer_matvec can run this layer on the current device, else the status it would
+ * return (CQ_ERR_UNSUPPORTED / CQ_ERR_TOO_LARGE); no GPU work. */
+int cq_rlayer_check(const cq_rlayer* layer);
 /* y (N) fp16 = [y +] x (K) fp16 . W^T, one activation row; allocates nothing, needs no scratch.
+ * CQ_ERR_UNSUPPORTED for layers outside the kernel's envelope (K - C > 14336 columns, more than 256
+ * cherry columns, or more than 248 cherry columns inside one warp's column range) and
+ * CQ_ERR_TOO_LARGE when not even two tiles fit shared memory: use cq_layer_matvec for those.
  * status_word: device uint32 that receives CQ_ERR_DEVICE_TIMEOUT bits if a bounded wait on the
  * kernel's own bulk copies ever runs out; may be NULL. */
 int cq_rlayer_matvec(const cq_rlayer* layer, const void* x_f16, void* y_f16, int accumulate,
@@ -262,7 +266,10 @@ int cq_tlayer_gemm(const cq_tlayer* layer, const void* x_f16, int ldx, void* y_f
  * `mul` is accumulated into (the caller pre-zeroes it, llama/qlinear.py:177).
  * The re-packed layer is cached inside the library, keyed by the four buffer
  * addresses, the dimensions and version_tag (pass any value that changes when
- * the buffers' contents change, e.g. a sum of tensor version counters).
+ * the buffers' contents change, e.g. a sum of tensor version counters); a copy
+ * is made per kernel family actually used (1 row / 2..7 rows / 8 rows and more).
+ * Addresses alone do not identify a buffer for ever: call cq_cache_evict when the
+ * buffers are freed or re-filled.
  * ---------------------------------------------------------------------- */
 int cq_vecquant4matmul_cherryq(const void* vec_f16, const uint8_t* qweight,
                                const void* cherry_weight_f16, const int16_t* cherry_indices,
@@ -294,6 +301,11 @@ int cq_dequantize4_normal(const uint8_t* qweight, const float* scaling_factors, 
 
 /* Drop every cached re-packed layer (frees device memory). */
 int cq_cache_clear(void);
+/* Drop the cached copies made from this set of buffer addresses on the current device (the
+ * reference's ops keep no references, csrc/quant_cuda.cpp:56-69: a caller that frees or re-uses
+ * the buffers tells the cache so; the torch module does it by watching the tensors' storages). */
+int cq_cache_evict(const void* qweight, const void* scales_f16, const void* cherry_weight_f16,
+                   const void* cherry_indices);
 /* Number of cached layers and the bytes they hold. */
 int cq_cache_stats(int* n_layers, uint64_t* bytes);
 

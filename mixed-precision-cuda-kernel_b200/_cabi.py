@@ -15,13 +15,14 @@ SYMBOLS = [
     "cq_layer_init", "cq_layer_prepare", "cq_layer_unprepare", "cq_scratch_bytes", "cq_layer_matvec",
     "cq_vecquant4matmul_cherryq", "cq_vecquant3matmul_cherryq",
     "cq_dequantize3_normal", "cq_dequantize4_normal",
-    "cq_cache_clear", "cq_cache_stats", "cq_poll",
+    "cq_cache_clear", "cq_cache_stats", "cq_cache_evict", "cq_poll",
     "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense", "cq_trace_set_timeline",
     "cq_tlayer_init", "cq_tlayer_prepare", "cq_tlayer_unprepare", "cq_tlayer_matvec",
     "cq_layer_matvec_static", "cq_tlayer_gemm_workspace_bytes", "cq_tlayer_gemm",
     "cq_selftest_bounded_wait", "cq_rmsnorm", "cq_rope_cache", "cq_silu_mul", "cq_attn_decode",
     "cq_peer_region_bytes", "cq_peer_region_create", "cq_peer_region_destroy", "cq_peer_region_export",
     "cq_peer_region_open", "cq_peer_region_close", "cq_peer_allgather",
+    "cq_rlayer_init", "cq_rlayer_prepare", "cq_rlayer_unprepare", "cq_rlayer_check", "cq_rlayer_matvec",
 ]
 
 
@@ -37,6 +38,13 @@ class cq_tlayer(C.Structure):
                 ("bits", "K", "N", "C", "G", "Kc", "Kp", "Cp", "n_gran", "n_tile", "n_cher", "sets", "gran_bytes",
                  "tile_bytes")]
     _fields_ += [(n, C.c_uint64) for n in ("off_stream", "off_cidx", "off_osh", "blob_bytes")]
+    _fields_ += [("blob", C.c_void_p)]
+
+
+class cq_rlayer(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("bits", "K", "N", "C", "G", "Kc", "NG", "sets", "Cp", "NT", "tile_bytes")]
+    _fields_ += [(n, C.c_uint64) for n in ("off_tiles", "off_perm", "off_cidx", "blob_bytes")]
     _fields_ += [("blob", C.c_void_p)]
 
 
@@ -62,6 +70,11 @@ def lib():
     L.cq_layer_unprepare.argtypes = [C.POINTER(cq_layer), vp, vp, vp, vp, vp]
     L.cq_layer_matvec.argtypes = [C.POINTER(cq_layer), vp, i32, vp, i32, i32, i32, vp, vp, vp]
     L.cq_layer_matvec_static.argtypes = [C.POINTER(cq_layer), vp, i32, vp, i32, i32, i32, vp, vp]
+    L.cq_rlayer_init.argtypes = [C.POINTER(cq_rlayer), i32, i32, i32, i32, i32, vp]
+    L.cq_rlayer_prepare.argtypes = [C.POINTER(cq_rlayer), vp, vp, vp, vp, vp]
+    L.cq_rlayer_unprepare.argtypes = [C.POINTER(cq_rlayer), vp, vp, vp, vp, vp]
+    L.cq_rlayer_check.argtypes = [C.POINTER(cq_rlayer)]
+    L.cq_rlayer_matvec.argtypes = [C.POINTER(cq_rlayer), vp, vp, i32, vp, vp]
     L.cq_tlayer_init.argtypes = [C.POINTER(cq_tlayer), i32, i32, i32, i32, i32, vp]
     L.cq_tlayer_prepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]
     L.cq_tlayer_unprepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]
@@ -74,6 +87,7 @@ def lib():
     L.cq_dequantize3_normal.argtypes = [vp, vp, vp] + [i32] * 5 + [vp]
     L.cq_dequantize4_normal.argtypes = [vp, vp, vp] + [i32] * 5 + [vp]
     L.cq_cache_stats.argtypes = [C.POINTER(C.c_int), C.POINTER(C.c_uint64)]
+    L.cq_cache_evict.argtypes = [vp, vp, vp, vp]
     L.cq_poll.argtypes = [vp]
     L.cq_trace_set_timeline.argtypes = [vp]
     L.cq_pack.argtypes = [vp, i32, vp] + [i32] * 5 + [vp] * 6
@@ -103,6 +117,12 @@ def check(rc: int, what: str = "cherryq"):
 def layer_init(bits, K, N, Cn, G, blob_ptr=None) -> cq_layer:
     L = cq_layer()
     check(lib().cq_layer_init(C.byref(L), bits, K, N, Cn, G, blob_ptr), "cq_layer_init")
+    return L
+
+
+def rlayer_init(bits, K, N, Cn, G, blob_ptr=None) -> cq_rlayer:
+    L = cq_rlayer()
+    check(lib().cq_rlayer_init(C.byref(L), bits, K, N, Cn, G, blob_ptr), "cq_rlayer_init")
     return L
 
 

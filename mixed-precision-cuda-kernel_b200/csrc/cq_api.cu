@@ -1,9 +1,13 @@
 // extern "C" entry points that keep the reference's operator signatures
 // (csrc/quant_cuda.cpp:41-69 of the reference project) on top of the prepared
-// layer interface: the first call with a given set of reference buffers re-packs
-// them on the GPU into the stream layout and caches the result; every call then
-// runs the stream matvec.  Calls with 8 or more activation rows (large decode batches, prefill) take the tensor-core
-// GEMM on a second cached copy in the tile layout.
+// layer interfaces: the first call with a given set of reference buffers re-packs
+// them on the GPU into the layout of the kernel that serves the call's batch size
+// and caches the result.  One activation row: row-tile layout (cq_rlayer) when the
+// layer fits that kernel; 2..7 rows (and the layers it does not fit): stream layout
+// (cq_layer); 8 rows or more (large decode batches, prefill): tile layout and the
+// tensor-core GEMM.  A layer only pays for the layouts it is actually called with.
+// cq_cache_evict drops the copies of one buffer set (the torch shim calls it when
+// the tensors behind a cached address have been freed).
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -45,6 +49,7 @@ constexpr int PREFILL_CHUNK_ROWS = 4096;  // rows per GEMM call (bounds the work
 std::mutex g_mu;
 std::map<CacheKey, cq_layer> g_cache;
 std::map<CacheKey, cq_tlayer> g_tcache;
+std::map<CacheKey, cq_rlayer> g_rcache;
 std::map<int, DeviceState> g_dev;
 
 int device_state(int dev, DeviceState* out) {
@@ -124,6 +129,31 @@ int legacy_matmul(int bits, const void* vec, const uint8_t* qweight, const void*
                      cherry_size, group_size, tag};
   if (batch >= PREFILL_MIN_ROWS)
     return legacy_gemm(key, dev, vec, qweight, cherry_weight, cherry_indices, scales, mul, batch, ds.status, st);
+  if (batch == 1) {
+    auto rit = g_rcache.find(key);
+    if (rit == g_rcache.end()) {
+      cq_rlayer R;
+      rc = cq_rlayer_init(&R, bits, vec_height, width, cherry_size, group_size, nullptr);
+      if (rc == CQ_OK) rc = cq_rlayer_check(&R);
+      if (rc == CQ_OK) {
+        void* blob = nullptr;
+        CQ_CUDA_TRY(cudaMalloc(&blob, R.blob_bytes));
+        R.blob = blob;
+        rc = cq_rlayer_prepare(&R, qweight, scales, cherry_weight, cherry_indices, st);
+        if (rc) {
+          cudaFree(blob);
+          return rc;
+        }
+        // the kernel copies weights ahead of stream order: finish the re-pack first
+        CQ_CUDA_TRY(cudaStreamSynchronize(st));
+        rit = g_rcache.emplace(key, R).first;
+      } else if (rc != CQ_ERR_UNSUPPORTED && rc != CQ_ERR_TOO_LARGE) {
+        return rc;
+      }
+    }
+    if (rit != g_rcache.end())
+      return cq_rlayer_matvec(&rit->second, vec, mul, /*accumulate=*/1, ds.status, st);
+  }
   auto it = g_cache.find(key);
   if (it == g_cache.end()) {
     cq_layer L;
@@ -151,7 +181,7 @@ int legacy_matmul(int bits, const void* vec, const uint8_t* qweight, const void*
 void cq_set_cuda_error(int err) { g_last_cuda_error = err; }
 
 extern "C" int cq_last_cuda_error(void) { return g_last_cuda_error; }
-extern "C" int cq_abi_version(void) { return 1; }
+extern "C" int cq_abi_version(void) { return 2; }
 
 extern "C" const char* cq_strerror(int status) {
   switch (status) {
@@ -224,6 +254,42 @@ extern "C" int cq_cache_clear(void) {
     if (cur != kv.first.dev) cudaSetDevice(cur);
   }
   g_tcache.clear();
+  for (auto& kv : g_rcache) {
+    int cur = 0;
+    cudaGetDevice(&cur);
+    if (cur != kv.first.dev) cudaSetDevice(kv.first.dev);
+    cudaFree(kv.second.blob);
+    if (cur != kv.first.dev) cudaSetDevice(cur);
+  }
+  g_rcache.clear();
+  return CQ_OK;
+}
+
+// Drops every cached copy made from this set of buffer addresses on the current device
+// (any dimensions, any tag).  Synchronises the device first: a launch may still read a copy.
+extern "C" int cq_cache_evict(const void* qweight, const void* scales, const void* cherry_weight,
+                              const void* cherry_indices) {
+  int dev = 0;
+  CQ_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto match = [&](const CacheKey& k) {
+    return k.dev == dev && k.q == qweight && k.s == scales && k.cw == cherry_weight && k.idx == cherry_indices;
+  };
+  bool synced = false;
+  auto drop = [&](auto& cache) {
+    for (auto it = cache.begin(); it != cache.end();) {
+      if (match(it->first)) {
+        if (!synced) { cudaDeviceSynchronize(); synced = true; }
+        cudaFree(it->second.blob);
+        it = cache.erase(it);
+      } else {
+        ++it;
+      }
+    }
+  };
+  drop(g_cache);
+  drop(g_tcache);
+  drop(g_rcache);
   return CQ_OK;
 }
 
@@ -232,7 +298,8 @@ extern "C" int cq_cache_stats(int* n_layers, uint64_t* bytes) {
   uint64_t b = 0;
   for (auto& kv : g_cache) b += kv.second.blob_bytes;
   for (auto& kv : g_tcache) b += kv.second.blob_bytes;
-  if (n_layers) *n_layers = (int)(g_cache.size() + g_tcache.size());
+  for (auto& kv : g_rcache) b += kv.second.blob_bytes;
+  if (n_layers) *n_layers = (int)(g_cache.size() + g_tcache.size() + g_rcache.size());
   if (bytes) *bytes = b;
   return CQ_OK;
 }

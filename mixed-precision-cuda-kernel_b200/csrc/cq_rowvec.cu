@@ -1,48 +1,64 @@
-// Row-layout decode matvec: y (1, N) fp16 = [y +] x (1, K) fp16 . W^T for ONE activation row.
+// Decode matvec for ONE activation row: y (1, N) fp16 = [y +] x (1, K) fp16 . W^T.
 //
 // Replaces the reference's batch-1 use of VecQuant4MatMulKernelCherryQBatchedHalf and
 // VecQuant3MatMulKernelCherryQBatched(G64)Half (csrc/quant_cuda_kernel.cu:718-835, 558-672,
 // 316-438 of the reference project): one thread per output column there, byte loads at stride N,
-// fp16 atomics.  Here:
+// fp16 atomics.
 //
-//   * layout: every output row is one contiguous record (cq_rlayer, include/cherryq.h).  A CTA
-//     owns a contiguous range of rows, i.e. one contiguous byte range of the layer, a warp owns
-//     whole rows, lane l owns the 128 compact columns of group l of its K slice;
-//   * the CTA's byte range is requested with a handful of bulk async copies (cp.async.bulk +
-//     mbarrier transaction counts) into shared memory the moment the CTA starts, BEFORE it waits
-//     for the previous kernel in the stream (programmatic dependent launch): weights are
-//     constants, only x is not.  HBM streams while the activations are staged; the rows are then
-//     read from shared memory with conflict-free 16-byte loads.  Rows beyond the shared-memory
-//     capacity (large layers) are read from global memory with a register pipeline D rows deep;
-//   * the activations of a lane never change from row to row: they sit in registers for the whole
-//     kernel as two signed-byte planes (q = 128 hi + lo, |q| <= 16256, one step size per group),
-//     so a row costs two masks and four integer dot products (dp4a, u8 x s8) per 8 weights:
-//         sum_k (u_k - off) x_k = sx (sum u q - off sum q),  sum u q exact in 32-bit integers;
-//   * no cross-CTA traffic, no atomics, no scratch: a row's partial sums meet in one warp
-//     (shuffles) or, for K > 4096 (several slices), in the CTA's shared memory, in a fixed order.
+// What bounds a batch-1 matvec in a chain of dependent launches is not only the bytes: every CTA
+// has to wait for the previous kernel (about 1.3 us after its last CTA left), and everything that
+// needs x is serial after that wait.  The kernel is built around making that serial part short:
+//
+//   * layout (cq_rlayer, include/cherryq.h): tiles of 16 output rows, one contiguous record per
+//     tile; a CTA owns consecutive tiles, i.e. one contiguous byte range.  It asks for that range
+//     with bulk async copies (cp.async.bulk + mbarrier transaction counts) into shared memory the
+//     moment it starts, BEFORE the dependency wait: weights are constants, only x is not.  HBM
+//     streams while the CTA waits and stages.  A ring of tile slots serves layers whose share
+//     exceeds shared memory;
+//   * K is split over the warps of the CTA: warp w owns a few 128-column groups of EVERY tile.
+//     So a warp needs only its own slice of x: it loads that slice itself (coalesced, no
+//     CTA-wide barrier), quantises it to two signed-byte planes (q = 128 hi + lo, |q| <= 16256,
+//     one step size per group) and keeps the result as B fragments of the integer tensor-core
+//     instruction mma.sync.m16n8k32 (u8 x s8 -> s32) in registers for the whole kernel;
+//   * per tile and group a lane reads 32 (4-bit) / 24 (3-bit) bytes, masks them into A fragments
+//     (one logic operation per four codes; the high nibbles stay where they are, as 16 u) and
+//     issues four MMAs; columns 0 / 1 of B carry the hi / lo plane, so the sums are exact:
+//         sum_k (u_k - off) x_k = sx (128 sum u hi + sum u lo) - off sx sum q;
+//     cherry columns are one fp16 mma.sync.m16n8k16 per tile;
+//   * the warps' partial sums of a tile meet in shared memory and are added in a fixed order:
+//     no atomics, no scratch, no cross-CTA traffic, bit-identical runs.
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "cq_common.cuh"
 
 namespace {
 
-constexpr int RV_NBAR = 32;                 // mbarriers (groups of row iterations) per CTA
+#ifndef CQ_ROWVEC_INFLIGHT
+#define CQ_ROWVEC_INFLIGHT 0   // tiles the copy warp keeps outstanding; 0 = chosen per layer
+#endif
 constexpr uint32_t RV_WAIT_LIMIT = 1u << 22;
+constexpr int RV_MAX_SLOTS = 16;            // ring slots (tiles resident in shared memory at a time)
 
 struct RowvecParams {
-  const uint8_t* rows;      // records: [codes row_bytes][scales srow_bytes][cherry 2 C]
-  const uint16_t* perm;
-  const uint16_t* cidx;
+  const uint8_t* tiles;     // tile records: [NG groups][scales][cherry blocks]
+  const uint16_t* perm;     // [NG * 128] original column of each compact column, K for padding
+  const uint16_t* cidx;     // [Cp] sorted cherry columns
   const __half* x;
   __half* y;
   uint32_t* status;         // may be null
-  int K, N, C, NG, nsl, gps, cps, accumulate;
-  int row_bytes, srow_bytes, rec_bytes;
-  int rows_q, rows_r;       // CTA b owns rows_q (+1 if b < rows_r) consecutive rows
-  int smem_rows;            // rows of a CTA that fit its shared-memory row area
-  int pre_pct;              // share (percent) of the shared-memory rows requested before the dependency wait
-  int l2_prefetch;          // the rest is asked into L2 at once (1) or not (0)
-  int off_planes, off_sx, off_part, off_bar, off_rows;    // shared-memory sections (bytes)
+  int K, N, C, NG, ncb;     // ncb = cherry blocks of 16 columns
+  int tile_bytes, scal_off, cher_off;
+  int tiles_q, tiles_r;     // CTA b owns tiles_q (+1 if b < tiles_r) consecutive tiles
+  int slots;                // ring slots in use
+  int inflight;             // tiles the copy warp keeps outstanding
+  int slice_halves;         // halves of a warp's raw activation slice in shared memory
+  int off_slice, off_part, off_bar, off_tiles;   // shared-memory sections (bytes)
+  int accumulate;
 #ifdef CQ_ROWVEC_TRACE
   int trace_launch;
+  unsigned long long* trace;   // passed as a kernel parameter: a stamp must not cost a global load
 #endif
 };
 
@@ -53,6 +69,9 @@ __device__ __forceinline__ void rv_mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void rv_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void rv_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool rv_mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -90,451 +109,402 @@ __device__ __forceinline__ void rv_bulk_g2s(uint32_t dst, const void* src, uint3
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
+// D (16 x 8, s32) += A (16 x 32, u8) . B (32 x 8, s8)
+__device__ __forceinline__ void rv_imma(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t ldg_stream4(const void* p) {
-  uint32_t v;
-  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
+// D (16 x 8, f32) += A (16 x 16, f16) . B (16 x 8, f16)
+__device__ __forceinline__ void rv_hmma(float (&d)[4], const uint4 a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t ldg_stream2(const void* p) {
-  uint16_t v;
-  asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
-  int d;
-  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ float h2f_bits(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
 
-// 16 x sum over one half group (64 columns) of u_k q_k, for both halves of a lane's 128 columns.
-//   4-bit word w (columns 8w .. 8w+7): low nibbles of its bytes = columns 8w..8w+3, high nibbles =
-//   columns 8w+4..8w+7; the high nibbles are used where they are (16 u), hence the factor 16.
-//   3-bit words A, B, C of a 32-column set: bits 0-2 / 4-6 of byte b = columns 4f + b of fields
-//   f = 0..5, bit 3 / bit 7 of the three words = bit planes of fields 6 / 7.
-template <int BITS>
-__device__ __forceinline__ void dot_halves(const uint32_t (&w)[4 * BITS], const int (&xh)[32], const int (&xl)[32],
-                                           int (&t)[2]) {
-  int a1h[2] = {0, 0}, a1l[2] = {0, 0}, a16h[2] = {0, 0}, a16l[2] = {0, 0};
-#ifdef CQ_ROWVEC_NOCOMPUTE   // tuning builds: loads only
-  {
-    uint32_t v = 0;
-#pragma unroll
-    for (int i = 0; i < 4 * BITS; ++i) v ^= w[i];
-    t[0] = (int)v + xh[0]; t[1] = xl[0];
-    return;
+#ifdef CQ_ROWVEC_TRACE   // tuning builds: per-CTA stamps, buffer [16 launches][1024 CTAs][16]
+// Slot 0 holds %globaltimer at entry (one slow read), slot 1 the SM cycle counter at entry; every other slot
+// holds the cycle counter (cheap), so intervals inside a CTA are not distorted by the stamping itself.
+unsigned long long* cq_rv_trace_host = nullptr;
+__device__ __forceinline__ void rv_stamp_to(unsigned long long* buf, int launch, int slot) {
+  if (buf) {
+    unsigned long long* row = buf + ((size_t)(launch & 15) * 1024 + blockIdx.x) * 16;
+    if (slot == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      row[0] = t;
+      row[1] = (unsigned long long)clock64();
+    } else {
+      row[slot] = (unsigned long long)clock64();
+    }
   }
+}
+#ifndef CQ_ROWVEC_TRACE_TID
+#define CQ_ROWVEC_TRACE_TID 0
 #endif
-  if (BITS == 4) {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int h = i >> 3;
-      const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = w[i] & 0xF0F0F0F0u;
-      a1h[h] = dp4a_us(lo, xh[2 * i], a1h[h]);
-      a1l[h] = dp4a_us(lo, xl[2 * i], a1l[h]);
-      a16h[h] = dp4a_us(hi, xh[2 * i + 1], a16h[h]);
-      a16l[h] = dp4a_us(hi, xl[2 * i + 1], a16l[h]);
-    }
-  } else {
-#pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      const int h = s >> 1, xb = 8 * s;
-      const uint32_t A = w[3 * s], B = w[3 * s + 1], Cw = w[3 * s + 2];
-      const uint32_t f0 = A & 0x07070707u, f1 = A & 0x70707070u;
-      const uint32_t f2 = B & 0x07070707u, f3 = B & 0x70707070u;
-      const uint32_t f4 = Cw & 0x07070707u, f5 = Cw & 0x70707070u;
-      const uint32_t f6 = ((A >> 3) & 0x01010101u) | ((B >> 2) & 0x02020202u) | ((Cw >> 1) & 0x04040404u);
-      const uint32_t f7 = ((A >> 7) & 0x01010101u) | ((B >> 6) & 0x02020202u) | ((Cw >> 5) & 0x04040404u);
-      a1h[h] = dp4a_us(f0, xh[xb + 0], a1h[h]);   a1l[h] = dp4a_us(f0, xl[xb + 0], a1l[h]);
-      a16h[h] = dp4a_us(f1, xh[xb + 1], a16h[h]); a16l[h] = dp4a_us(f1, xl[xb + 1], a16l[h]);
-      a1h[h] = dp4a_us(f2, xh[xb + 2], a1h[h]);   a1l[h] = dp4a_us(f2, xl[xb + 2], a1l[h]);
-      a16h[h] = dp4a_us(f3, xh[xb + 3], a16h[h]); a16l[h] = dp4a_us(f3, xl[xb + 3], a16l[h]);
-      a1h[h] = dp4a_us(f4, xh[xb + 4], a1h[h]);   a1l[h] = dp4a_us(f4, xl[xb + 4], a1l[h]);
-      a16h[h] = dp4a_us(f5, xh[xb + 5], a16h[h]); a16l[h] = dp4a_us(f5, xl[xb + 5], a16l[h]);
-      a1h[h] = dp4a_us(f6, xh[xb + 6], a1h[h]);   a1l[h] = dp4a_us(f6, xl[xb + 6], a1l[h]);
-      a1h[h] = dp4a_us(f7, xh[xb + 7], a1h[h]);   a1l[h] = dp4a_us(f7, xl[xb + 7], a1l[h]);
-    }
-  }
-#pragma unroll
-  for (int h = 0; h < 2; ++h) t[h] = ((a1h[h] * 128 + a1l[h]) << 4) + (a16h[h] * 128 + a16l[h]);
-}
-
-#ifdef CQ_ROWVEC_TRACE   // tuning builds: %globaltimer stamps per CTA, buffer [16 launches][1024 CTAs][16]
-__device__ unsigned long long* cq_rv_trace = nullptr;
-__device__ __forceinline__ void rv_stamp(int launch, int slot) {
-  if (cq_rv_trace && threadIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    cq_rv_trace[((size_t)(launch & 15) * 1024 + blockIdx.x) * 16 + slot] = t;
-  }
-}
-#define RV_STAMP(s) rv_stamp(p.trace_launch, s)
+__device__ __forceinline__ void rv_stamp(unsigned long long* buf, int launch, int slot) { if (threadIdx.x == CQ_ROWVEC_TRACE_TID) rv_stamp_to(buf, launch, slot); }
+#define RV_STAMP(s) rv_stamp(p.trace, p.trace_launch, s)
 #else
 #define RV_STAMP(s)
 #endif
 
-// Quantises octet o of the compact activations (columns `cols` of the fp16 row in shared memory)
-// and stores its bytes of the two planes; the first thread of a group also stores the group's
-// step and offset terms.  All 32 lanes of a warp call it.
-template <int SETS>
-__device__ __forceinline__ void stage_octet(const __half* raw, const uint4 cols, int o, int n_oct, int NG, float OFF,
-                                            unsigned char* planes, float* gsx, float* gcq) {
-  const uint32_t pw[4] = {cols.x, cols.y, cols.z, cols.w};
-  float v[8];
-  float m = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t col = (pw[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
-    v[i] = __half2float(raw[col]);                 // padding columns point at the zero slot raw[K]
-    m = fmaxf(m, fabsf(v[i]));
-  }
-#pragma unroll
-  for (int s = 1; s < 16; s <<= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, s));
-  const float step = m * (1.0f / 16256.0f);
-  const float inv = m > 0.f ? 16256.0f / m : 0.f;
-  uint32_t hi[8], lo[8];
-  int sq = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int q = __float2int_rn(v[i] * inv);
-    const int t = q + 64;
-    hi[i] = (uint32_t)(t >> 7);                    // floor((q + 64) / 128) in [-127, 127]
-    lo[i] = (uint32_t)((t & 127) - 64);            // q - 128 hi in [-64, 63]
-    sq += q;
-  }
-  uint32_t hw[2], lw[2];
-#pragma unroll
-  for (int k = 0; k < 2; ++k) {                    // low bytes of four values -> one word
-    hw[k] = __byte_perm(__byte_perm(hi[4 * k], hi[4 * k + 1], 0x0040), __byte_perm(hi[4 * k + 2], hi[4 * k + 3], 0x0040), 0x5410);
-    lw[k] = __byte_perm(__byte_perm(lo[4 * k], lo[4 * k + 1], 0x0040), __byte_perm(lo[4 * k + 2], lo[4 * k + 3], 0x0040), 0x5410);
-  }
-  // sums of q over the two 64-column halves of the group
-  sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 1);
-  sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 2);
-  sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 4);
-  const int sq_other = __shfl_xor_sync(0xFFFFFFFFu, sq, 8);
-  if (o < n_oct) {
-    const int gg = o >> 4, oo = o & 15;
-    unsigned char* dst = planes + ((size_t)(oo >> 1) * NG + gg) * 16 + (oo & 1) * 8;
-    *reinterpret_cast<uint2*>(dst) = make_uint2(hw[0], hw[1]);
-    *reinterpret_cast<uint2*>(dst + (size_t)8 * NG * 16) = make_uint2(lw[0], lw[1]);
-    if (oo == 0) {
-      gsx[gg] = step * (1.0f / 16.0f);
-      if (SETS == 2) {
-        gcq[2 * gg] = -OFF * step * (float)sq;
-        gcq[2 * gg + 1] = -OFF * step * (float)sq_other;
-      } else {
-        gcq[gg] = -OFF * step * (float)(sq + sq_other);
-      }
-    }
+// Requests tile `tile` of the layer into ring slot `slot`; one thread calls it.
+__device__ __forceinline__ void issue_tile(const RowvecParams& p, unsigned char* stiles, uint32_t bar_full, int tile, int slot) {
+  const uint8_t* src = p.tiles + (size_t)tile * p.tile_bytes;
+  const uint32_t dst = rv_smem_u32(stiles) + (uint32_t)slot * p.tile_bytes;
+  const uint32_t bar = bar_full + 8 * slot;
+  rv_mbar_expect_tx(bar, (uint32_t)p.tile_bytes);
+  for (uint32_t off = 0; off < (uint32_t)p.tile_bytes; off += 32768) {
+    const uint32_t sz = (uint32_t)p.tile_bytes - off < 32768 ? (uint32_t)p.tile_bytes - off : 32768;
+    rv_bulk_g2s(dst + off, src + off, sz, bar);
   }
 }
 
-// One row of one lane: the integer dot products, the group's scale(s), the cherry product.
-template <int BITS, int SETS>
-__device__ __forceinline__ float row_value(const uint32_t (&w)[4 * BITS], uint32_t scw, uint32_t chw, const int (&xh)[32],
-                                           const int (&xl)[32], float sx16, float cq0, float cq1, float xc, bool lane_on) {
-  int t[2];
-  dot_halves<BITS>(w, xh, xl, t);
-  float acc;
-  if (SETS == 2) {
-    acc = h2f_bits(scw & 0xFFFFu) * fmaf((float)t[0], sx16, cq0) + h2f_bits(scw >> 16) * fmaf((float)t[1], sx16, cq1);
-  } else {
-    acc = h2f_bits(scw & 0xFFFFu) * fmaf((float)(t[0] + t[1]), sx16, cq0);
-  }
-  acc = lane_on ? acc : 0.f;
-  return fmaf(h2f_bits(chw & 0xFFFFu), xc, acc);
-}
-
-// Sums R per-lane values over the 32 lanes; afterwards lane (32 / R) * r holds the total of value r.
-template <int R>
-__device__ __forceinline__ float reduce_rows(const float (&acc)[R], int lane) {
-  if (R == 4) {
-    const bool b4 = lane & 16, b3 = lane & 8;
-    float a = (b4 ? acc[2] : acc[0]) + __shfl_xor_sync(0xFFFFFFFFu, b4 ? acc[0] : acc[2], 16);
-    float b = (b4 ? acc[3] : acc[1]) + __shfl_xor_sync(0xFFFFFFFFu, b4 ? acc[1] : acc[3], 16);
-    float c = (b3 ? b : a) + __shfl_xor_sync(0xFFFFFFFFu, b3 ? a : b, 8);
-    c += __shfl_xor_sync(0xFFFFFFFFu, c, 4);
-    c += __shfl_xor_sync(0xFFFFFFFFu, c, 2);
-    c += __shfl_xor_sync(0xFFFFFFFFu, c, 1);
-    return c;
-  } else if (R == 2) {
-    const bool b4 = lane & 16;
-    float c = (b4 ? acc[1] : acc[0]) + __shfl_xor_sync(0xFFFFFFFFu, b4 ? acc[0] : acc[1], 16);
-#pragma unroll
-    for (int s = 8; s >= 1; s >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, s);
-    return c;
-  } else {
-    float c = acc[0];
-#pragma unroll
-    for (int s = 16; s >= 1; s >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, s);
-    return c;
-  }
-}
-
-// Requests the CTA's records of barriers [b0, b1) from global memory, in the order the warps
-// consume them; one thread calls it.
-__device__ __noinline__ void issue_rows(const RowvecParams& p, unsigned char* srows, uint32_t bar0, int r0, int n_smem,
-                                        int rows_per_bar, int b0, int b1) {
-  const uint8_t* src = p.rows + (size_t)r0 * p.rec_bytes;
-  const uint32_t dst = rv_smem_u32(srows);
-  for (int b = b0; b < b1; ++b) {
-    const int ra = b * rows_per_bar, rb = min(n_smem, ra + rows_per_bar);
-    const uint32_t bytes = (uint32_t)(rb - ra) * p.rec_bytes;
-    rv_mbar_expect_tx(bar0 + 8 * b, bytes);
-    for (uint32_t off = 0; off < bytes; off += 32768) {
-      const uint32_t sz = bytes - off < 32768 ? bytes - off : 32768;
-      rv_bulk_g2s(dst + (uint32_t)ra * p.rec_bytes + off, src + (size_t)ra * p.rec_bytes + off, sz, bar0 + 8 * b);
-    }
-  }
-}
-
-// BITS 3 | 4; SETS scale sets per 128 columns (2 for 64-wide groups); W warps per CTA;
-// D rows of a lane in flight on the global-memory path (0: the kernel has no such path and every
-// row of the CTA must fit shared memory); R rows of a warp are worked on together.
-template <int BITS, int SETS, int W, int D, int R>
-__global__ void __launch_bounds__(W * 32, 1) cq_rowvec_kernel(const RowvecParams p) {
+// BITS 3 | 4; SETS scale sets per 128 columns (2 for 64-wide groups); W working warps per CTA plus
+// one warp that only issues the bulk copies (a bulk copy instruction blocks its thread while
+// the copy queue is full, i.e. for most of the streaming time: that thread must not have other
+// work); GPW groups of 128 columns a warp can own (its activations stay in 8 * GPW registers).
+template <int BITS, int SETS, int W, int GPW>
+__global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const RowvecParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
-  constexpr int J = BITS;              // 16-byte chunks per lane and row
-  constexpr int NW = 4 * BITS;         // 32-bit words per lane and row
-  constexpr int NTHR = W * 32;
-  constexpr int DG = D > 0 ? D : 1;
+  constexpr int NTHR = (W + 1) * 32;
+  constexpr int GRP_BYTES = 256 * BITS;      // 16 rows x 128 codes
+  constexpr int PVW = (GPW + 1) / 2;         // octets of activations a lane stages (16 per group, 32 lanes)
+  constexpr int XCH = GPW / 2 + 1;           // 16-byte pieces of the raw slice a lane loads
   constexpr float OFF = BITS == 4 ? 7.5f : 3.5f;
-  constexpr int PV = 4;                // octets of activations a thread stages with preloaded column lists
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g8 = lane >> 2, t4 = lane & 3;
   RV_STAMP(0);
 
-  __half* raw = reinterpret_cast<__half*>(smem);
-  unsigned char* planes = smem + p.off_planes;
-  float* gsx = reinterpret_cast<float*>(smem + p.off_sx);   // [NG]      step / 16 of the group's activations
-  float* gcq = gsx + p.NG;                                   // [NG][SETS] -off * step * sum q
+  __half* slice = reinterpret_cast<__half*>(smem + p.off_slice) + (size_t)warp * p.slice_halves;
+  uint32_t* plane = reinterpret_cast<uint32_t*>(slice);      // the planes replace the raw slice once it has been read
   float* part = reinterpret_cast<float*>(smem + p.off_part);
-  const uint32_t bar0 = rv_smem_u32(smem + p.off_bar);
-  unsigned char* srows = smem + p.off_rows;
+  const uint32_t bar_full = rv_smem_u32(smem + p.off_bar);
+  const uint32_t bar_empty = bar_full + 8 * RV_MAX_SLOTS;
+  unsigned char* stiles = smem + p.off_tiles;
 
-  const int NG = p.NG, nsl = p.nsl;
-  const int r0 = (int)blockIdx.x * p.rows_q + min((int)blockIdx.x, p.rows_r);
-  const int r1 = r0 + p.rows_q + ((int)blockIdx.x < p.rows_r ? 1 : 0);
-  const int RL = W / nsl;                         // warps that work on different rows at a time
-  const int n_smem = min(r1 - r0, p.smem_rows);   // rows of this CTA that go through shared memory
-  // rows are handed out in iterations of RL rows; a barrier covers `ipb` iterations
-  const int smem_iters = (n_smem + RL - 1) / RL;
-  const int ipb = max(1, (smem_iters + RV_NBAR - 1) / RV_NBAR);
+  const int tile0 = (int)blockIdx.x * p.tiles_q + min((int)blockIdx.x, p.tiles_r);
+  const int nt = p.tiles_q + ((int)blockIdx.x < p.tiles_r ? 1 : 0);
+  const int S = p.slots;
 
-  const int rows_per_bar = ipb * RL;
-  const int nbar = (n_smem + rows_per_bar - 1) / rows_per_bar;      // barriers in use
-  const int nbar_pre = (nbar * p.pre_pct + 99) / 100;               // ... requested before the wait
   if (tid == 0) {
     s_abort = 0;
-    for (int b = 0; b < RV_NBAR; ++b) rv_mbar_init(bar0 + 8 * b, 1);
+    for (int s = 0; s < S; ++s) {
+      rv_mbar_init(bar_full + 8 * s, 1);
+      rv_mbar_init(bar_empty + 8 * s, W);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    issue_rows(p, srows, bar0, r0, n_smem, rows_per_bar, 0, nbar_pre);
   }
-  if (p.l2_prefetch && nbar_pre < nbar) {
-    // the records that are copied after the wait: ask for them to be brought into L2 meanwhile
-    const uint8_t* lo = p.rows + ((size_t)r0 + (size_t)nbar_pre * rows_per_bar) * p.rec_bytes;
-    const uint8_t* hi = p.rows + ((size_t)r0 + n_smem) * p.rec_bytes;
-    for (const uint8_t* a = lo + (size_t)tid * 128; a < hi; a += (size_t)NTHR * 128)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-  }
-
-  const int sl = warp % nsl, rl = warp / nsl;     // K slice and row lane of this warp
-  const int g0 = sl * p.gps;
-  const int gcount = min(p.gps, NG - g0);
-  const bool lane_on = lane < gcount;
-  const int g = lane_on ? g0 + lane : g0;
-  const int c0 = sl * p.cps;
-  const bool cher_on = lane < min(p.cps, p.C - c0);
-  const int nrows = rl < RL ? max(0, (r1 - r0 - rl + RL - 1) / RL) : 0;          // rows of this warp
-  const int nrows_s = rl < RL ? max(0, (n_smem - rl + RL - 1) / RL) : 0;        // ... of which from shared memory
-
-  // byte offsets inside a record
-  const int woff = g0 * (16 * BITS) + (lane_on ? lane : 0) * 16;   // idle lanes re-read lane 0's bytes and drop the result
-  const int jstride = gcount * 16;
-  const int soff = p.row_bytes + g * (2 * SETS);
-  const int coff = cher_on ? p.row_bytes + p.srow_bytes + (c0 + lane) * 2 : 0;   // lanes without a cherry read code bytes and ignore them
-
-  // global-memory path: request the first D of its rows now
-  const uint8_t* gptr = p.rows + ((size_t)r0 + rl + (size_t)nrows_s * RL) * p.rec_bytes;
-  const size_t gstep = (size_t)RL * p.rec_bytes;
-  const int nrows_g = nrows - nrows_s;
-  uint4 wb[DG][J];
-  uint32_t sc[DG], ch[DG];
-  if (D > 0) {
-#pragma unroll
-    for (int d = 0; d < DG; ++d) {
-      sc[d] = 0; ch[d] = 0;
-#pragma unroll
-      for (int j = 0; j < J; ++j) wb[d][j] = make_uint4(0, 0, 0, 0);
-      if (d < nrows_g) {
-        const uint8_t* rp = gptr + d * gstep;
-        if (lane_on) {
-#pragma unroll
-          for (int j = 0; j < J; ++j) wb[d][j] = ldg_stream16(rp + woff + j * jstride);
-          sc[d] = SETS == 2 ? ldg_stream4(rp + soff) : ldg_stream2(rp + soff);
+  __syncthreads();
+  if (warp == W) {
+    // ---- copy warp.  Tiles are requested in order with at most `inflight` of them outstanding:
+    // enough bytes in flight to keep HBM busy, but short queues in the memory system, because the
+    // working warps' activation loads (issued after the dependency wait, in the middle of the
+    // stream) wait behind whatever is outstanding.  A ring slot is re-used once every working warp
+    // has released it.
+    if (lane == 0) {
+      asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+      int slot = 0, lslot = 0;                      // slot of the tile to issue / of the tile `inflight` back
+      uint32_t ephase = 0, lphase = 0;              // phases of the empty / full barriers waited on
+      for (int next = 0; next < nt; ++next) {
+        if (next >= p.inflight) {                   // tile next - inflight must have landed
+          rv_mbar_wait(bar_full + 8 * lslot, lphase, &s_abort, p.status);
+          if (++lslot == S) { lslot = 0; lphase ^= 1u; }
         }
-        if (cher_on) ch[d] = ldg_stream2(rp + coff);
+        if (next >= S) {                            // the slot's previous tile must have been consumed
+          rv_mbar_wait(bar_empty + 8 * slot, ephase, &s_abort, p.status);
+        }
+        issue_tile(p, stiles, bar_full, tile0 + next, slot);
+        if (++slot == S) { slot = 0; if (next >= S) ephase ^= 1u; }
       }
     }
+#ifdef CQ_ROWVEC_TRACE
+    if (lane == 1 && p.trace) {      // arrival time of each tile of the first round
+      for (int i = 0; i < min(nt, S) && i < 8; ++i) {
+        rv_mbar_wait(bar_full + 8 * i, 0, &s_abort, p.status);
+        rv_stamp_to(p.trace, p.trace_launch, 8 + i);
+      }
+    }
+#endif
+  } else {
+  // ---- this warp's groups (contiguous) and cherry block
+  const int NG = p.NG;
+  const int gq = NG / W, gr = NG % W;
+  const int ngw = gq + (warp < gr ? 1 : 0);
+  const int gstart = warp * gq + min(warp, gr);
+  const bool has_cherry = warp < p.ncb;                      // cherry block `warp`
+  // the original columns the warp's compact columns span: [lo, hi]; the slice starts at lo rounded down to 8
+  int lo8 = 0, nchunk = 0;
+  if (ngw > 0) {
+    const int kc0 = gstart * 128, kc1 = min(p.K - p.C, (gstart + ngw) * 128) - 1;
+    const int lo = p.perm[kc0], hi = p.perm[kc1];
+    lo8 = lo & ~7;
+    nchunk = (hi - lo8) / 8 + 1;
   }
-  // layer constants of the activation staging: the column lists of this thread's first PV octets
-  const int n_oct = NG * 16;
+  // column lists of the octets this lane stages (octet lane + 32 u of the warp's groups), turned into
+  // byte offsets inside the slice here, ahead of the wait: two 16-bit fields per word, no field
+  // underflows (every column is >= lo8) or overflows (the slice is a few hundred halves).  Padding
+  // columns (= K) land on the zero slot at slice[K - lo8], which only the last group's warp has.
   const uint32_t padpair = (uint32_t)p.K * 0x10001u;
-  const uint4 padcols = make_uint4(padpair, padpair, padpair, padpair);
-  uint4 pv[PV];
+  uint4 pv[PVW];
 #pragma unroll
-  for (int u = 0; u < PV; ++u) {
-    const int o = u * NTHR + tid;
-    pv[u] = padcols;
-    if (o < n_oct) pv[u] = *reinterpret_cast<const uint4*>(p.perm + (size_t)o * 8);
+  for (int u = 0; u < PVW; ++u) {
+    const int ol = lane + 32 * u;
+    uint4 c = make_uint4(0, 0, 0, 0);
+    if (ol < ngw * 16) {
+      c = *reinterpret_cast<const uint4*>(p.perm + ((size_t)gstart * 16 + ol) * 8);
+      const uint32_t sub = (uint32_t)lo8 * 0x10001u;
+      c.x = (c.x - sub) * 2u; c.y = (c.y - sub) * 2u; c.z = (c.z - sub) * 2u; c.w = (c.w - sub) * 2u;
+    }
+    pv[u] = c;
   }
-  const int ccol = cher_on ? p.cidx[c0 + lane] : 0;
+  (void)padpair;
+  const bool owns_tail = ngw > 0 && gstart + ngw == NG;     // the warp whose last group may hold padding columns
+  int ccol = -1;
+  if (has_cherry && lane < 16 && warp * 16 + lane < p.C) ccol = p.cidx[warp * 16 + lane];
+  const bool x_aligned = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
 
-  RV_STAMP(1);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   RV_STAMP(2);
 
-  // ---- activations: the fp16 row goes to shared memory with coalesced 16-byte loads, then every
-  // thread quantises octets of compact columns: one step size per group (16 consecutive threads),
-  // two signed-byte planes.
-  if ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
-    for (int i = tid; i < p.K / 8; i += NTHR)
-      reinterpret_cast<uint4*>(raw)[i] = __ldcg(reinterpret_cast<const uint4*>(p.x) + i);
+  // ---- the warp's slice of x -> its shared-memory slice (coalesced 16-byte loads), cherry activations.
+  uint32_t xcv = 0;
+  if (x_aligned) {
+    uint4 xv[XCH];
+#pragma unroll
+    for (int c = 0; c < XCH; ++c) {
+      const int ch = lane + 32 * c;
+      xv[c] = make_uint4(0, 0, 0, 0);
+      if (ch < nchunk) xv[c] = __ldcg(reinterpret_cast<const uint4*>(p.x + lo8) + ch);
+    }
+    if (ccol >= 0) xcv = (uint32_t)__half_as_ushort(__ldcg(p.x + ccol));
+#pragma unroll
+    for (int c = 0; c < XCH; ++c) {
+      const int ch = lane + 32 * c;
+      if (ch < nchunk) reinterpret_cast<uint4*>(slice)[ch] = xv[c];
+    }
   } else {
-    for (int i = tid; i < p.K; i += NTHR) raw[i] = p.x[i];
+    if (ccol >= 0) xcv = (uint32_t)__half_as_ushort(__ldcg(p.x + ccol));
+    for (int i = lane; i < nchunk * 8; i += 32) slice[i] = p.x[lo8 + i];
   }
-  if (tid < 8) raw[p.K + tid] = __float2half(0.f);
-  if (tid == 0 && nbar_pre < nbar) issue_rows(p, srows, bar0, r0, n_smem, rows_per_bar, nbar_pre, nbar);
-  __syncthreads();
+  if (owns_tail && lane == 0) slice[p.K - lo8] = __float2half(0.f);   // zero slot for padding columns
+  __syncwarp();
   RV_STAMP(6);
-  const float xc = cher_on ? __half2float(raw[ccol]) : 0.f;
-#pragma unroll 1
-  for (int u = 0; u * NTHR < n_oct; ++u) {
-    const int o = u * NTHR + tid;
-    uint4 pw = u == 0 ? pv[0] : (u == 1 ? pv[1] : (u == 2 ? pv[2] : pv[3]));
-    if (u >= PV) {
-      pw = padcols;
-      if (o < n_oct) pw = *reinterpret_cast<const uint4*>(p.perm + (size_t)o * 8);
+
+  // ---- gather every octet of this lane first: the planes written below re-use the slice's memory
+  uint32_t xg[PVW][4];
+#pragma unroll
+  for (int u = 0; u < PVW; ++u) {
+    const uint32_t pw[4] = {pv[u].x, pv[u].y, pv[u].z, pv[u].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t a = *reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(slice) + (pw[i] & 0xFFFFu));
+      const uint32_t b = *reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(slice) + (pw[i] >> 16));
+      xg[u][i] = a | (b << 16);
     }
-    RV_STAMP(8);
-#ifndef CQ_ROWVEC_NOSTAGE   // tuning builds can leave the quantisation out to count its instructions
-    stage_octet<SETS>(raw, pw, o, n_oct, NG, OFF, planes, gsx, gcq);
-#else
-    if (o == 0x7fffffff) planes[0] = (unsigned char)pw.x;
-#endif
-    RV_STAMP(9);
   }
-  __syncthreads();
-  RV_STAMP(10);
-
-  int xh[32], xl[32];
+  __syncwarp();
+  // ---- quantise: one step size per group (16 consecutive lanes), two signed-byte planes, stored
+  // where the B-fragment lanes pick them up with two 16-byte loads per group
+  float sx16[GPW], cq[GPW][SETS];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const uint4 a = *reinterpret_cast<const uint4*>(planes + ((size_t)c * NG + g) * 16);
-    const uint4 b = *reinterpret_cast<const uint4*>(planes + ((size_t)(c + 8) * NG + g) * 16);
-    xh[4 * c] = (int)a.x; xh[4 * c + 1] = (int)a.y; xh[4 * c + 2] = (int)a.z; xh[4 * c + 3] = (int)a.w;
-    xl[4 * c] = (int)b.x; xl[4 * c + 1] = (int)b.y; xl[4 * c + 2] = (int)b.z; xl[4 * c + 3] = (int)b.w;
-  }
-  const float sx16 = gsx[g];
-  const float cq0 = gcq[g * SETS], cq1 = SETS == 2 ? gcq[g * SETS + 1] : 0.f;
-
-  RV_STAMP(3);
-  // ---- rows that were copied to shared memory, R at a time: the lanes' partial sums of R rows are
-  // reduced together (lanes end up holding different rows), so a row costs 18 / R shuffle-class
-  // instructions instead of 10 and the R dot products overlap.
-  int bar_i = 0, bar_c = 0;                       // barrier of iteration i = i / ipb, kept without a division
-#pragma unroll 1
-  for (int i = 0; i < nrows_s; i += R) {
-    float acc[R];
+  for (int u = 0; u < PVW; ++u) {
+    const int ol = lane + 32 * u;
+    float v[8];
+    float m = 0.f;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      acc[r] = 0.f;
-      if (i + r < nrows_s) {                      // warp-uniform
-        rv_mbar_wait(bar0 + 8 * bar_i, 0, &s_abort, p.status);
-        if (++bar_c == ipb) { bar_c = 0; ++bar_i; }
-        if (i + r == nrows_s - 1) RV_STAMP(7);
-        const unsigned char* rp = srows + (size_t)(rl + (i + r) * RL) * p.rec_bytes;
-        uint32_t w[NW];
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xg[u][i]));
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+      m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
 #pragma unroll
-        for (int j = 0; j < J; ++j) {
-          const uint4 v = *reinterpret_cast<const uint4*>(rp + woff + j * jstride);
-          w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
-        }
-        const uint32_t scw = SETS == 2 ? *reinterpret_cast<const uint32_t*>(rp + soff)
-                                       : (uint32_t)*reinterpret_cast<const uint16_t*>(rp + soff);
-        const uint32_t chw = *reinterpret_cast<const uint16_t*>(rp + coff);
-        acc[r] = row_value<BITS, SETS>(w, scw, cher_on ? chw : 0u, xh, xl, sx16, cq0, cq1, xc, lane_on);
+    for (int s = 1; s < 16; s <<= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, s));
+    const float step = m * (1.0f / 16256.0f);
+    const float inv = m > 0.f ? __fdividef(16256.0f, m) : 0.f;
+    uint32_t hi[8], lo[8];
+    int sq = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int q = __float2int_rn(v[i] * inv);     // |q| <= 16256 + 1 (approximate reciprocal): hi, lo still fit
+      const int t = q + 64;
+      hi[i] = (uint32_t)(t >> 7);                    // floor((q + 64) / 128) in [-127, 127]
+      lo[i] = (uint32_t)((t & 127) - 64);            // q - 128 hi in [-64, 63]
+      sq += q;
+    }
+    uint32_t hw[2], lw[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {                    // low bytes of four values -> one word
+      hw[k] = __byte_perm(__byte_perm(hi[4 * k], hi[4 * k + 1], 0x0040), __byte_perm(hi[4 * k + 2], hi[4 * k + 3], 0x0040), 0x5410);
+      lw[k] = __byte_perm(__byte_perm(lo[4 * k], lo[4 * k + 1], 0x0040), __byte_perm(lo[4 * k + 2], lo[4 * k + 3], 0x0040), 0x5410);
+    }
+    // sums of q over the two 64-column halves of the group
+    sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 1);
+    sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 2);
+    sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 4);
+    const int sq_other = __shfl_xor_sync(0xFFFFFFFFu, sq, 8);
+    const int sq_a = (lane & 8) ? sq_other : sq, sq_b = (lane & 8) ? sq : sq_other;   // first / second half
+    if (ol < ngw * 16) {
+      // word wI (columns 4 wI .. 4 wI + 3 of the group) goes to [plane][t = wI & 3][chunk wI >> 3][(wI >> 2) & 1]
+      const int gi = ol >> 4, oo = ol & 15;
+      uint32_t* gp = plane + gi * 64;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int wI = 2 * oo + k;
+        const int pos = (wI & 3) * 8 + (wI >> 3) * 2 + ((wI >> 2) & 1);
+        gp[pos] = hw[k];
+        gp[32 + pos] = lw[k];
       }
     }
-    const float tot = reduce_rows<R>(acc, lane);  // lane (32 / R) * r holds the total of row r
-    if ((lane & (32 / R - 1)) == 0) {
-      const int r = lane / (32 / R);
-      if (i + r < nrows_s) {
-        const int rr = rl + (i + r) * RL;
-        float v = tot;
-        if (nsl == 1) {
-          if (p.accumulate) v += __half2float(p.y[r0 + rr]);
-          p.y[r0 + rr] = __float2half_rn(v);
+    // every lane keeps the terms of both groups of this round (lanes 0-15: group 2u, 16-31: group 2u + 1)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (2 * u + h < GPW) {
+        const float st = __shfl_sync(0xFFFFFFFFu, step, 16 * h);
+        const int qa = __shfl_sync(0xFFFFFFFFu, sq_a, 16 * h), qb = __shfl_sync(0xFFFFFFFFu, sq_b, 16 * h);
+        sx16[2 * u + h] = st * (1.0f / 16.0f);
+        if (SETS == 2) {
+          cq[2 * u + h][0] = -OFF * st * (float)qa;
+          cq[2 * u + h][SETS - 1] = -OFF * st * (float)qb;
         } else {
-          part[rr * nsl + sl] = v;
+          cq[2 * u + h][0] = -OFF * st * (float)(qa + qb);
         }
       }
     }
   }
-  // ---- rows read from global memory
-  if (D > 0) {
-    for (int i = 0; i < nrows_g; i += DG) {
+  __syncwarp();
+  // B fragments: lanes 0-3 carry the hi plane (column 0 of B), lanes 4-7 the lo plane (column 1)
+  uint32_t xb[GPW][8];
 #pragma unroll
-      for (int d = 0; d < DG; ++d) {
-        const int ii = i + d;
-        if (ii < nrows_g) {
-          uint32_t w[NW];
+  for (int gi = 0; gi < GPW; ++gi) {
+    uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+    if (lane < 8 && gi < ngw) {
+      const uint4* src = reinterpret_cast<const uint4*>(plane + gi * 64 + g8 * 32 + t4 * 8);
+      a = src[0];
+      b = src[1];
+    }
+    xb[gi][0] = a.x; xb[gi][1] = a.y; xb[gi][2] = a.z; xb[gi][3] = a.w;
+    xb[gi][4] = b.x; xb[gi][5] = b.y; xb[gi][6] = b.z; xb[gi][7] = b.w;
+  }
+  // cherry B fragment: b0 = x_c[2t], x_c[2t + 1]; b1 = x_c[8 + 2t], x_c[9 + 2t] in lanes 0-3
+  uint32_t cb0 = 0, cb1 = 0;
+  if (has_cherry) {
+    const uint32_t v0 = __shfl_sync(0xFFFFFFFFu, xcv, 2 * t4), v1 = __shfl_sync(0xFFFFFFFFu, xcv, 2 * t4 + 1);
+    const uint32_t v2 = __shfl_sync(0xFFFFFFFFu, xcv, 8 + 2 * t4), v3 = __shfl_sync(0xFFFFFFFFu, xcv, 9 + 2 * t4);
+    cb0 = lane < 4 ? (v0 | (v1 << 16)) : 0u;
+    cb1 = lane < 4 ? (v2 | (v3 << 16)) : 0u;
+  }
+  RV_STAMP(3);
+
+  // ---- tiles.  Addresses: one base per kind (codes, scales, cherry, partial sums) computed here,
+  // the ring slot's offset kept incrementally, everything else is a compile-time displacement.
+  const unsigned char* gp0 = stiles + (size_t)gstart * GRP_BYTES + lane * 16;
+  const unsigned char* gq0 = stiles + (size_t)gstart * GRP_BYTES + 512 + lane * (BITS == 4 ? 16 : 8);
+  const unsigned char* sp0 = stiles + p.scal_off + (gstart * SETS * 8 + g8) * 4;
+  const unsigned char* cp0 = stiles + p.cher_off + warp * 512 + lane * 16;
+  float* pp = part + warp * 16 + g8;
+  int slot = 0;
+  uint32_t slot_off = 0, phase = 0;
+#pragma unroll 1
+  for (int i = 0; i < nt; ++i) {
+    rv_mbar_wait(bar_full + 8 * slot, phase, &s_abort, p.status);
+    if (i == nt - 1) RV_STAMP(7);
+    float acc0 = 0.f, acc1 = 0.f;                            // rows g8 and g8 + 8 of the tile
 #pragma unroll
-          for (int j = 0; j < J; ++j) {
-            w[4 * j] = wb[d][j].x; w[4 * j + 1] = wb[d][j].y; w[4 * j + 2] = wb[d][j].z; w[4 * j + 3] = wb[d][j].w;
+    for (int gi = 0; gi < GPW; ++gi) {
+      if (gi < ngw) {                                        // warp-uniform
+        const unsigned char* gp = gp0 + slot_off + gi * GRP_BYTES;
+        const unsigned char* gq = gq0 + slot_off + gi * GRP_BYTES;
+        int dP[SETS][4], dH[SETS][4];
+#pragma unroll
+        for (int s = 0; s < SETS; ++s)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { dP[s][e] = 0; dH[s][e] = 0; }
+        if (BITS == 4) {
+          const uint4 w0 = *reinterpret_cast<const uint4*>(gp);
+          const uint4 w1 = *reinterpret_cast<const uint4*>(gq);
+          const uint32_t wa[4] = {w0.x, w0.y, w0.z, w0.w}, wc[4] = {w1.x, w1.y, w1.z, w1.w};
+          uint32_t aP[4], aH[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { aP[j] = wa[j] & 0x0F0F0F0Fu; aH[j] = wa[j] & 0xF0F0F0F0u; }
+          rv_imma(dP[0], aP, xb[gi][0], xb[gi][1]);          // columns 0..31
+          rv_imma(dH[0], aH, xb[gi][2], xb[gi][3]);          // columns 32..63, as 16 u
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { aP[j] = wc[j] & 0x0F0F0F0Fu; aH[j] = wc[j] & 0xF0F0F0F0u; }
+          rv_imma(dP[SETS - 1], aP, xb[gi][4], xb[gi][5]);   // columns 64..95
+          rv_imma(dH[SETS - 1], aH, xb[gi][6], xb[gi][7]);   // columns 96..127
+        } else {
+          const uint4 w0 = *reinterpret_cast<const uint4*>(gp);
+          const uint2 w1 = *reinterpret_cast<const uint2*>(gq);
+          const uint32_t ws[2][3] = {{w0.x, w0.y, w0.z}, {w0.w, w1.x, w1.y}};
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            const uint32_t A = ws[s][0], B = ws[s][1], Cw = ws[s][2];
+            const uint32_t A3 = A >> 3, B2 = B >> 2, C1 = Cw >> 1;
+            uint32_t aP[4], aH[4];
+            aP[0] = A & 0x07070707u;  aH[0] = A & 0x70707070u;
+            aP[1] = B & 0x07070707u;  aH[1] = B & 0x70707070u;
+            aP[2] = Cw & 0x07070707u; aH[2] = Cw & 0x70707070u;
+            aP[3] = (A3 & 0x01010101u) | (B2 & 0x02020202u) | (C1 & 0x04040404u);
+            aH[3] = (A3 & 0x10101010u) | (B2 & 0x20202020u) | (C1 & 0x40404040u);
+            rv_imma(dP[s * (SETS - 1)], aP, xb[gi][4 * s], xb[gi][4 * s + 1]);       // columns 64 s .. 64 s + 31
+            rv_imma(dH[s * (SETS - 1)], aH, xb[gi][4 * s + 2], xb[gi][4 * s + 3]);   // columns 64 s + 32 .. 64 s + 63, as 16 u
           }
-          float acc = row_value<BITS, SETS>(w, sc[d], ch[d], xh, xl, sx16, cq0, cq1, xc, lane_on);
-          // the buffers of this row are free: request the row D steps ahead
-          const int nn = ii + DG;
-          if (nn < nrows_g) {
-            const uint8_t* rp = gptr + (size_t)nn * gstep;
-            if (lane_on) {
+        }
+        // lanes with t4 == 0 hold column 0 (hi sums) and column 1 (lo sums) of rows g8, g8 + 8
 #pragma unroll
-              for (int j = 0; j < J; ++j) wb[d][j] = ldg_stream16(rp + woff + j * jstride);
-              sc[d] = SETS == 2 ? ldg_stream4(rp + soff) : ldg_stream2(rp + soff);
-            }
-            if (cher_on) ch[d] = ldg_stream2(rp + coff);
-          }
-#pragma unroll
-          for (int s = 16; s >= 1; s >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, s);
-          if (lane == 0) {
-            const int rr = rl + (nrows_s + ii) * RL;
-            if (nsl == 1) {
-              if (p.accumulate) acc += __half2float(p.y[r0 + rr]);
-              p.y[r0 + rr] = __float2half_rn(acc);
-            } else {
-              part[rr * nsl + sl] = acc;
-            }
-          }
+        for (int s = 0; s < SETS; ++s) {
+          const __half2 sc2 = *reinterpret_cast<const __half2*>(sp0 + slot_off + (gi * SETS + s) * 32);
+          const float2 scf = __half22float2(sc2);
+          const int t0 = ((dP[s][0] * 128 + dP[s][1]) << 4) + (dH[s][0] * 128 + dH[s][1]);
+          const int t1 = ((dP[s][2] * 128 + dP[s][3]) << 4) + (dH[s][2] * 128 + dH[s][3]);
+          acc0 = fmaf(scf.x, fmaf((float)t0, sx16[gi], cq[gi][s]), acc0);
+          acc1 = fmaf(scf.y, fmaf((float)t1, sx16[gi], cq[gi][s]), acc1);
         }
       }
     }
+    if (has_cherry) {
+      const uint4 a = *reinterpret_cast<const uint4*>(cp0 + slot_off);
+      float dc[4] = {0.f, 0.f, 0.f, 0.f};
+      rv_hmma(dc, a, cb0, cb1);
+      acc0 += dc[0];
+      acc1 += dc[2];
+    }
+#ifdef CQ_ROWVEC_TRACE
+    if (i < 3) RV_STAMP(13 + i);
+#endif
+    if (t4 == 0) {
+      pp[0] = acc0;
+      pp[8] = acc1;
+    }
+    pp += W * 16;
+    if (i + S < nt) {
+      // ring: this warp is done with the slot; the copy warp refills it once every warp is
+      __syncwarp();
+      if (lane == 0) rv_mbar_arrive(bar_empty + 8 * slot);
+    }
+    ++slot;
+    slot_off += (uint32_t)p.tile_bytes;
+    if (slot == S) { slot = 0; slot_off = 0; phase ^= 1u; }
   }
   RV_STAMP(4);
-  if (nsl > 1) {
-    __syncthreads();
-    for (int rr = tid; rr < r1 - r0; rr += NTHR) {
-      float acc = p.accumulate ? __half2float(p.y[r0 + rr]) : 0.f;
-      for (int s = 0; s < nsl; ++s) acc += part[rr * nsl + s];
-      p.y[r0 + rr] = __float2half_rn(acc);
+  }   // working warps
+  __syncthreads();
+  // ---- the warps' partial sums of every row, in warp order
+  const int row0 = tile0 * 16;
+  for (int rr = tid; rr < nt * 16; rr += NTHR) {
+    const int row = row0 + rr;
+    if (row < p.N) {
+      const float* pp = part + (size_t)(rr >> 4) * W * 16 + (rr & 15);
+      float acc = p.accumulate ? __half2float(p.y[row]) : 0.f;
+#pragma unroll
+      for (int w = 0; w < W; ++w) acc += pp[w * 16];
+      p.y[row] = __float2half_rn(acc);
     }
   }
   RV_STAMP(5);
@@ -542,116 +512,123 @@ __global__ void __launch_bounds__(W * 32, 1) cq_rowvec_kernel(const RowvecParams
 
 // ------------------------------------------------------------------ layout kernels
 struct RlayerDev {
-  uint8_t* rows; uint16_t* perm; uint16_t* cidx;
-  int bits, K, N, C, G, Kc, NG, sets, nsl, gps, row_bytes, srow_bytes, rec_bytes;
+  uint8_t* tiles; uint16_t* perm; uint16_t* cidx;
+  int bits, K, N, C, G, Kc, NG, sets, Cp, NT, tile_bytes, scal_off, cher_off;
 };
 
 RlayerDev rl_view(const cq_rlayer* L) {
   RlayerDev d;
   uint8_t* b = (uint8_t*)L->blob;
-  d.rows = b + L->off_rows;
+  d.tiles = b + L->off_tiles;
   d.perm = (uint16_t*)(b + L->off_perm);
   d.cidx = (uint16_t*)(b + L->off_cidx);
   d.bits = L->bits; d.K = L->K; d.N = L->N; d.C = L->C; d.G = L->G; d.Kc = L->Kc; d.NG = L->NG;
-  d.sets = L->sets; d.nsl = L->nsl; d.gps = L->gps; d.row_bytes = L->row_bytes; d.srow_bytes = L->srow_bytes;
-  d.rec_bytes = L->rec_bytes;
+  d.sets = L->sets; d.Cp = L->Cp; d.NT = L->NT; d.tile_bytes = L->tile_bytes;
+  d.scal_off = L->NG * 256 * L->bits;
+  d.cher_off = d.scal_off + L->NG * L->sets * 32;
   return d;
 }
 
-// Byte offset (inside the record) of 32-bit word wi of group gg.
-__device__ __forceinline__ size_t rl_word_off(const RlayerDev& d, int gg, int wi) {
-  const int sl = gg / d.gps, ln = gg - sl * d.gps;
-  const int gcount = min(d.gps, d.NG - sl * d.gps);
-  return (size_t)sl * d.gps * 16 * d.bits + ((size_t)(wi >> 2) * gcount + ln) * 16 + (wi & 3) * 4;
+// Layout of one group block (16 rows x 128 compact columns) as the kernel's lanes read it.
+// Lane (g8, t) = 4 g8 + t; A-fragment register j of a 32-column chunk holds, as bytes b = 0..3,
+// row g8 + 8 (j & 1), columns 16 (j >> 1) + 4 t + b of the chunk.
+//   4-bit: two 16-byte loads per lane, [load l][lane][16 B]; word j of load l = register j of
+//     chunk 2 l in the low nibbles and of chunk 2 l + 1 in the high nibbles.
+//   3-bit: per 64-column half s the words A, B, C = wi 0, 1, 2, stored as [lane][16 B] =
+//     {A0, B0, C0, A1} and, from byte 512, [lane][8 B] = {B1, C1}.  Word wi holds register wi of
+//     chunk 2 s in bits 0-2 and of chunk 2 s + 1 in bits 4-6 of its bytes; register 3 is spread
+//     as bit planes: code bit wi of chunk 2 s (chunk 2 s + 1) in bit 3 (bit 7) of word wi.
+__device__ __forceinline__ int rl3_word_off(int lane, int widx) {     // widx = 3 s + wi, 0..5
+  return widx < 4 ? lane * 16 + widx * 4 : 512 + lane * 8 + (widx - 4) * 4;
 }
-__device__ __forceinline__ __half* rl_scale_ptr(const RlayerDev& d, int n, int gs) {
-  return reinterpret_cast<__half*>(d.rows + (size_t)n * d.rec_bytes + d.row_bytes) + gs;
-}
-__device__ __forceinline__ __half* rl_cherry_ptr(const RlayerDev& d, int n, int c) {
-  return reinterpret_cast<__half*>(d.rows + (size_t)n * d.rec_bytes + d.row_bytes + d.srow_bytes) + c;
-}
-
-// Where code e (0..127) of a group sits: first word index, per code bit the bit position, and how
-// far the word index advances per code bit (1 for the 3-bit bit-plane fields).
-__device__ __forceinline__ void rl_code_pos(int bits, int e, int* wi, int* bitpos, int* wstep) {
+// Byte offset (inside the group block) of the word that holds bit i of code (row rl, column kk), and the bit.
+__device__ __forceinline__ void rl_bit_pos(int bits, int rl, int kk, int i, int* off, int* bit) {
+  const int chunk = kk >> 5, k32 = kk & 31;
+  const int j = ((k32 >> 4) << 1) | (rl >> 3);
+  const int t = (k32 & 15) >> 2, b = k32 & 3;
+  const int lane = (rl & 7) * 4 + t;
   if (bits == 4) {
-    const int i = e & 7;
-    *wi = e >> 3; *wstep = 0;
-    const int sh = i < 4 ? 8 * i : 8 * (i - 4) + 4;
-    bitpos[0] = sh; bitpos[1] = sh + 1; bitpos[2] = sh + 2; bitpos[3] = sh + 3;
+    *off = (chunk >> 1) * 512 + lane * 16 + j * 4;
+    *bit = 8 * b + 4 * (chunk & 1) + i;
   } else {
-    const int s = e >> 5, r = e & 31, f = r >> 2, b = r & 3;
-    if (f < 6) {
-      *wi = 3 * s + (f >> 1); *wstep = 0;
-      const int sh = 8 * b + 4 * (f & 1);
-      bitpos[0] = sh; bitpos[1] = sh + 1; bitpos[2] = sh + 2;
-    } else {                      // bit planes: bit t of the code lives in word 3s + t
-      *wi = 3 * s; *wstep = 1;
-      const int sh = 8 * b + (f == 6 ? 3 : 7);
-      bitpos[0] = sh; bitpos[1] = sh; bitpos[2] = sh;
+    const int s = chunk >> 1;
+    if (j < 3) {
+      *off = rl3_word_off(lane, 3 * s + j);
+      *bit = 8 * b + 4 * (chunk & 1) + i;
+    } else {
+      *off = rl3_word_off(lane, 3 * s + i);
+      *bit = 8 * b + ((chunk & 1) ? 7 : 3);
     }
   }
 }
 
-__device__ __forceinline__ uint32_t rl_read_code(const RlayerDev& d, int n, int kc) {
-  const int gg = kc >> 7, e = kc & 127;
-  int wi, bp[4], ws;
-  rl_code_pos(d.bits, e, &wi, bp, &ws);
-  const uint8_t* row = d.rows + (size_t)n * d.rec_bytes;
-  uint32_t u = 0;
-  for (int t = 0; t < d.bits; ++t) {
-    const uint32_t w = *reinterpret_cast<const uint32_t*>(row + rl_word_off(d, gg, wi + ws * t));
-    u |= ((w >> bp[t]) & 1u) << t;
-  }
-  return u;
-}
-
-// one thread per (row n, group gg, word wi); n fastest so that the reference bytes are read coalesced
+// one thread per 32-bit word of a group block: gathers the codes the word holds
 __global__ void rl_prepare_codes_kernel(RlayerDev d, const uint8_t* __restrict__ q) {
-  const int nw = 4 * d.bits;
-  const size_t total = (size_t)d.N * d.NG * nw;
+  const int wpg = 64 * d.bits;                               // words per group block
+  const size_t total = (size_t)d.NT * d.NG * wpg;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-    const int n = (int)(idx % d.N);
-    const size_t rest = idx / d.N;
-    const int wi = (int)(rest % nw), gg = (int)(rest / nw);
+    const int wq = (int)(idx % wpg);
+    const size_t rest = idx / wpg;
+    const int gg = (int)(rest % d.NG), tile = (int)(rest / d.NG);
+    int lane, widx;                                          // which lane's word
+    if (d.bits == 4) { lane = (wq >> 2) & 31; widx = (wq >> 7) * 4 + (wq & 3); }          // widx = 4 l + j
+    else if (wq < 128) { lane = wq >> 2; widx = wq & 3; }
+    else { lane = (wq - 128) >> 1; widx = 4 + ((wq - 128) & 1); }
+    const int byte_off = d.bits == 4 ? (wq >> 7) * 512 + lane * 16 + (wq & 3) * 4 : rl3_word_off(lane, widx);
+    const int g8 = lane >> 2, t = lane & 3;
     uint32_t word = 0;
-    for (int e = 0; e < 128; ++e) {
-      int cwi, bp[4], ws;
-      rl_code_pos(d.bits, e, &cwi, bp, &ws);
-      const int kc = gg * 128 + e;
-      if (ws == 0) {
-        if (cwi != wi || kc >= d.Kc) continue;
-        const uint32_t u = cq_ref_code(q, d.bits, kc, n, d.N);
-        for (int t = 0; t < d.bits; ++t) word |= ((u >> t) & 1u) << bp[t];
-      } else {
-        const int t = wi - cwi;
-        if (t < 0 || t > 2 || kc >= d.Kc) continue;
-        const uint32_t u = cq_ref_code(q, d.bits, kc, n, d.N);
-        word |= ((u >> t) & 1u) << bp[t];
+    auto code = [&](int rl, int kk) -> uint32_t {
+      const int n = tile * 16 + rl, kc = gg * 128 + kk;
+      return (n < d.N && kc < d.Kc) ? cq_ref_code(q, d.bits, kc, n, d.N) : 0u;
+    };
+    if (d.bits == 4) {
+      const int l = widx >> 2, j = widx & 3;
+      const int rl = g8 + 8 * (j & 1), kb = 16 * (j >> 1) + 4 * t;
+      for (int b = 0; b < 4; ++b) {
+        word |= code(rl, 32 * (2 * l) + kb + b) << (8 * b);
+        word |= code(rl, 32 * (2 * l + 1) + kb + b) << (8 * b + 4);
+      }
+    } else {
+      const int s = widx / 3, wi = widx % 3;
+      const int rl = g8 + 8 * (wi & 1), kb = 16 * (wi >> 1) + 4 * t;          // register wi
+      const int rl3 = g8 + 8, kb3 = 16 + 4 * t;                               // register 3
+      for (int b = 0; b < 4; ++b) {
+        word |= code(rl, 32 * (2 * s) + kb + b) << (8 * b);
+        word |= code(rl, 32 * (2 * s + 1) + kb + b) << (8 * b + 4);
+        word |= ((code(rl3, 32 * (2 * s) + kb3 + b) >> wi) & 1u) << (8 * b + 3);
+        word |= ((code(rl3, 32 * (2 * s + 1) + kb3 + b) >> wi) & 1u) << (8 * b + 7);
       }
     }
-    *reinterpret_cast<uint32_t*>(d.rows + (size_t)n * d.rec_bytes + rl_word_off(d, gg, wi)) = word;
+    *reinterpret_cast<uint32_t*>(d.tiles + (size_t)tile * d.tile_bytes + (size_t)gg * wpg * 4 + byte_off) = word;
   }
 }
 
-// scales (per 128-column group and set), cherry values, column permutation and cherry list
+// scales, cherry values, column permutation and cherry list
 __global__ void rl_prepare_rest_kernel(RlayerDev d, const __half* __restrict__ scales, const __half* __restrict__ cw,
                                        const int16_t* __restrict__ ci) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int ngr = (d.Kc + d.G - 1) / d.G;            // scale rows of the reference
-  const int spr = d.srow_bytes / 2;                  // scale slots per row, padding included
-  for (size_t idx = t0; idx < (size_t)d.N * spr; idx += stride) {
-    const int n = (int)(idx % d.N);
-    const int gs = (int)(idx / d.N);
+  const size_t rows = (size_t)d.NT * 16;
+  // scales: [group][set][g8][row g8, row g8 + 8]
+  for (size_t idx = t0; idx < rows * d.NG * d.sets; idx += stride) {
+    const int n = (int)(idx % rows);
+    const int gs = (int)(idx / rows);
     const int kc = (gs / d.sets) * 128 + (gs % d.sets) * 64;
     const int gi = kc / d.G;
-    const bool real = gs < d.NG * d.sets && kc < d.Kc && gi < ngr;
-    *rl_scale_ptr(d, n, gs) = real ? scales[(size_t)gi * d.N + n] : __float2half(0.f);
+    const bool real = n < d.N && kc < d.Kc && gi < ngr;
+    __half* sp = reinterpret_cast<__half*>(d.tiles + (size_t)(n >> 4) * d.tile_bytes + d.scal_off) +
+                 ((size_t)gs * 8 + (n & 7)) * 2 + ((n >> 3) & 1);
+    *sp = real ? scales[(size_t)gi * d.N + n] : __float2half(0.f);
   }
-  for (size_t idx = t0; idx < (size_t)d.N * d.C; idx += stride) {
-    const int n = (int)(idx % d.N), c = (int)(idx / d.N);
-    *rl_cherry_ptr(d, n, c) = cw[(size_t)c * d.N + n];
+  // cherry A fragments (m16n8k16): register j of lane (g8, t): row g8 + 8 (j & 1), columns 8 (j >> 1) + 2 t + {0, 1}
+  for (size_t idx = t0; idx < rows * d.Cp; idx += stride) {
+    const int n = (int)(idx % rows), c = (int)(idx / rows);
+    const int rl = n & 15, cc = c & 15;
+    const int lane = (rl & 7) * 4 + ((cc & 7) >> 1), j = ((cc >> 3) << 1) | (rl >> 3);
+    __half* cp = reinterpret_cast<__half*>(d.tiles + (size_t)(n >> 4) * d.tile_bytes + d.cher_off + (size_t)(c >> 4) * 512 +
+                                           lane * 16 + j * 4) + (cc & 1);
+    *cp = (n < d.N && c < d.C) ? cw[(size_t)c * d.N + n] : __float2half(0.f);
   }
   for (size_t idx = t0; idx < (size_t)d.NG * 128; idx += stride) {
     const int kc = (int)idx;
@@ -668,7 +645,7 @@ __global__ void rl_prepare_rest_kernel(RlayerDev d, const __half* __restrict__ s
     }
     d.perm[kc] = (uint16_t)col;
   }
-  for (size_t idx = t0; idx < (size_t)d.C; idx += stride) d.cidx[idx] = (uint16_t)ci[idx];
+  for (size_t idx = t0; idx < (size_t)d.Cp; idx += stride) d.cidx[idx] = idx < (size_t)d.C ? (uint16_t)ci[idx] : (uint16_t)d.K;
 }
 
 __global__ void rl_unprepare_kernel(RlayerDev d, uint8_t* __restrict__ q, __half* __restrict__ scales,
@@ -680,7 +657,17 @@ __global__ void rl_unprepare_kernel(RlayerDev d, uint8_t* __restrict__ q, __half
   for (size_t idx = t0; idx < no; idx += stride) {
     const int n = (int)(idx % d.N), o = (int)(idx / d.N);
     uint32_t u[8];
-    for (int i = 0; i < 8; ++i) u[i] = rl_read_code(d, n, 8 * o + i);
+    for (int e = 0; e < 8; ++e) {
+      const int kc = 8 * o + e;
+      const uint8_t* gp = d.tiles + (size_t)(n >> 4) * d.tile_bytes + (size_t)(kc >> 7) * 256 * d.bits;
+      uint32_t v = 0;
+      for (int i = 0; i < d.bits; ++i) {
+        int off, bit;
+        rl_bit_pos(d.bits, n & 15, kc & 127, i, &off, &bit);
+        v |= ((*reinterpret_cast<const uint32_t*>(gp + off) >> bit) & 1u) << i;
+      }
+      u[e] = v;
+    }
     if (d.bits == 4) {
       for (int i = 0; i < 4; ++i) q[(size_t)(4 * o + i) * d.N + n] = (uint8_t)(u[2 * i] | (u[2 * i + 1] << 4));
     } else {
@@ -693,11 +680,18 @@ __global__ void rl_unprepare_kernel(RlayerDev d, uint8_t* __restrict__ q, __half
   for (size_t idx = t0; idx < (size_t)d.N * ngr; idx += stride) {
     const int n = (int)(idx % d.N), gi = (int)(idx / d.N);
     const int kc = gi * d.G;
-    scales[(size_t)gi * d.N + n] = *rl_scale_ptr(d, n, (kc >> 7) * d.sets + ((kc >> 6) & (d.sets - 1)));
+    const int gs = (kc >> 7) * d.sets + ((kc >> 6) & (d.sets - 1));
+    const __half* sp = reinterpret_cast<const __half*>(d.tiles + (size_t)(n >> 4) * d.tile_bytes + d.scal_off) +
+                       ((size_t)gs * 8 + (n & 7)) * 2 + ((n >> 3) & 1);
+    scales[(size_t)gi * d.N + n] = *sp;
   }
   for (size_t idx = t0; idx < (size_t)d.N * d.C; idx += stride) {
     const int n = (int)(idx % d.N), c = (int)(idx / d.N);
-    cw[(size_t)c * d.N + n] = *rl_cherry_ptr(d, n, c);
+    const int rl = n & 15, cc = c & 15;
+    const int lane = (rl & 7) * 4 + ((cc & 7) >> 1), j = ((cc >> 3) << 1) | (rl >> 3);
+    const __half* cp = reinterpret_cast<const __half*>(d.tiles + (size_t)(n >> 4) * d.tile_bytes + d.cher_off +
+                                                       (size_t)(c >> 4) * 512 + lane * 16 + j * 4) + (cc & 1);
+    cw[(size_t)c * d.N + n] = *cp;
   }
   for (size_t idx = t0; idx < (size_t)d.C; idx += stride) ci[idx] = (int16_t)d.cidx[idx];
 }
@@ -721,63 +715,88 @@ RvDevice rv_device(int dev) {
 
 inline int rv_align(int v, int a) { return (v + a - 1) / a * a; }
 
-template <int W, int D, int R>
+template <int W, int GPW>
 RowvecFn rv_pick(int bits, int sets) {
-  if (bits == 4) return sets == 1 ? cq_rowvec_kernel<4, 1, W, D, R> : cq_rowvec_kernel<4, 2, W, D, R>;
-  return sets == 1 ? cq_rowvec_kernel<3, 1, W, D, R> : cq_rowvec_kernel<3, 2, W, D, R>;
+  if (bits == 4) return cq_rowvec_kernel<4, 1, W, GPW>;
+  return sets == 1 ? cq_rowvec_kernel<3, 1, W, GPW> : cq_rowvec_kernel<3, 2, W, GPW>;
 }
 
-// One launch; `fn`'s warp count is W and its global-memory pipeline depth D (0: none).
-// smem_kb caps the shared memory a CTA takes (0: all of it).
-int rv_launch(RowvecFn fn, int W, int D, int pre_pct, int smem_kb, const cq_rlayer* L, const __half* x, __half* y,
+// Shared-memory plan of a kernel with W working warps that own up to GPW groups each; fills the
+// launch parameters that do not depend on the call.  Returns a status code.
+int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* L, const RvDevice& di, RowvecParams* p, int* grid_out,
+            int* smem_out) {
+  if ((L->NG + W - 1) / W > GPW) return CQ_ERR_UNSUPPORTED;
+  if (L->Cp / 16 > W) return CQ_ERR_UNSUPPORTED;
+  if (GPW * 128 + L->C + 8 > (GPW / 2 + 1) * 256) return CQ_ERR_UNSUPPORTED;   // a warp's slice of x: XCH pieces per lane
+  const int grid = di.sms < L->NT ? di.sms : L->NT;
+  const int nt_max = (L->NT + grid - 1) / grid;
+  p->K = L->K; p->N = L->N; p->C = L->C; p->NG = L->NG; p->ncb = L->Cp / 16;
+  p->tile_bytes = L->tile_bytes;
+  p->scal_off = L->NG * 256 * L->bits;
+  p->cher_off = p->scal_off + L->NG * L->sets * 32;
+  p->tiles_q = L->NT / grid; p->tiles_r = L->NT % grid;
+  // a warp's staging area: the raw slice (its column range + alignment slack + zero slot), later its planes
+  const int gmax = (L->NG + W - 1) / W;
+  p->slice_halves = rv_align(gmax * 128 + L->C + 8 + 8 + 8, 8);
+  if (p->slice_halves < gmax * 128) p->slice_halves = gmax * 128;     // planes: 256 bytes per group
+  int off = 0;
+  p->off_slice = off; off = rv_align(off + W * p->slice_halves * 2, 16);
+  p->off_part = off;  off = rv_align(off + nt_max * W * 16 * 4, 16);
+  p->off_bar = off;   off = rv_align(off + 2 * RV_MAX_SLOTS * 8, 128);
+  p->off_tiles = off;
+  int budget = di.max_smem - 1024;          // the kernel also has a small static allocation; keep clear of the limit
+  if (smem_kb > 0 && smem_kb * 1024 < budget) budget = smem_kb * 1024;
+  int slots = (budget - off) / L->tile_bytes;
+  if (slots > nt_max) slots = nt_max;
+  if (slots > RV_MAX_SLOTS) slots = RV_MAX_SLOTS;
+  if (slots < 1 || (slots < 2 && nt_max > 1)) return CQ_ERR_TOO_LARGE;
+  p->slots = slots;
+  // measured on B200: two tiles outstanding stream best when a CTA has several tiles (4096 -> 11008: 5.7 us
+  // against 6.6 with one and 6.1 with three); with one or two tiles per CTA a single outstanding tile is faster
+  if (inflight <= 0) inflight = nt_max >= 3 ? 2 : 1;
+  p->inflight = inflight > slots ? slots : inflight;
+  *grid_out = grid;
+  *smem_out = off + slots * L->tile_bytes;
+  return CQ_OK;
+}
+
+// One launch of a kernel whose warp count is W and whose warps can own GPW groups.
+// inflight: tiles the copy warp keeps outstanding.
+int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_rlayer* L, const __half* x, __half* y,
               int accumulate, uint32_t* status, cudaStream_t st) {
   int dev = 0;
   CQ_CUDA_TRY(cudaGetDevice(&dev));
   const RvDevice di = rv_device(dev);
   if (!di.ok) return CQ_ERR_NO_DEVICE;
-  if (L->nsl > W) return CQ_ERR_UNSUPPORTED;
-  int grid = di.sms;
-  const int RL = W / L->nsl;
-  const int want = (L->N + RL - 1) / RL;
-  if (grid > want) grid = want;
-  if (grid < 1) grid = 1;
-  const int rows_max = (L->N + grid - 1) / grid + 1;
-
   RowvecParams p;
+  int grid = 0, smem = 0;
+  const int rc = rv_plan(W, GPW, inflight, smem_kb, L, di, &p, &grid, &smem);
+  if (rc != CQ_OK) return rc;
   const uint8_t* blob = (const uint8_t*)L->blob;
-  p.rows = blob + L->off_rows;
+  p.tiles = blob + L->off_tiles;
   p.perm = (const uint16_t*)(blob + L->off_perm);
   p.cidx = (const uint16_t*)(blob + L->off_cidx);
   p.x = x; p.y = y; p.status = status;
-  p.K = L->K; p.N = L->N; p.C = L->C; p.NG = L->NG; p.nsl = L->nsl; p.gps = L->gps; p.cps = L->cps;
-  p.accumulate = accumulate; p.row_bytes = L->row_bytes; p.srow_bytes = L->srow_bytes; p.rec_bytes = L->rec_bytes;
+  p.accumulate = accumulate;
 #ifdef CQ_ROWVEC_TRACE
   static int launch_no = 0;
   p.trace_launch = launch_no++;
+  p.trace = cq_rv_trace_host;
 #endif
-  int off = rv_align((L->K + 8) * 2, 16);
-  p.off_planes = off; off += 256 * L->NG;
-  p.off_sx = off; off = rv_align(off + (1 + L->sets) * 4 * L->NG, 16);
-  p.off_part = off; off = rv_align(off + (L->nsl > 1 ? rows_max * L->nsl * 4 : 0), 16);
-  p.off_bar = off; off = rv_align(off + RV_NBAR * 8, 128);
-  p.off_rows = off;
-  int budget = di.max_smem - 64;            // the kernel also has a small static allocation
-  if (smem_kb > 0 && smem_kb * 1024 < budget) budget = smem_kb * 1024;
-  int smem_rows = (budget - off) / L->rec_bytes;
-  if (smem_rows < 0) smem_rows = 0;
-  if (smem_rows > rows_max) smem_rows = rows_max;
-  if (D == 0 && smem_rows < rows_max) return CQ_ERR_TOO_LARGE;
-  p.smem_rows = smem_rows;
-  p.rows_q = L->N / grid; p.rows_r = L->N % grid;
-  p.pre_pct = pre_pct % 1000;
-  p.l2_prefetch = pre_pct / 1000;
-  const int smem = off + smem_rows * L->rec_bytes;
-  if (smem > di.max_smem) return CQ_ERR_TOO_LARGE;
-  CQ_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-
+  {
+    // opt in to the dynamic shared memory this launch needs (remembered per kernel and device)
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, int> granted;
+    std::lock_guard<std::mutex> lk(mu);
+    int& have = granted[{(const void*)fn, dev}];
+    if (smem > have) {
+      CQ_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      have = smem;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(W * 32);
+  cfg.blockDim = dim3((W + 1) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -788,15 +807,13 @@ int rv_launch(RowvecFn fn, int W, int D, int pre_pct, int smem_kb, const cq_rlay
   CQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, fn, p));
   return CQ_OK;
 }
-}  // namespace
 
-#ifndef CQ_ROWVEC_W
-#define CQ_ROWVEC_W 12
-#define CQ_ROWVEC_D 2
-#define CQ_ROWVEC_PRE 60
-#define CQ_ROWVEC_R 4
-#define CQ_ROWVEC_PF 0
-#endif
+constexpr int RV_W = 16;                      // working warps of the product kernels
+inline int rv_gpw_for(const cq_rlayer* L) {   // smallest instantiated groups-per-warp that holds the layer, 0 if none
+  const int need = (L->NG + RV_W - 1) / RV_W;
+  return need <= 2 ? 2 : (need <= 4 ? 4 : (need <= 7 ? 7 : 0));
+}
+}  // namespace
 
 extern "C" int cq_rlayer_init(cq_rlayer* L, int bits, int K, int N, int C, int G, void* blob) {
   if (!L) return CQ_ERR_BAD_ARG;
@@ -809,17 +826,13 @@ extern "C" int cq_rlayer_init(cq_rlayer* L, int bits, int K, int N, int C, int G
   L->Kc = K - C;
   L->NG = (L->Kc + 127) / 128;
   L->sets = G == 64 ? 2 : 1;
-  L->nsl = (L->NG + 31) / 32;
-  L->gps = (L->NG + L->nsl - 1) / L->nsl;
-  L->cps = (C + L->nsl - 1) / L->nsl;
-  if (L->cps > 32) return CQ_ERR_UNSUPPORTED;      // more than 32 cherry columns per 4096 columns
-  L->row_bytes = L->NG * 16 * bits;
-  L->srow_bytes = (L->NG * L->sets * 2 + 15) / 16 * 16;
-  L->rec_bytes = L->row_bytes + L->srow_bytes + C * 2;
+  L->Cp = (C + 15) / 16 * 16;
+  L->NT = (N + 15) / 16;
+  L->tile_bytes = L->NG * 256 * bits + L->NG * L->sets * 32 + (L->Cp / 16) * 512;
   uint64_t off = 0;
-  L->off_rows = off;   off += (uint64_t)N * L->rec_bytes;           off = (off + 255) / 256 * 256;
-  L->off_perm = off;   off += (uint64_t)L->NG * 128 * 2;            off = (off + 255) / 256 * 256;
-  L->off_cidx = off;   off += (uint64_t)(C > 0 ? C : 8) * 2;        off = (off + 255) / 256 * 256;
+  L->off_tiles = off;  off += (uint64_t)L->NT * L->tile_bytes;        off = (off + 255) / 256 * 256;
+  L->off_perm = off;   off += (uint64_t)L->NG * 128 * 2;              off = (off + 255) / 256 * 256;
+  L->off_cidx = off;   off += (uint64_t)(L->Cp > 0 ? L->Cp : 16) * 2; off = (off + 255) / 256 * 256;
   L->blob_bytes = off;
   L->blob = blob;
   return CQ_OK;
@@ -850,18 +863,38 @@ extern "C" int cq_rlayer_unprepare(const cq_rlayer* L, uint8_t* qweight, void* s
   return CQ_OK;
 }
 
+extern "C" int cq_rlayer_check(const cq_rlayer* L) {
+  if (!L) return CQ_ERR_BAD_ARG;
+  int dev = 0;
+  CQ_CUDA_TRY(cudaGetDevice(&dev));
+  const RvDevice di = rv_device(dev);
+  if (!di.ok) return CQ_ERR_NO_DEVICE;
+  const int gpw = rv_gpw_for(L);
+  if (!gpw) return CQ_ERR_UNSUPPORTED;
+  RowvecParams p;
+  int grid = 0, smem = 0;
+  return rv_plan(RV_W, gpw, CQ_ROWVEC_INFLIGHT, 0, L, di, &p, &grid, &smem);
+}
+
 extern "C" int cq_rlayer_matvec(const cq_rlayer* L, const void* x, void* y, int accumulate, uint32_t* status_word,
                                 cq_stream_t stream) {
   if (!L || !L->blob || !x || !y) return CQ_ERR_BAD_ARG;
   if (((uintptr_t)x & 1) || ((uintptr_t)y & 1)) return CQ_ERR_BAD_ARG;
-  return rv_launch(rv_pick<CQ_ROWVEC_W, CQ_ROWVEC_D, CQ_ROWVEC_R>(L->bits, L->sets), CQ_ROWVEC_W, CQ_ROWVEC_D, CQ_ROWVEC_PRE + 1000 * CQ_ROWVEC_PF, 0, L,
-                   (const __half*)x, (__half*)y, accumulate, status_word, (cudaStream_t)stream);
+  const __half* xp = (const __half*)x;
+  __half* yp = (__half*)y;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (rv_gpw_for(L)) {
+    case 2: return rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, L, xp, yp, accumulate, status_word, st);
+    case 4: return rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, L, xp, yp, accumulate, status_word, st);
+    case 7: return rv_launch(rv_pick<RV_W, 7>(L->bits, L->sets), RV_W, 7, CQ_ROWVEC_INFLIGHT, 0, L, xp, yp, accumulate, status_word, st);
+    default: return CQ_ERR_UNSUPPORTED;
+  }
 }
 
 #ifdef CQ_ROWVEC_SWEEP
 // Tuning build only (not part of the library): a table of kernel shapes behind one entry point.
-#define RV_CASE(id, W, D, R, SMEM_KB, PRE, PF) \
-  case id: return rv_launch(rv_pick<W, D, R>(L->bits, L->sets), W, D, PRE + 1000 * PF, SMEM_KB, L, (const __half*)x, (__half*)y, accumulate, status_word, (cudaStream_t)stream);
+#define RV_CASE(id, W, GPW, SMEM_KB, INFL) \
+  case id: return rv_launch(rv_pick<W, GPW>(L->bits, L->sets), W, GPW, INFL, SMEM_KB, L, (const __half*)x, (__half*)y, accumulate, status_word, (cudaStream_t)stream);
 extern "C" int cq_rlayer_matvec_variant(int variant, const cq_rlayer* L, const void* x, void* y, int accumulate,
                                         uint32_t* status_word, cq_stream_t stream) {
   switch (variant) {
@@ -871,8 +904,7 @@ extern "C" int cq_rlayer_matvec_variant(int variant, const cq_rlayer* L, const v
 }
 #ifdef CQ_ROWVEC_TRACE
 extern "C" int cq_rv_set_trace(void* device_buffer) {
-  unsigned long long* ptr = (unsigned long long*)device_buffer;
-  CQ_CUDA_TRY(cudaMemcpyToSymbol(cq_rv_trace, &ptr, sizeof(ptr)));
+  cq_rv_trace_host = (unsigned long long*)device_buffer;
   return CQ_OK;
 }
 #endif

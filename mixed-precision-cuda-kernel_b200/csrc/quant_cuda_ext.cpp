@@ -16,8 +16,10 @@
 #include <torch/extension.h>
 #include <cmath>
 
+#include <array>
 #include <map>
 #include <mutex>
+#include <vector>
 
 #include "cherryq.h"
 
@@ -42,6 +44,56 @@ void check_tensor(const torch::Tensor& t, const char* name, c10::ScalarType dtyp
 
 cq_stream_t current_stream() { return (cq_stream_t)c10::cuda::getCurrentCUDAStream().stream(); }
 
+// The C library caches re-packed copies by buffer ADDRESS.  Torch's allocator hands a freed block to
+// the next tensor of the same size, so an address alone does not identify a buffer: every cached set
+// is paired here with weak references to the four tensors' storages.  A call whose storages are not
+// the ones on record (or whose record has expired) evicts the library's copies for these addresses
+// before it proceeds, and every such miss also sweeps the records whose storages have died, which
+// frees their copies.  The reference's ops keep no state at all (csrc/quant_cuda.cpp:56-69).
+struct StorageGuard {
+  std::vector<c10::weak_intrusive_ptr<c10::StorageImpl>> w;   // four entries
+  const void* ptr[4];
+  int device;
+};
+std::mutex g_guard_mu;
+std::map<std::array<const void*, 4>, StorageGuard> g_guards;
+
+void guard_buffers(const torch::Tensor& q, const torch::Tensor& s, const torch::Tensor& cw, const torch::Tensor& ci) {
+  const torch::Tensor* t[4] = {&q, &s, &cw, &ci};
+  std::array<const void*, 4> key = {q.data_ptr(), s.data_ptr(), cw.data_ptr(), ci.data_ptr()};
+  std::lock_guard<std::mutex> lock(g_guard_mu);
+  auto it = g_guards.find(key);
+  if (it != g_guards.end()) {
+    bool same = true;
+    for (int i = 0; i < 4; ++i) {
+      auto sp = it->second.w[i].lock();
+      same = same && sp && sp.get() == t[i]->storage().unsafeGetStorageImpl();
+    }
+    if (same) return;
+    g_guards.erase(it);
+  }
+  // unknown or recycled addresses: whatever the library holds for them is stale
+  cq_cache_evict(key[0], key[1], key[2], key[3]);
+  for (auto g = g_guards.begin(); g != g_guards.end();) {
+    bool dead = false;
+    for (int i = 0; i < 4; ++i) dead = dead || g->second.w[i].expired();
+    if (dead) {
+      const at::cuda::OptionalCUDAGuard dg(c10::Device(c10::kCUDA, (c10::DeviceIndex)g->second.device));
+      cq_cache_evict(g->second.ptr[0], g->second.ptr[1], g->second.ptr[2], g->second.ptr[3]);
+      g = g_guards.erase(g);
+    } else {
+      ++g;
+    }
+  }
+  StorageGuard ng;
+  for (int i = 0; i < 4; ++i) {
+    ng.w.push_back(t[i]->storage().getWeakStorageImpl());
+    ng.ptr[i] = key[i];
+  }
+  ng.device = q.device().index();
+  g_guards.emplace(key, std::move(ng));
+}
+
 uint64_t version_tag(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& c,
                      const torch::Tensor& d) {
   // inference tensors (created under torch.inference_mode) keep no version counter
@@ -64,6 +116,7 @@ void vecquant3matmul_cherryq(torch::Tensor vec, torch::Tensor qweight, torch::Te
   TORCH_CHECK(vec.dim() == 2 && qweight.dim() == 2 && mul.dim() == 2, "vec, qweight and mul must be 2-D");
   TORCH_CHECK(mul.size(0) == vec.size(0) && mul.size(1) == qweight.size(1), "mul must be (batch, width)");
   TORCH_CHECK(cherry_weight.numel() == cherry_indices.size(0) * qweight.size(1), "cherry_weight must be (C, width)");
+  if (fp16) guard_buffers(qweight, scaling_factors, cherry_weight, cherry_indices);
   check_status(cq_vecquant3matmul_cherryq(
                    vec.data_ptr(), qweight.data_ptr<uint8_t>(), cherry_weight.data_ptr(), cherry_indices.data_ptr(),
                    scaling_factors.data_ptr(), mul.data_ptr(), (int)vec.size(0), (int)vec.size(1),
@@ -85,6 +138,7 @@ void vecquant4matmul_cherryq(torch::Tensor vec, torch::Tensor qweight, torch::Te
   TORCH_CHECK(vec.dim() == 2 && qweight.dim() == 2 && mul.dim() == 2, "vec, qweight and mul must be 2-D");
   TORCH_CHECK(mul.size(0) == vec.size(0) && mul.size(1) == qweight.size(1), "mul must be (batch, width)");
   TORCH_CHECK(cherry_weight.numel() == cherry_indices.size(0) * qweight.size(1), "cherry_weight must be (C, width)");
+  guard_buffers(qweight, scaling_factors, cherry_weight, cherry_indices);
   check_status(cq_vecquant4matmul_cherryq(
                    vec.data_ptr(), qweight.data_ptr<uint8_t>(), cherry_weight.data_ptr(),
                    (const int16_t*)cherry_indices.data_ptr(), scaling_factors.data_ptr(), mul.data_ptr(),
@@ -237,6 +291,69 @@ struct PreparedLayer {
   }
 };
 
+// A layer re-packed into the row-tile layout of the one-row decode kernel; owns its device blob.
+struct RowLayer {
+  cq_rlayer layer;
+  torch::Tensor blob;
+
+  // CQ_OK if the one-row kernel can run such a layer on the current device
+  static bool supported(int bits, int in_features, int out_features, int num_cherries, int group_size) {
+    cq_rlayer L;
+    if (cq_rlayer_init(&L, bits, in_features, out_features, num_cherries, group_size, nullptr) != CQ_OK) return false;
+    return cq_rlayer_check(&L) == CQ_OK;
+  }
+
+  RowLayer(torch::Tensor qweight, torch::Tensor scales, torch::Tensor cherry_weight, torch::Tensor cherry_indices,
+           int bits, int in_features, int group_size) {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(qweight));
+    check_tensor(qweight, "qweight", torch::kUInt8, qweight);
+    check_tensor(scales, "scales", torch::kFloat16, qweight);
+    check_tensor(cherry_weight, "cherry_weight", torch::kFloat16, qweight);
+    check_tensor(cherry_indices, "cherry_indices", torch::kInt16, qweight);
+    const int N = (int)qweight.size(1), C = (int)cherry_indices.numel();
+    check_status(cq_rlayer_init(&layer, bits, in_features, N, C, group_size, nullptr), "RowLayer");
+    check_status(cq_rlayer_check(&layer), "RowLayer");
+    TORCH_CHECK(qweight.size(0) == layer.Kc / 8 * bits, "qweight has ", qweight.size(0), " rows, expected ",
+                layer.Kc / 8 * bits);
+    TORCH_CHECK(scales.size(0) == (layer.Kc + layer.G - 1) / layer.G && scales.size(1) == N, "scales must be (ceil(K'/G), N)");
+    blob = torch::empty({(int64_t)layer.blob_bytes}, qweight.options());
+    layer.blob = blob.data_ptr();
+    check_status(cq_rlayer_prepare(&layer, qweight.data_ptr<uint8_t>(), scales.data_ptr(), cherry_weight.data_ptr(),
+                                   (const int16_t*)cherry_indices.data_ptr(), current_stream()),
+                 "RowLayer");
+    // the kernel copies weights ahead of stream order: finish the re-pack first
+    c10::cuda::getCurrentCUDAStream().synchronize();
+  }
+
+  // out (1, N) fp16 = [out +] x (1, K) fp16 . W^T
+  void matvec(torch::Tensor x, torch::Tensor out, bool accumulate) {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(x));
+    check_tensor(x, "x", torch::kFloat16, blob);
+    check_tensor(out, "out", torch::kFloat16, blob);
+    TORCH_CHECK(x.numel() == layer.K, "x must hold one row of ", layer.K, " activations");
+    TORCH_CHECK(out.numel() == layer.N, "out must hold one row of ", layer.N, " values");
+    auto scratch = scratch_for(x.device());
+    uint8_t* sp = scratch.data_ptr<uint8_t>();
+    check_status(cq_rlayer_matvec(&layer, x.data_ptr(), out.data_ptr(), accumulate ? 1 : 0,
+                                  (uint32_t*)(sp + cq_scratch_bytes()), current_stream()),
+                 "RowLayer.matvec");
+  }
+
+  // Back to the reference's four buffers: (qweight, scales, cherry_weight, cherry_indices).
+  std::vector<torch::Tensor> unprepare() {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(blob));
+    auto o = blob.options();
+    auto qweight = torch::empty({layer.Kc / 8 * layer.bits, layer.N}, o);
+    auto scales = torch::empty({(layer.Kc + layer.G - 1) / layer.G, layer.N}, o.dtype(torch::kFloat16));
+    auto cw = torch::empty({layer.C, layer.N}, o.dtype(torch::kFloat16));
+    auto idx = torch::empty({layer.C}, o.dtype(torch::kInt16));
+    check_status(cq_rlayer_unprepare(&layer, qweight.data_ptr<uint8_t>(), scales.data_ptr(), cw.data_ptr(),
+                                     (int16_t*)idx.data_ptr(), current_stream()),
+                 "RowLayer.unprepare");
+    return {qweight, scales, cw, idx};
+  }
+};
+
 // Reads and clears the status word the PreparedLayer launches report into.
 bool device_timed_out(int device_index) {
   torch::Tensor t;
@@ -339,7 +456,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("Dequantize4Normal", &Dequantize4Normal, "Dequantize4Normal");
   m.def("pack", &pack, "GPU QuantLinear.pack");
   m.def("unpack_dense", &unpack_dense, "GPU QuantLinear.unpack");
-  m.def("cache_clear", []() { check_status(cq_cache_clear(), "cache_clear"); });
+  m.def("cache_clear", []() {
+    check_status(cq_cache_clear(), "cache_clear");
+    std::lock_guard<std::mutex> lock(g_guard_mu);
+    g_guards.clear();
+  });
   m.def("cache_stats", []() {
     int n = 0;
     uint64_t b = 0;
@@ -353,6 +474,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("poll", []() { check_status(cq_poll(current_stream()), "poll"); });
   m.def("device_timed_out", &device_timed_out);
   m.def("abi_version", &cq_abi_version);
+  py::class_<RowLayer>(m, "RowLayer")
+      .def(py::init<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int, int, int>())
+      .def_static("supported", &RowLayer::supported)
+      .def("matvec", &RowLayer::matvec)
+      .def("unprepare", &RowLayer::unprepare)
+      .def_readonly("blob", &RowLayer::blob)
+      .def_property_readonly("out_features", [](const RowLayer& p) { return p.layer.N; })
+      .def_property_readonly("in_features", [](const RowLayer& p) { return p.layer.K; });
   py::class_<PreparedLayer>(m, "PreparedLayer")
       .def(py::init<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int, int, int>())
       .def(py::init<torch::Tensor, int, int, int, int, int>())

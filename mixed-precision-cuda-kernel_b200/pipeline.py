@@ -182,7 +182,7 @@ def load_decoder_state_dict(dec, state: Dict[str, torch.Tensor]):
                     raise ValueError(f"{base}{hf}.{b}: expected {tuple(cur.shape)} {cur.dtype}, found "
                                      f"{tuple(src.shape)} {src.dtype}")
                 setattr(ql, b, src.to(cur.device).contiguous())
-            ql._prepared = None
+            ql._drop_copies()
             if dec.dense:
                 ql.dense_weight = ql.unpack()
     dec.graph = None

@@ -4,9 +4,13 @@ Same constructor, buffers (`cherry_indices` int16 (C,), `cherry_weight` fp16 (C,
 `qweight` uint8 (K'/8*bits, N), `scales` fp16 (ceil(K'/G), N), optional `bias`),
 `pack()`, `unpack()`, `forward()` and class-level `dmode()` switch as the reference,
 so a state dict written by the reference loads into it.  What runs underneath is
-different: pack and unpack are GPU kernels, and forward runs the stream matvec on
-a re-packed copy of the buffers (made on first use; `release_reference_buffers()`
-drops the originals afterwards).  All of it needs a CUDA device.
+different: pack and unpack are GPU kernels, and forward runs on re-packed copies of
+the buffers that the module owns (made on first use of the kernel family that needs
+them; `release_reference_buffers()` drops the originals afterwards):
+  one activation row    row-tile layout, the one-row decode kernel (where the layer fits it)
+  2..7 rows             stream layout, the stream matvec
+  8 rows or more        the drop-in op's tensor-core GEMM (tile layout, cached by the library)
+All of it needs a CUDA device.
 """
 import math
 from contextlib import contextmanager
@@ -53,7 +57,9 @@ class QuantLinear(nn.Module):
         else:
             self.bias = None
         self.dequantized = False
-        self._prepared = None
+        self._prepared = None        # stream layout (PreparedLayer)
+        self._row = None             # row-tile layout (RowLayer)
+        self._row_ok = None          # None = not asked yet
         self._prepared_key = None
 
     # ------------------------------------------------------------------ pack / unpack
@@ -75,7 +81,7 @@ class QuantLinear(nn.Module):
         gs = linear.group_size if linear.group_size != -1 else self.in_features
         q, s, cw, ci = qc.pack(weight, idx, self.w_bits, gs)
         self.qweight, self.scales, self.cherry_weight, self.cherry_indices = q, s, cw, ci
-        self._prepared = None
+        self._drop_copies()
 
     @torch.inference_mode()
     def unpack(self):
@@ -96,28 +102,64 @@ class QuantLinear(nn.Module):
         bufs = (self.qweight, self.scales, self.cherry_weight, self.cherry_indices)
         return tuple(t.data_ptr() for t in bufs) + tuple(ver(t) for t in bufs)
 
+    def _drop_copies(self):
+        self._prepared = None
+        self._row = None
+        self._row_ok = None
+        self._prepared_key = None
+
+    def _sync_key(self):
+        """Forgets the re-packed copies when the reference buffers were replaced or written to."""
+        if self._prepared_key == "released":
+            return
+        key = self._buffer_key()
+        if self._prepared_key != key:
+            self._drop_copies()
+            self._prepared_key = key
+
+    def _source_buffers(self):
+        """The four reference buffers: the module's own, or rebuilt from a copy after a release."""
+        if self._prepared_key != "released":
+            return self.qweight, self.scales, self.cherry_weight, self.cherry_indices
+        src = self._row if self._row is not None else self._prepared
+        return src.unprepare()
+
     def prepared(self):
         """The stream-layout copy of this layer (built on first use)."""
-        key = self._buffer_key()
-        if self._prepared is None or self._prepared_key != key:
+        self._sync_key()
+        if self._prepared is None:
             qc = load_quant_cuda()
             self._require_cuda()
-            self._prepared = qc.PreparedLayer(self.qweight, self.scales, self.cherry_weight, self.cherry_indices,
-                                              self.w_bits, self.in_features, self.group_size)
-            self._prepared_key = key
+            q, s, cw, ci = self._source_buffers()
+            self._prepared = qc.PreparedLayer(q, s, cw, ci, self.w_bits, self.in_features, self.group_size)
         return self._prepared
 
+    def row_layer(self):
+        """The row-tile copy for the one-row decode kernel, or None where the layer does not fit it."""
+        self._sync_key()
+        if self._row_ok is None:
+            qc = load_quant_cuda()
+            self._require_cuda()
+            self._row_ok = qc.RowLayer.supported(self.w_bits, self.in_features, self.out_features,
+                                                 self.num_cherries, self.group_size)
+        if self._row_ok and self._row is None:
+            qc = load_quant_cuda()
+            q, s, cw, ci = self._source_buffers()
+            self._row = qc.RowLayer(q, s, cw, ci, self.w_bits, self.in_features, self.group_size)
+        return self._row
+
     def release_reference_buffers(self):
-        """Keeps only the stream-layout copy (halves the weight memory); `restore_reference_buffers`
-        rebuilds the four buffers bit-exactly."""
-        self.prepared()
+        """Keeps only the re-packed copies (roughly halves the weight memory);
+        `restore_reference_buffers` rebuilds the four buffers bit-exactly."""
+        if self.row_layer() is None:
+            self.prepared()
         dev = self.qweight.device
         for name in ("qweight", "scales", "cherry_weight", "cherry_indices"):
             setattr(self, name, torch.empty(0, dtype=getattr(self, name).dtype, device=dev))
         self._prepared_key = "released"
 
     def restore_reference_buffers(self):
-        q, s, cw, ci = self._prepared.unprepare()
+        q, s, cw, ci = self._source_buffers()
         self.qweight, self.scales, self.cherry_weight, self.cherry_indices = q, s, cw, ci
         self._prepared_key = self._buffer_key()
 
@@ -126,16 +168,20 @@ class QuantLinear(nn.Module):
         if self._layerwise_dequantize:
             if self.w_bits not in (3, 4):
                 raise NotImplementedError(f"{self.w_bits} bit kernel is not implemented yet.")
-            layer = self._prepared if self._prepared_key == "released" else self.prepared()
             out_shape = x.shape[:-1] + (self.out_features,)
             x2 = x.reshape(-1, x.shape[-1])
             if x2.dtype != torch.float16:
                 x2 = x2.half()
             x2 = x2.contiguous()
-            if x2.shape[0] >= 8 and self._prepared_key != "released":
+            rows = x2.shape[0]
+            row = self.row_layer() if rows == 1 else None
+            if row is not None:
+                out = torch.empty(1, self.out_features, dtype=torch.float16, device=x2.device)
+                row.matvec(x2, out, False)
+            elif rows >= 8 and self._prepared_key != "released":
                 # 8 rows or more: the drop-in op routes them to the tensor-core GEMM (faster from there on)
                 qc = load_quant_cuda()
-                out = torch.zeros(x2.shape[0], self.out_features, dtype=torch.float16, device=x2.device)
+                out = torch.zeros(rows, self.out_features, dtype=torch.float16, device=x2.device)
                 if self.w_bits == 4:
                     qc.vecquant4matmul_cherryq(x2, self.qweight, self.cherry_weight, self.cherry_indices,
                                                self.scales, out, self.group_size)
@@ -143,8 +189,8 @@ class QuantLinear(nn.Module):
                     qc.vecquant3matmul_cherryq(x2, self.qweight, self.cherry_weight, self.cherry_indices,
                                                self.scales, out, self.group_size, True)
             else:
-                out = torch.empty(x2.shape[0], self.out_features, dtype=torch.float16, device=x2.device)
-                layer.matvec(x2, out, False)
+                out = torch.empty(rows, self.out_features, dtype=torch.float16, device=x2.device)
+                self.prepared().matvec(x2, out, False)
             out = out.reshape(out_shape).to(x.dtype)
         else:
             if not self.dequantized:
@@ -152,7 +198,7 @@ class QuantLinear(nn.Module):
                 del self.cherry_indices
                 del self.cherry_weight
                 del self.scales
-                self._prepared = None
+                self._drop_copies()
                 torch.cuda.empty_cache()
                 self.dequantized = True
             out = nn.functional.linear(x, self.qweight)

@@ -32,13 +32,17 @@ def test_library_exports_every_declared_symbol():
 def test_host_only_entry_points():
     from cherryq_b200 import _cabi
     lib = _cabi.lib()
-    assert lib.cq_abi_version() == 1
+    assert lib.cq_abi_version() == 2
     assert _cabi.strerror(0) == "ok"
     assert "multiple of 128" in _cabi.strerror(3)
     L = _cabi.layer_init(4, 4096, 11008, 16, 128)
     assert (L.Kc, L.n_gran, L.n_sub, L.gran_bytes) == (4080, 32, 688, 1056)
     T = _cabi.tlayer_init(3, 8192, 28672, 32, 128)
     assert (T.n_tile, T.n_cher, T.gran_bytes) == (224, 2, 6400)
+    R = _cabi.rlayer_init(4, 4096, 11008, 16, 128)
+    assert (R.NG, R.NT, R.Cp, R.tile_bytes) == (32, 688, 16, 32 * 1024 + 32 * 32 + 512)
+    R3 = _cabi.rlayer_init(3, 640, 40, 0, 64)
+    assert (R3.NG, R3.sets, R3.NT, R3.tile_bytes) == (5, 2, 3, 5 * 768 + 5 * 2 * 32)
     assert lib.cq_scratch_bytes() >= 2 * 1024 * 1024
     for bad in [(5, 4096, 64, 16, 128), (4, 4100, 64, 16, 128), (4, 4096, 64, 16, 96)]:
         with pytest.raises(RuntimeError):

@@ -1,0 +1,265 @@
+"""GPU parity of the one-row decode kernel (cq_rlayer_*), all through the C ABI (ctypes, raw device
+pointers): re-pack against the numpy layout model and back, matvec against the fp64 dequantised
+matmul of the oracle, on the golden fixtures, the LLaMA 7B / 13B / 70B shapes, edge shapes and
+heavy-tailed activations."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+
+import rowtile_model as RM
+from conftest import golden_cases, load_golden
+from oracle import cherryq_oracle as O
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-2     # north-star bound: max |y - y_ref| / max |y_ref| against the fp64 dequantised matmul
+TIGHT_TOL = 2e-3   # what exact integer sums + fp32 scaling + one fp16 store actually deliver
+
+
+@pytest.fixture(scope="module")
+def cabi():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from cherryq_b200 import _cabi
+    _cabi.lib()
+    return _cabi
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def ptr(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def rel_err(y, ref):
+    return float(np.abs(np.asarray(y, dtype=np.float64) - ref).max() / np.abs(ref).max())
+
+
+class RowPrepared:
+    """A layer in the row-tile layout, prepared through the C ABI from reference-format buffers (device tensors)."""
+
+    def __init__(self, cabi, q, s, cw, ci, bits, K, G):
+        self.cabi, self.t = cabi, [q, s, cw, ci]
+        self.L = cabi.rlayer_init(bits, K, q.shape[1], ci.shape[0], G)
+        self.check = cabi.lib().cq_rlayer_check(C.byref(self.L))
+        self.blob = torch.zeros(self.L.blob_bytes, dtype=torch.uint8, device="cuda")
+        self.L.blob = self.blob.data_ptr()
+        cabi.check(cabi.lib().cq_rlayer_prepare(C.byref(self.L), *[ptr(t) for t in self.t], None), "prepare")
+        torch.cuda.synchronize()
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def matvec(self, x, y=None, accumulate=False):
+        if y is None:
+            y = torch.full((1, self.L.N), float("nan"), dtype=torch.float16, device="cuda")
+        self.cabi.check(self.cabi.lib().cq_rlayer_matvec(C.byref(self.L), ptr(x), ptr(y), int(accumulate),
+                                                         ptr(self.status), None), "matvec")
+        torch.cuda.synchronize()
+        assert int(self.status.item()) == 0, "a device-side wait timed out"
+        return y
+
+    def unprepare(self):
+        outs = [torch.zeros_like(t) for t in self.t]
+        self.cabi.check(self.cabi.lib().cq_rlayer_unprepare(C.byref(self.L), *[ptr(t) for t in outs], None), "unprepare")
+        torch.cuda.synchronize()
+        return outs
+
+
+def golden_prepared(cabi, g):
+    return RowPrepared(cabi, dev(g["qweight"]), dev(g["scales"]), dev(g["cherry_weight"]), dev(g["cherry_indices"]),
+                       g["bits"], g["K"], g["G"])
+
+
+# ------------------------------------------------------------------ re-pack
+@pytest.mark.parametrize("name", golden_cases())
+def test_prepare_matches_layout_model_and_roundtrips(cabi, name):
+    g = load_golden(name)
+    p = golden_prepared(cabi, g)
+    model, d = RM.build_blob(g["qweight"], g["scales"], g["cherry_weight"], g["cherry_indices"], g["bits"], g["K"], g["G"])
+    got = p.blob.cpu().numpy()
+    assert d["blob_bytes"] == p.L.blob_bytes
+    for sec, nbytes in (("off_tiles", d["NT"] * d["tile_bytes"]), ("off_perm", d["NG"] * 256), ("off_cidx", d["Cp"] * 2)):
+        o = d[sec]
+        assert np.array_equal(got[o:o + nbytes], model[o:o + nbytes]), sec
+    for a, b in zip(p.unprepare(), p.t):
+        assert torch.equal(a, b)
+
+
+# ------------------------------------------------------------------ matvec on the golden layers
+@pytest.mark.parametrize("name", golden_cases())
+def test_matvec_golden(cabi, name):
+    g = load_golden(name)
+    p = golden_prepared(cabi, g)
+    assert p.check == 0
+    for row in range(3):
+        x = dev(g["x"][row:row + 1])
+        y = p.matvec(x).cpu().numpy()
+        assert np.isfinite(y).all()
+        assert rel_err(y, g["y"][row:row + 1].astype(np.float64)) <= TIGHT_TOL
+        ref = O.kernel_forward(g["x"][row:row + 1], g["qweight"], g["cherry_weight"], g["cherry_indices"], g["scales"],
+                               g["bits"], g["G"])
+        assert rel_err(y, ref) <= 1e-3
+        # bit-identical on a second run (fixed summation order, no atomics)
+        y2 = p.matvec(x).cpu().numpy()
+        assert np.array_equal(y.view(np.uint16), y2.view(np.uint16))
+
+
+def test_matvec_accumulates_like_the_reference(cabi):
+    g = load_golden("k256_n32_b4_g128_f16")
+    p = golden_prepared(cabi, g)
+    base = np.random.default_rng(0).normal(size=(1, g["N"])).astype(np.float16)
+    y = p.matvec(dev(g["x"][:1]), y=dev(base.copy()), accumulate=True).cpu().numpy()
+    assert rel_err(y, g["y"][:1].astype(np.float64) + base.astype(np.float64)) <= TIGHT_TOL
+
+
+def test_unaligned_activation_pointer(cabi):
+    """x that is only 2-byte aligned takes the kernel's scalar staging path."""
+    g = load_golden("k2048_n16_b4_g128_f16")
+    p = golden_prepared(cabi, g)
+    buf = torch.zeros(g["K"] + 8, dtype=torch.float16, device="cuda")
+    buf[1:1 + g["K"]] = dev(g["x"][0])
+    y = p.matvec(buf[1:1 + g["K"]]).cpu().numpy()
+    assert rel_err(y, g["y"][:1].astype(np.float64)) <= TIGHT_TOL
+
+
+# ------------------------------------------------------------------ model shapes
+def gpu_layer(K, N, bits, G, seed, frac=1 / 256):
+    """Synthetic layer with the configurations' distributions, packed by the GPU pack kernel (byte-identical to
+    the oracle's pack, tests/test_gpu_parity.py) and unpacked by the GPU dense unpack (byte-identical to the
+    oracle's unpack, same file): the fp64 reference of the big shapes is x . dense^T computed by torch in fp64."""
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    c = math.ceil(K * frac) // 8 * 8
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    idx = torch.randperm(K, device="cuda", generator=g)[:c].to(torch.int32)
+    if c:
+        w[:, idx.long()] = torch.randn(N, c, device="cuda", generator=g) * 0.2
+    q, s, cw, ci = qc.pack(w.half().contiguous(), idx.contiguous(), bits, G)
+    dense = qc.unpack_dense(q, s, cw, ci, bits, K, G)
+    return q, s, cw, ci, dense
+
+
+def ref64(x, dense):
+    return (x.double() @ dense.double().T).cpu().numpy()
+
+
+MODEL_SHAPES = [
+    (4096, 4096, 4), (4096, 11008, 4), (11008, 4096, 4), (4096, 4096, 3), (4096, 11008, 3), (11008, 4096, 3),   # 7B
+    (5120, 5120, 3), (5120, 13824, 3), (13824, 5120, 3),                                                       # 13B, C = 16 / 48
+    (8192, 8192, 3), (8192, 1024, 3), (8192, 28672, 3),                                                        # 70B, C = 32
+]
+
+
+@pytest.mark.parametrize("K,N,bits", MODEL_SHAPES)
+def test_matvec_model_shapes(cabi, K, N, bits):
+    q, s, cw, ci, dense = gpu_layer(K, N, bits, 128, seed=K + N + bits)
+    p = RowPrepared(cabi, q, s, cw, ci, bits, K, 128)
+    assert p.check == 0
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for _ in range(2):
+        x = torch.randn(1, K, device="cuda", generator=g).half()
+        assert rel_err(p.matvec(x).cpu().numpy(), ref64(x, dense)) <= TIGHT_TOL, (K, N, bits)
+    for a, b in zip(p.unprepare(), p.t):
+        assert torch.equal(a, b)
+
+
+def test_layers_outside_the_envelope_are_refused_and_the_op_falls_back(cabi):
+    """28672 -> 8192 (224 groups) is beyond the one-row kernel: the C ABI says so and the drop-in op serves
+    the call with the stream kernel."""
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    K, N = 28672, 1024
+    q, s, cw, ci, dense = gpu_layer(K, N, 3, 128, seed=9)
+    L = cabi.rlayer_init(3, K, N, ci.shape[0], 128)
+    assert cabi.lib().cq_rlayer_check(C.byref(L)) == 9          # CQ_ERR_UNSUPPORTED
+    assert cabi.lib().cq_rlayer_matvec(C.byref(L), ptr(q), ptr(q), 0, None, None) in (1, 9)   # no blob / unsupported
+    x = torch.randn(1, K, device="cuda").half()
+    out = torch.zeros(1, N, dtype=torch.float16, device="cuda")
+    qc.vecquant3matmul_cherryq(x, q, cw, ci, s, out, 128, True)
+    torch.cuda.synchronize()
+    assert rel_err(out.cpu().numpy(), ref64(x, dense)) <= TIGHT_TOL
+
+
+@pytest.mark.parametrize("K,N,bits,G,frac", [
+    (256, 8, 4, 128, 1 / 16),         # one tile, half of it padding rows
+    (136, 24, 3, 128, 1 / 17),        # K' = 128 exactly after 8 cherries
+    (264, 40, 4, 128, 1 / 33),        # K' = 256, N not a multiple of 16
+    (1024, 4744, 4, 128, 1 / 64),     # more tiles than SMs, ragged last tile
+    (2048, 512, 3, 64, 1 / 256),      # 64-wide groups
+    (2048, 512, 4, 2048, 1 / 256),    # one group per row
+    (2048, 512, 4, -1, 1 / 256),      # group_size -1 = whole row
+    (512, 64, 4, 128, 0.0),           # no cherries at all
+    (4096, 256, 4, 128, 112 / 4096),  # 112 cherry columns: seven cherry blocks
+    (12288, 64, 3, 128, 1 / 256),     # widest layer of the smallest register variant boundary (96 groups)
+    (14336, 48, 4, 128, 1 / 256),     # widest layer the kernel takes (112 groups)
+])
+def test_matvec_edge_shapes(cabi, K, N, bits, G, frac):
+    q, s, cw, ci, dense = gpu_layer(K, N, bits, G if G != -1 else K, seed=K * 7 + N, frac=frac)
+    p = RowPrepared(cabi, q, s, cw, ci, bits, K, G)
+    assert p.check == 0
+    x = torch.randn(1, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1)).half()
+    assert rel_err(p.matvec(x).cpu().numpy(), ref64(x, dense)) <= TIGHT_TOL
+    for a, b in zip(p.unprepare(), p.t):
+        assert torch.equal(a, b)
+
+
+def test_linearity_zero_and_unit_vectors_at_full_size(cabi):
+    """Size-independent properties on the north-star layer (4096 -> 11008, 4-bit)."""
+    K, N = 4096, 11008
+    q, s, cw, ci, dense = gpu_layer(K, N, 4, 128, seed=0)
+    p = RowPrepared(cabi, q, s, cw, ci, 4, K, 128)
+    x1 = torch.randn(1, K, device="cuda").half()
+    assert torch.count_nonzero(p.matvec(torch.zeros_like(x1))) == 0
+    y1 = p.matvec(x1).float()
+    y2 = p.matvec((x1 * 2).half()).float()
+    assert float((y2 - 2 * y1).abs().max() / y2.abs().max()) <= 2e-3
+    for col in (0, int(ci[0]), 4095, 1234):
+        e = torch.zeros(1, K, dtype=torch.float16, device="cuda")
+        e[0, col] = 1.0
+        y = p.matvec(e)[0].float()
+        assert float((y - dense[:, col].float()).abs().max()) <= 1e-3 * float(dense[:, col].float().abs().max())
+
+
+# ------------------------------------------------------------------ heavy-tailed activations
+def elementwise_error(y, ref, floor_frac=1e-2):
+    """max over elements of |y - ref| / max(|ref|, floor) with floor = floor_frac * rms(ref)."""
+    floor = floor_frac * float(np.sqrt(np.mean(ref ** 2)))
+    return float((np.abs(np.asarray(y, dtype=np.float64) - ref) / np.maximum(np.abs(ref), floor)).max())
+
+
+@pytest.mark.parametrize("bits", [4, 3])
+@pytest.mark.parametrize("scale", [100.0, 1000.0])
+def test_outlier_channels(cabi, bits, scale):
+    """LLaMA activations have a few channels 100-1000 times larger than the rest.  The kernel quantises every
+    128-column group of x to 15 bits relative to the group's largest magnitude, so an outlier costs its 127
+    group mates precision: with a 100 sigma outlier the step is 0.006 sigma, the 127 mates carry an rms
+    error of 0.0018 sigma each, i.e. about 3e-4 of a typical |y| per output.  The max-norm bound must hold
+    with room; element-wise, relative to max(|ref|, floor), the error is asserted for two floors (10 % and
+    1 % of rms(ref)): outputs that happen to be near zero see the absolute error of their neighbours, as they
+    do with the reference's fp16 atomic accumulation."""
+    K, N = 4096, 11008
+    q, s, cw, ci, dense = gpu_layer(K, N, bits, 128, seed=77 + bits)
+    p = RowPrepared(cabi, q, s, cw, ci, bits, K, 128)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    cherry = int(ci[3])
+    normal = [c for c in range(K) if c not in set(ci.cpu().numpy().tolist())]
+    cases = {
+        "inside a group": [normal[700]],
+        "on a group boundary": [normal[127], normal[128]],
+        "on a cherry column": [cherry],
+        "four channels": [normal[5], normal[1500], normal[2047], normal[4000]],
+    }
+    for where, cols in cases.items():
+        x = torch.randn(1, K, device="cuda", generator=g)
+        x[0, cols] *= scale
+        x = x.half()
+        ref = ref64(x, dense)
+        y = p.matvec(x).cpu().numpy()
+        assert rel_err(y, ref) <= TIGHT_TOL, (where, scale, bits)
+        e10, e1 = elementwise_error(y, ref, 0.1), elementwise_error(y, ref, 0.01)
+        assert e10 <= 2e-2 and e1 <= 2e-1, (where, scale, bits, e10, e1)
