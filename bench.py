@@ -3,7 +3,7 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[1], the layer the north-star target is quoted on): one
+Workload (the layer the headline target is quoted on): one
 LLaMA-7B gate/up projection, 4096 -> 11008, 4-bit, group 128, cherry ratio 1/256 (16 fp16
 columns), fp16 activations ~N(0,1), batch 1.  Weights are synthetic with the configuration's
 distributions (dense ~N(0, 0.02), cherry columns ~N(0, 0.2)), quantised and packed by the GPU
@@ -12,12 +12,15 @@ the 126 MB L2, consecutive steps walk over enough distinct copies of the layer t
 
 metric  : algorithmic bytes of the reference format (qweight + scales + cherry values + indices
           + x + y) per second, in GB/s - the number the HBM roofline is judged against.
-value   : inputs resident in HBM, stream matvec through the C ABI, CUDA graph of the copies.
+value   : inputs resident in HBM, the one-row decode kernel through the C ABI (cq_rlayer_matvec), every launch
+          of the timed region a CUDA-graph node; the region is timed --repeats times, the median is reported.
 e2e     : the same metric through the drop-in `quant_cuda.vecquant4matmul_cherryq` call with HOST
           activations: every step copies x from pinned host memory, zero-fills the output (the
           operator accumulates, as the reference's forward does), runs the op and reads y back.
 N > 1   : the layer is sharded column-parallel (N/P output rows per GPU), every rank runs its
-          shard and the slices are all-gathered with NCCL: strong scaling of one layer.
+          shard and the slices are exchanged (peer-memory kernel, or NCCL): strong scaling of one layer.
+          Rank 0 checks the gathered vector bit for bit against the unsharded layer before timing.
+model_70b : LLaMA-2-70B-architecture 3-bit greedy decode on the same GPUs, tokens/s (every N).
 --impl reference : the reference's CPU path (unpack to dense fp16 + F.linear per call, restated
           in oracle/torch_port.py because the Python reference does not travel) on the host cores.
 """
@@ -102,22 +105,37 @@ def make_layer_gpu(qc, torch, k, n, bits, group, seed, device):
     return q, s, cw, ci, c
 
 
-def cpu_baseline(seconds=12.0):
-    """The reference's dequantize-then-matmul CPU path on a bounded sample: repeated calls on the
-    full-size layer for about `seconds`."""
-    import numpy as np
-    import torch
+def reference_inputs(torch):
+    """Buffers of the reference format with the workload's shapes (the CPU path's cost does not depend on the values)."""
     from oracle import cherryq_oracle as O
-    from oracle import torch_port as TP
     torch.manual_seed(0)
     c = O.num_cherries(K_IN, 1 / 256)
     kc = K_IN - c
-    # random codes / scales of the right shapes: the CPU path's cost does not depend on the values
     q = torch.randint(0, 256, (kc // 8 * BITS, N_OUT), dtype=torch.uint8)
     s = (torch.rand(math.ceil(kc / GROUP), N_OUT) * 0.01 + 0.001).half()
     cw = (torch.randn(c, N_OUT) * 0.2).half()
     ci = torch.sort(torch.randperm(K_IN)[:c]).values.to(torch.int16)
     x = torch.randn(1, K_IN).half()
+    return x, q, s, cw, ci, c
+
+
+def host_threads():
+    """Threads the CPU legs use: every core this process may run on (torchrun sets OMP_NUM_THREADS=1,
+    which would otherwise leave the reference arm on one core), at most 32."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, min(n, 32))
+
+
+def cpu_baseline(seconds=12.0):
+    """The reference's dequantize-then-matmul CPU path on a bounded sample: repeated calls on the
+    full-size layer for about `seconds`."""
+    import torch
+    from oracle import torch_port as TP
+    torch.set_num_threads(host_threads())
+    x, q, s, cw, ci, c = reference_inputs(torch)
     TP.forward_dequantize_then_matmul(x, q, s, cw, ci, BITS, GROUP)
     calls, t0 = 0, time.perf_counter()
     while time.perf_counter() - t0 < seconds or calls < 3:
@@ -130,21 +148,21 @@ def cpu_baseline(seconds=12.0):
             "ms_per_call": dt * 1e3}
 
 
+def workload_config(**extra):
+    """Keys both arms print, so that their `config` objects name the same workload."""
+    cfg = {"workload": WORKLOAD, "bits": BITS, "group": GROUP, "K": K_IN, "N": N_OUT, "batch": 1}
+    cfg.update(extra)
+    return cfg
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import torch
-    from oracle import cherryq_oracle as O
     from oracle import torch_port as TP
-    c = O.num_cherries(K_IN, 1 / 256)
-    kc = K_IN - c
-    torch.manual_seed(0)
-    q = torch.randint(0, 256, (kc // 8 * BITS, N_OUT), dtype=torch.uint8)
-    s = (torch.rand(math.ceil(kc / GROUP), N_OUT) * 0.01 + 0.001).half()
-    cw = (torch.randn(c, N_OUT) * 0.2).half()
-    ci = torch.sort(torch.randperm(K_IN)[:c]).values.to(torch.int16)
-    x = torch.randn(1, K_IN).half()
+    torch.set_num_threads(host_threads())
+    x, q, s, cw, ci, c = reference_inputs(torch)
     for _ in range(max(args.warmup, 1)):
         TP.forward_dequantize_then_matmul(x, q, s, cw, ci, BITS, GROUP)
     t0 = time.perf_counter()
@@ -158,47 +176,59 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "path": "reference CPU path: unpack() to dense fp16 + F.linear per call"},
+        "config": workload_config(path="reference CPU path: unpack() to dense fp16 + F.linear per call"),
         "cpu_baseline": {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": f"{args.steps} full-layer calls per run"},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one cq_matvec_kernel launch on this workload, from the
-# ncu capture summarised in profiles/stream_matvec_4096x11008_4bit_batch1_ncu.md (23,815,424 + 256 bytes)
-NCU_DRAM_BYTES_PER_LAUNCH = 23_815_680
+# dram__bytes_read.sum + dram__bytes_write.sum of one cq_rowvec_kernel launch on this workload (one ncu capture,
+# --clock-control none, two launches, the layer rotated over 17 copies)
+NCU_DRAM_BYTES_PER_LAUNCH = None
 PREFILL_TOKENS = 2048
 
 
-def phase_timeline(torch, lib, _cabi, layers, ncopies, x, y, n_local, scratch, status, dev):
-    """Per-phase nanosecond stamps (%globaltimer, written by every CTA through the library's tracing
-    hook cq_trace_set_timeline) of back-to-back launches; printed to stderr as a small table."""
-    def ptr(t):
-        return C.c_void_p(t.data_ptr())
-    n = min(ncopies, 8)
-    bufs = [torch.zeros(1024 * 64, dtype=torch.int64, device=dev) for _ in range(n)]
-    for _ in range(3):
-        for i in range(n):
-            lib.cq_trace_set_timeline(ptr(bufs[i]))
-            _cabi.check(lib.cq_layer_matvec(C.byref(layers[i]), ptr(x), K_IN, ptr(y), n_local, 1, 0,
-                                            ptr(scratch), ptr(status), None), "matvec")
-    torch.cuda.synchronize()
-    lib.cq_trace_set_timeline(None)
-    import numpy as np
-    grid = torch.cuda.get_device_properties(dev).multi_processor_count
-    t = np.stack([b.cpu().numpy().reshape(1024, 64)[:grid] for b in bufs]).astype(np.float64)
-    names = ["CTA entry", "barriers ready", "layer constants staged", "previous kernel done (wait returned)",
-             "activations staged", "first weights landed", "last granule done", "exit",
-             "first bulk copy issued", "last bulk copy issued"]
-    print("phase timeline, ns after the previous launch's last CTA exit (min / median / max over CTAs), "
-          "launch %d of a chain:" % (n - 2), file=sys.stderr)
-    li = n - 2
-    t0 = t[li - 1][:, 7].max()
-    for si, nm in enumerate(names):
-        col = t[li][:, si] - t0
-        print(f"  {nm:38s} {col.min():8.0f} {np.median(col):8.0f} {col.max():8.0f}", file=sys.stderr)
-    print(f"  period (exit to exit)                  {t[li][:, 7].max() - t0:8.0f}", file=sys.stderr)
+def median(v):
+    v = sorted(v)
+    return v[len(v) // 2]
+
+
+class Region:
+    """`steps` launches as CUDA graphs: every launch of the timed region is a graph node, none comes from
+    Python.  The launches walk round-robin over the layer copies; when `steps` exceeds the number of copies
+    a graph of one round is replayed and a second graph holds the remainder."""
+
+    def __init__(self, torch, stream, launch, steps, ncopies):
+        self.torch, self.stream = torch, stream
+        self.rounds, rem = divmod(steps, ncopies)
+        self.g_round = self._capture(launch, range(ncopies)) if self.rounds else None
+        self.g_rem = self._capture(launch, range(rem)) if rem else None
+        self.what = (f"CUDA graphs only: {self.rounds} replays of a graph of {ncopies} launches" if self.rounds else
+                     "CUDA graphs only:") + (f" + one graph of {rem} launches" if rem else "")
+
+    def _capture(self, launch, idx):
+        g = self.torch.cuda.CUDAGraph()
+        with self.torch.cuda.graph(g, stream=self.stream):
+            for i in idx:
+                launch(i)
+        return g
+
+    def run(self):
+        for _ in range(self.rounds):
+            self.g_round.replay()
+        if self.g_rem is not None:
+            self.g_rem.replay()
+
+    def time(self, repeats):
+        """Device time (ms) of `repeats` back-to-back runs of the region, one pair of events each."""
+        ev = [(self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)) for _ in range(repeats)]
+        for e0, e1 in ev:
+            e0.record(self.stream)
+            self.run()
+            e1.record(self.stream)
+        self.stream.synchronize()
+        return [e0.elapsed_time(e1) for e0, e1 in ev]
 
 
 def run_ours(args):
@@ -219,39 +249,47 @@ def run_ours(args):
     qc = cherryq_b200.load_quant_cuda()
     lib = _cabi.lib()
 
-    n_local = N_OUT // world // 16 * 16 if world > 1 else N_OUT
-    if world > 1 and n_local * world != N_OUT:
-        # 11008 = 688 sub-tiles of 16 rows: split whole sub-tiles, the last rank takes the remainder
-        per = (N_OUT // 16) // world * 16
-        n_local = per if rank < world - 1 else N_OUT - per * (world - 1)
-    q, s, cw, ci, c = make_layer_gpu(qc, torch, K_IN, n_local, BITS, GROUP, 1234 + rank, dev)
+    if N_OUT % (16 * world):
+        raise RuntimeError(f"{world} ranks do not divide the layer's 16-row tiles")
+    n_local = N_OUT // world
+    # every rank draws the whole layer (same seed) and keeps its rows: rank 0 can check the gathered vector
+    g = torch.Generator(device=dev).manual_seed(1234)
+    c = math.ceil(K_IN / 256) // 8 * 8
+    w = torch.randn(N_OUT, K_IN, device=dev, generator=g) * 0.02
+    idx = torch.randperm(K_IN, device=dev, generator=g)[:c].to(torch.int32)
+    w[:, idx.long()] = torch.randn(N_OUT, c, device=dev, generator=g) * 0.2
+    w = w.half()
+    q, s, cw, ci = qc.pack(w[rank * n_local:(rank + 1) * n_local].contiguous(), idx.contiguous(), BITS, GROUP)
     alg = algorithmic_bytes(K_IN, N_OUT, BITS, GROUP, 1, c)          # whole layer, all ranks
     alg_local = algorithmic_bytes(K_IN, n_local, BITS, GROUP, 1, c)
 
     def ptr(t):
         return C.c_void_p(t.data_ptr())
 
-    # distinct copies of the prepared layer: > 3x L2 in total
-    L0 = _cabi.layer_init(BITS, K_IN, n_local, c, GROUP)
-    ncopies = max(2, math.ceil(3 * L2_BYTES / L0.blob_bytes))
-    layers, blobs = [], []
-    for i in range(ncopies):
-        L = _cabi.layer_init(BITS, K_IN, n_local, c, GROUP)
+    def prepared(qq, ss, cc, ii, n):
+        L = _cabi.rlayer_init(BITS, K_IN, n, c, GROUP)
+        _cabi.check(lib.cq_rlayer_check(C.byref(L)), "cq_rlayer_check")
         b = torch.empty(L.blob_bytes, dtype=torch.uint8, device=dev)
         L.blob = b.data_ptr()
-        if i == 0:
-            _cabi.check(lib.cq_layer_prepare(C.byref(L), ptr(q), ptr(s), ptr(cw), ptr(ci), None), "prepare")
-            torch.cuda.synchronize()
-        else:
-            b.copy_(blobs[0])
+        _cabi.check(lib.cq_rlayer_prepare(C.byref(L), ptr(qq), ptr(ss), ptr(cc), ptr(ii), None), "prepare")
+        torch.cuda.synchronize()
+        return L, b
+
+    # distinct copies of the prepared layer: > 3x L2 in total
+    L0, blob0 = prepared(q, s, cw, ci, n_local)
+    ncopies = max(2, math.ceil(3 * L2_BYTES / L0.blob_bytes))
+    layers, blobs = [L0], [blob0]
+    for i in range(1, ncopies):
+        L = _cabi.rlayer_init(BITS, K_IN, n_local, c, GROUP)
+        b = blob0.clone()
+        L.blob = b.data_ptr()
         layers.append(L)
         blobs.append(b)
     torch.cuda.synchronize()
 
-    x = torch.randn(1, K_IN, device=dev).half()
+    x = torch.randn(1, K_IN, device=dev, generator=g).half()
     y = torch.zeros(1, n_local, dtype=torch.float16, device=dev)
-    y_all = torch.zeros(world, n_local, dtype=torch.float16, device=dev) if world > 1 else None
-    scratch = torch.zeros(lib.cq_scratch_bytes(), dtype=torch.uint8, device=dev)
+    y_all = torch.zeros(1, N_OUT, dtype=torch.float16, device=dev) if world > 1 else None
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.Stream(device=dev)
     sp = C.c_void_p(stream.cuda_stream)
@@ -261,7 +299,7 @@ def run_ours(args):
     peer, gather_kind = None, "none"
     if world > 1:
         gather_kind = "NCCL all-gather"
-        if args.gather == "peer" and n_local * world == N_OUT:
+        if args.gather == "peer":
             from cherryq_b200.parallel import PeerAllGather
             try:
                 peer = PeerAllGather(dist.group.WORLD, dev, capacity_bytes=1 << 20)
@@ -270,13 +308,18 @@ def run_ours(args):
                 if rank == 0:
                     print(f"peer memory unavailable, using NCCL: {exc}", file=sys.stderr)
 
-    def launch(i):
-        _cabi.check(lib.cq_layer_matvec(C.byref(layers[i % ncopies]), ptr(x), K_IN, ptr(y), n_local, 1, 0,
-                                        ptr(scratch), ptr(status), sp), "matvec")
+    def matvec(i):
+        _cabi.check(lib.cq_rlayer_matvec(C.byref(layers[i % ncopies]), ptr(x), ptr(y), 0, ptr(status), sp), "matvec")
+
+    def gather():
         if peer is not None:
             peer.gather_into(y, y_all, stream)
         elif world > 1:
-            dist.all_gather_into_tensor(y_all, y)
+            dist.all_gather_into_tensor(y_all.view(-1), y.view(-1))
+
+    def step(i):
+        matvec(i)
+        gather()
 
     def barrier():
         torch.cuda.synchronize()
@@ -284,66 +327,63 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    repeats = max(1, args.repeats)
+    gather_checked = None
+    own_kernels_per_step = 2 if peer is not None else 1       # the matvec, and the exchange kernel when it is this library's
     with torch.cuda.stream(stream):
-        # warm-up (also builds the kernels' attributes before any capture)
-        for i in range(max(args.warmup, 3)):
-            launch(i)
+        for i in range(max(args.warmup, 3)):          # warm-up: also sets kernel attributes before any capture
+            step(i)
         stream.synchronize()
-        graph = None
-        if world == 1 or peer is not None:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                for i in range(ncopies):
-                    launch(i)
-            graph.replay()
-            stream.synchronize()
+        if world > 1:
+            # rank 0 computes the whole vector from the unsharded layer with the same kernel: every output element
+            # is the same arithmetic whichever rank owns its row, so the gathered vector must match bit for bit
+            ok = torch.ones(1, dtype=torch.int32, device=dev)
+            if rank == 0:
+                qf, sf, cwf, cif = qc.pack(w.contiguous(), idx.contiguous(), BITS, GROUP)
+                Lf, bf = prepared(qf, sf, cwf, cif, N_OUT)
+                yf = torch.zeros(1, N_OUT, dtype=torch.float16, device=dev)
+                _cabi.check(lib.cq_rlayer_matvec(C.byref(Lf), ptr(x), ptr(yf), 0, ptr(status), sp), "matvec")
+                stream.synchronize()
+                ok[0] = int(torch.equal(yf.view(torch.int16), y_all.view(torch.int16)))
+                del qf, sf, cwf, cif, bf, yf
+            dist.broadcast(ok, src=0)
+            gather_checked = bool(int(ok.item()))
+            if not gather_checked:
+                raise RuntimeError("the gathered output differs from the unsharded layer's")
+        del w
+        region = Region(torch, stream, step, args.steps, ncopies)
+        region.run()                                   # one untimed pass of the graphs
+        stream.synchronize()
         barrier()
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        done = 0
-        if graph is not None:
-            while done + ncopies <= args.steps:
-                graph.replay()
-                done += ncopies
-        while done < args.steps:
-            launch(done)
-            done += 1
-        e1.record(stream)
-        stream.synchronize()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+        times = region.time(repeats)
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+        # the kernel alone (N == 1: the region holds nothing else)
+        kern_times = times
+        if world > 1:
+            kregion = Region(torch, stream, matvec, args.steps, ncopies)
+            kregion.run()
+            stream.synchronize()
+            kern_times = kregion.time(repeats)
     if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        t = torch.tensor([times, kern_times], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)       # per repeat, the slowest rank
+        times, kern_times = t[0].tolist(), t[1].tolist()
     if int(status.item()) != 0 or (peer is not None and int(peer.status.item()) != 0):
         raise RuntimeError("a device-side wait timed out during the benchmark")
-    ms_step = ms / args.steps
+    ms_step = median(times) / args.steps
+    kern_ms = median(kern_times) / args.steps
     value = alg / (ms_step * 1e-3) / 1e9
 
-    # kernel time alone (N == 1: the graph holds nothing else; N > 1: events around the kernel only)
-    kern_ms = ms_step
-    if world > 1:
-        with torch.cuda.stream(stream):
-            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            k0.record(stream)
-            for i in range(200):
-                _cabi.check(lib.cq_layer_matvec(C.byref(layers[i % ncopies]), ptr(x), K_IN, ptr(y), n_local, 1, 0,
-                                                ptr(scratch), ptr(status), sp), "matvec")
-            k1.record(stream)
-            stream.synchronize()
-        kern_ms = k0.elapsed_time(k1) / 200
-
     # ---------------------------------------------------------------- end to end through the drop-in op
-    e2e = None
     xh = torch.randn(1, K_IN).half().pin_memory()
-    yh = torch.empty(1, n_local, dtype=torch.float16).pin_memory()
+    yh = torch.empty(1, N_OUT if rank == 0 else n_local, dtype=torch.float16).pin_memory()
     xd = torch.empty(1, K_IN, dtype=torch.float16, device=dev)
     out = torch.empty(1, n_local, dtype=torch.float16, device=dev)
+    out_all = torch.empty(1, N_OUT, dtype=torch.float16, device=dev) if world > 1 else None
     refs = []
     for i in range(ncopies):                 # the op's own weight buffers (reference format), > 3x L2 in total
         refs.append((q, cw, ci, s) if i == 0 else tuple(t.clone() for t in (q, cw, ci, s)))
@@ -353,7 +393,15 @@ def run_ours(args):
         xd.copy_(xh, non_blocking=True)
         out.zero_()
         qc.vecquant4matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP)
-        yh.copy_(out, non_blocking=True)
+        if world > 1:
+            if peer is not None:
+                peer.gather_into(out, out_all)
+            else:
+                dist.all_gather_into_tensor(out_all.view(-1), out.view(-1))
+            if rank == 0:
+                yh.copy_(out_all, non_blocking=True)      # the whole output vector reaches the host on rank 0
+        else:
+            yh.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = min(args.steps, 2000)
@@ -374,11 +422,9 @@ def run_ours(args):
         e2e_ms = float(t.item())
     qc.poll()
     e2e = {"value": alg / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": K_IN * 2,
-           "d2h_bytes_per_step": n_local * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
-           "path": "quant_cuda.vecquant4matmul_cherryq with pinned host x / y per rank"}
-
-    if args.timeline and rank == 0:
-        phase_timeline(torch, lib, _cabi, layers, ncopies, x, y, n_local, scratch, status, dev)
+           "d2h_bytes_per_step": N_OUT * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "path": "quant_cuda.vecquant4matmul_cherryq with pinned host x per rank" +
+                   (f", {gather_kind}, the whole y read back on rank 0" if world > 1 else " and y")}
 
     # the reference project's own CUDA kernel on the same layer copies (built by oracle/build_ref.py;
     # information only: batch 1, device-resident inputs, CUDA events)
@@ -406,12 +452,27 @@ def run_ours(args):
             ref_gpu = {"kernel": "VecQuant4MatMulKernelCherryQBatchedHalf (reference csrc/quant_cuda_kernel.cu, unmodified, sm_100a)",
                        "us_per_call": rms * 1e3, "GBps": alg / (rms * 1e-3) / 1e9, "steps": rsteps}
 
+    region_what = region.what
+    del layers, blobs, refs, region
+    if world > 1:
+        del kregion
+    torch.cuda.empty_cache()
+
     # the other half of the path, same layer: the 2048-token prefill GEMM (single-GPU runs only)
     prefill = None
     if world == 1 and not args.no_cpu:
-        del layers, blobs, refs
-        torch.cuda.empty_cache()
         prefill = prefill_measure(torch, dist, dev, world, rank, local, 60, 5)
+
+    # the model-level number the metric names: LLaMA-2-70B-architecture 3-bit decode, tokens/s on these GPUs
+    model70 = None
+    if not args.no_model:
+        if peer is not None:
+            peer.close()
+            peer = None
+        try:
+            model70 = model_measure(args, torch, dist, dev, world, rank, local, "70b", gen=64)
+        except Exception as exc:          # the record says why it is missing; the headline line still prints
+            model70 = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -420,18 +481,25 @@ def run_ours(args):
             "metric": "matvec_algorithmic_GBps_batch1", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "bits": BITS, "group": GROUP, "K": K_IN, "N": N_OUT, "batch": 1,
-                       "l2_defeat": f"{ncopies} distinct layer copies ({ncopies * L0.blob_bytes / 1e6:.0f} MB) walked "
-                                    "round-robin, inputs larger than L2",
-                       "parallelism": "single GPU" if world == 1 else f"column-parallel over {world} GPUs + {gather_kind}",
-                       "launch": "CUDA graph of the copies" if graph is not None else "stream launches"},
+            "config": workload_config(
+                l2_defeat=f"{ncopies} distinct layer copies ({ncopies * L0.blob_bytes / 1e6:.0f} MB) walked "
+                          "round-robin, inputs larger than L2",
+                parallelism="single GPU" if world == 1 else f"column-parallel over {world} GPUs + {gather_kind}",
+                launch=region_what,
+                timing=f"median of {repeats} back-to-back timed regions of {args.steps} steps each (CUDA events on the "
+                       "launching stream, max over ranks per region)"),
             "pct_of_nominal_8TBps": value / world / 8000.0 * 100.0 if world == 1 else None,
+            "region_ms": {"median": median(times), "min": min(times), "max": max(times), "repeats": repeats},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH * alg_local / alg, "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
-                         "kernel": "cq_matvec_kernel<4,1,1,...>", "alg_bytes_per_launch": alg_local,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH * alg_local / alg if NCU_DRAM_BYTES_PER_LAUNCH else None,
+                         "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
+                         "kernel": "cq_rowvec_kernel<4,1,16,2>", "alg_bytes_per_launch": alg_local,
                          "launch_us": kern_ms * 1e3},
-            "e2e": e2e, "gpu_launches": args.steps * world * (2 if peer is not None else 1), "clocks": clocks,
+            "e2e": e2e, "gpu_launches": args.steps * world * own_kernels_per_step,
+            "clocks": clocks,
         }
+        if gather_checked is not None:
+            line["gather_checked"] = gather_checked
         line["cpu_baseline"] = cpu_baseline() if world == 1 and not args.no_cpu else None
         line["reference_gpu_kernel"] = ref_gpu
         if ref_gpu is not None:
@@ -439,9 +507,23 @@ def run_ours(args):
         if prefill is not None:
             line["prefill"] = {k: prefill[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "roofline", "e2e")}
             line["prefill"]["workload"] = prefill["config"]["workload"]
+        line["model_70b"] = model70
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    leave(torch, dist, world)
+
+
+def leave(torch, dist, world):
+    """End of a multi-rank run.  The decode graphs of the model leg hold NCCL or peer-memory kernels; destroying
+    the process group under live graphs blocked in the communicator's teardown when it was tried, so the ranks
+    meet once more and leave the process without it."""
+    if world <= 1:
+        return
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def measured_tensor_peak():
@@ -607,8 +689,8 @@ def prefill_measure(torch, dist, dev, world, rank, local, steps_arg, warmup_arg)
 
 
 def run_model(args):
-    """Greedy decode of 256 tokens after a 128-token random prompt on the LLaMA-2-7B architecture with
-    random-init 4-bit CherryQ weights (batch 1): decode tokens/s, with the share of the quantized linears."""
+    """Greedy decode of 256 tokens after a 128-token random prompt on a LLaMA-2 architecture with random-init
+    CherryQ weights (batch 1): decode tokens/s, with the share of the quantized linears."""
     import torch
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
@@ -620,13 +702,22 @@ def run_model(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    line = model_measure(args, torch, dist, dev, world, rank, local, args.model, gen=256)
+    if rank == 0:
+        print(json.dumps(line))
+    leave(torch, dist, world)
+
+
+def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, prompt_len=128):
+    """Builds the model, decodes `gen` tokens greedily after a `prompt_len`-token random prompt (one CUDA graph
+    per decode step, as benchmark_perplexity.py:92-113 of the reference times its per-token loop) and returns
+    the JSON record (rank 0; None elsewhere)."""
     from cherryq_b200 import decoder as D
-    base = {"7b": D.LLAMA2_7B, "13b": D.LLAMA2_13B, "70b": D.LLAMA2_70B}[args.model]
+    base = {"7b": D.LLAMA2_7B, "13b": D.LLAMA2_13B, "70b": D.LLAMA2_70B}[name]
     cfg = D.DecoderConfig(**{**base.__dict__, "max_seq": 512})
-    prompt_len, gen = 128, 256
     t_build = time.time()
     model = D.CherryDecoder(cfg, device=dev, seed=1234, tp_group=dist.group.WORLD if world > 1 else None,
-                            tp_gather=args.gather)
+                            tp_gather=args.gather, release_reference_buffers=True)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
     prompt = torch.randint(0, cfg.vocab, (prompt_len,), device=dev, generator=torch.Generator(device=dev).manual_seed(0))
@@ -653,13 +744,17 @@ def run_model(args):
         sampler.start()
     gen_ms, toks = timed(lambda: model.generate(gen))
     clocks = sampler.stop() if rank == 0 else None
+    ranks_agree = None
     if world > 1:
         tt = torch.tensor([gen_ms, prefill_ms], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         gen_ms, prefill_ms = float(tt[0]), float(tt[1])
         same = toks.clone()
         dist.broadcast(same, src=0)
-        if not torch.equal(same, toks):
+        agree = torch.tensor([int(torch.equal(same, toks))], device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        ranks_agree = bool(int(agree.item()))
+        if not ranks_agree:
             raise RuntimeError("the ranks generated different tokens")
     tok_s = gen / (gen_ms * 1e-3)
 
@@ -670,8 +765,8 @@ def run_model(args):
     with torch.cuda.stream(s), torch.inference_mode():
         def all_linears():
             for lay in model.layers:
-                for name in model.PROJ:
-                    lay[name](xin[model.shapes[name][0]])
+                for nm in model.PROJ:
+                    lay[nm](xin[model.shapes[nm][0]])
         all_linears()
         s.synchronize()
         gl = torch.cuda.CUDAGraph()
@@ -688,27 +783,16 @@ def run_model(args):
     head_ms /= 50
 
     qbytes, hbytes = model.quantized_bytes_per_token() * world, model.lm_head_bytes()
-
-    def leave():
-        # Captured graphs hold NCCL kernels; tearing the communicator down under them has hung.  All
-        # ranks meet once more, drop their graphs and leave the process without the teardown.
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
-
     if rank != 0:
-        leave()
+        return None
     peak, peak_kind = measured_peak()
     ms_tok = gen_ms / gen
-    line = {
+    return {
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": gen, "warmup": 8,
         "ms_per_step": ms_tok, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": f"llama2_{args.model}_arch_{cfg.bits}bit_g128_cherry1/256_prompt128_greedy256_batch1",
+        "config": {"workload": f"llama2_{name}_arch_{cfg.bits}bit_g128_cherry1/256_prompt{prompt_len}_greedy{gen}_batch1",
                    "layers": cfg.n_layers, "kv_heads": cfg.n_kv_heads,
                    "hidden": cfg.hidden, "ffn": cfg.ffn, "vocab": cfg.vocab, "bits": cfg.bits,
                    "l2_defeat": f"{qbytes / 1e9:.1f} GB of quantized weights + {hbytes / 1e6:.0f} MB lm_head per token, "
@@ -729,11 +813,8 @@ def run_model(args):
                 "note": "the decode loop lives on the device (token ids are read back once at the end: "
                         f"{gen * 8} bytes); prompt upload {prompt_len * 8} bytes once"},
         "gpu_launches": gen * (cfg.n_layers * 7) * world, "clocks": clocks, "cpu_baseline": None,
-        "build_s": t_build, "first_tokens": [int(t) for t in toks[:8].tolist()],
+        "build_s": t_build, "first_tokens": [int(t) for t in toks[:8].tolist()], "ranks_agree": ranks_agree,
     }
-    print(json.dumps(line))
-    if world > 1:
-        leave()
 
 
 def main():
@@ -750,8 +831,9 @@ def main():
                     help="architecture of the model workload: LLaMA-2 7B (4-bit), 13B (3-bit) or 70B (3-bit, GQA)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="exchange step at N > 1: this library's peer-memory kernel (default) or NCCL")
-    ap.add_argument("--timeline", action="store_true",
-                    help="also print the kernel's per-phase device timeline to stderr (after the timed region)")
+    ap.add_argument("--repeats", type=int, default=50,
+                    help="timed regions of --steps steps run back to back; the median is reported")
+    ap.add_argument("--no-model", action="store_true", help="skip the 70B-architecture decode leg")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 200:

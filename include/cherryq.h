@@ -201,13 +201,14 @@ int cq_rmsnorm(const void* x_f16, const void* residual_f16, const void* weight_f
                void* h_out_f16, int rows, int hidden, float eps, cq_stream_t stream);
 /* Rotary embedding ("rotate half" convention) of q (T, H, D) and k (T, KV, D) in place at
  * positions[t] (device int64), tables (max_seq, D/2) fp32; k and v rows are written to the caches
- * (max_seq, KV, D) at the same positions. */
+ * (max_seq, KV, D) at the same positions.  A token whose position is outside [0, max_seq) is left
+ * alone: nothing is read from the tables or written to the caches for it. */
 int cq_rope_cache(void* q_f16, void* k_f16, const void* v_f16, const float* cos_table,
                   const float* sin_table, const long long* positions, void* k_cache_f16,
-                  void* v_cache_f16, int T, int n_heads, int n_kv_heads, int head_dim,
+                  void* v_cache_f16, int T, int n_heads, int n_kv_heads, int head_dim, int max_seq,
                   cq_stream_t stream);
 /* Single-query attention over the caches (max_seq, KV, D): out (H, D) = softmax(q . K^T * scale) . V
- * over positions 0..position[0] (device int64), grouped-query heads allowed; head_dim divides 256,
+ * over positions 0..min(position[0], max_seq - 1) (device int64), grouped-query heads allowed; head_dim divides 256,
  * max_seq <= 8192 (the reference calls PyTorch's attention, llama/modeling_llama_quant.py:371-419). */
 int cq_attn_decode(const void* q_f16, const void* k_cache_f16, const void* v_cache_f16,
                    const long long* position, void* out_f16, int n_heads, int n_kv_heads, int head_dim,
@@ -339,7 +340,7 @@ int cq_unpack_dense(const uint8_t* qweight, const void* scales_f16,
  * fp16 slice into a landing area of every rank with plain peer stores, each 8-byte word carrying
  * 4 payload bytes and the call's sequence number, polls its own landing area until every word
  * carries that number (bounded by timeout_ms, then CQ_ERR_DEVICE_TIMEOUT bits in *status_word and
- * the output is left untouched) and writes the gathered (rows, P * cols_local) fp16 matrix.
+ * the output is filled with NaN) and writes the gathered (rows, P * cols_local) fp16 matrix.
  * One rank per GPU: ranks never share a device.  Every rank makes the same sequence of calls.
  *
  * A region is cq_peer_region_bytes(capacity) bytes of device memory, zeroed at creation;

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const __half* __restrict_
 __global__ void rope_cache_kernel(__half* __restrict__ q, __half* __restrict__ k, const __half* __restrict__ v,
                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                   const long long* __restrict__ pos, __half* __restrict__ k_cache,
-                                  __half* __restrict__ v_cache, int T, int H, int KV, int D) {
+                                  __half* __restrict__ v_cache, int T, int H, int KV, int D, int max_seq) {
   // programmatic dependent launch: let the next kernel start its prologue, then wait for our inputs
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -90,6 +90,7 @@ __global__ void rope_cache_kernel(__half* __restrict__ q, __half* __restrict__ k
     const int hh = (int)((id / half) % (H + 2 * KV));
     const int t = (int)(id / ((long long)half * (H + 2 * KV)));
     const long long p = pos[t];
+    if (p < 0 || p >= max_seq) continue;      // a position outside the tables and caches: nothing is read or written
     if (hh < H + KV) {
       __half* base = hh < H ? q + ((size_t)t * H + hh) * D : k + ((size_t)t * KV + (hh - H)) * D;
       const float c = cos_t[p * half + i], s = sin_t[p * half + i];
@@ -133,14 +134,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
                                                                   const __half* __restrict__ v_cache,
                                                                   const long long* __restrict__ pos,
                                                                   __half* __restrict__ out, int H, int KV, int D,
-                                                                  float scale) {
+                                                                  int max_seq, float scale) {
   // programmatic dependent launch: let the next kernel start its prologue, then wait for our inputs
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   extern __shared__ float sc[];              // [n_pos] scores, then [ATT_THREADS] reduction scratch
   const int head = blockIdx.x, kvh = head / (H / KV);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int n_pos = (int)pos[0] + 1;
+  // positions beyond the cache are not attended to (the host refuses such steps; this keeps a stray
+  // launch inside its shared-memory score array and the caches)
+  const long long p0 = pos[0];
+  const int n_pos = p0 < 0 ? 1 : (p0 >= max_seq ? max_seq : (int)p0 + 1);
   float* red = sc + n_pos;
   const __half* qh = q + (size_t)head * D;
   // scores: a warp per position, four positions in flight per warp, lanes over the head dimension
@@ -261,13 +265,13 @@ extern "C" int cq_rmsnorm(const void* x, const void* residual, const void* weigh
 
 extern "C" int cq_rope_cache(void* q, void* k, const void* v, const float* cos_table, const float* sin_table,
                              const long long* positions, void* k_cache, void* v_cache, int T, int n_heads,
-                             int n_kv_heads, int head_dim, cq_stream_t stream) {
+                             int n_kv_heads, int head_dim, int max_seq, cq_stream_t stream) {
   if (!q || !k || !v || !cos_table || !sin_table || !positions || !k_cache || !v_cache) return CQ_ERR_BAD_ARG;
-  if (T < 1 || n_heads < 1 || n_kv_heads < 1 || head_dim < 2 || (head_dim & 1)) return CQ_ERR_BAD_ARG;
+  if (T < 1 || n_heads < 1 || n_kv_heads < 1 || head_dim < 2 || (head_dim & 1) || max_seq < 1) return CQ_ERR_BAD_ARG;
   const long long total = (long long)T * (n_heads + 2 * n_kv_heads) * (head_dim / 2);
   CQ_CUDA_TRY(launch_pdl(rope_cache_kernel, dim3(blocks_for(total, 256, 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
                          (__half*)q, (__half*)k, (const __half*)v, cos_table, sin_table, positions, (__half*)k_cache,
-                         (__half*)v_cache, T, n_heads, n_kv_heads, head_dim));
+                         (__half*)v_cache, T, n_heads, n_kv_heads, head_dim, max_seq));
   return CQ_OK;
 }
 
@@ -288,6 +292,6 @@ extern "C" int cq_attn_decode(const void* q, const void* k_cache, const void* v_
   const int smem = (max_seq + ATT_THREADS) * (int)sizeof(float);
   CQ_CUDA_TRY(launch_pdl(attn_decode_kernel, dim3(n_heads), dim3(ATT_THREADS), (size_t)smem, (cudaStream_t)stream,
                          (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, position, (__half*)out, n_heads,
-                         n_kv_heads, head_dim, scale));
+                         n_kv_heads, head_dim, max_seq, scale));
   return CQ_OK;
 }

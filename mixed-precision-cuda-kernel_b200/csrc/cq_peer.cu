@@ -98,7 +98,9 @@ __global__ void __launch_bounds__(GATHER_THREADS) peer_allgather_kernel(const Pe
   if (failed) s_fail = 1;
   __syncthreads();
   if (s_fail) {
-    // a peer never delivered: report, keep the call counter in step, leave the output untouched
+    // a peer never delivered: report, keep the call counter in step, and fill the whole output with
+    // NaN so that nothing downstream can take stale memory for a result
+    for (uint32_t idx = tid; idx < total; idx += GATHER_THREADS) p.out[idx] = make_uint2(0x7e007e00u, 0x7e007e00u);
     if (tid == 0) {
       if (p.status) atomicOr(p.status, (uint32_t)CQ_ERR_DEVICE_TIMEOUT);
       *reinterpret_cast<volatile uint32_t*>(own + EPOCH_OFF) = e;

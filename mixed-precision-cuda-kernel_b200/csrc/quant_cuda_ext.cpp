@@ -416,7 +416,7 @@ void rope_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor
               "caches must be (max_seq, KV, D) with max_seq within the rotary tables");
   check_status(cq_rope_cache(q.data_ptr(), k.data_ptr(), v.data_ptr(), cos_table.data_ptr<float>(),
                              sin_table.data_ptr<float>(), (const long long*)positions.data_ptr(), k_cache.data_ptr(),
-                             v_cache.data_ptr(), T, H, KV, D, current_stream()),
+                             v_cache.data_ptr(), T, H, KV, D, (int)k_cache.size(0), current_stream()),
                "rope_cache");
 }
 

@@ -92,7 +92,11 @@ class CherryDecoder:
         self.peer = None
         if self.tp > 1 and tp_gather == "peer":
             from .parallel import PeerAllGather
-            self.peer = PeerAllGather(tp_group, self.dev)
+            try:
+                self.peer = PeerAllGather(tp_group, self.dev)
+            except RuntimeError as e:       # raised on every rank together: all of them take NCCL
+                import warnings
+                warnings.warn(f"peer-memory exchange unavailable ({e}); the sharded projections use NCCL")
         elif tp_gather not in ("peer", "nccl"):
             raise ValueError("tp_gather is 'peer' or 'nccl'")
         g = torch.Generator(device=self.dev).manual_seed(seed)
@@ -125,6 +129,7 @@ class CherryDecoder:
         # state of the decode loop, all on the device
         self.tok = torch.zeros(1, dtype=torch.long, device=self.dev)
         self.pos = torch.zeros(1, dtype=torch.long, device=self.dev)
+        self.pos_host = 0           # the host's copy of `pos`: every step is checked against max_seq before it is launched
         self.graph = None
 
     # ------------------------------------------------------------------ construction
@@ -206,13 +211,16 @@ class CherryDecoder:
     def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
         """Runs the prompt (T,) through the model, fills the cache, returns the last position's logits."""
         t = tokens.shape[0]
-        assert 0 < t < self.cfg.max_seq
+        if not 0 < t < self.cfg.max_seq:
+            raise ValueError(f"a prompt of {t} tokens does not fit max_seq = {self.cfg.max_seq} (one position must stay free)")
         pos = torch.arange(t, device=self.dev)
         h, delta = self.embed[tokens], None
         for li in range(self.cfg.n_layers):
             h, delta = self._layer(li, h, delta, pos, decode=False)
         logits = self._logits(h[-1:].contiguous(), delta[-1:].contiguous())
+        self._check_exchange()
         self.pos.fill_(t)
+        self.pos_host = t
         self.tok.copy_(logits.argmax(-1))
         return logits
 
@@ -230,7 +238,12 @@ class CherryDecoder:
     @torch.inference_mode()
     def capture(self):
         """Captures one decode step in a CUDA graph (the state tensors are saved and restored)."""
+        if self.cfg.max_seq < 4:
+            raise ValueError("max_seq must be at least 4")
         saved = (self.tok.clone(), self.pos.clone(), self.k_cache.clone(), self.v_cache.clone())
+        # the warm-up and the captured step run at positions 0, 1, 2: always inside the cache, whatever
+        # the current position is (state and caches are restored below)
+        self.pos.zero_()
         s = torch.cuda.Stream(device=self.dev)
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -249,6 +262,9 @@ class CherryDecoder:
     def generate(self, n_tokens: int, use_graph: bool = True) -> torch.Tensor:
         """Greedy continuation after `prefill`: returns the n_tokens generated ids (the first one is
         the prefill's argmax)."""
+        if n_tokens < 0 or self.pos_host + n_tokens > self.cfg.max_seq:
+            raise ValueError(f"{n_tokens} more tokens after position {self.pos_host} do not fit max_seq = "
+                             f"{self.cfg.max_seq}: the KV cache holds max_seq positions")
         out = torch.empty(n_tokens, dtype=torch.long, device=self.dev)
         if use_graph and self.graph is None:
             self.capture()
@@ -258,4 +274,14 @@ class CherryDecoder:
                 self.graph.replay()
             else:
                 self._step()
+        self.pos_host += n_tokens
+        self._check_exchange()
         return out
+
+    def _check_exchange(self):
+        """Raises if a peer never delivered a slice (the kernel fills that output with NaN and sets a
+        status bit) or a bounded device-side wait of a projection ran out: one host read per call."""
+        if self.peer is not None:
+            self.peer.check()
+        if self.qc.device_timed_out(self.dev.index if self.dev.index is not None else torch.cuda.current_device()):
+            raise RuntimeError("a bounded device-side wait of a quantized projection ran out")

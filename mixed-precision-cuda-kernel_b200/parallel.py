@@ -114,7 +114,7 @@ class PeerAllGather:
     together.  `__call__` enqueues one launch on the current stream and can be captured in a CUDA
     graph; every rank must make the same sequence of calls.  A peer that never delivers shows up
     as a timeout bit in `status` (a device word), read with `check()`; the output of that call is
-    then left untouched.  One rank per GPU.
+    then filled with NaN.  One rank per GPU.
     """
 
     def __init__(self, group, device, capacity_bytes: int = 4 << 20, timeout_ms: int = 2000):

@@ -119,3 +119,58 @@ def test_attention_decode_matches_torch(dec, H, KV, D, S, P):
     w = torch.softmax(torch.einsum("hd,phd->hp", q[0].float(), k) / D ** 0.5, dim=-1)
     ref = torch.einsum("hp,phd->hd", w, v)
     assert float((out[0].float() - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))
+
+
+def test_positions_are_bounded_by_max_seq(dec):
+    """The KV cache holds max_seq positions: the host refuses steps beyond it before anything is
+    launched, and a full cache is usable up to its last position."""
+    cfg = dec.DecoderConfig(n_layers=1, hidden=256, n_heads=4, n_kv_heads=4, ffn=512, vocab=500, bits=4,
+                            group=128, cherry_fraction=1 / 32, max_seq=16)
+    a = dec.CherryDecoder(cfg, seed=3)
+    prompt = torch.randint(0, cfg.vocab, (10,), device="cuda", generator=torch.Generator(device="cuda").manual_seed(4))
+    with pytest.raises(ValueError):
+        a.prefill(torch.zeros(16, dtype=torch.long, device="cuda"))         # no free position left
+    a.prefill(prompt)
+    with pytest.raises(ValueError):
+        a.generate(7)                                                       # 10 + 7 > 16
+    assert a.pos_host == 10 and int(a.pos.item()) == 10                     # nothing ran
+    full = a.generate(6)                                                    # positions 10..15: exactly fits
+    assert a.pos_host == 16 and int(a.pos.item()) == 16
+    with pytest.raises(ValueError):
+        a.generate(1)
+    # capture at a late position (the graph is built after the prefill of 15 tokens) stays inside the cache
+    b = dec.CherryDecoder(cfg, seed=3)
+    b.prefill(torch.cat([prompt, full[:5]]))
+    last = b.generate(1)
+    assert torch.equal(last, full[5:6])                                     # same greedy continuation
+
+
+def test_device_side_position_guards():
+    """Stray positions never reach memory: the rotary kernel skips tokens outside [0, max_seq) and the
+    attention kernel attends to at most max_seq positions."""
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    g = torch.Generator(device="cuda").manual_seed(9)
+    T, H, KV, D, S = 3, 4, 2, 64, 8
+    q = torch.randn(T, H, D, device="cuda", generator=g).half()
+    k = torch.randn(T, KV, D, device="cuda", generator=g).half()
+    v = torch.randn(T, KV, D, device="cuda", generator=g).half()
+    q0, k0 = q.clone(), k.clone()
+    ang = torch.outer(torch.arange(S, device="cuda", dtype=torch.float32), torch.ones(D // 2, device="cuda"))
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([2, 8, -1], device="cuda")                           # the last two are outside
+    kc = torch.zeros(S, KV, D, dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    qc.rope_cache(q, k, v, cos, sin, pos, kc, vc)
+    torch.cuda.synchronize()
+    assert torch.equal(q[1:], q0[1:]) and torch.equal(k[1:], k0[1:])        # skipped tokens are left alone
+    assert not torch.equal(q[0], q0[0]) and torch.equal(kc[2], k[0]) and torch.equal(vc[2], v[0])
+    mask = torch.ones(S, dtype=torch.bool, device="cuda")
+    mask[2] = False
+    assert not bool(kc[mask].any()) and not bool(vc[mask].any())
+    # attention at a position beyond the cache equals attention over the whole cache
+    kcr = torch.randn(S, KV, D, device="cuda", generator=g).half()
+    vcr = torch.randn(S, KV, D, device="cuda", generator=g).half()
+    a = qc.attn_decode(q[:1].contiguous(), kcr, vcr, torch.tensor([S + 5], device="cuda"))
+    b = qc.attn_decode(q[:1].contiguous(), kcr, vcr, torch.tensor([S - 1], device="cuda"))
+    assert torch.equal(a, b)
