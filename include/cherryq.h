@@ -96,15 +96,6 @@ int cq_layer_prepare(const cq_layer* layer, const uint8_t* qweight, const void* 
 int cq_layer_unprepare(const cq_layer* layer, uint8_t* qweight, void* scales_f16,
                        void* cherry_weight_f16, int16_t* cherry_indices, cq_stream_t stream);
 
-/* Tracing hook (no counterpart in the reference, which only has host wall-clock timers,
- * benchmark_speed.py:8-17): when device_buffer (1024 x 64 uint64, device memory) is not NULL,
- * each CTA of later cq_layer_matvec launches stores nanosecond %globaltimer stamps of its
- * phases there: 0 entry, 1 barriers ready, 2 layer constants staged, 3 previous kernel done,
- * 4 activations staged, 5 first weights landed, 6 last granule done, 7 exit, 8/9 first and
- * last bulk copy issued, 16+c consumer passed the wait for ring copy c, 40+c copy c issued
- * (c < 24).  Pass NULL to switch it off. */
-int cq_trace_set_timeline(void* device_buffer);
-
 /* Bytes of scratch the matvec needs on a device (cross-CTA partial sums and flags).
  * The scratch must be zero-filled once before its first use and must not be shared
  * by launches that can overlap on the GPU. */
@@ -124,7 +115,7 @@ int cq_selftest_bounded_wait(uint32_t* status_word, cq_stream_t stream);
 
 /* cq_layer_matvec without a scratch argument and without any allocation (no counterpart in the
  * reference, whose kernels accumulate with atomicAdd and need no scratch,
- * csrc/quant_cuda_kernel.cu:672-676).  For callers that have no scratch buffer to hand over and may
+ * csrc/quant_cuda_kernel.cu:670, :833).  For callers that have no scratch buffer to hand over and may
  * not allocate one: runtimes whose device memory is planned up front, plugins living in another
  * process's memory pool, latency-critical loops where an allocation would stall the device.  The
  * cross-CTA partial sums and flags live in a fixed array inside the library's device image
@@ -241,12 +232,6 @@ int cq_tlayer_prepare(const cq_tlayer* layer, const uint8_t* qweight, const void
                       cq_stream_t stream);
 int cq_tlayer_unprepare(const cq_tlayer* layer, uint8_t* qweight, void* scales_f16,
                         void* cherry_weight_f16, int16_t* cherry_indices, cq_stream_t stream);
-/* y (M, N) fp16 = [y +] x (M, K) fp16 . W^T for 1 <= M <= 16 per launch (larger M is walked in
- * slices of 16).  Same scratch and status conventions as cq_layer_matvec. */
-int cq_tlayer_matvec(const cq_tlayer* layer, const void* x_f16, int ldx, void* y_f16, int ldy,
-                     int M, int accumulate, void* scratch, uint32_t* status_word,
-                     cq_stream_t stream);
-
 /* Prefill GEMM: y (M, N) fp16 = [y +] x (M, K) fp16 . W^T for many activation rows, on the tcgen05
  * tensor cores (weights dequantised to fp16 on the fly into tensor memory, fp32 accumulation).
  * Replaces the reference's dense mode, QuantLinear.unpack() followed by F.linear

@@ -20,7 +20,7 @@ ROOT = os.path.dirname(HERE)
 
 LIB = os.path.join(HERE, "libcherryq.so")
 CUDA_SOURCES = ["cq_api.cu", "cq_layout.cu", "cq_matvec.cu", "cq_rowvec.cu", "cq_pack.cu", "cq_legacy_f32.cu",
-                "cq_tile_layout.cu", "cq_umma_matvec.cu", "cq_prefill.cu", "cq_model_ops.cu", "cq_peer.cu"]
+                "cq_tile_layout.cu", "cq_prefill.cu", "cq_model_ops.cu", "cq_peer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--fmad=true",

@@ -16,8 +16,8 @@ SYMBOLS = [
     "cq_vecquant4matmul_cherryq", "cq_vecquant3matmul_cherryq",
     "cq_dequantize3_normal", "cq_dequantize4_normal",
     "cq_cache_clear", "cq_cache_stats", "cq_cache_evict", "cq_poll",
-    "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense", "cq_trace_set_timeline",
-    "cq_tlayer_init", "cq_tlayer_prepare", "cq_tlayer_unprepare", "cq_tlayer_matvec",
+    "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense",
+    "cq_tlayer_init", "cq_tlayer_prepare", "cq_tlayer_unprepare",
     "cq_layer_matvec_static", "cq_tlayer_gemm_workspace_bytes", "cq_tlayer_gemm",
     "cq_selftest_bounded_wait", "cq_rmsnorm", "cq_rope_cache", "cq_silu_mul", "cq_attn_decode",
     "cq_peer_region_bytes", "cq_peer_region_create", "cq_peer_region_destroy", "cq_peer_region_export",
@@ -78,7 +78,6 @@ def lib():
     L.cq_tlayer_init.argtypes = [C.POINTER(cq_tlayer), i32, i32, i32, i32, i32, vp]
     L.cq_tlayer_prepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]
     L.cq_tlayer_unprepare.argtypes = [C.POINTER(cq_tlayer), vp, vp, vp, vp, vp]
-    L.cq_tlayer_matvec.argtypes = [C.POINTER(cq_tlayer), vp, i32, vp, i32, i32, i32, vp, vp, vp]
     L.cq_tlayer_gemm.argtypes = [C.POINTER(cq_tlayer), vp, i32, vp, i32, i32, i32, vp, vp, vp]
     L.cq_tlayer_gemm_workspace_bytes.argtypes = [C.POINTER(cq_tlayer), i32]
     L.cq_tlayer_gemm_workspace_bytes.restype = C.c_size_t
@@ -89,7 +88,6 @@ def lib():
     L.cq_cache_stats.argtypes = [C.POINTER(C.c_int), C.POINTER(C.c_uint64)]
     L.cq_cache_evict.argtypes = [vp, vp, vp, vp]
     L.cq_poll.argtypes = [vp]
-    L.cq_trace_set_timeline.argtypes = [vp]
     L.cq_pack.argtypes = [vp, i32, vp] + [i32] * 5 + [vp] * 6
     L.cq_unpack_dense.argtypes = [vp] * 4 + [i32] * 5 + [vp, vp]
     L.cq_peer_region_bytes.argtypes = [C.c_size_t]

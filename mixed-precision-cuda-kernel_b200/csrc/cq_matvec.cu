@@ -35,7 +35,9 @@
 
 #include "cq_common.cuh"
 
-unsigned long long* cq_g_timeline = nullptr;   // tracing buffer, see cq_trace_set_timeline
+#ifdef CQ_MATVEC_TRACE
+unsigned long long* cq_g_timeline = nullptr;   // tracing buffer of instrumented builds, see cq_trace_set_timeline
+#endif
 
 namespace {
 
@@ -194,7 +196,7 @@ template <int SETS> struct Raw<4, SETS> { uint4 a, b; uint32_t sc[SETS]; };
 template <int SETS> struct Raw<3, SETS> { uint4 a; uint2 b; uint32_t sc[SETS]; };
 
 // MB = activation tiles of four rows (two B columns per row); MAXR = register cap per thread
-// (see SHAPES on the host side).
+// (SMALL_NCW / LARGE_NCW on the host side).
 template <int BITS, int SETS, int MB, int NCW, int MAXR>
 __global__ void __launch_bounds__((NCW + 1) * 32) __maxnreg__(MAXR) cq_matvec_kernel(const MatvecParams p) {
   constexpr int NCONS = NCW * 32;
@@ -801,62 +803,34 @@ DeviceInfo device_info(int dev) {
 
 typedef void (*KernelFn)(const MatvecParams);
 
-// Kernel shapes: consumer warps (a pair of granules per warp per ring stage) and the register cap.
-// Shape 0 is the product: 19 consumer warps with the whole SM to themselves measured fastest on the
-// LLaMA-7B layers (more warps hide more of the per-instruction latency of the unpack code than
-// sharing the SM with the next launch's prefetch gains).  Shapes 1..3 are capped so that two CTAs
-// fit one SM (registers are split over four sub-partitions, so ceil(warps / 4) warps of each CTA
-// land on one of them: 2 * ceil(warps / 4) * 32 * regs <= 16384); they need CQ_SMEM_KB <= 111.
-// Launches of more than four activation rows use one shape and the whole register file.
-struct Shape { int ncw; };
-constexpr Shape SHAPES[] = {{19}, {11}, {8}, {15}, {23}};
-constexpr int N_SHAPES = sizeof(SHAPES) / sizeof(SHAPES[0]);
+// The product shape for launches of up to four activation rows: 19 consumer warps (a pair of granules per
+// warp per ring stage) with the whole SM to themselves, 96 registers; it measured fastest on the LLaMA-7B
+// layers (more warps hide more of the per-instruction latency of the unpack code than sharing the SM
+// with the next launch's prefetch gains).  Launches of more than four activation rows use 11 consumer
+// warps and the whole register file.
+constexpr int SMALL_NCW = 19, SMALL_REGS = 96, LARGE_NCW = 11;
+constexpr int SMEM_TARGET_KB = 220;      // shared memory per CTA (the whole SM)
+constexpr int MAX_STAGES = 16;           // ring stages
+constexpr int INFLIGHT = 2;              // ring stages outstanding at a time
 
-template <int NCW, int MAXR>
 KernelFn pick_small(int bits, int sets) {
-  if (bits == 4) return sets == 1 ? cq_matvec_kernel<4, 1, 1, NCW, MAXR> : cq_matvec_kernel<4, 2, 1, NCW, MAXR>;
-  return sets == 1 ? cq_matvec_kernel<3, 1, 1, NCW, MAXR> : cq_matvec_kernel<3, 2, 1, NCW, MAXR>;
+  if (bits == 4) return sets == 1 ? cq_matvec_kernel<4, 1, 1, SMALL_NCW, SMALL_REGS> : cq_matvec_kernel<4, 2, 1, SMALL_NCW, SMALL_REGS>;
+  return sets == 1 ? cq_matvec_kernel<3, 1, 1, SMALL_NCW, SMALL_REGS> : cq_matvec_kernel<3, 2, 1, SMALL_NCW, SMALL_REGS>;
 }
 template <int MB>
 KernelFn pick_large(int bits, int sets) {
-  if (bits == 4) return sets == 1 ? cq_matvec_kernel<4, 1, MB, 11, 128> : cq_matvec_kernel<4, 2, MB, 11, 128>;
-  return sets == 1 ? cq_matvec_kernel<3, 1, MB, 11, 128> : cq_matvec_kernel<3, 2, MB, 11, 128>;
+  if (bits == 4) return sets == 1 ? cq_matvec_kernel<4, 1, MB, LARGE_NCW, 128> : cq_matvec_kernel<4, 2, MB, LARGE_NCW, 128>;
+  return sets == 1 ? cq_matvec_kernel<3, 1, MB, LARGE_NCW, 128> : cq_matvec_kernel<3, 2, MB, LARGE_NCW, 128>;
 }
 
 // mb = activation tiles of four rows: 1, 2 or 4.  Returns the kernel and its consumer warp count.
-KernelFn pick_kernel(int shape, int bits, int sets, int mb, int* ncw) {
+KernelFn pick_kernel(int bits, int sets, int mb, int* ncw) {
   if (mb == 1) {
-    *ncw = SHAPES[shape].ncw;
-    switch (shape) {
-      case 0: return pick_small<19, 96>(bits, sets);
-      case 1: return pick_small<11, 80>(bits, sets);
-      case 2: return pick_small<8, 80>(bits, sets);
-      case 3: return pick_small<15, 64>(bits, sets);
-      default: return pick_small<23, 80>(bits, sets);
-    }
+    *ncw = SMALL_NCW;
+    return pick_small(bits, sets);
   }
-  *ncw = 11;
+  *ncw = LARGE_NCW;
   return mb == 2 ? pick_large<2>(bits, sets) : pick_large<4>(bits, sets);
-}
-
-// Tuning knobs read once from the environment (for experiments; defaults are the product):
-//   CQ_SHAPE  index into SHAPES      CQ_SMEM_KB  shared-memory target per CTA
-//   CQ_PDL    0 disables programmatic dependent launch   CQ_INFLIGHT  ring stages outstanding at a time
-struct Knobs { int shape, smem_kb, pdl, max_stages, inflight; };
-Knobs knobs() {
-  static Knobs k = [] {
-    Knobs v{0, 220, 1, 16, 2};
-    if (const char* e = getenv("CQ_SHAPE")) v.shape = atoi(e);
-    if (const char* e = getenv("CQ_SMEM_KB")) v.smem_kb = atoi(e);
-    if (const char* e = getenv("CQ_PDL")) v.pdl = atoi(e);
-    if (const char* e = getenv("CQ_MAX_STAGES")) v.max_stages = atoi(e);
-    if (const char* e = getenv("CQ_INFLIGHT")) v.inflight = atoi(e);
-    if (v.inflight < 1) v.inflight = 1;
-    if (v.max_stages < 2) v.max_stages = 2;
-    if (v.shape < 0 || v.shape >= N_SHAPES) v.shape = 0;
-    return v;
-  }();
-  return k;
 }
 
 int align_up(int v, int a) { return (v + a - 1) / a * a; }
@@ -925,12 +899,17 @@ cudaError_t prepare_kernel(KernelFn fn, int smem) {
 
 }  // namespace
 
-// Tracing: when a device buffer of 1024 x 16 uint64 is set, every CTA of the following matvec
-// launches stores %globaltimer stamps of its phases there (slot meanings in cq_matvec_kernel).
+#ifdef CQ_MATVEC_TRACE
+// Instrumented builds only (not part of the library's interface): when a device buffer of 1024 x 64
+// uint64 is set, every CTA of the following matvec launches stores %globaltimer stamps of its phases
+// there: 0 entry, 1 barriers ready, 2 layer constants staged, 3 previous kernel done, 4 activations
+// staged, 5 first weights landed, 6 last granule done, 7 exit, 8/9 first and last bulk copy issued,
+// 16+c consumer passed the wait for ring copy c, 40+c copy c issued (c < 24).  Not thread-safe.
 extern "C" int cq_trace_set_timeline(void* device_buffer) {
   cq_g_timeline = (unsigned long long*)device_buffer;
   return CQ_OK;
 }
+#endif
 
 extern "C" size_t cq_scratch_bytes(void) {
   // stream kernel: up to 1024 CTAs x 256 floats of partial, flags behind them at 1 MiB;
@@ -947,7 +926,6 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   CQ_CUDA_TRY(cudaGetDevice(&dev));
   const DeviceInfo di = device_info(dev);
   if (!di.ok) return CQ_ERR_NO_DEVICE;
-  const Knobs kn = knobs();
   const uint32_t T = (uint32_t)L->n_sub * (uint32_t)L->n_gran;
   int grid = di.sms < 1024 ? di.sms : 1024;
   if ((uint32_t)grid > T) grid = (int)T;
@@ -957,8 +935,8 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   int smem = -1, ncw = 0;
   KernelFn fn = nullptr;
   for (; rows >= 1; --rows) {
-    fn = pick_kernel(kn.shape, L->bits, L->sets, tiles_of(rows), &ncw);
-    smem = plan_smem(L, rows, grid, di.max_smem, ncw, kn.smem_kb, kn.max_stages, &p);
+    fn = pick_kernel(L->bits, L->sets, tiles_of(rows), &ncw);
+    smem = plan_smem(L, rows, grid, di.max_smem, ncw, SMEM_TARGET_KB, MAX_STAGES, &p);
     if (smem >= 0) break;
   }
   if (smem < 0) return CQ_ERR_TOO_LARGE;
@@ -971,12 +949,16 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   p.partial = (float*)scratch;
   p.flag = (uint32_t*)((uint8_t*)scratch + (size_t)1024 * 256 * sizeof(float));
   p.status = status;
+#ifdef CQ_MATVEC_TRACE
   p.timeline = cq_g_timeline;
+#else
+  p.timeline = nullptr;
+#endif
   p.M = rows; p.K = L->K; p.N = L->N; p.C = L->C; p.Cp = L->Cp; p.Kp = L->Kp;
   p.n_gran = L->n_gran; p.n_sub = L->n_sub; p.gran_bytes = L->gran_bytes; p.cher_bytes = L->cher_bytes;
   p.ldx = ldx; p.ldy = ldy; p.accumulate = accumulate;
   p.T = T;
-  p.inflight = kn.inflight;
+  p.inflight = INFLIGHT;
 
   CQ_CUDA_TRY(prepare_kernel(fn, smem));
   cudaLaunchConfig_t cfg = {};
@@ -988,7 +970,7 @@ static int launch_rows(const cq_layer* L, const __half* x, int ldx, __half* y, i
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = kn.pdl ? 1 : 0;
+  cfg.numAttrs = 1;
   CQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, fn, p));
   *rows_done = rows;
   return CQ_OK;
@@ -1104,7 +1086,6 @@ extern "C" int cq_layer_matvec_static(const cq_layer* L, const void* x, int ldx,
   const DeviceInfo di = device_info(dev);
   if (!di.ok) return CQ_ERR_NO_DEVICE;
   if (di.sms > CQ_STATIC_MAX_CTAS) return CQ_ERR_STATIC_LIMIT;
-  const Knobs kn = knobs();
   const uint32_t T = (uint32_t)L->n_sub * (uint32_t)L->n_gran;
   int grid = di.sms;
   if ((uint32_t)grid > T) grid = (int)T;
@@ -1112,8 +1093,8 @@ extern "C" int cq_layer_matvec_static(const cq_layer* L, const void* x, int ldx,
   // one launch must take all M rows: the array has room for one launch's partial sums only
   MatvecParams p;
   int ncw = 0;
-  KernelFn fn = pick_kernel(kn.shape, L->bits, L->sets, tiles_of(M), &ncw);
-  const int smem = plan_smem(L, M, grid, di.max_smem, ncw, kn.smem_kb, kn.max_stages, &p);
+  KernelFn fn = pick_kernel(L->bits, L->sets, tiles_of(M), &ncw);
+  const int smem = plan_smem(L, M, grid, di.max_smem, ncw, SMEM_TARGET_KB, MAX_STAGES, &p);
   if (smem < 0) return CQ_ERR_STATIC_LIMIT;
 
   unsigned char* base = nullptr;
@@ -1136,7 +1117,7 @@ extern "C" int cq_layer_matvec_static(const cq_layer* L, const void* x, int ldx,
   p.n_gran = L->n_gran; p.n_sub = L->n_sub; p.gran_bytes = L->gran_bytes; p.cher_bytes = L->cher_bytes;
   p.ldx = ldx; p.ldy = ldy; p.accumulate = accumulate;
   p.T = T;
-  p.inflight = kn.inflight;
+  p.inflight = INFLIGHT;
 
   CQ_CUDA_TRY(prepare_kernel(fn, smem));
   cudaLaunchConfig_t cfg = {};

@@ -597,10 +597,8 @@ PKernelFn ppick(int bits, int sets) {
 }
 
 // Tile shape for a call of M rows: 0 = 128 rows x 128 tokens (two accumulator buffers), 1 = 128 x 256,
-// 2 = 256 x 128.  CQ_PREFILL_SHAPE overrides, for experiments.
+// 2 = 256 x 128.
 int tile_shape(int M, int n_tile) {
-  static int forced = [] { const char* e = getenv("CQ_PREFILL_SHAPE"); return e ? atoi(e) : -1; }();
-  if (forced >= 0 && forced <= 2) return forced;
   (void)n_tile;
   // measured on 4096 -> 11008, 2048 tokens: 128 x 256 tiles 938 TFLOP/s, 128 x 128 673, 256 x 128 613: the
   // tensor-memory MMA only reaches its rate at N = 256
@@ -612,14 +610,11 @@ unsigned long long xb_block_bytes(const cq_tlayer* L, int nt) {
 }
 
 // Split-K for calls whose units do not fill the SMs (few tokens): into how many parts the items of
-// a unit are divided so that the parts fill the SMs about evenly (CQ_PREFILL_SPLIT overrides).
+// a unit are divided so that the parts fill the SMs about evenly.
 constexpr int MAX_SPLIT = 4;
 int pick_split(int n_units, int items, int sms) {
-  static int forced = [] { const char* e = getenv("CQ_PREFILL_SPLIT"); return e ? atoi(e) : 0; }();
   int best = 1;
-  if (forced >= 1 && forced <= MAX_SPLIT) {
-    best = forced;
-  } else if (n_units < sms) {
+  if (n_units < sms) {
     double best_t = 1.0;                                   // makespan, in whole units
     for (int sp = 2; sp <= MAX_SPLIT; ++sp) {
       const int waves = (n_units * sp + sms - 1) / sms;

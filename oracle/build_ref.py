@@ -79,6 +79,12 @@ def load():
     return mod
 
 
+def reference_root() -> str:
+    """Where the reference project's checkout is looked for: $CHERRYQ_REFERENCE_ROOT, else a directory
+    named `reference` beside this repository."""
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return os.environ.get("CHERRYQ_REFERENCE_ROOT") or os.path.join(os.path.dirname(here), "reference")
+
+
 if __name__ == "__main__":
-    default_root = os.environ.get("CHERRYQ_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
-    build(sys.argv[1] if len(sys.argv) > 1 else default_root, verbose=True)
+    build(sys.argv[1] if len(sys.argv) > 1 else reference_root(), verbose=True)

@@ -135,7 +135,7 @@ SHAPES = [(4096, 4096), (4096, 11008), (11008, 4096)]
 @pytest.mark.parametrize("bits", [4, 3])
 @pytest.mark.parametrize("K,N", SHAPES)
 def test_matvec_llama7b_shapes(cabi, K, N, bits):
-    """BASELINE configs[1]: LLaMA-7B linear shapes, 3- and 4-bit, group 128, cherry ratio 1/256, batch 1/4/16."""
+    """The headline configuration: LLaMA-7B linear shapes, 3- and 4-bit, group 128, cherry ratio 1/256, batch 1/4/16."""
     w, idx, p, dense = make_case(K, N, bits, 128, seed=K + N + bits)
     prep = Prepared(cabi, p["qweight"], p["scales"], p["cherry_weight"], p["cherry_indices"], bits, K, 128)
     rng = np.random.default_rng(5)

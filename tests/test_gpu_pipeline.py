@@ -76,3 +76,23 @@ def test_decoder_checkpoint_round_trip_in_the_reference_layout(mods, tmp_path):
     a.prefill(prompt)
     b.prefill(prompt)
     assert torch.equal(a.generate(16, use_graph=False), b.generate(16, use_graph=False))
+
+
+@pytest.mark.parametrize("k,fraction", [(4096, 1 / 256), (11008, 1 / 256), (28672, 1 / 256), (512, 1 / 16)])
+def test_select_cherries_on_the_gpu_matches_numpy(mods, k, fraction):
+    """Cherry selection on a device-resident impact vector (estimate_impact.py:85-87 of the reference: the
+    top of a descending argsort) against numpy's stable argsort, ties included."""
+    _, _, P, _ = mods
+    rng = np.random.default_rng(k)
+    impact = rng.random(k).astype(np.float32)
+    impact[rng.integers(0, k, 64)] = impact.max()          # ties at the top: the lower index wins
+    got = P.select_cherries(torch.from_numpy(impact).cuda(), fraction)
+    n = P.num_cherries(k, fraction)
+    want = np.argsort(-impact, kind="stable")[:n]
+    assert got.dtype == torch.int32 and got.device.type == "cpu" and got.shape == (n,)
+    assert np.array_equal(got.numpy(), want)
+    # a batch of vectors (one per layer) in one call
+    many = rng.random((5, k)).astype(np.float32)
+    gm = P.select_cherries(torch.from_numpy(many).cuda(), fraction).numpy()
+    for r in range(5):
+        assert np.array_equal(gm[r], np.argsort(-many[r], kind="stable")[:n])
