@@ -404,27 +404,44 @@ def run_ours(args):
             yh.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
+    def timed_host_loop(fn, n):
+        """ms per call of n synchronous host-side calls (each returns with its result in host memory)."""
+        for i in range(ncopies + 3):
+            fn(i)
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(n):
+            fn(i)
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / n
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
     e2e_steps = min(args.steps, 2000)
-    for i in range(ncopies + 3):
-        e2e_step(i)
-    barrier()
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    t1.record()
-    torch.cuda.synchronize()
-    e2e_ms = t0.elapsed_time(t1) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    op_ms = timed_host_loop(e2e_step, e2e_steps)
     qc.poll()
+    op_path = ("quant_cuda.vecquant4matmul_cherryq with pinned host x per rank" +
+               (f", {gather_kind}, the whole y read back on rank 0" if world > 1 else " and y"))
+    if world == 1:
+        # the C ABI's host-buffer call: x from pinned host memory, y in pinned host memory when it returns
+        xhp, yhp = C.c_void_p(xh.data_ptr()), C.c_void_p(yh.data_ptr())
+
+        def host_step(i):
+            _cabi.check(lib.cq_rlayer_matvec_host(C.byref(layers[i % ncopies]), xhp, yhp, ptr(xd), ptr(out), ptr(status),
+                                                  None), "matvec_host")
+        e2e_ms = timed_host_loop(host_step, e2e_steps)
+        e2e_path = "cq_rlayer_matvec_host (C ABI): pinned host x in, pinned host y out, one call per step"
+    else:
+        e2e_ms, e2e_path = op_ms, op_path
     e2e = {"value": alg / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": K_IN * 2,
-           "d2h_bytes_per_step": N_OUT * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
-           "path": "quant_cuda.vecquant4matmul_cherryq with pinned host x per rank" +
-                   (f", {gather_kind}, the whole y read back on rank 0" if world > 1 else " and y")}
+           "d2h_bytes_per_step": N_OUT * 2, "ms_per_step": e2e_ms, "steps": e2e_steps, "path": e2e_path,
+           "through_the_torch_op": {"ms_per_step": op_ms, "value": alg / (op_ms * 1e-3) / 1e9, "path": op_path}}
 
     # the reference project's own CUDA kernel on the same layer copies (built by oracle/build_ref.py;
     # information only: batch 1, device-resident inputs, CUDA events)

@@ -181,6 +181,24 @@ int cq_rlayer_check(const cq_rlayer* layer);
  * kernel's own bulk copies ever runs out; may be NULL. */
 int cq_rlayer_matvec(const cq_rlayer* layer, const void* x_f16, void* y_f16, int accumulate,
                      uint32_t* status_word, cq_stream_t stream);
+/* cq_rlayer_matvec for callers that hold their activations in HOST memory (a foreign-function
+ * binding with no device tensors of its own; the reference's op only takes device tensors,
+ * csrc/quant_cuda.cpp:56-69): copies x_host (K fp16) to the device staging buffer x_dev, runs the
+ * kernel into y_dev, copies the N fp16 results to y_host and returns when y_host is complete (the
+ * stream is synchronised).  Page-locked host memory keeps the two copies asynchronous and short;
+ * pageable memory works.  x_dev / y_dev: device memory of K and N fp16 owned by the caller. */
+int cq_rlayer_matvec_host(const cq_rlayer* layer, const void* x_host_f16, void* y_host_f16,
+                          void* x_dev_f16, void* y_dev_f16, uint32_t* status_word,
+                          cq_stream_t stream);
+/* One launch for up to 4 layers that take the same activation row (q / k / v, gate / up of the
+ * reference's LLaMA, llama/modeling_llama_quant.py: LlamaAttention.forward, LlamaMLP.forward, which
+ * calls them one after the other): ys[i] (N_i) fp16 = [ys[i] +] x (K) fp16 . W_i^T.  The layers must
+ * agree in bits, K, cherry count and group size (CQ_ERR_BAD_SHAPE otherwise); the SMs are divided
+ * among them in proportion to their rows.  Every output element is computed exactly as by
+ * cq_rlayer_matvec on that layer alone (bit-identical).  Same limits and status word. */
+int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, const void* x_f16,
+                      void* const* ys_f16, int accumulate, uint32_t* status_word,
+                      cq_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Element-wise kernels of the decode harness around the quantized linear (fp16 in / out, fp32

@@ -41,16 +41,26 @@ namespace {
 constexpr uint32_t RV_WAIT_LIMIT = 1u << 22;
 constexpr int RV_MAX_SLOTS = 16;            // ring slots (tiles resident in shared memory at a time)
 
-struct RowvecParams {
+constexpr int RV_MAX_SEG = 4;               // layers one launch can serve (they share the activation row)
+
+// One layer of a launch: a range of CTAs works on it.
+struct RowvecSeg {
   const uint8_t* tiles;     // tile records: [NG groups][scales][cherry blocks]
   const uint16_t* perm;     // [NG * 128] original column of each compact column, K for padding
   const uint16_t* cidx;     // [Cp] sorted cherry columns
-  const __half* x;
   __half* y;
+  int N;
+  int cta0;                 // first CTA of the range
+  int tiles_q, tiles_r;     // CTA b of the range owns tiles_q (+1 if b < tiles_r) consecutive tiles
+};
+
+struct RowvecParams {
+  RowvecSeg seg[RV_MAX_SEG];
+  int nseg;
+  const __half* x;
   uint32_t* status;         // may be null
-  int K, N, C, NG, ncb;     // ncb = cherry blocks of 16 columns
+  int K, C, NG, ncb;        // common to the layers of a launch; ncb = cherry blocks of 16 columns
   int tile_bytes, scal_off, cher_off;
-  int tiles_q, tiles_r;     // CTA b owns tiles_q (+1 if b < tiles_r) consecutive tiles
   int slots;                // ring slots in use
   int inflight;             // tiles the copy warp keeps outstanding
   int slice_halves;         // halves of a warp's raw activation slice in shared memory
@@ -151,8 +161,8 @@ __device__ __forceinline__ void rv_stamp(unsigned long long* buf, int launch, in
 #endif
 
 // Requests tile `tile` of the layer into ring slot `slot`; one thread calls it.
-__device__ __forceinline__ void issue_tile(const RowvecParams& p, unsigned char* stiles, uint32_t bar_full, int tile, int slot) {
-  const uint8_t* src = p.tiles + (size_t)tile * p.tile_bytes;
+__device__ __forceinline__ void issue_tile(const RowvecParams& p, const uint8_t* tiles, unsigned char* stiles, uint32_t bar_full, int tile, int slot) {
+  const uint8_t* src = tiles + (size_t)tile * p.tile_bytes;
   const uint32_t dst = rv_smem_u32(stiles) + (uint32_t)slot * p.tile_bytes;
   const uint32_t bar = bar_full + 8 * slot;
   rv_mbar_expect_tx(bar, (uint32_t)p.tile_bytes);
@@ -186,8 +196,15 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   const uint32_t bar_empty = bar_full + 8 * RV_MAX_SLOTS;
   unsigned char* stiles = smem + p.off_tiles;
 
-  const int tile0 = (int)blockIdx.x * p.tiles_q + min((int)blockIdx.x, p.tiles_r);
-  const int nt = p.tiles_q + ((int)blockIdx.x < p.tiles_r ? 1 : 0);
+  // the layer this CTA works on, and its tiles of it
+  int si = 0;
+#pragma unroll
+  for (int s = 1; s < RV_MAX_SEG; ++s)
+    if (s < p.nseg && (int)blockIdx.x >= p.seg[s].cta0) si = s;
+  const RowvecSeg& sg = p.seg[si];
+  const int bseg = (int)blockIdx.x - sg.cta0;
+  const int tile0 = bseg * sg.tiles_q + min(bseg, sg.tiles_r);
+  const int nt = sg.tiles_q + (bseg < sg.tiles_r ? 1 : 0);
   const int S = p.slots;
 
   if (tid == 0) {
@@ -207,6 +224,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
     // has released it.
     if (lane == 0) {
       asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+      const uint8_t* seg_tiles = sg.tiles;
       int slot = 0, lslot = 0;                      // slot of the tile to issue / of the tile `inflight` back
       uint32_t ephase = 0, lphase = 0;              // phases of the empty / full barriers waited on
       for (int next = 0; next < nt; ++next) {
@@ -217,7 +235,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
         if (next >= S) {                            // the slot's previous tile must have been consumed
           rv_mbar_wait(bar_empty + 8 * slot, ephase, &s_abort, p.status);
         }
-        issue_tile(p, stiles, bar_full, tile0 + next, slot);
+        issue_tile(p, seg_tiles, stiles, bar_full, tile0 + next, slot);
         if (++slot == S) { slot = 0; if (next >= S) ephase ^= 1u; }
       }
     }
@@ -232,6 +250,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   } else {
   // ---- this warp's groups (contiguous) and cherry block
   const int NG = p.NG;
+  const uint16_t* seg_perm = sg.perm;
   const int gq = NG / W, gr = NG % W;
   const int ngw = gq + (warp < gr ? 1 : 0);
   const int gstart = warp * gq + min(warp, gr);
@@ -240,7 +259,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   int lo8 = 0, nchunk = 0;
   if (ngw > 0) {
     const int kc0 = gstart * 128, kc1 = min(p.K - p.C, (gstart + ngw) * 128) - 1;
-    const int lo = p.perm[kc0], hi = p.perm[kc1];
+    const int lo = seg_perm[kc0], hi = seg_perm[kc1];
     lo8 = lo & ~7;
     nchunk = (hi - lo8) / 8 + 1;
   }
@@ -255,7 +274,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
     const int ol = lane + 32 * u;
     uint4 c = make_uint4(0, 0, 0, 0);
     if (ol < ngw * 16) {
-      c = *reinterpret_cast<const uint4*>(p.perm + ((size_t)gstart * 16 + ol) * 8);
+      c = *reinterpret_cast<const uint4*>(seg_perm + ((size_t)gstart * 16 + ol) * 8);
       const uint32_t sub = (uint32_t)lo8 * 0x10001u;
       c.x = (c.x - sub) * 2u; c.y = (c.y - sub) * 2u; c.z = (c.z - sub) * 2u; c.w = (c.w - sub) * 2u;
     }
@@ -264,7 +283,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   (void)padpair;
   const bool owns_tail = ngw > 0 && gstart + ngw == NG;     // the warp whose last group may hold padding columns
   int ccol = -1;
-  if (has_cherry && lane < 16 && warp * 16 + lane < p.C) ccol = p.cidx[warp * 16 + lane];
+  if (has_cherry && lane < 16 && warp * 16 + lane < p.C) ccol = sg.cidx[warp * 16 + lane];
   const bool x_aligned = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -497,14 +516,16 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   __syncthreads();
   // ---- the warps' partial sums of every row, in warp order
   const int row0 = tile0 * 16;
+  __half* y = sg.y;
+  const int N = sg.N;
   for (int rr = tid; rr < nt * 16; rr += NTHR) {
     const int row = row0 + rr;
-    if (row < p.N) {
+    if (row < N) {
       const float* pp = part + (size_t)(rr >> 4) * W * 16 + (rr & 15);
-      float acc = p.accumulate ? __half2float(p.y[row]) : 0.f;
+      float acc = p.accumulate ? __half2float(y[row]) : 0.f;
 #pragma unroll
       for (int w = 0; w < W; ++w) acc += pp[w * 16];
-      p.y[row] = __float2half_rn(acc);
+      y[row] = __float2half_rn(acc);
     }
   }
   RV_STAMP(5);
@@ -721,20 +742,64 @@ RowvecFn rv_pick(int bits, int sets) {
   return sets == 1 ? cq_rowvec_kernel<3, 1, W, GPW> : cq_rowvec_kernel<3, 2, W, GPW>;
 }
 
-// Shared-memory plan of a kernel with W working warps that own up to GPW groups each; fills the
-// launch parameters that do not depend on the call.  Returns a status code.
-int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* L, const RvDevice& di, RowvecParams* p, int* grid_out,
-            int* smem_out) {
+// Plan of one launch over `n` layers that share the activation row (same bits, K, cherry count and
+// group size, hence the same tile record size): how the CTAs are divided among the layers, the
+// shared-memory sections, the ring.  W working warps own up to GPW groups each.  Fills the launch
+// parameters that do not depend on the call.  Returns a status code.
+int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, const RvDevice& di, RowvecParams* p,
+            int* grid_out, int* smem_out) {
+  if (n < 1 || n > RV_MAX_SEG) return CQ_ERR_BAD_ARG;
+  const cq_rlayer* L = Ls[0];
+  for (int i = 1; i < n; ++i)
+    if (Ls[i]->bits != L->bits || Ls[i]->K != L->K || Ls[i]->C != L->C || Ls[i]->G != L->G) return CQ_ERR_BAD_SHAPE;
   if ((L->NG + W - 1) / W > GPW) return CQ_ERR_UNSUPPORTED;
   if (L->Cp / 16 > W) return CQ_ERR_UNSUPPORTED;
   if (GPW * 128 + L->C + 8 > (GPW / 2 + 1) * 256) return CQ_ERR_UNSUPPORTED;   // a warp's slice of x: XCH pieces per lane
-  const int grid = di.sms < L->NT ? di.sms : L->NT;
-  const int nt_max = (L->NT + grid - 1) / grid;
-  p->K = L->K; p->N = L->N; p->C = L->C; p->NG = L->NG; p->ncb = L->Cp / 16;
+  // CTAs per layer: every layer at least one, the rest to whichever layer has the most tiles per CTA
+  long long total = 0;
+  for (int i = 0; i < n; ++i) total += Ls[i]->NT;
+  int ctas[RV_MAX_SEG];
+  int grid = 0;
+  if (total <= di.sms) {
+    for (int i = 0; i < n; ++i) { ctas[i] = Ls[i]->NT; grid += ctas[i]; }
+  } else {
+    if (di.sms < n) return CQ_ERR_NO_DEVICE;
+    for (int i = 0; i < n; ++i) {
+      ctas[i] = (int)((long long)di.sms * Ls[i]->NT / total);
+      if (ctas[i] < 1) ctas[i] = 1;
+      grid += ctas[i];
+    }
+    while (grid > di.sms) {                      // (rounding up the small layers can overshoot)
+      int big = 0;
+      for (int i = 1; i < n; ++i) if (ctas[i] > ctas[big]) big = i;
+      --ctas[big]; --grid;
+    }
+    for (; grid < di.sms; ++grid) {
+      int worst = -1, worst_t = 0;
+      for (int i = 0; i < n; ++i) {
+        const int t = (Ls[i]->NT + ctas[i] - 1) / ctas[i];
+        if (ctas[i] < Ls[i]->NT && t > worst_t) { worst = i; worst_t = t; }
+      }
+      if (worst < 0) break;
+      ++ctas[worst];
+    }
+  }
+  int nt_max = 0, cta0 = 0;
+  for (int i = 0; i < n; ++i) {
+    RowvecSeg& sg = p->seg[i];
+    sg.N = Ls[i]->N;
+    sg.cta0 = cta0;
+    sg.tiles_q = Ls[i]->NT / ctas[i];
+    sg.tiles_r = Ls[i]->NT % ctas[i];
+    const int t = (Ls[i]->NT + ctas[i] - 1) / ctas[i];
+    if (t > nt_max) nt_max = t;
+    cta0 += ctas[i];
+  }
+  p->nseg = n;
+  p->K = L->K; p->C = L->C; p->NG = L->NG; p->ncb = L->Cp / 16;
   p->tile_bytes = L->tile_bytes;
   p->scal_off = L->NG * 256 * L->bits;
   p->cher_off = p->scal_off + L->NG * L->sets * 32;
-  p->tiles_q = L->NT / grid; p->tiles_r = L->NT % grid;
   // a warp's staging area: the raw slice (its column range + alignment slack + zero slot), later its planes
   const int gmax = (L->NG + W - 1) / W;
   p->slice_halves = rv_align(gmax * 128 + L->C + 8 + 8 + 8, 8);
@@ -760,23 +825,29 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* L, const
   return CQ_OK;
 }
 
-// One launch of a kernel whose warp count is W and whose warps can own GPW groups.
+// One launch of a kernel whose warp count is W and whose warps can own GPW groups, over `n` layers
+// that take the same activation row x; ys[i] receives layer i's output.
 // inflight: tiles the copy warp keeps outstanding.
-int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_rlayer* L, const __half* x, __half* y,
-              int accumulate, uint32_t* status, cudaStream_t st) {
+int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, const __half* x,
+              __half* const* ys, int accumulate, uint32_t* status, cudaStream_t st) {
   int dev = 0;
   CQ_CUDA_TRY(cudaGetDevice(&dev));
   const RvDevice di = rv_device(dev);
   if (!di.ok) return CQ_ERR_NO_DEVICE;
   RowvecParams p;
   int grid = 0, smem = 0;
-  const int rc = rv_plan(W, GPW, inflight, smem_kb, L, di, &p, &grid, &smem);
+  const int rc = rv_plan(W, GPW, inflight, smem_kb, Ls, n, di, &p, &grid, &smem);
   if (rc != CQ_OK) return rc;
-  const uint8_t* blob = (const uint8_t*)L->blob;
-  p.tiles = blob + L->off_tiles;
-  p.perm = (const uint16_t*)(blob + L->off_perm);
-  p.cidx = (const uint16_t*)(blob + L->off_cidx);
-  p.x = x; p.y = y; p.status = status;
+  for (int i = 0; i < RV_MAX_SEG; ++i) {
+    const int j = i < n ? i : 0;                 // unused entries repeat the first layer (never selected)
+    const uint8_t* blob = (const uint8_t*)Ls[j]->blob;
+    p.seg[i].tiles = blob + Ls[j]->off_tiles;
+    p.seg[i].perm = (const uint16_t*)(blob + Ls[j]->off_perm);
+    p.seg[i].cidx = (const uint16_t*)(blob + Ls[j]->off_cidx);
+    p.seg[i].y = ys[j];
+    if (i >= n) { p.seg[i].N = 0; p.seg[i].cta0 = grid; p.seg[i].tiles_q = 0; p.seg[i].tiles_r = 0; }
+  }
+  p.x = x; p.status = status;
   p.accumulate = accumulate;
 #ifdef CQ_ROWVEC_TRACE
   static int launch_no = 0;
@@ -873,28 +944,50 @@ extern "C" int cq_rlayer_check(const cq_rlayer* L) {
   if (!gpw) return CQ_ERR_UNSUPPORTED;
   RowvecParams p;
   int grid = 0, smem = 0;
-  return rv_plan(RV_W, gpw, CQ_ROWVEC_INFLIGHT, 0, L, di, &p, &grid, &smem);
+  return rv_plan(RV_W, gpw, CQ_ROWVEC_INFLIGHT, 0, &L, 1, di, &p, &grid, &smem);
+}
+
+extern "C" int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, const void* x, void* const* ys, int accumulate,
+                                 uint32_t* status_word, cq_stream_t stream) {
+  if (!layers || !ys || !x || n_layers < 1 || n_layers > RV_MAX_SEG) return CQ_ERR_BAD_ARG;
+  if ((uintptr_t)x & 1) return CQ_ERR_BAD_ARG;
+  __half* yp[RV_MAX_SEG];
+  for (int i = 0; i < n_layers; ++i) {
+    if (!layers[i] || !layers[i]->blob || !ys[i] || ((uintptr_t)ys[i] & 1)) return CQ_ERR_BAD_ARG;
+    yp[i] = (__half*)ys[i];
+  }
+  const cq_rlayer* L = layers[0];
+  const __half* xp = (const __half*)x;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (rv_gpw_for(L)) {
+    case 2: return rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, yp, accumulate, status_word, st);
+    case 4: return rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, yp, accumulate, status_word, st);
+    case 7: return rv_launch(rv_pick<RV_W, 7>(L->bits, L->sets), RV_W, 7, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, yp, accumulate, status_word, st);
+    default: return CQ_ERR_UNSUPPORTED;
+  }
 }
 
 extern "C" int cq_rlayer_matvec(const cq_rlayer* L, const void* x, void* y, int accumulate, uint32_t* status_word,
                                 cq_stream_t stream) {
-  if (!L || !L->blob || !x || !y) return CQ_ERR_BAD_ARG;
-  if (((uintptr_t)x & 1) || ((uintptr_t)y & 1)) return CQ_ERR_BAD_ARG;
-  const __half* xp = (const __half*)x;
-  __half* yp = (__half*)y;
+  return cq_rlayers_matvec(&L, 1, x, &y, accumulate, status_word, stream);
+}
+
+extern "C" int cq_rlayer_matvec_host(const cq_rlayer* L, const void* x_host, void* y_host, void* x_dev, void* y_dev,
+                                     uint32_t* status_word, cq_stream_t stream) {
+  if (!L || !x_host || !y_host || !x_dev || !y_dev) return CQ_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
-  switch (rv_gpw_for(L)) {
-    case 2: return rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, L, xp, yp, accumulate, status_word, st);
-    case 4: return rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, L, xp, yp, accumulate, status_word, st);
-    case 7: return rv_launch(rv_pick<RV_W, 7>(L->bits, L->sets), RV_W, 7, CQ_ROWVEC_INFLIGHT, 0, L, xp, yp, accumulate, status_word, st);
-    default: return CQ_ERR_UNSUPPORTED;
-  }
+  CQ_CUDA_TRY(cudaMemcpyAsync(x_dev, x_host, (size_t)L->K * sizeof(__half), cudaMemcpyHostToDevice, st));
+  const int rc = cq_rlayer_matvec(L, x_dev, y_dev, 0, status_word, stream);
+  if (rc != CQ_OK) return rc;
+  CQ_CUDA_TRY(cudaMemcpyAsync(y_host, y_dev, (size_t)L->N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+  CQ_CUDA_TRY(cudaStreamSynchronize(st));
+  return CQ_OK;
 }
 
 #ifdef CQ_ROWVEC_SWEEP
 // Tuning build only (not part of the library): a table of kernel shapes behind one entry point.
 #define RV_CASE(id, W, GPW, SMEM_KB, INFL) \
-  case id: return rv_launch(rv_pick<W, GPW>(L->bits, L->sets), W, GPW, INFL, SMEM_KB, L, (const __half*)x, (__half*)y, accumulate, status_word, (cudaStream_t)stream);
+  case id: { __half* yv = (__half*)y; return rv_launch(rv_pick<W, GPW>(L->bits, L->sets), W, GPW, INFL, SMEM_KB, &L, 1, (const __half*)x, &yv, accumulate, status_word, (cudaStream_t)stream); }
 extern "C" int cq_rlayer_matvec_variant(int variant, const cq_rlayer* L, const void* x, void* y, int accumulate,
                                         uint32_t* status_word, cq_stream_t stream) {
   switch (variant) {

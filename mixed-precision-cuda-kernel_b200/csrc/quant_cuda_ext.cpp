@@ -354,6 +354,28 @@ struct RowLayer {
   }
 };
 
+// One launch for several row-tile layers that take the same activation row (q / k / v, gate / up):
+// outs[i] (1, N_i) fp16 = [outs[i] +] x (1, K) fp16 . W_i^T
+void row_layers_matvec(std::vector<RowLayer*> layers, torch::Tensor x, std::vector<torch::Tensor> outs, bool accumulate) {
+  TORCH_CHECK(!layers.empty() && layers.size() <= 4 && layers.size() == outs.size(), "1 to 4 layers, one output each");
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(x));
+  check_tensor(x, "x", torch::kFloat16, layers[0]->blob);
+  TORCH_CHECK(x.numel() == layers[0]->layer.K, "x must hold one row of ", layers[0]->layer.K, " activations");
+  const cq_rlayer* ls[4];
+  void* ys[4];
+  for (size_t i = 0; i < layers.size(); ++i) {
+    check_tensor(outs[i], "out", torch::kFloat16, layers[0]->blob);
+    TORCH_CHECK(outs[i].numel() == layers[i]->layer.N, "out ", i, " must hold one row of ", layers[i]->layer.N, " values");
+    ls[i] = &layers[i]->layer;
+    ys[i] = outs[i].data_ptr();
+  }
+  auto scratch = scratch_for(x.device());
+  uint8_t* sp = scratch.data_ptr<uint8_t>();
+  check_status(cq_rlayers_matvec(ls, (int)layers.size(), x.data_ptr(), ys, accumulate ? 1 : 0,
+                                 (uint32_t*)(sp + cq_scratch_bytes()), current_stream()),
+               "row_layers_matvec");
+}
+
 // Reads and clears the status word the PreparedLayer launches report into.
 bool device_timed_out(int device_index) {
   torch::Tensor t;
@@ -473,6 +495,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_decode", &attn_decode, "single-query attention over the KV cache");
   m.def("poll", []() { check_status(cq_poll(current_stream()), "poll"); });
   m.def("device_timed_out", &device_timed_out);
+  m.def("row_layers_matvec", &row_layers_matvec, "one launch for row-tile layers sharing an activation row");
   m.def("abi_version", &cq_abi_version);
   py::class_<RowLayer>(m, "RowLayer")
       .def(py::init<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int, int, int>())

@@ -37,7 +37,7 @@ import torch
 import torch.nn.functional as F
 
 from . import load_quant_cuda
-from .qlinear import QuantLinear
+from .qlinear import QuantLinear, forward_shared_input
 
 
 @dataclass
@@ -164,6 +164,12 @@ class CherryDecoder:
             return F.linear(x, ql.dense_weight)
         return ql(x)
 
+    def _lins(self, lay, names, x: torch.Tensor):
+        """The projections `names` of one layer on the same input: one launch where the kernel allows."""
+        if self.dense:
+            return [F.linear(x, lay[n].dense_weight) for n in names]
+        return forward_shared_input([lay[n] for n in names], x)
+
     def _gather(self, x: torch.Tensor) -> torch.Tensor:
         """(t, n_local) slices of all ranks -> (t, tp * n_local), in rank order."""
         if self.tp == 1:
@@ -189,9 +195,8 @@ class CherryDecoder:
         cfg, lay = self.cfg, self.layers[li]
         t, nh, kv, hd = h.shape[0], self.h_local, self.kv_local, cfg.head_dim
         xn, h = self._norm(h, delta, lay["norm1"])
-        q = self._lin(lay["q"], xn).view(t, nh, hd)
-        k = self._lin(lay["k"], xn).view(t, kv, hd)
-        v = self._lin(lay["v"], xn).view(t, kv, hd)
+        q, k, v = self._lins(lay, ("q", "k", "v"), xn)
+        q, k, v = q.view(t, nh, hd), k.view(t, kv, hd), v.view(t, kv, hd)
         self.qc.rope_cache(q, k, v, self.cos, self.sin, pos, self.k_cache[li], self.v_cache[li])
         if decode:
             a = self.qc.attn_decode(q, self.k_cache[li], self.v_cache[li], pos).view(t, nh * hd)
@@ -200,7 +205,8 @@ class CherryDecoder:
                                                v.transpose(0, 1)[None], is_causal=True, enable_gqa=(kv != nh))
             a = a[0].transpose(0, 1).reshape(t, nh * hd)
         xn, h = self._norm(h, self._gather(self._lin(lay["o"], self._gather(a))), lay["norm2"])
-        act = self.qc.silu_mul(self._lin(lay["gate"], xn), self._lin(lay["up"], xn))
+        gate, up = self._lins(lay, ("gate", "up"), xn)
+        act = self.qc.silu_mul(gate, up)
         return h, self._gather(self._lin(lay["down"], self._gather(act)))
 
     def _logits(self, h: torch.Tensor, delta) -> torch.Tensor:

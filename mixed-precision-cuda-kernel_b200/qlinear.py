@@ -205,3 +205,35 @@ class QuantLinear(nn.Module):
         if self.bias is not None:
             out += self.bias
         return out
+
+
+def forward_shared_input(layers, x: torch.Tensor):
+    """Outputs of several packed layers applied to the same input (q / k / v, gate / up of the
+    reference's LLaMA, llama/modeling_llama_quant.py): for one activation row and layers that agree
+    in bits, in_features, cherry count and group size this is ONE launch of the one-row kernel with
+    the SMs divided among the layers; every other case is the layers' own forward, one by one.
+    The results are bit-identical to the separate calls either way."""
+    layers = list(layers)
+    first = layers[0]
+    rows = x.numel() // x.shape[-1]
+    same = all((l.w_bits, l.in_features, l.num_cherries, l.group_size) ==
+               (first.w_bits, first.in_features, first.num_cherries, first.group_size) for l in layers)
+    if (rows == 1 and 1 < len(layers) <= 4 and same and QuantLinear._layerwise_dequantize
+            and first.w_bits in (3, 4)):
+        rls = [l.row_layer() for l in layers]
+        if all(r is not None for r in rls):
+            qc = load_quant_cuda()
+            x2 = x.reshape(1, x.shape[-1])
+            if x2.dtype != torch.float16:
+                x2 = x2.half()
+            x2 = x2.contiguous()
+            outs = [torch.empty(1, l.out_features, dtype=torch.float16, device=x2.device) for l in layers]
+            qc.row_layers_matvec(rls, x2, outs, False)
+            res = []
+            for l, o in zip(layers, outs):
+                o = o.reshape(x.shape[:-1] + (l.out_features,)).to(x.dtype)
+                if l.bias is not None:
+                    o += l.bias
+                res.append(o)
+            return res
+    return [l(x) for l in layers]

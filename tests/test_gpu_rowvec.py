@@ -263,3 +263,101 @@ def test_outlier_channels(cabi, bits, scale):
         assert rel_err(y, ref) <= TIGHT_TOL, (where, scale, bits)
         e10, e1 = elementwise_error(y, ref, 0.1), elementwise_error(y, ref, 0.01)
         assert e10 <= 2e-2 and e1 <= 2e-1, (where, scale, bits, e10, e1)
+
+
+# ------------------------------------------------------------------ several layers in one launch
+@pytest.mark.parametrize("K,Ns,bits,G", [
+    (4096, (4096, 4096, 4096), 4, 128),          # 7B q / k / v
+    (4096, (11008, 11008), 4, 128),              # 7B gate / up
+    (8192, (8192, 1024, 1024), 3, 128),          # 70B q / k / v (grouped-query heads: small k, v)
+    (5120, (13824, 13824), 3, 128),              # 13B gate / up
+    (1024, (48, 16, 8, 200), 3, 64),             # four small ragged layers, fewer tiles than SMs
+    (2048, (4096, 24), 4, 128),                  # very uneven
+])
+def test_shared_input_launch_is_bit_identical_to_separate_launches(cabi, K, Ns, bits, G):
+    lib = cabi.lib()
+    frac = 1 / 256 if K >= 2048 else 1 / 64
+    preps = []
+    for i, N in enumerate(Ns):
+        q, s, cw, ci, _ = gpu_layer(K, N, bits, G, seed=K + N + bits + 17 * i, frac=frac)
+        preps.append(RowPrepared(cabi, q, s, cw, ci, bits, K, G))
+    x = torch.randn(1, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(K)).half()
+    want = [p.matvec(x) for p in preps]
+    outs = [torch.full((1, N), float("nan"), dtype=torch.float16, device="cuda") for N in Ns]
+    n = len(Ns)
+    layers = (C.POINTER(cabi.cq_rlayer) * n)(*[C.pointer(p.L) for p in preps])
+    ys = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cabi.check(lib.cq_rlayers_matvec(layers, n, ptr(x), ys, 0, ptr(status), None), "rlayers_matvec")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for o, w in zip(outs, want):
+        assert torch.equal(o.view(torch.int16), w.view(torch.int16))
+    # accumulate adds to what the outputs hold
+    cabi.check(lib.cq_rlayers_matvec(layers, n, ptr(x), ys, 1, ptr(status), None), "rlayers_matvec")
+    torch.cuda.synchronize()
+    for o, p, w in zip(outs, preps, want):
+        again = p.matvec(x, y=w.clone(), accumulate=True)
+        assert torch.equal(o.view(torch.int16), again.view(torch.int16))
+
+
+def test_shared_input_launch_refuses_layers_that_do_not_agree(cabi):
+    lib = cabi.lib()
+    a = RowPrepared(cabi, *gpu_layer(1024, 64, 4, 128, seed=1)[:4], 4, 1024, 128)
+    b = RowPrepared(cabi, *gpu_layer(2048, 64, 4, 128, seed=2)[:4], 4, 2048, 128)
+    c = RowPrepared(cabi, *gpu_layer(1024, 64, 3, 128, seed=3)[:4], 3, 1024, 128)
+    x = torch.zeros(1, 2048, dtype=torch.float16, device="cuda")
+    outs = [torch.zeros(1, 64, dtype=torch.float16, device="cuda") for _ in range(2)]
+    ys = (C.c_void_p * 2)(*[o.data_ptr() for o in outs])
+    for pair in ((a, b), (a, c)):
+        layers = (C.POINTER(cabi.cq_rlayer) * 2)(*[C.pointer(p.L) for p in pair])
+        assert lib.cq_rlayers_matvec(layers, 2, ptr(x), ys, 0, None, None) == 4          # CQ_ERR_BAD_SHAPE
+    layers = (C.POINTER(cabi.cq_rlayer) * 2)(C.pointer(a.L), C.pointer(a.L))
+    assert lib.cq_rlayers_matvec(layers, 5, ptr(x), ys, 0, None, None) == 1              # more than four layers
+    assert lib.cq_rlayers_matvec(layers, 0, ptr(x), ys, 0, None, None) == 1
+
+
+def test_quantlinear_shared_input_forward_matches_separate_forwards():
+    import cherryq_b200
+    from cherryq_b200.qlinear import QuantLinear, forward_shared_input
+    qc = cherryq_b200.load_quant_cuda()
+    K = 2048
+    lins = []
+    for i, N in enumerate((512, 128, 128)):
+        q, s, cw, ci, _ = gpu_layer(K, N, 4, 128, seed=40 + i)
+        lin = QuantLinear(4, 128, None, 1 / 256, K, N, bias=(i == 1)).cuda()
+        lin.qweight, lin.scales, lin.cherry_weight, lin.cherry_indices = q, s, cw, ci
+        if lin.bias is not None:
+            lin.bias = torch.randn(N, device="cuda").half()
+        lins.append(lin)
+    for rows in (1, 3):
+        x = torch.randn(rows, K, device="cuda").half()
+        together = forward_shared_input(lins, x)
+        for lin, y in zip(lins, together):
+            assert torch.equal(y, lin(x))
+
+
+def test_host_buffer_entry_point(cabi):
+    """cq_rlayer_matvec_host: activations from host memory, the output back in host memory when the call returns."""
+    lib = cabi.lib()
+    K, N = 4096, 4096
+    q, s, cw, ci, dense = gpu_layer(K, N, 4, 128, seed=77)
+    p = RowPrepared(cabi, q, s, cw, ci, 4, K, 128)
+    xh = torch.randn(1, K).half().pin_memory()
+    yh = torch.zeros(1, N, dtype=torch.float16).pin_memory()
+    xd = torch.empty(1, K, dtype=torch.float16, device="cuda")
+    yd = torch.empty(1, N, dtype=torch.float16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    for _ in range(2):
+        yh.zero_()
+        cabi.check(lib.cq_rlayer_matvec_host(C.byref(p.L), C.c_void_p(xh.data_ptr()), C.c_void_p(yh.data_ptr()), ptr(xd), ptr(yd),
+                                             ptr(status), C.c_void_p(stream.cuda_stream)), "matvec_host")
+        want = p.matvec(xh.cuda())            # no synchronisation between the call above and this read of yh is needed
+        assert torch.equal(yh, want.cpu())
+    assert int(status.item()) == 0
+    # pageable host memory works too (the copies are then staged by the driver)
+    xp, yp = xh.clone(), torch.zeros(1, N, dtype=torch.float16)
+    cabi.check(lib.cq_rlayer_matvec_host(C.byref(p.L), C.c_void_p(xp.data_ptr()), C.c_void_p(yp.data_ptr()), ptr(xd), ptr(yd),
+                                         ptr(status), None), "matvec_host")
+    assert torch.equal(yp, want.cpu())
