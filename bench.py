@@ -780,10 +780,12 @@ def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, pro
     s = torch.cuda.Stream(device=dev)
     s.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(s), torch.inference_mode():
-        def all_linears():
+        def all_linears():            # the decoder's own call pattern: q/k/v and gate/up share a launch
             for lay in model.layers:
-                for nm in model.PROJ:
-                    lay[nm](xin[model.shapes[nm][0]])
+                model._lins(lay, ("q", "k", "v"), xin[model.shapes["q"][0]])
+                lay["o"](xin[model.shapes["o"][0]])
+                model._lins(lay, ("gate", "up"), xin[model.shapes["gate"][0]])
+                lay["down"](xin[model.shapes["down"][0]])
         all_linears()
         s.synchronize()
         gl = torch.cuda.CUDAGraph()
@@ -796,6 +798,9 @@ def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, pro
     lin_ms /= 20
     with torch.inference_mode():
         h = torch.randn(1, cfg.hidden, device=dev).half()
+        for _ in range(3):
+            torch.nn.functional.linear(h, model.lm_head)
+        torch.cuda.synchronize()
         head_ms, _ = timed(lambda: [torch.nn.functional.linear(h, model.lm_head) for _ in range(50)])
     head_ms /= 50
 
@@ -834,6 +839,115 @@ def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, pro
     }
 
 
+def run_sweep(args):
+    """The three LLaMA-7B linear shapes x {4, 3} bits x batch {1, 4, 16} through the drop-in ops
+    (`quant_cuda.vecquant{3,4}matmul_cherryq`, device-resident inputs, every call a CUDA-graph node, the
+    layer rotated over more than 3x L2 of distinct copies), and the reference's own micro-benchmark case
+    (benchmark_speed.py of the reference project: fp32 activations / scales / cherries / output, int32
+    indices, 4096 -> 13824, 3-bit, batch 16, 100 calls)."""
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    peak, peak_kind = measured_peak()
+    try:
+        from oracle import build_ref
+        rmod = build_ref.load()
+    except Exception:
+        rmod = None
+    stream = torch.cuda.Stream(device=dev)
+    repeats = max(3, min(args.repeats, 20))
+    rows = []
+    for (k, n) in ((4096, 4096), (4096, 11008), (11008, 4096)):
+        for bits in (4, 3):
+            q, s, cw, ci, c = make_layer_gpu(qc, torch, k, n, bits, GROUP, 1234, dev)
+            nbytes = q.numel() + 2 * s.numel() + 2 * cw.numel()
+            ncopies = max(2, math.ceil(3 * L2_BYTES / nbytes))
+            copies = [(q, cw, ci, s)] + [tuple(t.clone() for t in (q, cw, ci, s)) for _ in range(ncopies - 1)]
+            for m in (1, 4, 16):
+                x = torch.randn(m, k, device=dev).half()
+                out = torch.zeros(m, n, dtype=torch.float16, device=dev)
+
+                def call(i, mod=qc):
+                    qq, cc, ii, ss = copies[i % ncopies]
+                    if bits == 4:
+                        mod.vecquant4matmul_cherryq(x, qq, cc, ii, ss, out, GROUP)
+                    else:
+                        mod.vecquant3matmul_cherryq(x, qq, cc, ii, ss, out, GROUP, True)
+
+                with torch.cuda.stream(stream):
+                    for i in range(ncopies + 2):       # first use builds the re-packed copies (not capturable)
+                        call(i)
+                    stream.synchronize()
+                    region = Region(torch, stream, call, 4 * ncopies, ncopies)
+                    region.run()
+                    stream.synchronize()
+                    us = median(region.time(repeats)) * 1e3 / (4 * ncopies)
+                alg = algorithmic_bytes(k, n, bits, GROUP, m, c)
+                row = {"K": k, "N": n, "bits": bits, "batch": m, "us_per_call": us, "GBps": alg / us / 1e3,
+                       "frac_of_measured_hbm": alg / us / 1e3 / peak,
+                       "route": "one-row kernel" if m == 1 else ("stream kernel" if m < 8 else "tensor-core tile GEMM")}
+                if rmod is not None and m == 1:        # the reference's kernels race in shared memory beyond batch 1
+                    torch.cuda.synchronize()
+                    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    for i in range(ncopies):
+                        call(i, rmod)
+                    r0.record()
+                    for i in range(2 * ncopies):
+                        call(i, rmod)
+                    r1.record()
+                    torch.cuda.synchronize()
+                    row["reference_kernel_us"] = r0.elapsed_time(r1) * 1e3 / (2 * ncopies)
+                rows.append(row)
+            del copies
+            qc.cache_clear()
+            torch.cuda.empty_cache()
+
+    # the reference's micro-benchmark, with its tensors and its loop of 100 calls
+    bs, kk, nn = 16, 4096, 13824
+    vec = torch.randn(bs, kk, device=dev)
+    qweight = torch.randint(1, 5, (1530, nn), dtype=torch.uint8, device=dev)
+    cherry_weight = torch.randn(16, nn, device=dev)
+    cherry_indices = torch.randperm(16, dtype=torch.int32).sort().values.to(dev)
+    scaling = torch.ones(32, nn, device=dev)
+    mul = torch.zeros(bs, nn, device=dev)
+
+    def speed_case(mod):
+        mod.vecquant3matmul_cherryq(vec, qweight, cherry_weight, cherry_indices, scaling, mul, 128, False)   # warm-up
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(100):
+            mod.vecquant3matmul_cherryq(vec, qweight, cherry_weight, cherry_indices, scaling, mul, 128, False)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / 100 * 1e6
+
+    fp32_case = {"case": "reference micro-benchmark: 4096 -> 13824, 3-bit, group 128, batch 16, fp32 in / out, 100 calls, "
+                         "host clock around the loop as the reference script does",
+                 "us_per_call": speed_case(qc)}
+    if rmod is not None:
+        fp32_case["reference_kernel_us_per_call"] = speed_case(rmod)
+    wh = torch.randn(kk, nn, device=dev).half()
+    vh = vec.half()
+    torch.matmul(vh, wh)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(100):
+        torch.matmul(vh, wh)
+    torch.cuda.synchronize()
+    fp32_case["torch_fp16_matmul_us_per_call"] = (time.perf_counter() - t0) / 100 * 1e6
+    print(json.dumps({
+        "metric": "matvec_algorithmic_GBps_sweep", "unit": "GB/s", "n_gpus": 1, "higher_is_better": True,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "llama7b_linear_shapes_x_bits_x_batch_through_the_drop_in_ops", "group": GROUP,
+                   "l2_defeat": "distinct layer copies of more than 3x L2 walked round-robin",
+                   "timing": f"median of {repeats} regions of 4 rounds over the copies, CUDA graphs only",
+                   "peak": peak, "peak_kind": peak_kind + " copy bandwidth"},
+        "rows": rows, "fp32_path": fp32_case}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -841,9 +955,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=100)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "model", "sweep"],
                     help="decode: batch-1 matvec (the headline line); prefill: 2048-token GEMM of the same layer; "
-                         "model: LLaMA-2-7B-architecture greedy decode, tokens/s")
+                         "model: LLaMA-2-7B-architecture greedy decode, tokens/s; sweep: the 7B shapes x bits x batch table "
+                         "and the reference's fp32 micro-benchmark case")
     ap.add_argument("--model", default="7b", choices=["7b", "13b", "70b"],
                     help="architecture of the model workload: LLaMA-2 7B (4-bit), 13B (3-bit) or 70B (3-bit, GQA)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
@@ -860,6 +975,8 @@ def main():
         run_prefill(args)
     elif args.workload == "model":
         run_model(args)
+    elif args.workload == "sweep":
+        run_sweep(args)
     else:
         run_ours(args)
 
