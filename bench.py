@@ -719,25 +719,26 @@ def run_model(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    line = model_measure(args, torch, dist, dev, world, rank, local, args.model, gen=256)
+    line = model_measure(args, torch, dist, dev, world, rank, local, args.model, gen=args.gen, prompt_len=args.prompt,
+                         batch=args.batch, max_seq=args.max_seq)
     if rank == 0:
         print(json.dumps(line))
     leave(torch, dist, world)
 
 
-def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, prompt_len=128):
+def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, prompt_len=128, batch=1, max_seq=512):
     """Builds the model, decodes `gen` tokens greedily after a `prompt_len`-token random prompt (one CUDA graph
     per decode step, as benchmark_perplexity.py:92-113 of the reference times its per-token loop) and returns
     the JSON record (rank 0; None elsewhere)."""
     from cherryq_b200 import decoder as D
     base = {"7b": D.LLAMA2_7B, "13b": D.LLAMA2_13B, "70b": D.LLAMA2_70B}[name]
-    cfg = D.DecoderConfig(**{**base.__dict__, "max_seq": 512})
+    cfg = D.DecoderConfig(**{**base.__dict__, "max_seq": max_seq})
     t_build = time.time()
     model = D.CherryDecoder(cfg, device=dev, seed=1234, tp_group=dist.group.WORLD if world > 1 else None,
-                            tp_gather=args.gather, release_reference_buffers=True)
+                            tp_gather=args.gather, release_reference_buffers=True, batch=batch)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
-    prompt = torch.randint(0, cfg.vocab, (prompt_len,), device=dev, generator=torch.Generator(device=dev).manual_seed(0))
+    prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), device=dev, generator=torch.Generator(device=dev).manual_seed(0))
 
     def timed(fn):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -773,10 +774,10 @@ def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, pro
         ranks_agree = bool(int(agree.item()))
         if not ranks_agree:
             raise RuntimeError("the ranks generated different tokens")
-    tok_s = gen / (gen_ms * 1e-3)
+    tok_s = gen * batch / (gen_ms * 1e-3)
 
     # the quantized projections alone, same call sequence, captured the same way
-    xin = {k: torch.randn(1, k, device=dev).half() for k in {kk for kk, _ in model.shapes.values()}}
+    xin = {k: torch.randn(batch, k, device=dev).half() for k in {kk for kk, _ in model.shapes.values()}}
     s = torch.cuda.Stream(device=dev)
     s.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(s), torch.inference_mode():
@@ -797,7 +798,7 @@ def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, pro
     lin_ms, _ = timed(lambda: [gl.replay() for _ in range(20)])
     lin_ms /= 20
     with torch.inference_mode():
-        h = torch.randn(1, cfg.hidden, device=dev).half()
+        h = torch.randn(batch, cfg.hidden, device=dev).half()
         for _ in range(3):
             torch.nn.functional.linear(h, model.lm_head)
         torch.cuda.synchronize()
@@ -814,7 +815,8 @@ def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, pro
         "ms_per_step": ms_tok, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": f"llama2_{name}_arch_{cfg.bits}bit_g128_cherry1/256_prompt{prompt_len}_greedy{gen}_batch1",
+        "config": {"workload": f"llama2_{name}_arch_{cfg.bits}bit_g128_cherry1/256_prompt{prompt_len}_greedy{gen}_batch{batch}",
+                   "batch": batch, "max_seq": max_seq,
                    "layers": cfg.n_layers, "kv_heads": cfg.n_kv_heads,
                    "hidden": cfg.hidden, "ffn": cfg.ffn, "vocab": cfg.vocab, "bits": cfg.bits,
                    "l2_defeat": f"{qbytes / 1e9:.1f} GB of quantized weights + {hbytes / 1e6:.0f} MB lm_head per token, "
@@ -835,7 +837,7 @@ def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, pro
                 "note": "the decode loop lives on the device (token ids are read back once at the end: "
                         f"{gen * 8} bytes); prompt upload {prompt_len * 8} bytes once"},
         "gpu_launches": gen * (cfg.n_layers * 7) * world, "clocks": clocks, "cpu_baseline": None,
-        "build_s": t_build, "first_tokens": [int(t) for t in toks[:8].tolist()], "ranks_agree": ranks_agree,
+        "build_s": t_build, "first_tokens": [int(t) for t in toks.reshape(gen, -1)[:8, 0].tolist()], "ranks_agree": ranks_agree,
     }
 
 
@@ -961,6 +963,10 @@ def main():
                          "and the reference's fp32 micro-benchmark case")
     ap.add_argument("--model", default="7b", choices=["7b", "13b", "70b"],
                     help="architecture of the model workload: LLaMA-2 7B (4-bit), 13B (3-bit) or 70B (3-bit, GQA)")
+    ap.add_argument("--batch", type=int, default=1, help="model workload: sequences decoded in lockstep")
+    ap.add_argument("--max-seq", type=int, default=512, help="model workload: positions of the KV cache")
+    ap.add_argument("--prompt", type=int, default=128, help="model workload: prompt tokens per sequence")
+    ap.add_argument("--gen", type=int, default=256, help="model workload: tokens generated per sequence")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="exchange step at N > 1: this library's peer-memory kernel (default) or NCCL")
     ap.add_argument("--repeats", type=int, default=50,

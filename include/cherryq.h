@@ -174,13 +174,17 @@ int cq_rlayer_unprepare(const cq_rlayer* layer, uint8_t* qweight, void* scales_f
  * return (CQ_ERR_UNSUPPORTED / CQ_ERR_TOO_LARGE); no GPU work. */
 int cq_rlayer_check(const cq_rlayer* layer);
 /* y (N) fp16 = [y +] x (K) fp16 . W^T, one activation row; allocates nothing, needs no scratch.
- * CQ_ERR_UNSUPPORTED for layers outside the kernel's envelope (K - C > 14336 columns, more than 256
+ * CQ_ERR_UNSUPPORTED for layers outside the kernel's envelope (K - C > 15360 columns, more than 240
  * cherry columns, or more than 248 cherry columns inside one warp's column range) and
  * CQ_ERR_TOO_LARGE when not even two tiles fit shared memory: use cq_layer_matvec for those.
  * status_word: device uint32 that receives CQ_ERR_DEVICE_TIMEOUT bits if a bounded wait on the
  * kernel's own bulk copies ever runs out; may be NULL. */
 int cq_rlayer_matvec(const cq_rlayer* layer, const void* x_f16, void* y_f16, int accumulate,
                      uint32_t* status_word, cq_stream_t stream);
+/* The largest batch for which cq_rlayers_matvec is the faster path for this layer (beyond it
+ * cq_tlayer_gemm is): 16 for layers of up to 8192 quantized columns, 4 for wider ones, 0 for layers
+ * the kernel does not take.  No GPU work. */
+int cq_rlayer_preferred_rows(const cq_rlayer* layer);
 /* cq_rlayer_matvec for callers that hold their activations in HOST memory (a foreign-function
  * binding with no device tensors of its own; the reference's op only takes device tensors,
  * csrc/quant_cuda.cpp:56-69): copies x_host (K fp16) to the device staging buffer x_dev, runs the
@@ -190,15 +194,20 @@ int cq_rlayer_matvec(const cq_rlayer* layer, const void* x_f16, void* y_f16, int
 int cq_rlayer_matvec_host(const cq_rlayer* layer, const void* x_host_f16, void* y_host_f16,
                           void* x_dev_f16, void* y_dev_f16, uint32_t* status_word,
                           cq_stream_t stream);
-/* One launch for up to 4 layers that take the same activation row (q / k / v, gate / up of the
+/* The general form: up to 4 layers that take the same activations (q / k / v, gate / up of the
  * reference's LLaMA, llama/modeling_llama_quant.py: LlamaAttention.forward, LlamaMLP.forward, which
- * calls them one after the other): ys[i] (N_i) fp16 = [ys[i] +] x (K) fp16 . W_i^T.  The layers must
- * agree in bits, K, cherry count and group size (CQ_ERR_BAD_SHAPE otherwise); the SMs are divided
- * among them in proportion to their rows.  Every output element is computed exactly as by
- * cq_rlayer_matvec on that layer alone (bit-identical).  Same limits and status word. */
-int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, const void* x_f16,
-                      void* const* ys_f16, int accumulate, uint32_t* status_word,
-                      cq_stream_t stream);
+ * calls them one after the other) in one launch, M >= 1 activation rows:
+ *   ys[i] (M, N_i) fp16 = [ys[i] +] x (M, K) fp16 . W_i^T,  ldx / ldy row strides in elements
+ * (ldy is shared by the outputs).  The layers must agree in bits, K, cherry count and group size
+ * (CQ_ERR_BAD_SHAPE otherwise); the SMs are divided among them in proportion to their rows.  Up to
+ * four activation rows ride in one launch (they fill the unused columns of the same integer MMAs:
+ * a row more costs about a quarter of a launch); more rows are walked in slices of four, each reading
+ * the weights again.  Layers of more than 8192 quantized columns take one row per launch.
+ * Every output element is computed exactly as by cq_rlayer_matvec on that layer and row alone
+ * (bit-identical).  Same limits and status word. */
+int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, const void* x_f16, int ldx,
+                      void* const* ys_f16, int ldy, int M, int accumulate,
+                      uint32_t* status_word, cq_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Element-wise kernels of the decode harness around the quantized linear (fp16 in / out, fp32
@@ -210,18 +219,22 @@ int cq_rmsnorm(const void* x_f16, const void* residual_f16, const void* weight_f
                void* h_out_f16, int rows, int hidden, float eps, cq_stream_t stream);
 /* Rotary embedding ("rotate half" convention) of q (T, H, D) and k (T, KV, D) in place at
  * positions[t] (device int64), tables (max_seq, D/2) fp32; k and v rows are written to the caches
- * (max_seq, KV, D) at the same positions.  A token whose position is outside [0, max_seq) is left
- * alone: nothing is read from the tables or written to the caches for it. */
+ * (sequences, max_seq, KV, D) at the same positions: token t belongs to sequence
+ * t / tokens_per_seq (a prompt of T tokens: tokens_per_seq = T; a decode step of B sequences:
+ * T = B, tokens_per_seq = 1).  A token whose position is outside [0, max_seq) is left alone:
+ * nothing is read from the tables or written to the caches for it. */
 int cq_rope_cache(void* q_f16, void* k_f16, const void* v_f16, const float* cos_table,
                   const float* sin_table, const long long* positions, void* k_cache_f16,
                   void* v_cache_f16, int T, int n_heads, int n_kv_heads, int head_dim, int max_seq,
-                  cq_stream_t stream);
-/* Single-query attention over the caches (max_seq, KV, D): out (H, D) = softmax(q . K^T * scale) . V
- * over positions 0..min(position[0], max_seq - 1) (device int64), grouped-query heads allowed; head_dim divides 256,
- * max_seq <= 8192 (the reference calls PyTorch's attention, llama/modeling_llama_quant.py:371-419). */
+                  int tokens_per_seq, cq_stream_t stream);
+/* Single-query attention over the caches (sequences, max_seq, KV, D), one query per sequence:
+ * out (sequences, H, D) = softmax(q . K^T * scale) . V over positions
+ * 0..min(position[sequence], max_seq - 1) (device int64), grouped-query heads allowed; head_dim
+ * divides 256, max_seq <= 8192 (the reference calls PyTorch's attention,
+ * llama/modeling_llama_quant.py:371-419). */
 int cq_attn_decode(const void* q_f16, const void* k_cache_f16, const void* v_cache_f16,
-                   const long long* position, void* out_f16, int n_heads, int n_kv_heads, int head_dim,
-                   int max_seq, float scale, cq_stream_t stream);
+                   const long long* position, void* out_f16, int sequences, int n_heads,
+                   int n_kv_heads, int head_dim, int max_seq, float scale, cq_stream_t stream);
 /* out = silu(gate) * up, n elements. */
 int cq_silu_mul(const void* gate_f16, const void* up_f16, void* out_f16, long long n,
                 cq_stream_t stream);

@@ -127,9 +127,20 @@ int legacy_matmul(int bits, const void* vec, const uint8_t* qweight, const void*
   if (rc) return rc;
   const CacheKey key{dev, qweight, scales, cherry_weight, cherry_indices, bits, vec_height, width,
                      cherry_size, group_size, tag};
-  if (batch >= PREFILL_MIN_ROWS)
+  // decode batches: the row-tile kernel (four activation rows per launch) up to the batch where the tile
+  // GEMM overtakes it (16 rows, 4 for wide layers); layers the row kernel does not take: the stream kernel
+  // below 8 rows
+  int row_limit = PREFILL_MIN_ROWS - 1;
+  {
+    cq_rlayer probe;
+    if (cq_rlayer_init(&probe, bits, vec_height, width, cherry_size, group_size, nullptr) == CQ_OK) {
+      const int pr = cq_rlayer_preferred_rows(&probe);
+      if (pr > 0) row_limit = pr;
+    }
+  }
+  if (batch > row_limit)
     return legacy_gemm(key, dev, vec, qweight, cherry_weight, cherry_indices, scales, mul, batch, ds.status, st);
-  if (batch == 1) {
+  {
     auto rit = g_rcache.find(key);
     if (rit == g_rcache.end()) {
       cq_rlayer R;
@@ -152,7 +163,10 @@ int legacy_matmul(int bits, const void* vec, const uint8_t* qweight, const void*
       }
     }
     if (rit != g_rcache.end())
-      return cq_rlayer_matvec(&rit->second, vec, mul, /*accumulate=*/1, ds.status, st);
+    {
+      const cq_rlayer* R = &rit->second;
+      return cq_rlayers_matvec(&R, 1, vec, vec_height, &mul, width, batch, /*accumulate=*/1, ds.status, st);
+    }
   }
   auto it = g_cache.find(key);
   if (it == g_cache.end()) {
@@ -181,7 +195,7 @@ int legacy_matmul(int bits, const void* vec, const uint8_t* qweight, const void*
 void cq_set_cuda_error(int err) { g_last_cuda_error = err; }
 
 extern "C" int cq_last_cuda_error(void) { return g_last_cuda_error; }
-extern "C" int cq_abi_version(void) { return 2; }
+extern "C" int cq_abi_version(void) { return 3; }
 
 extern "C" const char* cq_strerror(int status) {
   switch (status) {

@@ -74,11 +74,13 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const __half* __restrict_
 }
 
 // Rotary embedding ("rotate half" convention) of q (T, H, D) and k (T, KV, D) in place at positions
-// pos[t], and the write of k, v rows into the caches (max_seq, KV, D).
+// pos[t], and the write of k, v rows into the caches (sequences, max_seq, KV, D): token t belongs to
+// sequence t / tokens_per_seq.
 __global__ void rope_cache_kernel(__half* __restrict__ q, __half* __restrict__ k, const __half* __restrict__ v,
                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                   const long long* __restrict__ pos, __half* __restrict__ k_cache,
-                                  __half* __restrict__ v_cache, int T, int H, int KV, int D, int max_seq) {
+                                  __half* __restrict__ v_cache, int T, int H, int KV, int D, int max_seq,
+                                  int tokens_per_seq) {
   // programmatic dependent launch: let the next kernel start its prologue, then wait for our inputs
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -91,6 +93,7 @@ __global__ void rope_cache_kernel(__half* __restrict__ q, __half* __restrict__ k
     const int t = (int)(id / ((long long)half * (H + 2 * KV)));
     const long long p = pos[t];
     if (p < 0 || p >= max_seq) continue;      // a position outside the tables and caches: nothing is read or written
+    const size_t crow = (size_t)(t / tokens_per_seq) * max_seq + (size_t)p;     // row of the caches
     if (hh < H + KV) {
       __half* base = hh < H ? q + ((size_t)t * H + hh) * D : k + ((size_t)t * KV + (hh - H)) * D;
       const float c = cos_t[p * half + i], s = sin_t[p * half + i];
@@ -99,14 +102,14 @@ __global__ void rope_cache_kernel(__half* __restrict__ q, __half* __restrict__ k
       base[i] = o1;
       base[i + half] = o2;
       if (hh >= H) {
-        __half* kc = k_cache + ((size_t)p * KV + (hh - H)) * D;
+        __half* kc = k_cache + (crow * KV + (hh - H)) * D;
         kc[i] = o1;
         kc[i + half] = o2;
       }
     } else {
       const int kvh = hh - H - KV;
       const __half* src = v + ((size_t)t * KV + kvh) * D;
-      __half* vc = v_cache + ((size_t)p * KV + kvh) * D;
+      __half* vc = v_cache + (crow * KV + kvh) * D;
       vc[i] = src[i];
       vc[i + half] = src[i + half];
     }
@@ -125,7 +128,8 @@ __global__ void silu_mul_kernel(const __half* __restrict__ gate, const __half* _
   }
 }
 
-// Single-query attention over the KV cache (decode): one CTA per query head.  Positions 0..pos[0]
+// Single-query attention over the KV cache (decode): one CTA per query head and sequence (blockIdx.y);
+// q and out are (sequences, H, D), the caches (sequences, max_seq, KV, D).  Positions 0..pos[sequence]
 // take part (pos is read on the device, so the same launch serves every step of a captured graph).
 // Scores and the weighted sum are fp32; softmax over at most `max_seq` positions held in shared memory.
 constexpr int ATT_THREADS = 1024, ATT_WARPS = ATT_THREADS / 32;
@@ -139,11 +143,15 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   extern __shared__ float sc[];              // [n_pos] scores, then [ATT_THREADS] reduction scratch
-  const int head = blockIdx.x, kvh = head / (H / KV);
+  const int head = blockIdx.x, kvh = head / (H / KV), seq = blockIdx.y;
+  q += (size_t)seq * H * D;
+  out += (size_t)seq * H * D;
+  k_cache += (size_t)seq * max_seq * KV * D;
+  v_cache += (size_t)seq * max_seq * KV * D;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // positions beyond the cache are not attended to (the host refuses such steps; this keeps a stray
   // launch inside its shared-memory score array and the caches)
-  const long long p0 = pos[0];
+  const long long p0 = pos[seq];
   const int n_pos = p0 < 0 ? 1 : (p0 >= max_seq ? max_seq : (int)p0 + 1);
   float* red = sc + n_pos;
   const __half* qh = q + (size_t)head * D;
@@ -265,13 +273,14 @@ extern "C" int cq_rmsnorm(const void* x, const void* residual, const void* weigh
 
 extern "C" int cq_rope_cache(void* q, void* k, const void* v, const float* cos_table, const float* sin_table,
                              const long long* positions, void* k_cache, void* v_cache, int T, int n_heads,
-                             int n_kv_heads, int head_dim, int max_seq, cq_stream_t stream) {
+                             int n_kv_heads, int head_dim, int max_seq, int tokens_per_seq, cq_stream_t stream) {
+  if (tokens_per_seq < 1 || T % tokens_per_seq) return CQ_ERR_BAD_ARG;
   if (!q || !k || !v || !cos_table || !sin_table || !positions || !k_cache || !v_cache) return CQ_ERR_BAD_ARG;
   if (T < 1 || n_heads < 1 || n_kv_heads < 1 || head_dim < 2 || (head_dim & 1) || max_seq < 1) return CQ_ERR_BAD_ARG;
   const long long total = (long long)T * (n_heads + 2 * n_kv_heads) * (head_dim / 2);
   CQ_CUDA_TRY(launch_pdl(rope_cache_kernel, dim3(blocks_for(total, 256, 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
                          (__half*)q, (__half*)k, (const __half*)v, cos_table, sin_table, positions, (__half*)k_cache,
-                         (__half*)v_cache, T, n_heads, n_kv_heads, head_dim, max_seq));
+                         (__half*)v_cache, T, n_heads, n_kv_heads, head_dim, max_seq, tokens_per_seq));
   return CQ_OK;
 }
 
@@ -283,14 +292,14 @@ extern "C" int cq_silu_mul(const void* gate, const void* up, void* out, long lon
 }
 
 extern "C" int cq_attn_decode(const void* q, const void* k_cache, const void* v_cache, const long long* position,
-                              void* out, int n_heads, int n_kv_heads, int head_dim, int max_seq, float scale,
-                              cq_stream_t stream) {
-  if (!q || !k_cache || !v_cache || !position || !out) return CQ_ERR_BAD_ARG;
+                              void* out, int sequences, int n_heads, int n_kv_heads, int head_dim, int max_seq,
+                              float scale, cq_stream_t stream) {
+  if (!q || !k_cache || !v_cache || !position || !out || sequences < 1 || sequences > 65535) return CQ_ERR_BAD_ARG;
   if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads || head_dim < 2 || head_dim > 256 || (head_dim & 1) ||
       256 % head_dim || max_seq < 1 || max_seq > 8192)
     return CQ_ERR_BAD_SHAPE;
   const int smem = (max_seq + ATT_THREADS) * (int)sizeof(float);
-  CQ_CUDA_TRY(launch_pdl(attn_decode_kernel, dim3(n_heads), dim3(ATT_THREADS), (size_t)smem, (cudaStream_t)stream,
+  CQ_CUDA_TRY(launch_pdl(attn_decode_kernel, dim3(n_heads, sequences), dim3(ATT_THREADS), (size_t)smem, (cudaStream_t)stream,
                          (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, position, (__half*)out, n_heads,
                          n_kv_heads, head_dim, max_seq, scale));
   return CQ_OK;

@@ -41,7 +41,8 @@ namespace {
 constexpr uint32_t RV_WAIT_LIMIT = 1u << 22;
 constexpr int RV_MAX_SLOTS = 16;            // ring slots (tiles resident in shared memory at a time)
 
-constexpr int RV_MAX_SEG = 4;               // layers one launch can serve (they share the activation row)
+constexpr int RV_MAX_SEG = 4;               // layers one launch can serve (they share the activations)
+constexpr int RV_MAX_ROWS = 4;              // activation rows one launch can serve (two MMA columns each)
 
 // One layer of a launch: a range of CTAs works on it.
 struct RowvecSeg {
@@ -58,6 +59,7 @@ struct RowvecParams {
   RowvecSeg seg[RV_MAX_SEG];
   int nseg;
   const __half* x;
+  int M, ldx, ldy;          // activation rows of the call (1..4) and the row strides of x and y, in elements
   uint32_t* status;         // may be null
   int K, C, NG, ncb;        // common to the layers of a launch; ncb = cherry blocks of 16 columns
   int tile_bytes, scal_off, cher_off;
@@ -176,7 +178,8 @@ __device__ __forceinline__ void issue_tile(const RowvecParams& p, const uint8_t*
 // one warp that only issues the bulk copies (a bulk copy instruction blocks its thread while
 // the copy queue is full, i.e. for most of the streaming time: that thread must not have other
 // work); GPW groups of 128 columns a warp can own (its activations stay in 8 * GPW registers).
-template <int BITS, int SETS, int W, int GPW>
+// MR = 1: one activation row (the row loop below collapses); MR = 4: p.M rows, 1..4.
+template <int BITS, int SETS, int W, int GPW, int MR>
 __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const RowvecParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
@@ -284,31 +287,65 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   const bool owns_tail = ngw > 0 && gstart + ngw == NG;     // the warp whose last group may hold padding columns
   int ccol = -1;
   if (has_cherry && lane < 16 && warp * 16 + lane < p.C) ccol = sg.cidx[warp * 16 + lane];
-  const bool x_aligned = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+  const bool x_aligned = ((reinterpret_cast<uintptr_t>(p.x) | (uintptr_t)(p.ldx * 2)) & 15) == 0;
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   RV_STAMP(2);
 
-  // ---- the warp's slice of x -> its shared-memory slice (coalesced 16-byte loads), cherry activations.
-  uint32_t xcv = 0;
+  // What a lane keeps of the activations.  The integer MMA's B operand has 8 columns: column 2 m holds
+  // the high plane of activation row m, column 2 m + 1 its low plane, so up to four rows ride in the MMAs
+  // one row needs.  A lane's B column is g8 (it holds the planes of row g8 >> 1), and the sums it gets back
+  // are those of row t4: sx16 / cq are row t4's terms.
+  float sx16[GPW], cq[GPW][SETS];
+  uint32_t xb[GPW][8];
+  uint32_t cb0 = 0, cb1 = 0;
+#pragma unroll
+  for (int gi = 0; gi < GPW; ++gi) {
+    sx16[gi] = 0.f;
+#pragma unroll
+    for (int s = 0; s < SETS; ++s) cq[gi][s] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xb[gi][e] = 0u;
+  }
+
+  const int Mrows = MR == 1 ? 1 : p.M;
+  // ---- the warp's slice of row m -> its shared-memory slice (coalesced 16-byte loads), cherry activations.
+  // The loads of row m + 1 are in flight while row m is gathered and quantised.
+  uint4 xv[XCH];
+  uint32_t xcv_next = 0;
   if (x_aligned) {
-    uint4 xv[XCH];
 #pragma unroll
     for (int c = 0; c < XCH; ++c) {
       const int ch = lane + 32 * c;
       xv[c] = make_uint4(0, 0, 0, 0);
       if (ch < nchunk) xv[c] = __ldcg(reinterpret_cast<const uint4*>(p.x + lo8) + ch);
     }
-    if (ccol >= 0) xcv = (uint32_t)__half_as_ushort(__ldcg(p.x + ccol));
+  }
+  if (ccol >= 0) xcv_next = (uint32_t)__half_as_ushort(__ldcg(p.x + ccol));
+#pragma unroll 1
+  for (int m = 0; m < Mrows; ++m) {
+  const uint32_t xcv = xcv_next;
+  if (x_aligned) {
 #pragma unroll
     for (int c = 0; c < XCH; ++c) {
       const int ch = lane + 32 * c;
       if (ch < nchunk) reinterpret_cast<uint4*>(slice)[ch] = xv[c];
     }
   } else {
-    if (ccol >= 0) xcv = (uint32_t)__half_as_ushort(__ldcg(p.x + ccol));
-    for (int i = lane; i < nchunk * 8; i += 32) slice[i] = p.x[lo8 + i];
+    const __half* xr = p.x + (size_t)m * p.ldx;
+    for (int i = lane; i < nchunk * 8; i += 32) slice[i] = xr[lo8 + i];
+  }
+  if (MR > 1 && m + 1 < Mrows) {
+    const __half* xn = p.x + (size_t)(m + 1) * p.ldx;
+    if (x_aligned) {
+#pragma unroll
+      for (int c = 0; c < XCH; ++c) {
+        const int ch = lane + 32 * c;
+        if (ch < nchunk) xv[c] = __ldcg(reinterpret_cast<const uint4*>(xn + lo8) + ch);
+      }
+    }
+    if (ccol >= 0) xcv_next = (uint32_t)__half_as_ushort(__ldcg(xn + ccol));
   }
   if (owns_tail && lane == 0) slice[p.K - lo8] = __float2half(0.f);   // zero slot for padding columns
   __syncwarp();
@@ -323,38 +360,44 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
     for (int i = 0; i < 4; ++i) {
       const uint32_t a = *reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(slice) + (pw[i] & 0xFFFFu));
       const uint32_t b = *reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(slice) + (pw[i] >> 16));
-      xg[u][i] = a | (b << 16);
+      xg[u][i] = __byte_perm(a, b, 0x5410);
     }
   }
   __syncwarp();
   // ---- quantise: one step size per group (16 consecutive lanes), two signed-byte planes, stored
   // where the B-fragment lanes pick them up with two 16-byte loads per group
-  float sx16[GPW], cq[GPW][SETS];
 #pragma unroll
   for (int u = 0; u < PVW; ++u) {
     const int ol = lane + 32 * u;
     float v[8];
-    float m = 0.f;
+    float mx = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xg[u][i]));
       v[2 * i] = f.x;
       v[2 * i + 1] = f.y;
-      m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+      mx = fmaxf(mx, fmaxf(fabsf(f.x), fabsf(f.y)));
     }
 #pragma unroll
-    for (int s = 1; s < 16; s <<= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, s));
-    const float step = m * (1.0f / 16256.0f);
-    const float inv = m > 0.f ? __fdividef(16256.0f, m) : 0.f;
+    for (int s = 1; s < 16; s <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, s));
+    const float step = mx * (1.0f / 16256.0f);
+    const float inv = mx > 0.f ? __fdividef(16256.0f, mx) : 0.f;
+    // q = rint(v * inv) as 128 hi + lo with hi = rint(q / 128) in [-127, 127], lo in [-64, 64], all in
+    // fp32 on the (full-rate) FMA pipe: adding 1.5 * 2^23 rounds to an integer and leaves it in the low
+    // mantissa bits, so the low byte of the float's bit pattern is the signed byte wanted; no
+    // float-to-int conversions, no integer arithmetic.  Any exact split q = 128 hi + lo gives the
+    // same integer sums downstream.
+    constexpr float MAGIC = 12582912.0f;
     uint32_t hi[8], lo[8];
-    int sq = 0;
+    float sq = 0.f;                                  // sums of q stay exact in fp32 (< 2^24)
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const int q = __float2int_rn(v[i] * inv);     // |q| <= 16256 + 1 (approximate reciprocal): hi, lo still fit
-      const int t = q + 64;
-      hi[i] = (uint32_t)(t >> 7);                    // floor((q + 64) / 128) in [-127, 127]
-      lo[i] = (uint32_t)((t & 127) - 64);            // q - 128 hi in [-64, 63]
-      sq += q;
+      const float qf = fmaf(v[i], inv, MAGIC) - MAGIC;          // |q| <= 16256 + 1 (approximate reciprocal)
+      const float hm = fmaf(qf, 1.0f / 128.0f, MAGIC);
+      const float lm = fmaf(hm - MAGIC, -128.0f, qf) + MAGIC;
+      hi[i] = __float_as_uint(hm);
+      lo[i] = __float_as_uint(lm);
+      sq += qf;
     }
     uint32_t hw[2], lw[2];
 #pragma unroll
@@ -366,8 +409,8 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
     sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 1);
     sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 2);
     sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 4);
-    const int sq_other = __shfl_xor_sync(0xFFFFFFFFu, sq, 8);
-    const int sq_a = (lane & 8) ? sq_other : sq, sq_b = (lane & 8) ? sq : sq_other;   // first / second half
+    const float sq_other = __shfl_xor_sync(0xFFFFFFFFu, sq, 8);
+    const float sq_a = (lane & 8) ? sq_other : sq, sq_b = (lane & 8) ? sq : sq_other;   // first / second half
     if (ol < ngw * 16) {
       // word wI (columns 4 wI .. 4 wI + 3 of the group) goes to [plane][t = wI & 3][chunk wI >> 3][(wI >> 2) & 1]
       const int gi = ol >> 4, oo = ol & 15;
@@ -380,44 +423,49 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
         gp[32 + pos] = lw[k];
       }
     }
-    // every lane keeps the terms of both groups of this round (lanes 0-15: group 2u, 16-31: group 2u + 1)
+    // the lanes that will receive row m's sums keep its terms of both groups of this round
+    // (lanes 0-15 quantised group 2u, lanes 16-31 group 2u + 1)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       if (2 * u + h < GPW) {
         const float st = __shfl_sync(0xFFFFFFFFu, step, 16 * h);
-        const int qa = __shfl_sync(0xFFFFFFFFu, sq_a, 16 * h), qb = __shfl_sync(0xFFFFFFFFu, sq_b, 16 * h);
-        sx16[2 * u + h] = st * (1.0f / 16.0f);
-        if (SETS == 2) {
-          cq[2 * u + h][0] = -OFF * st * (float)qa;
-          cq[2 * u + h][SETS - 1] = -OFF * st * (float)qb;
-        } else {
-          cq[2 * u + h][0] = -OFF * st * (float)(qa + qb);
+        const float qa = __shfl_sync(0xFFFFFFFFu, sq_a, 16 * h), qb = __shfl_sync(0xFFFFFFFFu, sq_b, 16 * h);
+        if (t4 == m) {
+          sx16[2 * u + h] = st * (1.0f / 16.0f);
+          if (SETS == 2) {
+            cq[2 * u + h][0] = -OFF * st * qa;
+            cq[2 * u + h][SETS - 1] = -OFF * st * qb;
+          } else {
+            cq[2 * u + h][0] = -OFF * st * (qa + qb);
+          }
         }
       }
     }
   }
   __syncwarp();
-  // B fragments: lanes 0-3 carry the hi plane (column 0 of B), lanes 4-7 the lo plane (column 1)
-  uint32_t xb[GPW][8];
+  // B fragments of row m: lanes with g8 == 2 m take the high plane, g8 == 2 m + 1 the low plane
+  const bool mine = (g8 >> 1) == m;
 #pragma unroll
   for (int gi = 0; gi < GPW; ++gi) {
-    uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
-    if (lane < 8 && gi < ngw) {
-      const uint4* src = reinterpret_cast<const uint4*>(plane + gi * 64 + g8 * 32 + t4 * 8);
-      a = src[0];
-      b = src[1];
+    if (mine && gi < ngw) {
+      const uint4* src = reinterpret_cast<const uint4*>(plane + gi * 64 + (g8 & 1) * 32 + t4 * 8);
+      const uint4 a = src[0], b = src[1];
+      xb[gi][0] = a.x; xb[gi][1] = a.y; xb[gi][2] = a.z; xb[gi][3] = a.w;
+      xb[gi][4] = b.x; xb[gi][5] = b.y; xb[gi][6] = b.z; xb[gi][7] = b.w;
     }
-    xb[gi][0] = a.x; xb[gi][1] = a.y; xb[gi][2] = a.z; xb[gi][3] = a.w;
-    xb[gi][4] = b.x; xb[gi][5] = b.y; xb[gi][6] = b.z; xb[gi][7] = b.w;
   }
-  // cherry B fragment: b0 = x_c[2t], x_c[2t + 1]; b1 = x_c[8 + 2t], x_c[9 + 2t] in lanes 0-3
-  uint32_t cb0 = 0, cb1 = 0;
+  // cherry B fragment (16 x 8 halves, column 2 m = row m's cherry activations, odd columns zero):
+  // b0 = x_c[2t], x_c[2t + 1]; b1 = x_c[8 + 2t], x_c[9 + 2t]
   if (has_cherry) {
     const uint32_t v0 = __shfl_sync(0xFFFFFFFFu, xcv, 2 * t4), v1 = __shfl_sync(0xFFFFFFFFu, xcv, 2 * t4 + 1);
     const uint32_t v2 = __shfl_sync(0xFFFFFFFFu, xcv, 8 + 2 * t4), v3 = __shfl_sync(0xFFFFFFFFu, xcv, 9 + 2 * t4);
-    cb0 = lane < 4 ? (v0 | (v1 << 16)) : 0u;
-    cb1 = lane < 4 ? (v2 | (v3 << 16)) : 0u;
+    if (g8 == 2 * m) {
+      cb0 = v0 | (v1 << 16);
+      cb1 = v2 | (v3 << 16);
+    }
   }
+  __syncwarp();                                       // the next row re-uses the slice
+  }   // activation rows
   RV_STAMP(3);
 
   // ---- tiles.  Addresses: one base per kind (codes, scales, cherry, partial sums) computed here,
@@ -426,7 +474,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   const unsigned char* gq0 = stiles + (size_t)gstart * GRP_BYTES + 512 + lane * (BITS == 4 ? 16 : 8);
   const unsigned char* sp0 = stiles + p.scal_off + (gstart * SETS * 8 + g8) * 4;
   const unsigned char* cp0 = stiles + p.cher_off + warp * 512 + lane * 16;
-  float* pp = part + warp * 16 + g8;
+  float* pp = part + (warp * Mrows + t4) * 16 + g8;
   int slot = 0;
   uint32_t slot_off = 0, phase = 0;
 #pragma unroll 1
@@ -497,11 +545,11 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
 #ifdef CQ_ROWVEC_TRACE
     if (i < 3) RV_STAMP(13 + i);
 #endif
-    if (t4 == 0) {
+    if (t4 < Mrows) {                                        // the sums of activation row t4
       pp[0] = acc0;
       pp[8] = acc1;
     }
-    pp += W * 16;
+    pp += W * Mrows * 16;
     if (i + S < nt) {
       // ring: this warp is done with the slot; the copy warp refills it once every warp is
       __syncwarp();
@@ -518,14 +566,18 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   const int row0 = tile0 * 16;
   __half* y = sg.y;
   const int N = sg.N;
-  for (int rr = tid; rr < nt * 16; rr += NTHR) {
-    const int row = row0 + rr;
+  const int M = MR == 1 ? 1 : p.M;
+  for (int idx = tid; idx < nt * 16 * M; idx += NTHR) {
+    const int tl = idx / (16 * M), rem = idx - tl * 16 * M;
+    const int m = rem >> 4, r = rem & 15;
+    const int row = row0 + tl * 16 + r;
     if (row < N) {
-      const float* pp = part + (size_t)(rr >> 4) * W * 16 + (rr & 15);
-      float acc = p.accumulate ? __half2float(y[row]) : 0.f;
+      const float* pp = part + ((size_t)tl * W * M + m) * 16 + r;
+      __half* yo = y + (size_t)m * p.ldy + row;
+      float acc = p.accumulate ? __half2float(*yo) : 0.f;
 #pragma unroll
-      for (int w = 0; w < W; ++w) acc += pp[w * 16];
-      y[row] = __float2half_rn(acc);
+      for (int w = 0; w < W; ++w) acc += pp[w * M * 16];
+      *yo = __float2half_rn(acc);
     }
   }
   RV_STAMP(5);
@@ -736,19 +788,37 @@ RvDevice rv_device(int dev) {
 
 inline int rv_align(int v, int a) { return (v + a - 1) / a * a; }
 
+// Kernel shapes of the product: working warps x groups a warp can own.  16 warps (+ the copy warp) leave
+// 96 registers per thread, which holds the activations of up to 4 groups; wider layers take 15 warps
+// (16 in all: 128 registers) owning up to 8 groups each, one activation row per launch (the staging of
+// several rows does not fit the registers beside 8 groups of activations; measured, a launch per row is
+// as fast there).  0 = no shape holds the layer.
+constexpr int RV_W = 16, RV_W_WIDE = 15, RV_GPW_WIDE = 8;
+inline int rv_gpw_for(const cq_rlayer* L) {
+  const int need = (L->NG + RV_W - 1) / RV_W;
+  if (need <= 2) return 2;
+  if (need <= 4) return 4;
+  return (L->NG + RV_W_WIDE - 1) / RV_W_WIDE <= RV_GPW_WIDE ? RV_GPW_WIDE : 0;
+}
+inline int rv_w_for(int gpw) { return gpw == RV_GPW_WIDE ? RV_W_WIDE : RV_W; }
+
 template <int W, int GPW>
-RowvecFn rv_pick(int bits, int sets) {
-  if (bits == 4) return cq_rowvec_kernel<4, 1, W, GPW>;
-  return sets == 1 ? cq_rowvec_kernel<3, 1, W, GPW> : cq_rowvec_kernel<3, 2, W, GPW>;
+RowvecFn rv_pick(int bits, int sets, int M = 1) {
+  if (M == 1 || GPW == RV_GPW_WIDE) {          // (the wide shape exists for one row only)
+    if (bits == 4) return cq_rowvec_kernel<4, 1, W, GPW, 1>;
+    return sets == 1 ? cq_rowvec_kernel<3, 1, W, GPW, 1> : cq_rowvec_kernel<3, 2, W, GPW, 1>;
+  }
+  if (bits == 4) return cq_rowvec_kernel<4, 1, W, GPW, RV_MAX_ROWS>;
+  return sets == 1 ? cq_rowvec_kernel<3, 1, W, GPW, RV_MAX_ROWS> : cq_rowvec_kernel<3, 2, W, GPW, RV_MAX_ROWS>;
 }
 
 // Plan of one launch over `n` layers that share the activation row (same bits, K, cherry count and
 // group size, hence the same tile record size): how the CTAs are divided among the layers, the
 // shared-memory sections, the ring.  W working warps own up to GPW groups each.  Fills the launch
 // parameters that do not depend on the call.  Returns a status code.
-int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, const RvDevice& di, RowvecParams* p,
-            int* grid_out, int* smem_out) {
-  if (n < 1 || n > RV_MAX_SEG) return CQ_ERR_BAD_ARG;
+int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, int M, const RvDevice& di,
+            RowvecParams* p, int* grid_out, int* smem_out) {
+  if (n < 1 || n > RV_MAX_SEG || M < 1 || M > RV_MAX_ROWS) return CQ_ERR_BAD_ARG;
   const cq_rlayer* L = Ls[0];
   for (int i = 1; i < n; ++i)
     if (Ls[i]->bits != L->bits || Ls[i]->K != L->K || Ls[i]->C != L->C || Ls[i]->G != L->G) return CQ_ERR_BAD_SHAPE;
@@ -806,7 +876,7 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
   if (p->slice_halves < gmax * 128) p->slice_halves = gmax * 128;     // planes: 256 bytes per group
   int off = 0;
   p->off_slice = off; off = rv_align(off + W * p->slice_halves * 2, 16);
-  p->off_part = off;  off = rv_align(off + nt_max * W * 16 * 4, 16);
+  p->off_part = off;  off = rv_align(off + nt_max * W * M * 16 * 4, 16);
   p->off_bar = off;   off = rv_align(off + 2 * RV_MAX_SLOTS * 8, 128);
   p->off_tiles = off;
   int budget = di.max_smem - 1024;          // the kernel also has a small static allocation; keep clear of the limit
@@ -828,15 +898,15 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
 // One launch of a kernel whose warp count is W and whose warps can own GPW groups, over `n` layers
 // that take the same activation row x; ys[i] receives layer i's output.
 // inflight: tiles the copy warp keeps outstanding.
-int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, const __half* x,
-              __half* const* ys, int accumulate, uint32_t* status, cudaStream_t st) {
+int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, const __half* x, int ldx,
+              __half* const* ys, int ldy, int M, int accumulate, uint32_t* status, cudaStream_t st) {
   int dev = 0;
   CQ_CUDA_TRY(cudaGetDevice(&dev));
   const RvDevice di = rv_device(dev);
   if (!di.ok) return CQ_ERR_NO_DEVICE;
   RowvecParams p;
   int grid = 0, smem = 0;
-  const int rc = rv_plan(W, GPW, inflight, smem_kb, Ls, n, di, &p, &grid, &smem);
+  const int rc = rv_plan(W, GPW, inflight, smem_kb, Ls, n, M, di, &p, &grid, &smem);
   if (rc != CQ_OK) return rc;
   for (int i = 0; i < RV_MAX_SEG; ++i) {
     const int j = i < n ? i : 0;                 // unused entries repeat the first layer (never selected)
@@ -848,6 +918,7 @@ int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_r
     if (i >= n) { p.seg[i].N = 0; p.seg[i].cta0 = grid; p.seg[i].tiles_q = 0; p.seg[i].tiles_r = 0; }
   }
   p.x = x; p.status = status;
+  p.M = M; p.ldx = ldx; p.ldy = ldy;
   p.accumulate = accumulate;
 #ifdef CQ_ROWVEC_TRACE
   static int launch_no = 0;
@@ -879,11 +950,6 @@ int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_r
   return CQ_OK;
 }
 
-constexpr int RV_W = 16;                      // working warps of the product kernels
-inline int rv_gpw_for(const cq_rlayer* L) {   // smallest instantiated groups-per-warp that holds the layer, 0 if none
-  const int need = (L->NG + RV_W - 1) / RV_W;
-  return need <= 2 ? 2 : (need <= 4 ? 4 : (need <= 7 ? 7 : 0));
-}
 }  // namespace
 
 extern "C" int cq_rlayer_init(cq_rlayer* L, int bits, int K, int N, int C, int G, void* blob) {
@@ -944,32 +1010,54 @@ extern "C" int cq_rlayer_check(const cq_rlayer* L) {
   if (!gpw) return CQ_ERR_UNSUPPORTED;
   RowvecParams p;
   int grid = 0, smem = 0;
-  return rv_plan(RV_W, gpw, CQ_ROWVEC_INFLIGHT, 0, &L, 1, di, &p, &grid, &smem);
+  return rv_plan(rv_w_for(gpw), gpw, CQ_ROWVEC_INFLIGHT, 0, &L, 1, RV_MAX_ROWS, di, &p, &grid, &smem);
 }
 
-extern "C" int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, const void* x, void* const* ys, int accumulate,
-                                 uint32_t* status_word, cq_stream_t stream) {
-  if (!layers || !ys || !x || n_layers < 1 || n_layers > RV_MAX_SEG) return CQ_ERR_BAD_ARG;
+extern "C" int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, const void* x, int ldx, void* const* ys, int ldy,
+                                 int M, int accumulate, uint32_t* status_word, cq_stream_t stream) {
+  if (!layers || !ys || !x || n_layers < 1 || n_layers > RV_MAX_SEG || M < 1) return CQ_ERR_BAD_ARG;
   if ((uintptr_t)x & 1) return CQ_ERR_BAD_ARG;
-  __half* yp[RV_MAX_SEG];
+  int nmax = 0;
   for (int i = 0; i < n_layers; ++i) {
     if (!layers[i] || !layers[i]->blob || !ys[i] || ((uintptr_t)ys[i] & 1)) return CQ_ERR_BAD_ARG;
-    yp[i] = (__half*)ys[i];
+    if (layers[i]->N > nmax) nmax = layers[i]->N;
   }
   const cq_rlayer* L = layers[0];
-  const __half* xp = (const __half*)x;
+  if (ldx < L->K || ldy < nmax) return CQ_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
-  switch (rv_gpw_for(L)) {
-    case 2: return rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, yp, accumulate, status_word, st);
-    case 4: return rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, yp, accumulate, status_word, st);
-    case 7: return rv_launch(rv_pick<RV_W, 7>(L->bits, L->sets), RV_W, 7, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, yp, accumulate, status_word, st);
-    default: return CQ_ERR_UNSUPPORTED;
+  // up to RV_MAX_ROWS activation rows per launch (one for the wide shape); more rows are walked in slices,
+  // each reading the weights again
+  const int per_launch = rv_gpw_for(L) == RV_GPW_WIDE ? 1 : RV_MAX_ROWS;
+  for (int m0 = 0; m0 < M; m0 += per_launch) {
+    const int rows = M - m0 < per_launch ? M - m0 : per_launch;
+    const __half* xp = (const __half*)x + (size_t)m0 * ldx;
+    __half* yp[RV_MAX_SEG];
+    for (int i = 0; i < n_layers; ++i) yp[i] = (__half*)ys[i] + (size_t)m0 * ldy;
+    int rc = CQ_ERR_UNSUPPORTED;
+    switch (rv_gpw_for(L)) {
+      case 2: rc = rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, rows), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
+      case 4: rc = rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, rows), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
+      case RV_GPW_WIDE: rc = rv_launch(rv_pick<RV_W_WIDE, RV_GPW_WIDE>(L->bits, L->sets, rows), RV_W_WIDE, RV_GPW_WIDE, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
+      default: break;
+    }
+    if (rc != CQ_OK) return rc;
   }
+  return CQ_OK;
+}
+
+extern "C" int cq_rlayer_preferred_rows(const cq_rlayer* L) {
+  if (!L) return 0;
+  const int gpw = rv_gpw_for(L);
+  if (!gpw) return 0;
+  // measured on B200 against the tile GEMM: four launches of four rows still win on the narrow shapes
+  // (16 rows: 24 / 32 us against 25 / 36 on 4096 -> 4096 / 11008); the wide shape pays one launch per row
+  return gpw == RV_GPW_WIDE ? 4 : 16;
 }
 
 extern "C" int cq_rlayer_matvec(const cq_rlayer* L, const void* x, void* y, int accumulate, uint32_t* status_word,
                                 cq_stream_t stream) {
-  return cq_rlayers_matvec(&L, 1, x, &y, accumulate, status_word, stream);
+  if (!L) return CQ_ERR_BAD_ARG;
+  return cq_rlayers_matvec(&L, 1, x, L->K, &y, L->N, 1, accumulate, status_word, stream);
 }
 
 extern "C" int cq_rlayer_matvec_host(const cq_rlayer* L, const void* x_host, void* y_host, void* x_dev, void* y_dev,
@@ -987,7 +1075,7 @@ extern "C" int cq_rlayer_matvec_host(const cq_rlayer* L, const void* x_host, voi
 #ifdef CQ_ROWVEC_SWEEP
 // Tuning build only (not part of the library): a table of kernel shapes behind one entry point.
 #define RV_CASE(id, W, GPW, SMEM_KB, INFL) \
-  case id: { __half* yv = (__half*)y; return rv_launch(rv_pick<W, GPW>(L->bits, L->sets), W, GPW, INFL, SMEM_KB, &L, 1, (const __half*)x, &yv, accumulate, status_word, (cudaStream_t)stream); }
+  case id: { __half* yv = (__half*)y; return rv_launch(rv_pick<W, GPW>(L->bits, L->sets), W, GPW, INFL, SMEM_KB, &L, 1, (const __half*)x, L->K, &yv, L->N, 1, accumulate, status_word, (cudaStream_t)stream); }
 extern "C" int cq_rlayer_matvec_variant(int variant, const cq_rlayer* L, const void* x, void* y, int accumulate,
                                         uint32_t* status_word, cq_stream_t stream) {
   switch (variant) {

@@ -325,17 +325,20 @@ struct RowLayer {
     c10::cuda::getCurrentCUDAStream().synchronize();
   }
 
-  // out (1, N) fp16 = [out +] x (1, K) fp16 . W^T
+  // out (M, N) fp16 = [out +] x (M, K) fp16 . W^T; four rows per launch
   void matvec(torch::Tensor x, torch::Tensor out, bool accumulate) {
     const at::cuda::OptionalCUDAGuard device_guard(device_of(x));
     check_tensor(x, "x", torch::kFloat16, blob);
     check_tensor(out, "out", torch::kFloat16, blob);
-    TORCH_CHECK(x.numel() == layer.K, "x must hold one row of ", layer.K, " activations");
-    TORCH_CHECK(out.numel() == layer.N, "out must hold one row of ", layer.N, " values");
+    TORCH_CHECK(x.numel() % layer.K == 0 && x.numel() > 0, "x must hold rows of ", layer.K, " activations");
+    const int M = (int)(x.numel() / layer.K);
+    TORCH_CHECK(out.numel() == (int64_t)M * layer.N, "out must hold ", M, " rows of ", layer.N, " values");
     auto scratch = scratch_for(x.device());
     uint8_t* sp = scratch.data_ptr<uint8_t>();
-    check_status(cq_rlayer_matvec(&layer, x.data_ptr(), out.data_ptr(), accumulate ? 1 : 0,
-                                  (uint32_t*)(sp + cq_scratch_bytes()), current_stream()),
+    const cq_rlayer* lp = &layer;
+    void* yp = out.data_ptr();
+    check_status(cq_rlayers_matvec(&lp, 1, x.data_ptr(), layer.K, &yp, layer.N, M, accumulate ? 1 : 0,
+                                   (uint32_t*)(sp + cq_scratch_bytes()), current_stream()),
                  "RowLayer.matvec");
   }
 
@@ -354,24 +357,82 @@ struct RowLayer {
   }
 };
 
-// One launch for several row-tile layers that take the same activation row (q / k / v, gate / up):
-// outs[i] (1, N_i) fp16 = [outs[i] +] x (1, K) fp16 . W_i^T
+// A layer re-packed into the tile layout of the tensor-core GEMM (prefill and large batches); owns its blob.
+struct TileLayer {
+  cq_tlayer layer;
+  torch::Tensor blob;
+
+  TileLayer(torch::Tensor qweight, torch::Tensor scales, torch::Tensor cherry_weight, torch::Tensor cherry_indices,
+            int bits, int in_features, int group_size) {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(qweight));
+    check_tensor(qweight, "qweight", torch::kUInt8, qweight);
+    check_tensor(scales, "scales", torch::kFloat16, qweight);
+    check_tensor(cherry_weight, "cherry_weight", torch::kFloat16, qweight);
+    check_tensor(cherry_indices, "cherry_indices", torch::kInt16, qweight);
+    const int N = (int)qweight.size(1), C = (int)cherry_indices.numel();
+    check_status(cq_tlayer_init(&layer, bits, in_features, N, C, group_size, nullptr), "TileLayer");
+    TORCH_CHECK(qweight.size(0) == (in_features - C) / 8 * bits, "qweight has ", qweight.size(0), " rows, expected ",
+                (in_features - C) / 8 * bits);
+    blob = torch::empty({(int64_t)layer.blob_bytes}, qweight.options());
+    layer.blob = blob.data_ptr();
+    check_status(cq_tlayer_prepare(&layer, qweight.data_ptr<uint8_t>(), scales.data_ptr(), cherry_weight.data_ptr(),
+                                   (const int16_t*)cherry_indices.data_ptr(), current_stream()),
+                 "TileLayer");
+  }
+
+  // out (M, N) fp16 = [out +] x (M, K) fp16 . W^T, walked in slices of 4096 rows (bounds the workspace)
+  void gemm(torch::Tensor x, torch::Tensor out, bool accumulate) {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(x));
+    check_tensor(x, "x", torch::kFloat16, blob);
+    check_tensor(out, "out", torch::kFloat16, blob);
+    TORCH_CHECK(x.dim() == 2 && x.size(1) == layer.K, "x must be (M, ", layer.K, ")");
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) == layer.N, "out must be (M, ", layer.N, ")");
+    const int M = (int)x.size(0), CH = 4096;
+    const int chunk = M < CH ? M : CH;
+    auto ws = torch::empty({(int64_t)cq_tlayer_gemm_workspace_bytes(&layer, chunk)}, blob.options());
+    auto scratch = scratch_for(x.device());
+    uint8_t* sp = scratch.data_ptr<uint8_t>();
+    const __half* xp = (const __half*)x.data_ptr();
+    __half* yp = (__half*)out.data_ptr();
+    for (int m0 = 0; m0 < M; m0 += CH) {
+      const int rows = M - m0 < CH ? M - m0 : CH;
+      check_status(cq_tlayer_gemm(&layer, xp + (size_t)m0 * layer.K, layer.K, yp + (size_t)m0 * layer.N, layer.N, rows,
+                                  accumulate ? 1 : 0, ws.data_ptr(), (uint32_t*)(sp + cq_scratch_bytes()), current_stream()),
+                   "TileLayer.gemm");
+    }
+  }
+};
+
+// One launch (per four activation rows) for several row-tile layers that take the same activations
+// (q / k / v, gate / up): outs[i] = [outs[i] +] x (M, K) fp16 . W_i^T.  The outputs are rows of `ldy`
+// elements each: views into one (M, ldy) buffer, or separate (M, N_i) tensors when every N_i == ldy.
 void row_layers_matvec(std::vector<RowLayer*> layers, torch::Tensor x, std::vector<torch::Tensor> outs, bool accumulate) {
   TORCH_CHECK(!layers.empty() && layers.size() <= 4 && layers.size() == outs.size(), "1 to 4 layers, one output each");
   const at::cuda::OptionalCUDAGuard device_guard(device_of(x));
   check_tensor(x, "x", torch::kFloat16, layers[0]->blob);
-  TORCH_CHECK(x.numel() == layers[0]->layer.K, "x must hold one row of ", layers[0]->layer.K, " activations");
+  const int K = layers[0]->layer.K;
+  TORCH_CHECK(x.numel() % K == 0 && x.numel() > 0, "x must hold rows of ", K, " activations");
+  const int M = (int)(x.numel() / K);
   const cq_rlayer* ls[4];
   void* ys[4];
+  int64_t ldy = -1;
   for (size_t i = 0; i < layers.size(); ++i) {
-    check_tensor(outs[i], "out", torch::kFloat16, layers[0]->blob);
-    TORCH_CHECK(outs[i].numel() == layers[i]->layer.N, "out ", i, " must hold one row of ", layers[i]->layer.N, " values");
+    const auto& o = outs[i];
+    TORCH_CHECK(o.is_cuda() && o.scalar_type() == torch::kFloat16 && o.device() == x.device() && o.dim() == 2 &&
+                o.size(0) == M && o.size(1) == layers[i]->layer.N && o.stride(1) == 1,
+                "out ", i, " must be a (", M, ", ", layers[i]->layer.N, ") fp16 CUDA tensor with unit column stride");
+    if (M == 1) {
+      ldy = std::max<int64_t>(ldy, o.size(1));          // a single row: the stride is never used
+    } else {
+      TORCH_CHECK(ldy < 0 || o.stride(0) == ldy, "the outputs must share one row stride (views of one buffer)");
+      ldy = o.stride(0);
+    }
     ls[i] = &layers[i]->layer;
-    ys[i] = outs[i].data_ptr();
+    ys[i] = o.data_ptr();
   }
   auto scratch = scratch_for(x.device());
   uint8_t* sp = scratch.data_ptr<uint8_t>();
-  check_status(cq_rlayers_matvec(ls, (int)layers.size(), x.data_ptr(), ys, accumulate ? 1 : 0,
+  check_status(cq_rlayers_matvec(ls, (int)layers.size(), x.data_ptr(), K, ys, (int)ldy, M, accumulate ? 1 : 0,
                                  (uint32_t*)(sp + cq_scratch_bytes()), current_stream()),
                "row_layers_matvec");
 }
@@ -433,12 +494,15 @@ void rope_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor
   TORCH_CHECK(positions.numel() == T, "positions must have T entries");
   TORCH_CHECK(cos_table.dim() == 2 && cos_table.size(1) == D / 2 && sin_table.sizes() == cos_table.sizes(),
               "cos / sin tables must be (max_seq, D / 2)");
-  TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(1) == KV && k_cache.size(2) == D && v_cache.sizes() == k_cache.sizes() &&
-                  k_cache.size(0) <= cos_table.size(0),
-              "caches must be (max_seq, KV, D) with max_seq within the rotary tables");
+  // caches (max_seq, KV, D): the T tokens are one sequence; (B, max_seq, KV, D): T / B consecutive tokens per sequence
+  TORCH_CHECK((k_cache.dim() == 3 || k_cache.dim() == 4) && v_cache.sizes() == k_cache.sizes(), "caches must be ([B,] max_seq, KV, D)");
+  const int cd = (int)k_cache.dim();
+  const int B = cd == 4 ? (int)k_cache.size(0) : 1;
+  TORCH_CHECK(k_cache.size(cd - 2) == KV && k_cache.size(cd - 1) == D && k_cache.size(cd - 3) <= cos_table.size(0) && T % B == 0,
+              "caches must be ([B,] max_seq, KV, D) with max_seq within the rotary tables and B dividing T");
   check_status(cq_rope_cache(q.data_ptr(), k.data_ptr(), v.data_ptr(), cos_table.data_ptr<float>(),
                              sin_table.data_ptr<float>(), (const long long*)positions.data_ptr(), k_cache.data_ptr(),
-                             v_cache.data_ptr(), T, H, KV, D, (int)k_cache.size(0), current_stream()),
+                             v_cache.data_ptr(), T, H, KV, D, (int)k_cache.size(cd - 3), T / B, current_stream()),
                "rope_cache");
 }
 
@@ -460,13 +524,17 @@ torch::Tensor attn_decode(torch::Tensor q, torch::Tensor k_cache, torch::Tensor 
   check_tensor(k_cache, "k_cache", torch::kFloat16, q);
   check_tensor(v_cache, "v_cache", torch::kFloat16, q);
   check_tensor(position, "position", torch::kInt64, q);
-  TORCH_CHECK(q.dim() == 3 && q.size(0) == 1, "q must be (1, H, D)");
-  TORCH_CHECK(k_cache.dim() == 3 && k_cache.size(2) == q.size(2) && v_cache.sizes() == k_cache.sizes(),
-              "caches must be (max_seq, KV, D)");
+  // q (B, H, D), one query per sequence; caches (B, max_seq, KV, D), or (max_seq, KV, D) for B == 1
+  TORCH_CHECK(q.dim() == 3, "q must be (B, H, D)");
+  const int B = (int)q.size(0);
+  const int cd = (int)k_cache.dim();
+  TORCH_CHECK((cd == 4 && k_cache.size(0) == B) || (cd == 3 && B == 1), "caches must be (B, max_seq, KV, D)");
+  TORCH_CHECK(k_cache.size(cd - 1) == q.size(2) && v_cache.sizes() == k_cache.sizes(), "caches must be ([B,] max_seq, KV, D)");
+  TORCH_CHECK(position.numel() == B, "one position per sequence");
   auto out = torch::empty_like(q);
   check_status(cq_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), (const long long*)position.data_ptr(),
-                              out.data_ptr(), (int)q.size(1), (int)k_cache.size(1), (int)q.size(2), (int)k_cache.size(0),
-                              1.0f / std::sqrt((float)q.size(2)), current_stream()),
+                              out.data_ptr(), B, (int)q.size(1), (int)k_cache.size(cd - 2), (int)q.size(2),
+                              (int)k_cache.size(cd - 3), 1.0f / std::sqrt((float)q.size(2)), current_stream()),
                "attn_decode");
   return out;
 }
@@ -503,8 +571,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("matvec", &RowLayer::matvec)
       .def("unprepare", &RowLayer::unprepare)
       .def_readonly("blob", &RowLayer::blob)
+      .def_property_readonly("preferred_rows", [](const RowLayer& p) { return cq_rlayer_preferred_rows(&p.layer); })
       .def_property_readonly("out_features", [](const RowLayer& p) { return p.layer.N; })
       .def_property_readonly("in_features", [](const RowLayer& p) { return p.layer.K; });
+  py::class_<TileLayer>(m, "TileLayer")
+      .def(py::init<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int, int, int>())
+      .def("gemm", &TileLayer::gemm)
+      .def_readonly("blob", &TileLayer::blob);
   py::class_<PreparedLayer>(m, "PreparedLayer")
       .def(py::init<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int, int, int>())
       .def(py::init<torch::Tensor, int, int, int, int, int>())

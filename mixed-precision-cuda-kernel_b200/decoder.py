@@ -76,10 +76,13 @@ class CherryDecoder:
     PROJ = ("q", "k", "v", "o", "gate", "up", "down")
 
     def __init__(self, cfg: DecoderConfig, device="cuda", seed: int = 0, dense: bool = False,
-                 release_reference_buffers: bool = False, tp_group=None, tp_gather: str = "peer"):
+                 release_reference_buffers: bool = False, tp_group=None, tp_gather: str = "peer", batch: int = 1):
         if not torch.cuda.is_available():
             raise RuntimeError("CherryDecoder needs a CUDA device (there is no CPU path)")
+        if batch < 1:
+            raise ValueError("batch must be at least 1")
         self.cfg, self.dev, self.dense = cfg, torch.device(device), dense
+        self.batch = batch          # sequences decoded in lockstep (same prompt length, one position counter)
         self.qc = load_quant_cuda()
         self.group = tp_group
         if tp_group is not None:
@@ -124,11 +127,11 @@ class CherryDecoder:
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=self.dev, dtype=torch.float32) / hd))
         ang = torch.outer(torch.arange(cfg.max_seq, device=self.dev, dtype=torch.float32), inv)
         self.cos, self.sin = ang.cos(), ang.sin()                      # (max_seq, hd / 2)
-        self.k_cache = torch.zeros(cfg.n_layers, cfg.max_seq, self.kv_local, hd, dtype=torch.float16, device=self.dev)
+        self.k_cache = torch.zeros(cfg.n_layers, batch, cfg.max_seq, self.kv_local, hd, dtype=torch.float16, device=self.dev)
         self.v_cache = torch.zeros_like(self.k_cache)
-        # state of the decode loop, all on the device
-        self.tok = torch.zeros(1, dtype=torch.long, device=self.dev)
-        self.pos = torch.zeros(1, dtype=torch.long, device=self.dev)
+        # state of the decode loop, all on the device: next token and position of every sequence
+        self.tok = torch.zeros(batch, dtype=torch.long, device=self.dev)
+        self.pos = torch.zeros(batch, dtype=torch.long, device=self.dev)
         self.pos_host = 0           # the host's copy of `pos`: every step is checked against max_seq before it is launched
         self.graph = None
 
@@ -193,7 +196,7 @@ class CherryDecoder:
         """One decoder layer on the residual stream h with the previous layer's MLP output `delta`
         still to be added; returns (h, delta) in the same form."""
         cfg, lay = self.cfg, self.layers[li]
-        t, nh, kv, hd = h.shape[0], self.h_local, self.kv_local, cfg.head_dim
+        t, nh, kv, hd, nb = h.shape[0], self.h_local, self.kv_local, cfg.head_dim, self.batch
         xn, h = self._norm(h, delta, lay["norm1"])
         q, k, v = self._lins(lay, ("q", "k", "v"), xn)
         q, k, v = q.view(t, nh, hd), k.view(t, kv, hd), v.view(t, kv, hd)
@@ -201,9 +204,10 @@ class CherryDecoder:
         if decode:
             a = self.qc.attn_decode(q, self.k_cache[li], self.v_cache[li], pos).view(t, nh * hd)
         else:
-            a = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
-                                               v.transpose(0, 1)[None], is_causal=True, enable_gqa=(kv != nh))
-            a = a[0].transpose(0, 1).reshape(t, nh * hd)
+            ts = t // nb              # tokens per sequence; rows are (sequence, token)
+            a = F.scaled_dot_product_attention(q.view(nb, ts, nh, hd).transpose(1, 2), k.view(nb, ts, kv, hd).transpose(1, 2),
+                                               v.view(nb, ts, kv, hd).transpose(1, 2), is_causal=True, enable_gqa=(kv != nh))
+            a = a.transpose(1, 2).reshape(t, nh * hd)
         xn, h = self._norm(h, self._gather(self._lin(lay["o"], self._gather(a))), lay["norm2"])
         gate, up = self._lins(lay, ("gate", "up"), xn)
         act = self.qc.silu_mul(gate, up)
@@ -215,15 +219,21 @@ class CherryDecoder:
     # ------------------------------------------------------------------ prefill / decode
     @torch.inference_mode()
     def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
-        """Runs the prompt (T,) through the model, fills the cache, returns the last position's logits."""
-        t = tokens.shape[0]
+        """Runs the prompts (T,) or (batch, T) through the model, fills the caches, returns the last
+        position's logits (batch, vocab)."""
+        if tokens.dim() == 1:
+            tokens = tokens[None]
+        if tokens.shape[0] != self.batch:
+            raise ValueError(f"{tokens.shape[0]} prompts for a decoder of batch {self.batch}")
+        t = tokens.shape[1]
         if not 0 < t < self.cfg.max_seq:
             raise ValueError(f"a prompt of {t} tokens does not fit max_seq = {self.cfg.max_seq} (one position must stay free)")
-        pos = torch.arange(t, device=self.dev)
-        h, delta = self.embed[tokens], None
+        pos = torch.arange(t, device=self.dev).repeat(self.batch)
+        h, delta = self.embed[tokens.reshape(-1)], None
         for li in range(self.cfg.n_layers):
             h, delta = self._layer(li, h, delta, pos, decode=False)
-        logits = self._logits(h[-1:].contiguous(), delta[-1:].contiguous())
+        last = torch.arange(self.batch, device=self.dev) * t + (t - 1)
+        logits = self._logits(h[last].contiguous(), delta[last].contiguous())
         self._check_exchange()
         self.pos.fill_(t)
         self.pos_host = t
@@ -246,9 +256,9 @@ class CherryDecoder:
         """Captures one decode step in a CUDA graph (the state tensors are saved and restored)."""
         if self.cfg.max_seq < 4:
             raise ValueError("max_seq must be at least 4")
-        saved = (self.tok.clone(), self.pos.clone(), self.k_cache.clone(), self.v_cache.clone())
         # the warm-up and the captured step run at positions 0, 1, 2: always inside the cache, whatever
-        # the current position is (state and caches are restored below)
+        # the current position is (state and those cache rows are restored below)
+        saved = (self.tok.clone(), self.pos.clone(), self.k_cache[:, :, :3].clone(), self.v_cache[:, :, :3].clone())
         self.pos.zero_()
         s = torch.cuda.Stream(device=self.dev)
         s.wait_stream(torch.cuda.current_stream())
@@ -261,17 +271,17 @@ class CherryDecoder:
                 self.graph_logits = self._step()
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
-        for dst, src in zip((self.tok, self.pos, self.k_cache, self.v_cache), saved):
+        for dst, src in zip((self.tok, self.pos, self.k_cache[:, :, :3], self.v_cache[:, :, :3]), saved):
             dst.copy_(src)
 
     @torch.inference_mode()
     def generate(self, n_tokens: int, use_graph: bool = True) -> torch.Tensor:
-        """Greedy continuation after `prefill`: returns the n_tokens generated ids (the first one is
-        the prefill's argmax)."""
+        """Greedy continuation after `prefill`: returns the n_tokens generated ids, (n_tokens,) for one
+        sequence and (n_tokens, batch) for more (the first one is the prefill's argmax)."""
         if n_tokens < 0 or self.pos_host + n_tokens > self.cfg.max_seq:
             raise ValueError(f"{n_tokens} more tokens after position {self.pos_host} do not fit max_seq = "
                              f"{self.cfg.max_seq}: the KV cache holds max_seq positions")
-        out = torch.empty(n_tokens, dtype=torch.long, device=self.dev)
+        out = torch.empty(n_tokens, self.batch, dtype=torch.long, device=self.dev)
         if use_graph and self.graph is None:
             self.capture()
         for i in range(n_tokens):
@@ -282,7 +292,7 @@ class CherryDecoder:
                 self._step()
         self.pos_host += n_tokens
         self._check_exchange()
-        return out
+        return out[:, 0] if self.batch == 1 else out
 
     def _check_exchange(self):
         """Raises if a peer never delivered a slice (the kernel fills that output with NaN and sets a

@@ -21,6 +21,12 @@ import torch.nn as nn
 from . import load_quant_cuda
 
 
+# No batch beyond this many rows goes to the row-tile decode kernel (four rows per launch, each launch
+# reads the weights once); a layer's own limit (RowLayer.preferred_rows) may be lower.  Larger batches
+# take the tensor-core GEMM.
+ROW_KERNEL_MAX_ROWS = 16
+
+
 class QuantLinear(nn.Module):
     _layerwise_dequantize = True
 
@@ -59,6 +65,7 @@ class QuantLinear(nn.Module):
         self.dequantized = False
         self._prepared = None        # stream layout (PreparedLayer)
         self._row = None             # row-tile layout (RowLayer)
+        self._tile = None            # tile layout of the GEMM (TileLayer), only built after a release
         self._row_ok = None          # None = not asked yet
         self._prepared_key = None
 
@@ -105,6 +112,7 @@ class QuantLinear(nn.Module):
     def _drop_copies(self):
         self._prepared = None
         self._row = None
+        self._tile = None
         self._row_ok = None
         self._prepared_key = None
 
@@ -174,12 +182,12 @@ class QuantLinear(nn.Module):
                 x2 = x2.half()
             x2 = x2.contiguous()
             rows = x2.shape[0]
-            row = self.row_layer() if rows == 1 else None
-            if row is not None:
-                out = torch.empty(1, self.out_features, dtype=torch.float16, device=x2.device)
+            row = self.row_layer() if rows <= ROW_KERNEL_MAX_ROWS else None
+            if row is not None and rows <= row.preferred_rows:
+                out = torch.empty(rows, self.out_features, dtype=torch.float16, device=x2.device)
                 row.matvec(x2, out, False)
             elif rows >= 8 and self._prepared_key != "released":
-                # 8 rows or more: the drop-in op routes them to the tensor-core GEMM (faster from there on)
+                # more rows: the drop-in op routes them to the tensor-core GEMM (faster from there on)
                 qc = load_quant_cuda()
                 out = torch.zeros(rows, self.out_features, dtype=torch.float16, device=x2.device)
                 if self.w_bits == 4:
@@ -188,6 +196,14 @@ class QuantLinear(nn.Module):
                 else:
                     qc.vecquant3matmul_cherryq(x2, self.qweight, self.cherry_weight, self.cherry_indices,
                                                self.scales, out, self.group_size, True)
+            elif rows >= 8:
+                # released buffers and a large batch: the GEMM on this module's own tile-layout copy
+                if self._tile is None:
+                    qc = load_quant_cuda()
+                    q, s, cw, ci = self._source_buffers()
+                    self._tile = qc.TileLayer(q, s, cw, ci, self.w_bits, self.in_features, self.group_size)
+                out = torch.empty(rows, self.out_features, dtype=torch.float16, device=x2.device)
+                self._tile.gemm(x2, out, False)
             else:
                 out = torch.empty(rows, self.out_features, dtype=torch.float16, device=x2.device)
                 self.prepared().matvec(x2, out, False)
@@ -209,25 +225,27 @@ class QuantLinear(nn.Module):
 
 def forward_shared_input(layers, x: torch.Tensor):
     """Outputs of several packed layers applied to the same input (q / k / v, gate / up of the
-    reference's LLaMA, llama/modeling_llama_quant.py): for one activation row and layers that agree
-    in bits, in_features, cherry count and group size this is ONE launch of the one-row kernel with
-    the SMs divided among the layers; every other case is the layers' own forward, one by one.
-    The results are bit-identical to the separate calls either way."""
+    reference's LLaMA, llama/modeling_llama_quant.py): for decode batches (up to ROW_KERNEL_MAX_ROWS
+    rows) and layers that agree in bits, in_features, cherry count and group size this is ONE launch
+    of the row-tile kernel per four rows, with the SMs divided among the layers; every other case is
+    the layers' own forward, one by one.  The results are bit-identical to the separate calls."""
     layers = list(layers)
     first = layers[0]
     rows = x.numel() // x.shape[-1]
     same = all((l.w_bits, l.in_features, l.num_cherries, l.group_size) ==
                (first.w_bits, first.in_features, first.num_cherries, first.group_size) for l in layers)
-    if (rows == 1 and 1 < len(layers) <= 4 and same and QuantLinear._layerwise_dequantize
+    if (rows <= ROW_KERNEL_MAX_ROWS and 1 < len(layers) <= 4 and same and QuantLinear._layerwise_dequantize
             and first.w_bits in (3, 4)):
         rls = [l.row_layer() for l in layers]
-        if all(r is not None for r in rls):
+        if all(r is not None and rows <= r.preferred_rows for r in rls):
             qc = load_quant_cuda()
-            x2 = x.reshape(1, x.shape[-1])
+            x2 = x.reshape(rows, x.shape[-1])
             if x2.dtype != torch.float16:
                 x2 = x2.half()
             x2 = x2.contiguous()
-            outs = [torch.empty(1, l.out_features, dtype=torch.float16, device=x2.device) for l in layers]
+            widths = [l.out_features for l in layers]
+            buf = torch.empty(rows, sum(widths), dtype=torch.float16, device=x2.device)
+            outs = list(buf.split(widths, dim=1))               # views of one buffer: one row stride
             qc.row_layers_matvec(rls, x2, outs, False)
             res = []
             for l, o in zip(layers, outs):

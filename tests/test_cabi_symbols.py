@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol():
 def test_host_only_entry_points():
     from cherryq_b200 import _cabi
     lib = _cabi.lib()
-    assert lib.cq_abi_version() == 2
+    assert lib.cq_abi_version() == 3
     assert _cabi.strerror(0) == "ok"
     assert "multiple of 128" in _cabi.strerror(3)
     L = _cabi.layer_init(4, 4096, 11008, 16, 128)

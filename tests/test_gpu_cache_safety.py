@@ -97,3 +97,28 @@ def test_quantlinear_owns_its_copy():
         y = lin(x).float().cpu().numpy().astype(np.float64)
         ref = x.cpu().numpy().astype(np.float64) @ dense(bufs).T
         assert np.abs(y - ref).max() <= 2e-3 * np.abs(ref).max()
+
+
+def test_released_layer_serves_every_batch_size_from_its_own_copies():
+    """After release_reference_buffers() the module answers decode batches from its row-tile copy and large
+    batches from its own tile-layout copy (built on first use), with the results of the unreleased module."""
+    import cherryq_b200
+    from cherryq_b200.qlinear import QuantLinear
+    qc = cherryq_b200.load_quant_cuda()
+    bufs = make_layer(qc, 500)
+    lin = QuantLinear(BITS, G, None, 1 / 64, K, N, bias=False).cuda()
+    lin.qweight, lin.scales, lin.cherry_weight, lin.cherry_indices = bufs
+    xs = {rows: torch.randn(rows, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rows)).half()
+          for rows in (1, 4, 7, 16, 64, 300)}
+    before = {rows: lin(x).clone() for rows, x in xs.items()}
+    ref = dense(bufs)
+    lin.release_reference_buffers()
+    assert lin.qweight.numel() == 0
+    for rows, x in xs.items():
+        y = lin(x)
+        want = x.cpu().numpy().astype(np.float64) @ ref.T
+        assert np.abs(y.float().cpu().numpy() - want).max() <= 2e-3 * np.abs(want).max()
+        assert float((y.float() - before[rows].float()).abs().max()) <= 2e-3 * float(before[rows].float().abs().max())
+    lin.restore_reference_buffers()
+    for got, want in zip((lin.qweight, lin.scales, lin.cherry_weight, lin.cherry_indices), bufs):
+        assert torch.equal(got, want)

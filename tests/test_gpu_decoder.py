@@ -174,3 +174,80 @@ def test_device_side_position_guards():
     a = qc.attn_decode(q[:1].contiguous(), kcr, vcr, torch.tensor([S + 5], device="cuda"))
     b = qc.attn_decode(q[:1].contiguous(), kcr, vcr, torch.tensor([S - 1], device="cuda"))
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("bits,kv,batch", [(4, 4, 3), (3, 2, 5)])
+def test_batched_decode_matches_single_sequences(dec, bits, kv, batch):
+    """`batch` sequences in lockstep (their own KV caches, four activation rows per kernel launch) against
+    one decoder per sequence with the same weights, teacher-forced with the batch's tokens."""
+    cfg = tiny(dec, bits, kv)
+    big = dec.CherryDecoder(cfg, seed=5, batch=batch)
+    singles = [dec.CherryDecoder(cfg, seed=5) for _ in range(batch)]
+    prompts = torch.randint(0, cfg.vocab, (batch, 21), device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+    lb = big.prefill(prompts)
+    scale = float(lb.float().abs().max())
+    for i, s in enumerate(singles):
+        ls = s.prefill(prompts[i])
+        assert float((lb[i].float() - ls[0].float()).abs().max()) <= 5e-3 * scale
+    for _ in range(10):
+        for i, s in enumerate(singles):
+            s.tok.copy_(big.tok[i:i + 1])
+        lb = big._step()
+        for i, s in enumerate(singles):
+            ls = s._step()
+            assert float((lb[i].float() - ls[0].float()).abs().max()) <= 5e-3 * scale
+    assert int(big.pos[0].item()) == 31 and bool((big.pos == 31).all())
+    # graph replay and eager steps agree for a batch too
+    big.prefill(prompts)
+    eager = big.generate(8, use_graph=False)
+    big.prefill(prompts)
+    graphed = big.generate(8, use_graph=True)
+    assert eager.shape == (8, batch) and torch.equal(eager, graphed)
+
+
+def test_batched_rope_cache_and_attention_match_torch():
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    g = torch.Generator(device="cuda").manual_seed(21)
+    B, H, KV, D, S = 3, 8, 2, 64, 96
+    # decode step: one token per sequence, each at its own position
+    q = torch.randn(B, H, D, device="cuda", generator=g).half()
+    k = torch.randn(B, KV, D, device="cuda", generator=g).half()
+    v = torch.randn(B, KV, D, device="cuda", generator=g).half()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda", dtype=torch.float32) / D))
+    ang = torch.outer(torch.arange(S, device="cuda", dtype=torch.float32), inv)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([5, 40, 95], device="cuda")
+
+    def rope(t, p):
+        c, s = cos[p][:, None, :], sin[p][:, None, :]
+        t1, t2 = t[..., : D // 2].float(), t[..., D // 2:].float()
+        return torch.cat((t1 * c - t2 * s, t2 * c + t1 * s), -1).half()
+    kc = torch.randn(B, S, KV, D, device="cuda", generator=g).half()
+    vc = torch.randn(B, S, KV, D, device="cuda", generator=g).half()
+    kc0, vc0 = kc.clone(), vc.clone()
+    rq, rk = rope(q, pos), rope(k, pos)
+    qc.rope_cache(q, k, v, cos, sin, pos, kc, vc)
+    assert float((q.float() - rq.float()).abs().max()) <= 2e-3 and float((k.float() - rk.float()).abs().max()) <= 2e-3
+    for b in range(B):
+        assert torch.equal(kc[b, pos[b]], k[b]) and torch.equal(vc[b, pos[b]], v[b])
+        kc0[b, pos[b]], vc0[b, pos[b]] = k[b], v[b]
+    assert torch.equal(kc, kc0) and torch.equal(vc, vc0)                 # nothing else was touched
+    out = qc.attn_decode(q, kc, vc, pos)
+    for b in range(B):
+        n = int(pos[b]) + 1
+        kk = kc[b, :n].float().repeat_interleave(H // KV, dim=1)
+        vv = vc[b, :n].float().repeat_interleave(H // KV, dim=1)
+        w = torch.softmax(torch.einsum("hd,phd->hp", q[b].float(), kk) / D ** 0.5, dim=-1)
+        ref = torch.einsum("hp,phd->hd", w, vv)
+        assert float((out[b].float() - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))
+    # prefill form: T tokens per sequence, rows ordered (sequence, token)
+    T = 4
+    q2 = torch.randn(B * T, H, D, device="cuda", generator=g).half()
+    k2 = torch.randn(B * T, KV, D, device="cuda", generator=g).half()
+    v2 = torch.randn(B * T, KV, D, device="cuda", generator=g).half()
+    kc2 = torch.zeros(B, S, KV, D, dtype=torch.float16, device="cuda")
+    vc2 = torch.zeros_like(kc2)
+    qc.rope_cache(q2, k2, v2, cos, sin, torch.arange(T, device="cuda").repeat(B), kc2, vc2)
+    assert torch.equal(kc2[:, :T].reshape(B * T, KV, D), k2) and torch.equal(vc2[:, :T].reshape(B * T, KV, D), v2)
+    assert not bool(kc2[:, T:].any())

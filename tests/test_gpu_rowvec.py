@@ -288,13 +288,13 @@ def test_shared_input_launch_is_bit_identical_to_separate_launches(cabi, K, Ns, 
     layers = (C.POINTER(cabi.cq_rlayer) * n)(*[C.pointer(p.L) for p in preps])
     ys = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    cabi.check(lib.cq_rlayers_matvec(layers, n, ptr(x), ys, 0, ptr(status), None), "rlayers_matvec")
+    cabi.check(lib.cq_rlayers_matvec(layers, n, ptr(x), K, ys, max(Ns), 1, 0, ptr(status), None), "rlayers_matvec")
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     for o, w in zip(outs, want):
         assert torch.equal(o.view(torch.int16), w.view(torch.int16))
     # accumulate adds to what the outputs hold
-    cabi.check(lib.cq_rlayers_matvec(layers, n, ptr(x), ys, 1, ptr(status), None), "rlayers_matvec")
+    cabi.check(lib.cq_rlayers_matvec(layers, n, ptr(x), K, ys, max(Ns), 1, 1, ptr(status), None), "rlayers_matvec")
     torch.cuda.synchronize()
     for o, p, w in zip(outs, preps, want):
         again = p.matvec(x, y=w.clone(), accumulate=True)
@@ -311,10 +311,13 @@ def test_shared_input_launch_refuses_layers_that_do_not_agree(cabi):
     ys = (C.c_void_p * 2)(*[o.data_ptr() for o in outs])
     for pair in ((a, b), (a, c)):
         layers = (C.POINTER(cabi.cq_rlayer) * 2)(*[C.pointer(p.L) for p in pair])
-        assert lib.cq_rlayers_matvec(layers, 2, ptr(x), ys, 0, None, None) == 4          # CQ_ERR_BAD_SHAPE
+        assert lib.cq_rlayers_matvec(layers, 2, ptr(x), 2048, ys, 64, 1, 0, None, None) == 4     # CQ_ERR_BAD_SHAPE
     layers = (C.POINTER(cabi.cq_rlayer) * 2)(C.pointer(a.L), C.pointer(a.L))
-    assert lib.cq_rlayers_matvec(layers, 5, ptr(x), ys, 0, None, None) == 1              # more than four layers
-    assert lib.cq_rlayers_matvec(layers, 0, ptr(x), ys, 0, None, None) == 1
+    assert lib.cq_rlayers_matvec(layers, 5, ptr(x), 2048, ys, 64, 1, 0, None, None) == 1         # more than four layers
+    assert lib.cq_rlayers_matvec(layers, 0, ptr(x), 2048, ys, 64, 1, 0, None, None) == 1
+    assert lib.cq_rlayers_matvec(layers, 2, ptr(x), 1000, ys, 64, 1, 0, None, None) == 1         # ldx < K
+    assert lib.cq_rlayers_matvec(layers, 2, ptr(x), 2048, ys, 32, 1, 0, None, None) == 1         # ldy < N
+    assert lib.cq_rlayers_matvec(layers, 2, ptr(x), 2048, ys, 64, 0, 0, None, None) == 1         # no rows
 
 
 def test_quantlinear_shared_input_forward_matches_separate_forwards():
@@ -330,7 +333,7 @@ def test_quantlinear_shared_input_forward_matches_separate_forwards():
         if lin.bias is not None:
             lin.bias = torch.randn(N, device="cuda").half()
         lins.append(lin)
-    for rows in (1, 3):
+    for rows in (1, 3, 4, 7, 8, 12):
         x = torch.randn(rows, K, device="cuda").half()
         together = forward_shared_input(lins, x)
         for lin, y in zip(lins, together):
@@ -361,3 +364,89 @@ def test_host_buffer_entry_point(cabi):
     cabi.check(lib.cq_rlayer_matvec_host(C.byref(p.L), C.c_void_p(xp.data_ptr()), C.c_void_p(yp.data_ptr()), ptr(xd), ptr(yd),
                                          ptr(status), None), "matvec_host")
     assert torch.equal(yp, want.cpu())
+
+
+# ------------------------------------------------------------------ several activation rows in one launch
+def rows_call(cabi, preps, x, ldx=None, pad=0, accumulate=False, base=None):
+    """cq_rlayers_matvec on M rows; the outputs are column slices of one (M, sum N + pad) buffer."""
+    lib = cabi.lib()
+    M, K = x.shape[0], preps[0].L.K
+    widths = [p.L.N for p in preps]
+    ldy = sum(widths) + pad
+    buf = torch.full((M, ldy), float("nan"), dtype=torch.float16, device="cuda") if base is None else base.clone()
+    outs = list(buf[:, :sum(widths)].split(widths, dim=1))
+    n = len(preps)
+    layers = (C.POINTER(cabi.cq_rlayer) * n)(*[C.pointer(p.L) for p in preps])
+    ys = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cabi.check(lib.cq_rlayers_matvec(layers, n, ptr(x), ldx or x.stride(0), ys, ldy, M, int(accumulate), ptr(status), None),
+               "rlayers_matvec")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    return buf, outs
+
+
+@pytest.mark.parametrize("K,N,bits,G", [(4096, 4096, 4, 128), (4096, 11008, 3, 128), (11008, 4096, 4, 128),
+                                        (13824, 5120, 3, 128), (8192, 1024, 3, 128), (1024, 200, 3, 64),
+                                        (640, 40, 4, 640)])
+@pytest.mark.parametrize("M", [2, 3, 4, 5, 8, 11])
+def test_rows_of_a_batch_are_bit_identical_to_single_row_calls(cabi, K, N, bits, G, M):
+    frac = 1 / 256 if K >= 2048 else 1 / 64
+    q, s, cw, ci, dense = gpu_layer(K, N, bits, G, seed=K + N + bits + M, frac=frac)
+    p = RowPrepared(cabi, q, s, cw, ci, bits, K, G)
+    g = torch.Generator(device="cuda").manual_seed(M)
+    x = (torch.randn(M, K, device="cuda", generator=g) * torch.logspace(-2, 1, M, device="cuda")[:, None]).half()
+    buf, (y,) = rows_call(cabi, [p], x)
+    for m in range(M):
+        want = p.matvec(x[m:m + 1].contiguous())
+        assert torch.equal(y[m:m + 1].contiguous().view(torch.int16), want.view(torch.int16)), m
+    assert rel_err(y.float().cpu().numpy(), ref64(x, dense)) <= TIGHT_TOL
+
+
+def test_batch_with_strides_padding_accumulate_and_shared_input(cabi):
+    K, Ns, bits = 2048, (512, 128, 136), 4
+    preps = []
+    for i, N in enumerate(Ns):
+        q, s, cw, ci, _ = gpu_layer(K, N, bits, 128, seed=900 + i)
+        preps.append(RowPrepared(cabi, q, s, cw, ci, bits, K, 128))
+    M = 6
+    wide = torch.randn(M, K + 24, device="cuda").half()
+    x = wide[:, 8:8 + K]                                     # row stride K + 24, rows 16-byte aligned
+    buf, outs = rows_call(cabi, preps, x, pad=5)
+    assert bool(torch.isnan(buf[:, sum(Ns):]).all())          # the padding columns are not written
+    for p, o in zip(preps, outs):
+        for m in range(M):
+            want = p.matvec(x[m:m + 1].contiguous())
+            assert torch.equal(o[m:m + 1].contiguous().view(torch.int16), want.view(torch.int16))
+    odd = wide[:, 3:3 + K]                                   # rows only 2-byte aligned: scalar staging path
+    _, outs2 = rows_call(cabi, preps, odd)
+    for p, o in zip(preps, outs2):
+        want = torch.cat([p.matvec(odd[m:m + 1].contiguous()) for m in range(M)])
+        assert torch.equal(o.contiguous().view(torch.int16), want.view(torch.int16))
+    base = torch.randn(M, sum(Ns), device="cuda").half()
+    acc, outs3 = rows_call(cabi, preps, x, accumulate=True, base=base)
+    col = 0
+    for p, o in zip(preps, outs3):
+        for m in range(M):
+            want = p.matvec(x[m:m + 1].contiguous(), y=base[m:m + 1, col:col + p.L.N].contiguous(), accumulate=True)
+            assert torch.equal(o[m:m + 1].contiguous().view(torch.int16), want.view(torch.int16))
+        col += p.L.N
+
+
+@pytest.mark.parametrize("bits", [4, 3])
+@pytest.mark.parametrize("M", [2, 4, 7, 8])
+def test_drop_in_ops_route_decode_batches_to_the_row_kernel(bits, M):
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    K, N = 4096, 1024
+    q, s, cw, ci, dense = gpu_layer(K, N, bits, 128, seed=bits * 10 + M)
+    x = torch.randn(M, K, device="cuda").half()
+    base = torch.randn(M, N, device="cuda").half()
+    out = base.clone()
+    if bits == 4:
+        qc.vecquant4matmul_cherryq(x, q, cw, ci, s, out, 128)
+    else:
+        qc.vecquant3matmul_cherryq(x, q, cw, ci, s, out, 128, True)
+    torch.cuda.synchronize()
+    ref = base.double().cpu().numpy() + ref64(x, dense)
+    assert rel_err(out.float().cpu().numpy(), ref) <= TIGHT_TOL
