@@ -392,8 +392,8 @@ struct TileLayer {
     auto ws = torch::empty({(int64_t)cq_tlayer_gemm_workspace_bytes(&layer, chunk)}, blob.options());
     auto scratch = scratch_for(x.device());
     uint8_t* sp = scratch.data_ptr<uint8_t>();
-    const __half* xp = (const __half*)x.data_ptr();
-    __half* yp = (__half*)out.data_ptr();
+    const uint16_t* xp = (const uint16_t*)x.data_ptr();      // fp16 elements
+    uint16_t* yp = (uint16_t*)out.data_ptr();
     for (int m0 = 0; m0 < M; m0 += CH) {
       const int rows = M - m0 < CH ? M - m0 : CH;
       check_status(cq_tlayer_gemm(&layer, xp + (size_t)m0 * layer.K, layer.K, yp + (size_t)m0 * layer.N, layer.N, rows,
