@@ -249,7 +249,7 @@ def forward_shared_input(layers, x: torch.Tensor):
             qc.row_layers_matvec(rls, x2, outs, False)
             res = []
             for l, o in zip(layers, outs):
-                o = o.reshape(x.shape[:-1] + (l.out_features,)).to(x.dtype)
+                o = o.contiguous().reshape(x.shape[:-1] + (l.out_features,)).to(x.dtype)
                 if l.bias is not None:
                     o += l.bias
                 res.append(o)
