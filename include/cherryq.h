@@ -230,11 +230,16 @@ int cq_rope_cache(void* q_f16, void* k_f16, const void* v_f16, const float* cos_
 /* Single-query attention over the caches (sequences, max_seq, KV, D), one query per sequence:
  * out (sequences, H, D) = softmax(q . K^T * scale) . V over positions
  * 0..min(position[sequence], max_seq - 1) (device int64), grouped-query heads allowed; head_dim
- * divides 256, max_seq <= 8192 (the reference calls PyTorch's attention,
- * llama/modeling_llama_quant.py:371-419). */
+ * divides 256 (the reference calls PyTorch's attention, llama/modeling_llama_quant.py:371-419).
+ * The positions of a head are divided among several CTAs so that a decode step fills the GPU; they
+ * meet in `workspace`: device memory of cq_attn_decode_workspace_bytes(...) bytes, 16-byte aligned,
+ * zero-filled once before its first use (every launch leaves it ready for the next), not shared by
+ * launches that can overlap on the GPU. */
+size_t cq_attn_decode_workspace_bytes(int sequences, int n_heads, int head_dim, int max_seq);
 int cq_attn_decode(const void* q_f16, const void* k_cache_f16, const void* v_cache_f16,
                    const long long* position, void* out_f16, int sequences, int n_heads,
-                   int n_kv_heads, int head_dim, int max_seq, float scale, cq_stream_t stream);
+                   int n_kv_heads, int head_dim, int max_seq, float scale, void* workspace,
+                   cq_stream_t stream);
 /* out = silu(gate) * up, n elements. */
 int cq_silu_mul(const void* gate_f16, const void* up_f16, void* out_f16, long long n,
                 cq_stream_t stream);

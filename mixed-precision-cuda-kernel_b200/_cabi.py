@@ -19,7 +19,7 @@ SYMBOLS = [
     "cq_pack_tmp_bytes", "cq_pack", "cq_unpack_dense",
     "cq_tlayer_init", "cq_tlayer_prepare", "cq_tlayer_unprepare",
     "cq_layer_matvec_static", "cq_tlayer_gemm_workspace_bytes", "cq_tlayer_gemm",
-    "cq_selftest_bounded_wait", "cq_rmsnorm", "cq_rope_cache", "cq_silu_mul", "cq_attn_decode",
+    "cq_selftest_bounded_wait", "cq_rmsnorm", "cq_rope_cache", "cq_silu_mul", "cq_attn_decode", "cq_attn_decode_workspace_bytes",
     "cq_peer_region_bytes", "cq_peer_region_create", "cq_peer_region_destroy", "cq_peer_region_export",
     "cq_peer_region_open", "cq_peer_region_close", "cq_peer_allgather",
     "cq_rlayer_init", "cq_rlayer_prepare", "cq_rlayer_unprepare", "cq_rlayer_check", "cq_rlayer_matvec", "cq_rlayers_matvec", "cq_rlayer_matvec_host", "cq_rlayer_preferred_rows",

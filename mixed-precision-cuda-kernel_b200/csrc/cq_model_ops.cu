@@ -128,22 +128,31 @@ __global__ void silu_mul_kernel(const __half* __restrict__ gate, const __half* _
   }
 }
 
-// Single-query attention over the KV cache (decode): one CTA per query head and sequence (blockIdx.y);
-// q and out are (sequences, H, D), the caches (sequences, max_seq, KV, D).  Positions 0..pos[sequence]
-// take part (pos is read on the device, so the same launch serves every step of a captured graph).
-// Scores and the weighted sum are fp32; softmax over at most `max_seq` positions held in shared memory.
-constexpr int ATT_THREADS = 1024, ATT_WARPS = ATT_THREADS / 32;
+// Single-query attention over the KV cache (decode).  q and out are (sequences, H, D), the caches
+// (sequences, max_seq, KV, D); positions 0..pos[sequence] take part (pos is read on the device, so
+// the same launch serves every step of a captured graph).  A CTA handles one query head of one
+// sequence (blockIdx.x, .y) and one of gridDim.z equal ranges of the positions: with one head per
+// CTA alone a decode step would use H of the 148 SMs and crawl through a long context.  Each CTA
+// computes its range's scores, their maximum m, the sum l of exp(score - m) and the unnormalised
+// weighted sum of V; with one range that is the result, otherwise the CTA that finishes last (an
+// atomic counter per head, which it resets) merges the ranges' (m, l, sum) from `part`.
+// Scores and sums are fp32; a range's scores are held in shared memory.
+constexpr int ATT_THREADS = 512, ATT_WARPS = ATT_THREADS / 32;
+constexpr int ATT_MAX_SPLITS = 32;
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* __restrict__ q,
                                                                   const __half* __restrict__ k_cache,
                                                                   const __half* __restrict__ v_cache,
                                                                   const long long* __restrict__ pos,
-                                                                  __half* __restrict__ out, int H, int KV, int D,
+                                                                  __half* __restrict__ out, float* __restrict__ part,
+                                                                  unsigned int* __restrict__ counters, int H, int KV, int D,
                                                                   int max_seq, float scale) {
   // programmatic dependent launch: let the next kernel start its prologue, then wait for our inputs
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  extern __shared__ float sc[];              // [n_pos] scores, then [ATT_THREADS] reduction scratch
+  extern __shared__ float sc[];              // [range] scores, then [ATT_THREADS] reduction scratch
+  __shared__ int s_last;
   const int head = blockIdx.x, kvh = head / (H / KV), seq = blockIdx.y;
+  const int split = blockIdx.z, nsplit = gridDim.z;
   q += (size_t)seq * H * D;
   out += (size_t)seq * H * D;
   k_cache += (size_t)seq * max_seq * KV * D;
@@ -151,10 +160,15 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // positions beyond the cache are not attended to (the host refuses such steps; this keeps a stray
   // launch inside its shared-memory score array and the caches)
-  const long long p0 = pos[seq];
-  const int n_pos = p0 < 0 ? 1 : (p0 >= max_seq ? max_seq : (int)p0 + 1);
-  float* red = sc + n_pos;
+  const long long pl = pos[seq];
+  const int n_all = pl < 0 ? 1 : (pl >= max_seq ? max_seq : (int)pl + 1);
+  const int range = (max_seq + nsplit - 1) / nsplit;           // shared-memory scores per CTA
+  const int chunk = (n_all + nsplit - 1) / nsplit;              // <= range
+  const int pbeg = split * chunk;
+  const int n_pos = max(0, min(n_all - pbeg, chunk));           // positions pbeg .. pbeg + n_pos - 1
+  float* red = sc + range;
   const __half* qh = q + (size_t)head * D;
+  const __half* kb = k_cache + ((size_t)pbeg * KV + kvh) * D;
   // scores: a warp per position, four positions in flight per warp, lanes over the head dimension
   float lmax = -INFINITY;
   for (int p0 = warp; p0 < n_pos; p0 += 4 * ATT_WARPS) {
@@ -163,7 +177,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int p = p0 + u * ATT_WARPS;
-      kr[u] = k_cache + ((size_t)(p < n_pos ? p : p0) * KV + kvh) * D;
+      kr[u] = kb + (size_t)(p < n_pos ? p : p0) * KV * D;
     }
     for (int d = 2 * lane; d < D; d += 64) {
       const float2 qv = __half22float2(*reinterpret_cast<const __half2*>(qh + d));
@@ -200,16 +214,15 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
   __syncthreads();
   float tot = 0.f;
   for (int i = 0; i < ATT_WARPS; ++i) tot += red[i];
-  const float inv = 1.f / tot;
   __syncthreads();
   // weighted sum: thread (d, part) adds the positions p = part, part + parts, ... (D divides ATT_THREADS)
   const int parts = ATT_THREADS / D;
-  const int d = tid % D, part = tid / D;
+  const int d = tid % D, prt = tid / D;
   float acc0 = 0.f, acc1 = 0.f;
   {
-    const __half* vb = v_cache + (size_t)kvh * D + d;
+    const __half* vb = v_cache + ((size_t)pbeg * KV + kvh) * D + d;
     const size_t vstride = (size_t)KV * D;
-    int p = part;
+    int p = prt;
     for (; p + 7 * parts < n_pos; p += 8 * parts) {       // eight loads in flight
       float v[8];
 #pragma unroll
@@ -224,11 +237,39 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
   }
   red[tid] = acc0 + acc1;
   __syncthreads();
-  if (tid < D) {
-    float v = 0.f;
-    for (int i = 0; i < parts; ++i) v += red[tid + i * D];
-    out[(size_t)head * D + tid] = __float2half(v * inv);
+  float vsum = 0.f;
+  if (tid < D)
+    for (int i = 0; i < parts; ++i) vsum += red[tid + i * D];
+  if (nsplit == 1) {
+    if (tid < D) out[(size_t)head * D + tid] = __float2half(vsum / tot);
+    return;
   }
+  // ---- several ranges: publish (m, l, sum), the last CTA of this head merges
+  const size_t hidx = (size_t)seq * H + head;
+  float* mine = part + (hidx * nsplit + split) * (size_t)(D + 2);
+  if (tid < D) mine[2 + tid] = vsum;
+  if (tid == 0) { mine[0] = m; mine[1] = tot; }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(&counters[hidx], 1u) == (unsigned int)(nsplit - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* all = part + hidx * nsplit * (size_t)(D + 2);
+  float mm = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, __ldcg(all + (size_t)s * (D + 2)));
+  if (tid < D) {
+    float l = 0.f, v = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float* ps = all + (size_t)s * (D + 2);
+      const float ms = __ldcg(ps);
+      const float w = ms == -INFINITY ? 0.f : __expf(ms - mm);       // an empty range carries no weight
+      l += w * __ldcg(ps + 1);
+      v += w * __ldcg(ps + 2 + tid);
+    }
+    out[(size_t)head * D + tid] = __float2half(v / l);
+  }
+  if (tid == 0) counters[hidx] = 0u;                                  // ready for the next launch
 }
 
 int blocks_for(long long total, int threads, int cap) {
@@ -291,16 +332,45 @@ extern "C" int cq_silu_mul(const void* gate, const void* up, void* out, long lon
   return CQ_OK;
 }
 
+namespace {
+// ranges of positions per head: enough CTAs for about two per SM, at least 64 positions per range
+int attn_splits(int sequences, int n_heads, int max_seq) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int s = (2 * sms + sequences * n_heads - 1) / (sequences * n_heads);
+  const int by_len = (max_seq + 63) / 64;
+  if (s > by_len) s = by_len;
+  if (s > ATT_MAX_SPLITS) s = ATT_MAX_SPLITS;
+  return s < 1 ? 1 : s;
+}
+}  // namespace
+
+extern "C" size_t cq_attn_decode_workspace_bytes(int sequences, int n_heads, int head_dim, int max_seq) {
+  if (sequences < 1 || n_heads < 1 || head_dim < 2 || max_seq < 1) return 0;
+  const size_t heads = (size_t)sequences * n_heads;
+  // [heads] counters (zero before the first use; every launch leaves them zero), then the ranges' partial results
+  return heads * sizeof(unsigned int) + 256 + heads * attn_splits(sequences, n_heads, max_seq) * (size_t)(head_dim + 2) * sizeof(float);
+}
+
 extern "C" int cq_attn_decode(const void* q, const void* k_cache, const void* v_cache, const long long* position,
                               void* out, int sequences, int n_heads, int n_kv_heads, int head_dim, int max_seq,
-                              float scale, cq_stream_t stream) {
-  if (!q || !k_cache || !v_cache || !position || !out || sequences < 1 || sequences > 65535) return CQ_ERR_BAD_ARG;
+                              float scale, void* workspace, cq_stream_t stream) {
+  if (!q || !k_cache || !v_cache || !position || !out || !workspace || sequences < 1 || sequences > 65535) return CQ_ERR_BAD_ARG;
+  if ((uintptr_t)workspace & 15) return CQ_ERR_BAD_ARG;
   if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads || head_dim < 2 || head_dim > 256 || (head_dim & 1) ||
-      256 % head_dim || max_seq < 1 || max_seq > 8192)
+      256 % head_dim || max_seq < 1 || max_seq > 65536)
     return CQ_ERR_BAD_SHAPE;
-  const int smem = (max_seq + ATT_THREADS) * (int)sizeof(float);
-  CQ_CUDA_TRY(launch_pdl(attn_decode_kernel, dim3(n_heads, sequences), dim3(ATT_THREADS), (size_t)smem, (cudaStream_t)stream,
-                         (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, position, (__half*)out, n_heads,
-                         n_kv_heads, head_dim, max_seq, scale));
+  const int splits = attn_splits(sequences, n_heads, max_seq);
+  const int range = (max_seq + splits - 1) / splits;
+  const int smem = (range + ATT_THREADS) * (int)sizeof(float);
+  if (smem > 200 * 1024) return CQ_ERR_TOO_LARGE;
+  if (smem > 48 * 1024)
+    CQ_CUDA_TRY(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  const size_t heads = (size_t)sequences * n_heads;
+  unsigned int* counters = (unsigned int*)workspace;
+  float* part = (float*)((uint8_t*)workspace + (heads * sizeof(unsigned int) + 255) / 256 * 256);
+  CQ_CUDA_TRY(launch_pdl(attn_decode_kernel, dim3(n_heads, sequences, splits), dim3(ATT_THREADS), (size_t)smem,
+                         (cudaStream_t)stream, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, position,
+                         (__half*)out, part, counters, n_heads, n_kv_heads, head_dim, max_seq, scale));
   return CQ_OK;
 }

@@ -215,6 +215,7 @@ torch::Tensor unpack_dense(torch::Tensor qweight, torch::Tensor scales, torch::T
 
 std::mutex g_mu;
 std::map<int, torch::Tensor> g_scratch;  // per device: matvec scratch followed by a status word
+std::map<int, torch::Tensor> g_attn_ws;  // per device: workspace of the decode attention
 
 torch::Tensor scratch_for(const torch::Device& dev) {
   std::lock_guard<std::mutex> lock(g_mu);
@@ -532,9 +533,20 @@ torch::Tensor attn_decode(torch::Tensor q, torch::Tensor k_cache, torch::Tensor 
   TORCH_CHECK(k_cache.size(cd - 1) == q.size(2) && v_cache.sizes() == k_cache.sizes(), "caches must be ([B,] max_seq, KV, D)");
   TORCH_CHECK(position.numel() == B, "one position per sequence");
   auto out = torch::empty_like(q);
+  // the ranges of a head meet in a per-device workspace (grow-only, zero-filled when created; launches of one
+  // stream follow one another, which is how the decode harness calls this)
+  const size_t need = cq_attn_decode_workspace_bytes(B, (int)q.size(1), (int)q.size(2), (int)k_cache.size(cd - 3));
+  torch::Tensor ws;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto& slot = g_attn_ws[q.device().index()];
+    if (!slot.defined() || (size_t)slot.numel() < need)
+      slot = torch::zeros({(int64_t)need}, torch::TensorOptions().device(q.device()).dtype(torch::kUInt8));
+    ws = slot;
+  }
   check_status(cq_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), (const long long*)position.data_ptr(),
                               out.data_ptr(), B, (int)q.size(1), (int)k_cache.size(cd - 2), (int)q.size(2),
-                              (int)k_cache.size(cd - 3), 1.0f / std::sqrt((float)q.size(2)), current_stream()),
+                              (int)k_cache.size(cd - 3), 1.0f / std::sqrt((float)q.size(2)), ws.data_ptr(), current_stream()),
                "attn_decode");
   return out;
 }

@@ -104,7 +104,9 @@ def test_fused_elementwise_ops_match_torch(dec):
     assert not bool(kc[untouched].any()) and not bool(vc[untouched].any())
 
 
-@pytest.mark.parametrize("H,KV,D,S,P", [(8, 8, 128, 512, 300), (8, 2, 64, 128, 0), (4, 4, 128, 2048, 2047)])
+@pytest.mark.parametrize("H,KV,D,S,P", [(8, 8, 128, 512, 300), (8, 2, 64, 128, 0), (4, 4, 128, 2048, 2047),
+                                       (64, 8, 128, 4096, 4000), (8, 8, 128, 4096, 3), (2, 1, 256, 8192, 8191),
+                                       (40, 40, 128, 300, 299)])
 def test_attention_decode_matches_torch(dec, H, KV, D, S, P):
     import cherryq_b200
     qc = cherryq_b200.load_quant_cuda()
