@@ -76,13 +76,28 @@ class CherryDecoder:
     PROJ = ("q", "k", "v", "o", "gate", "up", "down")
 
     def __init__(self, cfg: DecoderConfig, device="cuda", seed: int = 0, dense: bool = False,
-                 release_reference_buffers: bool = False, tp_group=None, tp_gather: str = "peer", batch: int = 1):
+                 release_reference_buffers: bool = False, tp_group=None, tp_gather: str = "peer", batch: int = 1,
+                 attention: str = "auto"):
         if not torch.cuda.is_available():
             raise RuntimeError("CherryDecoder needs a CUDA device (there is no CPU path)")
         if batch < 1:
             raise ValueError("batch must be at least 1")
         self.cfg, self.dev, self.dense = cfg, torch.device(device), dense
         self.batch = batch          # sequences decoded in lockstep (same prompt length, one position counter)
+        # decode attention over the KV cache: "own" = this library's kernel (cq_attn_decode); "flash" = the
+        # flash_attn package's flash_attn_with_kvcache (a library call, like the lm_head's cuBLAS matmul: it reads
+        # a KV head once for all the query heads that share it, which matters for grouped-query models at long
+        # context); "auto" = flash where that package imports, else own
+        if attention not in ("auto", "own", "flash"):
+            raise ValueError("attention is 'auto', 'own' or 'flash'")
+        self._flash = None
+        if attention in ("auto", "flash"):
+            try:
+                from flash_attn import flash_attn_with_kvcache
+                self._flash = flash_attn_with_kvcache
+            except Exception:
+                if attention == "flash":
+                    raise
         self.qc = load_quant_cuda()
         self.group = tp_group
         if tp_group is not None:
@@ -202,7 +217,11 @@ class CherryDecoder:
         q, k, v = q.view(t, nh, hd), k.view(t, kv, hd), v.view(t, kv, hd)
         self.qc.rope_cache(q, k, v, self.cos, self.sin, pos, self.k_cache[li], self.v_cache[li])
         if decode:
-            a = self.qc.attn_decode(q, self.k_cache[li], self.v_cache[li], pos).view(t, nh * hd)
+            if self._flash is not None:
+                a = self._flash(q.view(t, 1, nh, hd), self.k_cache[li], self.v_cache[li],
+                                cache_seqlens=(pos + 1).to(torch.int32), causal=True).view(t, nh * hd)
+            else:
+                a = self.qc.attn_decode(q, self.k_cache[li], self.v_cache[li], pos).view(t, nh * hd)
         else:
             ts = t // nb              # tokens per sequence; rows are (sequence, token)
             a = F.scaled_dot_product_attention(q.view(nb, ts, nh, hd).transpose(1, 2), k.view(nb, ts, kv, hd).transpose(1, 2),

@@ -178,13 +178,16 @@ def test_device_side_position_guards():
     assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("attention", ["own", "flash"])
 @pytest.mark.parametrize("bits,kv,batch", [(4, 4, 3), (3, 2, 5)])
-def test_batched_decode_matches_single_sequences(dec, bits, kv, batch):
+def test_batched_decode_matches_single_sequences(dec, bits, kv, batch, attention):
     """`batch` sequences in lockstep (their own KV caches, four activation rows per kernel launch) against
     one decoder per sequence with the same weights, teacher-forced with the batch's tokens."""
+    if attention == "flash":
+        pytest.importorskip("flash_attn")
     cfg = tiny(dec, bits, kv)
-    big = dec.CherryDecoder(cfg, seed=5, batch=batch)
-    singles = [dec.CherryDecoder(cfg, seed=5) for _ in range(batch)]
+    big = dec.CherryDecoder(cfg, seed=5, batch=batch, attention=attention)
+    singles = [dec.CherryDecoder(cfg, seed=5, attention="own") for _ in range(batch)]
     prompts = torch.randint(0, cfg.vocab, (batch, 21), device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
     lb = big.prefill(prompts)
     scale = float(lb.float().abs().max())
