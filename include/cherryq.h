@@ -149,7 +149,13 @@ int cq_layer_matvec_static(const cq_layer* layer, const void* x_f16, int ldx, vo
  * followed by
  *   perm    [groups x 128] uint16: original column of each compact column, K past K'
  *   cidx    [Cp] uint16 sorted cherry columns, K past C
- * Same role as cq_layer; no scratch.
+ *   work    only for layers of more than 64 groups (K - C > 8192), whose tiles are shared by ksplit
+ *           CTAs, each taking a part of the columns: [ksplit][NT][4][16] fp32 partial sums and [NT]
+ *           uint32 arrival counters (zeroed by cq_rlayer_prepare, left zero by every launch).  The
+ *           CTA that arrives last adds the parts in part order, so results do not depend on timing.
+ *           Launches of such a layer that can overlap on the GPU (different streams) would share
+ *           this area: serialise them.
+ * Same role as cq_layer; no caller-provided scratch.
  * ---------------------------------------------------------------------- */
 typedef struct cq_rlayer {
   int32_t bits, K, N, C, G;
@@ -159,7 +165,8 @@ typedef struct cq_rlayer {
   int32_t Cp;          /* C rounded up to 16                                             */
   int32_t NT;          /* 16-row tiles = ceil(N / 16)                                    */
   int32_t tile_bytes;  /* NG * 256 * bits + NG * sets * 32 + Cp / 16 * 512               */
-  uint64_t off_tiles, off_perm, off_cidx, blob_bytes;
+  int32_t ksplit;      /* CTAs that share a tile, each taking NG / ksplit groups: ceil(NG / 64) */
+  uint64_t off_tiles, off_perm, off_cidx, off_work, blob_bytes;
   void* blob;          /* device memory, blob_bytes long, 256-byte aligned               */
 } cq_rlayer;
 
@@ -174,15 +181,15 @@ int cq_rlayer_unprepare(const cq_rlayer* layer, uint8_t* qweight, void* scales_f
  * return (CQ_ERR_UNSUPPORTED / CQ_ERR_TOO_LARGE); no GPU work. */
 int cq_rlayer_check(const cq_rlayer* layer);
 /* y (N) fp16 = [y +] x (K) fp16 . W^T, one activation row; allocates nothing, needs no scratch.
- * CQ_ERR_UNSUPPORTED for layers outside the kernel's envelope (K - C > 15360 columns, more than 240
- * cherry columns, or more than 248 cherry columns inside one warp's column range) and
+ * CQ_ERR_UNSUPPORTED for layers outside the kernel's envelope (more than 256 cherry columns, or more
+ * than 248 cherry columns inside one warp's column range) and
  * CQ_ERR_TOO_LARGE when not even two tiles fit shared memory: use cq_layer_matvec for those.
  * status_word: device uint32 that receives CQ_ERR_DEVICE_TIMEOUT bits if a bounded wait on the
  * kernel's own bulk copies ever runs out; may be NULL. */
 int cq_rlayer_matvec(const cq_rlayer* layer, const void* x_f16, void* y_f16, int accumulate,
                      uint32_t* status_word, cq_stream_t stream);
 /* The largest batch for which cq_rlayers_matvec is the faster path for this layer (beyond it
- * cq_tlayer_gemm is): 16 for layers of up to 8192 quantized columns, 4 for wider ones, 0 for layers
+ * cq_tlayer_gemm is): 16 for layers of up to 8192 quantized columns, 8 for wider ones, 0 for layers
  * the kernel does not take.  No GPU work. */
 int cq_rlayer_preferred_rows(const cq_rlayer* layer);
 /* cq_rlayer_matvec for callers that hold their activations in HOST memory (a foreign-function
@@ -202,7 +209,7 @@ int cq_rlayer_matvec_host(const cq_rlayer* layer, const void* x_host_f16, void* 
  * (CQ_ERR_BAD_SHAPE otherwise); the SMs are divided among them in proportion to their rows.  Up to
  * four activation rows ride in one launch (they fill the unused columns of the same integer MMAs:
  * a row more costs about a quarter of a launch); more rows are walked in slices of four, each reading
- * the weights again.  Layers of more than 8192 quantized columns take one row per launch.
+ * the weights again.
  * Every output element is computed exactly as by cq_rlayer_matvec on that layer and row alone
  * (bit-identical).  Same limits and status word. */
 int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, const void* x_f16, int ldx,

@@ -43,8 +43,8 @@ class cq_tlayer(C.Structure):
 
 class cq_rlayer(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
-                ("bits", "K", "N", "C", "G", "Kc", "NG", "sets", "Cp", "NT", "tile_bytes")]
-    _fields_ += [(n, C.c_uint64) for n in ("off_tiles", "off_perm", "off_cidx", "blob_bytes")]
+                ("bits", "K", "N", "C", "G", "Kc", "NG", "sets", "Cp", "NT", "tile_bytes", "ksplit")]
+    _fields_ += [(n, C.c_uint64) for n in ("off_tiles", "off_perm", "off_cidx", "off_work", "blob_bytes")]
     _fields_ += [("blob", C.c_void_p)]
 
 

@@ -43,6 +43,7 @@ constexpr int RV_MAX_SLOTS = 16;            // ring slots (tiles resident in sha
 
 constexpr int RV_MAX_SEG = 4;               // layers one launch can serve (they share the activations)
 constexpr int RV_MAX_ROWS = 4;              // activation rows one launch can serve (two MMA columns each)
+constexpr int RV_MAX_KSPLIT = 8;            // CTAs that can share a tile, each taking a part of the columns
 
 // One layer of a launch: a range of CTAs works on it.
 struct RowvecSeg {
@@ -50,9 +51,11 @@ struct RowvecSeg {
   const uint16_t* perm;     // [NG * 128] original column of each compact column, K for padding
   const uint16_t* cidx;     // [Cp] sorted cherry columns
   __half* y;
-  int N;
+  float* work;              // [ks][NT][M][16] partial sums of the column parts (layers split along K only)
+  unsigned int* counters;   // [NT] arrivals per unit, indexed by the unit's first tile; zero between launches
+  int N, NT;
   int cta0;                 // first CTA of the range
-  int tiles_q, tiles_r;     // CTA b of the range owns tiles_q (+1 if b < tiles_r) consecutive tiles
+  int tiles_q, tiles_r;     // unit u of the range (ks consecutive CTAs) owns tiles_q (+1 if u < tiles_r) consecutive tiles
 };
 
 struct RowvecParams {
@@ -62,7 +65,13 @@ struct RowvecParams {
   int M, ldx, ldy;          // activation rows of the call (1..4) and the row strides of x and y, in elements
   uint32_t* status;         // may be null
   int K, C, NG, ncb;        // common to the layers of a launch; ncb = cherry blocks of 16 columns
-  int tile_bytes, scal_off, cher_off;
+  int tile_bytes, scal_off, cher_off;        // a tile record in global memory
+  // Layers of more than 64 groups are split along K: ks consecutive CTAs (a unit) share their tiles, CTA j of a
+  // unit takes groups [j NGp, (j + 1) NGp) (and the cherry columns if j == 0) and keeps only that part of a
+  // tile in its ring slot; the unit's CTA that finishes last adds the parts' sums in part order.
+  int ks, NGp;
+  int grp_bytes, set_bytes;                  // 256 * bits; sets * 32 (scales of one group)
+  int slot_bytes, scal_off_s, cher_off_s;    // a ring slot: [groups of the part][their scales][cherry blocks]
   int slots;                // ring slots in use
   int inflight;             // tiles the copy warp keeps outstanding
   int slice_halves;         // halves of a warp's raw activation slice in shared memory
@@ -162,16 +171,31 @@ __device__ __forceinline__ void rv_stamp(unsigned long long* buf, int launch, in
 #define RV_STAMP(s)
 #endif
 
-// Requests tile `tile` of the layer into ring slot `slot`; one thread calls it.
-__device__ __forceinline__ void issue_tile(const RowvecParams& p, const uint8_t* tiles, unsigned char* stiles, uint32_t bar_full, int tile, int slot) {
+// Requests tile `tile` of the layer (the groups [gb, gb + gn) of it, with the cherry blocks if `cherry`)
+// into ring slot `slot`; one thread calls it.
+__device__ __forceinline__ void issue_tile(const RowvecParams& p, const uint8_t* tiles, unsigned char* stiles, uint32_t bar_full,
+                                           int tile, int slot, int gb, int gn, bool cherry) {
   const uint8_t* src = tiles + (size_t)tile * p.tile_bytes;
-  const uint32_t dst = rv_smem_u32(stiles) + (uint32_t)slot * p.tile_bytes;
+  const uint32_t dst = rv_smem_u32(stiles) + (uint32_t)slot * p.slot_bytes;
   const uint32_t bar = bar_full + 8 * slot;
-  rv_mbar_expect_tx(bar, (uint32_t)p.tile_bytes);
-  for (uint32_t off = 0; off < (uint32_t)p.tile_bytes; off += 32768) {
-    const uint32_t sz = (uint32_t)p.tile_bytes - off < 32768 ? (uint32_t)p.tile_bytes - off : 32768;
-    rv_bulk_g2s(dst + off, src + off, sz, bar);
+  if (p.ks == 1) {                       // the whole record, which is also the slot's layout
+    rv_mbar_expect_tx(bar, (uint32_t)p.tile_bytes);
+    for (uint32_t off = 0; off < (uint32_t)p.tile_bytes; off += 32768) {
+      const uint32_t sz = (uint32_t)p.tile_bytes - off < 32768 ? (uint32_t)p.tile_bytes - off : 32768;
+      rv_bulk_g2s(dst + off, src + off, sz, bar);
+    }
+    return;
   }
+  const uint32_t gbytes = (uint32_t)gn * p.grp_bytes, sbytes = (uint32_t)gn * p.set_bytes;
+  const uint32_t cbytes = cherry ? (uint32_t)p.ncb * 512u : 0u;
+  rv_mbar_expect_tx(bar, gbytes + sbytes + cbytes);
+  const uint8_t* gsrc = src + (size_t)gb * p.grp_bytes;
+  for (uint32_t off = 0; off < gbytes; off += 32768) {
+    const uint32_t sz = gbytes - off < 32768 ? gbytes - off : 32768;
+    rv_bulk_g2s(dst + off, gsrc + off, sz, bar);
+  }
+  rv_bulk_g2s(dst + p.scal_off_s, src + p.scal_off + (size_t)gb * p.set_bytes, sbytes, bar);
+  if (cbytes) rv_bulk_g2s(dst + p.cher_off_s, src + p.cher_off, cbytes, bar);
 }
 
 // BITS 3 | 4; SETS scale sets per 128 columns (2 for 64-wide groups); W working warps per CTA plus
@@ -182,7 +206,7 @@ __device__ __forceinline__ void issue_tile(const RowvecParams& p, const uint8_t*
 template <int BITS, int SETS, int W, int GPW, int MR>
 __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const RowvecParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int s_abort;
+  __shared__ int s_abort, s_last;
   constexpr int NTHR = (W + 1) * 32;
   constexpr int GRP_BYTES = 256 * BITS;      // 16 rows x 128 codes
   constexpr int PVW = (GPW + 1) / 2;         // octets of activations a lane stages (16 per group, 32 lanes)
@@ -206,8 +230,13 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
     if (s < p.nseg && (int)blockIdx.x >= p.seg[s].cta0) si = s;
   const RowvecSeg& sg = p.seg[si];
   const int bseg = (int)blockIdx.x - sg.cta0;
-  const int tile0 = bseg * sg.tiles_q + min(bseg, sg.tiles_r);
-  const int nt = sg.tiles_q + (bseg < sg.tiles_r ? 1 : 0);
+  const int ks = p.ks;
+  const int unit = ks == 1 ? bseg : bseg / ks;            // CTAs of a unit share tiles, each takes a part of the columns
+  const int kpart = ks == 1 ? 0 : bseg - unit * ks;
+  const int tile0 = unit * sg.tiles_q + min(unit, sg.tiles_r);
+  const int nt = sg.tiles_q + (unit < sg.tiles_r ? 1 : 0);
+  const int gb = kpart * p.NGp;                           // first group of this CTA's part
+  const int NGl = min(p.NG - gb, p.NGp);                  // its groups
   const int S = p.slots;
 
   if (tid == 0) {
@@ -238,7 +267,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
         if (next >= S) {                            // the slot's previous tile must have been consumed
           rv_mbar_wait(bar_empty + 8 * slot, ephase, &s_abort, p.status);
         }
-        issue_tile(p, seg_tiles, stiles, bar_full, tile0 + next, slot);
+        issue_tile(p, seg_tiles, stiles, bar_full, tile0 + next, slot, gb, NGl, kpart == 0);
         if (++slot == S) { slot = 0; if (next >= S) ephase ^= 1u; }
       }
     }
@@ -252,16 +281,16 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
 #endif
   } else {
   // ---- this warp's groups (contiguous) and cherry block
-  const int NG = p.NG;
   const uint16_t* seg_perm = sg.perm;
-  const int gq = NG / W, gr = NG % W;
+  const int gq = NGl / W, gr = NGl % W;
   const int ngw = gq + (warp < gr ? 1 : 0);
-  const int gstart = warp * gq + min(warp, gr);
-  const bool has_cherry = warp < p.ncb;                      // cherry block `warp`
+  const int gstart = warp * gq + min(warp, gr);              // within the CTA's part (= within its ring slots)
+  const int g0 = gb + gstart;                                // within the layer
+  const bool has_cherry = warp < p.ncb && kpart == 0;        // cherry block `warp`
   // the original columns the warp's compact columns span: [lo, hi]; the slice starts at lo rounded down to 8
   int lo8 = 0, nchunk = 0;
   if (ngw > 0) {
-    const int kc0 = gstart * 128, kc1 = min(p.K - p.C, (gstart + ngw) * 128) - 1;
+    const int kc0 = g0 * 128, kc1 = min(p.K - p.C, (g0 + ngw) * 128) - 1;
     const int lo = seg_perm[kc0], hi = seg_perm[kc1];
     lo8 = lo & ~7;
     nchunk = (hi - lo8) / 8 + 1;
@@ -277,14 +306,14 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
     const int ol = lane + 32 * u;
     uint4 c = make_uint4(0, 0, 0, 0);
     if (ol < ngw * 16) {
-      c = *reinterpret_cast<const uint4*>(seg_perm + ((size_t)gstart * 16 + ol) * 8);
+      c = *reinterpret_cast<const uint4*>(seg_perm + ((size_t)g0 * 16 + ol) * 8);
       const uint32_t sub = (uint32_t)lo8 * 0x10001u;
       c.x = (c.x - sub) * 2u; c.y = (c.y - sub) * 2u; c.z = (c.z - sub) * 2u; c.w = (c.w - sub) * 2u;
     }
     pv[u] = c;
   }
   (void)padpair;
-  const bool owns_tail = ngw > 0 && gstart + ngw == NG;     // the warp whose last group may hold padding columns
+  const bool owns_tail = ngw > 0 && g0 + ngw == p.NG;       // the warp whose last group may hold padding columns
   int ccol = -1;
   if (has_cherry && lane < 16 && warp * 16 + lane < p.C) ccol = sg.cidx[warp * 16 + lane];
   const bool x_aligned = ((reinterpret_cast<uintptr_t>(p.x) | (uintptr_t)(p.ldx * 2)) & 15) == 0;
@@ -472,8 +501,8 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   // the ring slot's offset kept incrementally, everything else is a compile-time displacement.
   const unsigned char* gp0 = stiles + (size_t)gstart * GRP_BYTES + lane * 16;
   const unsigned char* gq0 = stiles + (size_t)gstart * GRP_BYTES + 512 + lane * (BITS == 4 ? 16 : 8);
-  const unsigned char* sp0 = stiles + p.scal_off + (gstart * SETS * 8 + g8) * 4;
-  const unsigned char* cp0 = stiles + p.cher_off + warp * 512 + lane * 16;
+  const unsigned char* sp0 = stiles + p.scal_off_s + (gstart * SETS * 8 + g8) * 4;
+  const unsigned char* cp0 = stiles + p.cher_off_s + warp * 512 + lane * 16;
   float* pp = part + (warp * Mrows + t4) * 16 + g8;
   int slot = 0;
   uint32_t slot_off = 0, phase = 0;
@@ -556,7 +585,7 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
       if (lane == 0) rv_mbar_arrive(bar_empty + 8 * slot);
     }
     ++slot;
-    slot_off += (uint32_t)p.tile_bytes;
+    slot_off += (uint32_t)p.slot_bytes;
     if (slot == S) { slot = 0; slot_off = 0; phase ^= 1u; }
   }
   RV_STAMP(4);
@@ -567,17 +596,51 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   __half* y = sg.y;
   const int N = sg.N;
   const int M = MR == 1 ? 1 : p.M;
-  for (int idx = tid; idx < nt * 16 * M; idx += NTHR) {
-    const int tl = idx / (16 * M), rem = idx - tl * 16 * M;
-    const int m = rem >> 4, r = rem & 15;
-    const int row = row0 + tl * 16 + r;
-    if (row < N) {
-      const float* pp = part + ((size_t)tl * W * M + m) * 16 + r;
-      __half* yo = y + (size_t)m * p.ldy + row;
-      float acc = p.accumulate ? __half2float(*yo) : 0.f;
+  if (ks == 1) {
+    for (int idx = tid; idx < nt * 16 * M; idx += NTHR) {
+      const int tl = idx / (16 * M), rem = idx - tl * 16 * M;
+      const int m = rem >> 4, r = rem & 15;
+      const int row = row0 + tl * 16 + r;
+      if (row < N) {
+        const float* pp = part + ((size_t)tl * W * M + m) * 16 + r;
+        __half* yo = y + (size_t)m * p.ldy + row;
+        float acc = p.accumulate ? __half2float(*yo) : 0.f;
+#pragma unroll
+        for (int w = 0; w < W; ++w) acc += pp[w * M * 16];
+        *yo = __float2half_rn(acc);
+      }
+    }
+  } else {
+    // this part's sums -> global; the CTA of the unit that arrives last adds the parts in part order
+    const size_t per_part = (size_t)sg.NT * 16 * M;
+    float* mine = sg.work + kpart * per_part + (size_t)tile0 * 16 * M;
+    for (int idx = tid; idx < nt * 16 * M; idx += NTHR) {
+      const int tl = idx / (16 * M), rem = idx - tl * 16 * M;
+      const float* pp = part + ((size_t)tl * W * M + (rem >> 4)) * 16 + (rem & 15);
+      float acc = 0.f;
 #pragma unroll
       for (int w = 0; w < W; ++w) acc += pp[w * M * 16];
-      *yo = __float2half_rn(acc);
+      mine[idx] = acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&sg.counters[tile0], 1u) == (unsigned int)(ks - 1);
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      const float* all = sg.work + (size_t)tile0 * 16 * M;
+      for (int idx = tid; idx < nt * 16 * M; idx += NTHR) {
+        const int tl = idx / (16 * M), rem = idx - tl * 16 * M;
+        const int m = rem >> 4, r = rem & 15;
+        const int row = row0 + tl * 16 + r;
+        if (row < N) {
+          __half* yo = y + (size_t)m * p.ldy + row;
+          float acc = p.accumulate ? __half2float(*yo) : 0.f;
+          for (int j = 0; j < ks; ++j) acc += __ldcg(all + j * per_part + idx);
+          *yo = __float2half_rn(acc);
+        }
+      }
+      if (tid == 0) sg.counters[tile0] = 0u;               // ready for the next launch
     }
   }
   RV_STAMP(5);
@@ -788,23 +851,20 @@ RvDevice rv_device(int dev) {
 
 inline int rv_align(int v, int a) { return (v + a - 1) / a * a; }
 
-// Kernel shapes of the product: working warps x groups a warp can own.  16 warps (+ the copy warp) leave
-// 96 registers per thread, which holds the activations of up to 4 groups; wider layers take 15 warps
-// (16 in all: 128 registers) owning up to 8 groups each, one activation row per launch (the staging of
-// several rows does not fit the registers beside 8 groups of activations; measured, a launch per row is
-// as fast there).  0 = no shape holds the layer.
-constexpr int RV_W = 16, RV_W_WIDE = 15, RV_GPW_WIDE = 8;
+// Kernel shapes of the product: 16 working warps (+ the copy warp: 96 registers per thread) that own up to 2
+// or up to 4 groups each, i.e. up to 64 groups per CTA; wider layers are split along K among several CTAs
+// per tile (cq_rlayer.ksplit), which keeps every CTA inside these shapes.  0 = no shape holds the layer.
+constexpr int RV_W = 16;
+inline int rv_part_groups(const cq_rlayer* L) { return (L->NG + L->ksplit - 1) / L->ksplit; }   // groups a CTA works on
 inline int rv_gpw_for(const cq_rlayer* L) {
-  const int need = (L->NG + RV_W - 1) / RV_W;
-  if (need <= 2) return 2;
-  if (need <= 4) return 4;
-  return (L->NG + RV_W_WIDE - 1) / RV_W_WIDE <= RV_GPW_WIDE ? RV_GPW_WIDE : 0;
+  if (L->ksplit < 1 || L->ksplit > RV_MAX_KSPLIT) return 0;
+  const int need = (rv_part_groups(L) + RV_W - 1) / RV_W;
+  return need <= 2 ? 2 : (need <= 4 ? 4 : 0);
 }
-inline int rv_w_for(int gpw) { return gpw == RV_GPW_WIDE ? RV_W_WIDE : RV_W; }
 
 template <int W, int GPW>
 RowvecFn rv_pick(int bits, int sets, int M = 1) {
-  if (M == 1 || GPW == RV_GPW_WIDE) {          // (the wide shape exists for one row only)
+  if (M == 1) {
     if (bits == 4) return cq_rowvec_kernel<4, 1, W, GPW, 1>;
     return sets == 1 ? cq_rowvec_kernel<3, 1, W, GPW, 1> : cq_rowvec_kernel<3, 2, W, GPW, 1>;
   }
@@ -821,30 +881,34 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
   if (n < 1 || n > RV_MAX_SEG || M < 1 || M > RV_MAX_ROWS) return CQ_ERR_BAD_ARG;
   const cq_rlayer* L = Ls[0];
   for (int i = 1; i < n; ++i)
-    if (Ls[i]->bits != L->bits || Ls[i]->K != L->K || Ls[i]->C != L->C || Ls[i]->G != L->G) return CQ_ERR_BAD_SHAPE;
-  if ((L->NG + W - 1) / W > GPW) return CQ_ERR_UNSUPPORTED;
+    if (Ls[i]->bits != L->bits || Ls[i]->K != L->K || Ls[i]->C != L->C || Ls[i]->G != L->G || Ls[i]->ksplit != L->ksplit) return CQ_ERR_BAD_SHAPE;
+  const int ks = L->ksplit, ngp = rv_part_groups(L);
+  if (ks < 1 || ks > RV_MAX_KSPLIT) return CQ_ERR_UNSUPPORTED;
+  if ((ngp + W - 1) / W > GPW) return CQ_ERR_UNSUPPORTED;
   if (L->Cp / 16 > W) return CQ_ERR_UNSUPPORTED;
   if (GPW * 128 + L->C + 8 > (GPW / 2 + 1) * 256) return CQ_ERR_UNSUPPORTED;   // a warp's slice of x: XCH pieces per lane
-  // CTAs per layer: every layer at least one, the rest to whichever layer has the most tiles per CTA
+  // units (ks CTAs sharing their tiles) per layer: every layer at least one, the rest to whichever layer has
+  // the most tiles per unit
+  const int units_avail = di.sms / ks;
   long long total = 0;
   for (int i = 0; i < n; ++i) total += Ls[i]->NT;
-  int ctas[RV_MAX_SEG];
+  int ctas[RV_MAX_SEG];                           // units per layer
   int grid = 0;
-  if (total <= di.sms) {
+  if (total <= units_avail) {
     for (int i = 0; i < n; ++i) { ctas[i] = Ls[i]->NT; grid += ctas[i]; }
   } else {
-    if (di.sms < n) return CQ_ERR_NO_DEVICE;
+    if (units_avail < n) return CQ_ERR_NO_DEVICE;
     for (int i = 0; i < n; ++i) {
-      ctas[i] = (int)((long long)di.sms * Ls[i]->NT / total);
+      ctas[i] = (int)((long long)units_avail * Ls[i]->NT / total);
       if (ctas[i] < 1) ctas[i] = 1;
       grid += ctas[i];
     }
-    while (grid > di.sms) {                      // (rounding up the small layers can overshoot)
+    while (grid > units_avail) {                 // (rounding up the small layers can overshoot)
       int big = 0;
       for (int i = 1; i < n; ++i) if (ctas[i] > ctas[big]) big = i;
       --ctas[big]; --grid;
     }
-    for (; grid < di.sms; ++grid) {
+    for (; grid < units_avail; ++grid) {
       int worst = -1, worst_t = 0;
       for (int i = 0; i < n; ++i) {
         const int t = (Ls[i]->NT + ctas[i] - 1) / ctas[i];
@@ -854,24 +918,32 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
       ++ctas[worst];
     }
   }
+  grid *= ks;
   int nt_max = 0, cta0 = 0;
   for (int i = 0; i < n; ++i) {
     RowvecSeg& sg = p->seg[i];
     sg.N = Ls[i]->N;
+    sg.NT = Ls[i]->NT;
     sg.cta0 = cta0;
     sg.tiles_q = Ls[i]->NT / ctas[i];
     sg.tiles_r = Ls[i]->NT % ctas[i];
     const int t = (Ls[i]->NT + ctas[i] - 1) / ctas[i];
     if (t > nt_max) nt_max = t;
-    cta0 += ctas[i];
+    cta0 += ctas[i] * ks;
   }
   p->nseg = n;
   p->K = L->K; p->C = L->C; p->NG = L->NG; p->ncb = L->Cp / 16;
   p->tile_bytes = L->tile_bytes;
-  p->scal_off = L->NG * 256 * L->bits;
-  p->cher_off = p->scal_off + L->NG * L->sets * 32;
+  p->grp_bytes = 256 * L->bits;
+  p->set_bytes = L->sets * 32;
+  p->scal_off = L->NG * p->grp_bytes;
+  p->cher_off = p->scal_off + L->NG * p->set_bytes;
+  p->ks = ks; p->NGp = ngp;
+  p->scal_off_s = ngp * p->grp_bytes;
+  p->cher_off_s = p->scal_off_s + ngp * p->set_bytes;
+  p->slot_bytes = p->cher_off_s + p->ncb * 512;        // ks == 1: the record itself (ngp == NG)
   // a warp's staging area: the raw slice (its column range + alignment slack + zero slot), later its planes
-  const int gmax = (L->NG + W - 1) / W;
+  const int gmax = (ngp + W - 1) / W;
   p->slice_halves = rv_align(gmax * 128 + L->C + 8 + 8 + 8, 8);
   if (p->slice_halves < gmax * 128) p->slice_halves = gmax * 128;     // planes: 256 bytes per group
   int off = 0;
@@ -881,7 +953,7 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
   p->off_tiles = off;
   int budget = di.max_smem - 1024;          // the kernel also has a small static allocation; keep clear of the limit
   if (smem_kb > 0 && smem_kb * 1024 < budget) budget = smem_kb * 1024;
-  int slots = (budget - off) / L->tile_bytes;
+  int slots = (budget - off) / p->slot_bytes;
   if (slots > nt_max) slots = nt_max;
   if (slots > RV_MAX_SLOTS) slots = RV_MAX_SLOTS;
   if (slots < 1 || (slots < 2 && nt_max > 1)) return CQ_ERR_TOO_LARGE;
@@ -891,7 +963,7 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
   if (inflight <= 0) inflight = nt_max >= 3 ? 2 : 1;
   p->inflight = inflight > slots ? slots : inflight;
   *grid_out = grid;
-  *smem_out = off + slots * L->tile_bytes;
+  *smem_out = off + slots * p->slot_bytes;
   return CQ_OK;
 }
 
@@ -915,6 +987,8 @@ int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_r
     p.seg[i].perm = (const uint16_t*)(blob + Ls[j]->off_perm);
     p.seg[i].cidx = (const uint16_t*)(blob + Ls[j]->off_cidx);
     p.seg[i].y = ys[j];
+    p.seg[i].work = (float*)(blob + Ls[j]->off_work);
+    p.seg[i].counters = (unsigned int*)(blob + Ls[j]->off_work + (size_t)Ls[j]->ksplit * Ls[j]->NT * 16 * RV_MAX_ROWS * sizeof(float));
     if (i >= n) { p.seg[i].N = 0; p.seg[i].cta0 = grid; p.seg[i].tiles_q = 0; p.seg[i].tiles_r = 0; }
   }
   p.x = x; p.status = status;
@@ -970,6 +1044,14 @@ extern "C" int cq_rlayer_init(cq_rlayer* L, int bits, int K, int N, int C, int G
   L->off_tiles = off;  off += (uint64_t)L->NT * L->tile_bytes;        off = (off + 255) / 256 * 256;
   L->off_perm = off;   off += (uint64_t)L->NG * 128 * 2;              off = (off + 255) / 256 * 256;
   L->off_cidx = off;   off += (uint64_t)(L->Cp > 0 ? L->Cp : 16) * 2; off = (off + 255) / 256 * 256;
+  // layers of more than 64 groups are split along K among ksplit CTAs per tile; their partial sums
+  // ([ksplit][NT][4 rows][16] fp32) and arrival counters ([NT] uint32) live behind the tables
+  L->ksplit = (L->NG + 63) / 64;
+  L->off_work = off;
+  if (L->ksplit > 1) {
+    off += (uint64_t)L->ksplit * L->NT * 16 * RV_MAX_ROWS * sizeof(float) + (uint64_t)L->NT * sizeof(uint32_t);
+    off = (off + 255) / 256 * 256;
+  }
   L->blob_bytes = off;
   L->blob = blob;
   return CQ_OK;
@@ -982,6 +1064,8 @@ extern "C" int cq_rlayer_prepare(const cq_rlayer* L, const uint8_t* qweight, con
   if ((uintptr_t)L->blob & 255) return CQ_ERR_BAD_ARG;
   const RlayerDev d = rl_view(L);
   cudaStream_t st = (cudaStream_t)stream;
+  if (L->blob_bytes > L->off_work)
+    CQ_CUDA_TRY(cudaMemsetAsync((uint8_t*)L->blob + L->off_work, 0, L->blob_bytes - L->off_work, st));
   rl_prepare_codes_kernel<<<2048, 256, 0, st>>>(d, qweight);
   CQ_CUDA_TRY(cudaGetLastError());
   rl_prepare_rest_kernel<<<1024, 256, 0, st>>>(d, (const __half*)scales, (const __half*)cherry_weight, cherry_indices);
@@ -1010,7 +1094,7 @@ extern "C" int cq_rlayer_check(const cq_rlayer* L) {
   if (!gpw) return CQ_ERR_UNSUPPORTED;
   RowvecParams p;
   int grid = 0, smem = 0;
-  return rv_plan(rv_w_for(gpw), gpw, CQ_ROWVEC_INFLIGHT, 0, &L, 1, RV_MAX_ROWS, di, &p, &grid, &smem);
+  return rv_plan(RV_W, gpw, CQ_ROWVEC_INFLIGHT, 0, &L, 1, RV_MAX_ROWS, di, &p, &grid, &smem);
 }
 
 extern "C" int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, const void* x, int ldx, void* const* ys, int ldy,
@@ -1025,11 +1109,9 @@ extern "C" int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, c
   const cq_rlayer* L = layers[0];
   if (ldx < L->K || ldy < nmax) return CQ_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
-  // up to RV_MAX_ROWS activation rows per launch (one for the wide shape); more rows are walked in slices,
-  // each reading the weights again
-  const int per_launch = rv_gpw_for(L) == RV_GPW_WIDE ? 1 : RV_MAX_ROWS;
-  for (int m0 = 0; m0 < M; m0 += per_launch) {
-    const int rows = M - m0 < per_launch ? M - m0 : per_launch;
+  // up to RV_MAX_ROWS activation rows per launch; more rows are walked in slices, each reading the weights again
+  for (int m0 = 0; m0 < M; m0 += RV_MAX_ROWS) {
+    const int rows = M - m0 < RV_MAX_ROWS ? M - m0 : RV_MAX_ROWS;
     const __half* xp = (const __half*)x + (size_t)m0 * ldx;
     __half* yp[RV_MAX_SEG];
     for (int i = 0; i < n_layers; ++i) yp[i] = (__half*)ys[i] + (size_t)m0 * ldy;
@@ -1037,7 +1119,6 @@ extern "C" int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, c
     switch (rv_gpw_for(L)) {
       case 2: rc = rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, rows), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
       case 4: rc = rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, rows), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
-      case RV_GPW_WIDE: rc = rv_launch(rv_pick<RV_W_WIDE, RV_GPW_WIDE>(L->bits, L->sets, rows), RV_W_WIDE, RV_GPW_WIDE, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
       default: break;
     }
     if (rc != CQ_OK) return rc;
@@ -1049,9 +1130,10 @@ extern "C" int cq_rlayer_preferred_rows(const cq_rlayer* L) {
   if (!L) return 0;
   const int gpw = rv_gpw_for(L);
   if (!gpw) return 0;
-  // measured on B200 against the tile GEMM: four launches of four rows still win on the narrow shapes
-  // (16 rows: 24 / 32 us against 25 / 36 on 4096 -> 4096 / 11008); the wide shape pays one launch per row
-  return gpw == RV_GPW_WIDE ? 4 : 16;
+  // measured on B200 against the tile GEMM at 16 rows: four launches of four rows take 24 / 32 us on
+  // 4096 -> 4096 / 11008 against the GEMM's 25 / 36; layers split along K (11008 -> 4096: 4 x 13.8 us
+  // against 35) give way to the GEMM beyond 8 rows
+  return L->ksplit > 1 ? 8 : 16;
 }
 
 extern "C" int cq_rlayer_matvec(const cq_rlayer* L, const void* x, void* y, int accumulate, uint32_t* status_word,

@@ -19,8 +19,11 @@ def dims(bits, K, N, Cn, G):
     off_tiles = 0
     off_perm = al(NT * tile_bytes)
     off_cidx = al(off_perm + NG * 128 * 2)
-    blob_bytes = al(off_cidx + max(Cp, 16) * 2)
+    off_work = al(off_cidx + max(Cp, 16) * 2)
+    ksplit = (NG + 63) // 64           # layers of more than 64 groups carry a work area for their column parts
+    blob_bytes = off_work if ksplit == 1 else al(off_work + ksplit * NT * 16 * 4 * 4 + NT * 4)
     return dict(bits=bits, K=K, N=N, C=Cn, G=G, Kc=Kc, NG=NG, sets=sets, Cp=Cp, NT=NT, tile_bytes=tile_bytes,
+                ksplit=ksplit, off_work=off_work,
                 scal_off=NG * 256 * bits, cher_off=NG * 256 * bits + NG * sets * 32, off_tiles=off_tiles,
                 off_perm=off_perm, off_cidx=off_cidx, blob_bytes=blob_bytes)
 

@@ -151,7 +151,7 @@ def ref64(x, dense):
 MODEL_SHAPES = [
     (4096, 4096, 4), (4096, 11008, 4), (11008, 4096, 4), (4096, 4096, 3), (4096, 11008, 3), (11008, 4096, 3),   # 7B
     (5120, 5120, 3), (5120, 13824, 3), (13824, 5120, 3),                                                       # 13B, C = 16 / 48
-    (8192, 8192, 3), (8192, 1024, 3), (8192, 28672, 3),                                                        # 70B, C = 32
+    (8192, 8192, 3), (8192, 1024, 3), (8192, 28672, 3), (28672, 8192, 3),                                      # 70B, C = 32 / 112
 ]
 
 
@@ -169,20 +169,22 @@ def test_matvec_model_shapes(cabi, K, N, bits):
 
 
 def test_layers_outside_the_envelope_are_refused_and_the_op_falls_back(cabi):
-    """28672 -> 8192 (224 groups) is beyond the one-row kernel: the C ABI says so and the drop-in op serves
-    the call with the stream kernel."""
+    """256 cherry columns (cherry ratio 1/16 of 4096) are more than a warp's slice of the activations holds:
+    the C ABI says so and the drop-in op serves the call with the stream kernel."""
     import cherryq_b200
     qc = cherryq_b200.load_quant_cuda()
-    K, N = 28672, 1024
-    q, s, cw, ci, dense = gpu_layer(K, N, 3, 128, seed=9)
+    K, N = 4096, 1024
+    q, s, cw, ci, dense = gpu_layer(K, N, 3, 128, seed=9, frac=1 / 16)
+    assert ci.shape[0] == 256
     L = cabi.rlayer_init(3, K, N, ci.shape[0], 128)
     assert cabi.lib().cq_rlayer_check(C.byref(L)) == 9          # CQ_ERR_UNSUPPORTED
     assert cabi.lib().cq_rlayer_matvec(C.byref(L), ptr(q), ptr(q), 0, None, None) in (1, 9)   # no blob / unsupported
-    x = torch.randn(1, K, device="cuda").half()
-    out = torch.zeros(1, N, dtype=torch.float16, device="cuda")
-    qc.vecquant3matmul_cherryq(x, q, cw, ci, s, out, 128, True)
-    torch.cuda.synchronize()
-    assert rel_err(out.cpu().numpy(), ref64(x, dense)) <= TIGHT_TOL
+    for M in (1, 5):
+        x = torch.randn(M, K, device="cuda").half()
+        out = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+        qc.vecquant3matmul_cherryq(x, q, cw, ci, s, out, 128, True)
+        torch.cuda.synchronize()
+        assert rel_err(out.cpu().numpy(), ref64(x, dense)) <= TIGHT_TOL
 
 
 @pytest.mark.parametrize("K,N,bits,G,frac", [
@@ -195,8 +197,12 @@ def test_layers_outside_the_envelope_are_refused_and_the_op_falls_back(cabi):
     (2048, 512, 4, -1, 1 / 256),      # group_size -1 = whole row
     (512, 64, 4, 128, 0.0),           # no cherries at all
     (4096, 256, 4, 128, 112 / 4096),  # 112 cherry columns: seven cherry blocks
-    (12288, 64, 3, 128, 1 / 256),     # widest layer of the smallest register variant boundary (96 groups)
-    (14336, 48, 4, 128, 1 / 256),     # widest layer the kernel takes (112 groups)
+    (8192 + 32, 64, 3, 128, 1 / 256), # 64 groups exactly: the widest layer one CTA per tile takes
+    (8192 + 160, 64, 4, 128, 1 / 256),# 65 groups: two CTAs per tile, 33 + 32 groups
+    (12288, 64, 3, 128, 1 / 256),     # 96 groups: two CTAs per tile
+    (16384 + 200, 48, 4, 128, 1 / 256),   # 130 groups: three CTAs per tile (44 + 44 + 42), ragged last group
+    (28672, 72, 3, 64, 1 / 256),      # 224 groups of two scale sets: four CTAs per tile
+    (32760, 16, 4, 128, 1 / 512),     # the widest row whose cherry columns fit the format's int16 indices (256 groups)
 ])
 def test_matvec_edge_shapes(cabi, K, N, bits, G, frac):
     q, s, cw, ci, dense = gpu_layer(K, N, bits, G if G != -1 else K, seed=K * 7 + N, frac=frac)
@@ -271,6 +277,7 @@ def test_outlier_channels(cabi, bits, scale):
     (4096, (11008, 11008), 4, 128),              # 7B gate / up
     (8192, (8192, 1024, 1024), 3, 128),          # 70B q / k / v (grouped-query heads: small k, v)
     (5120, (13824, 13824), 3, 128),              # 13B gate / up
+    (11008, (4096, 512), 4, 128),                # two wide layers (two CTAs per tile each)
     (1024, (48, 16, 8, 200), 3, 64),             # four small ragged layers, fewer tiles than SMs
     (2048, (4096, 24), 4, 128),                  # very uneven
 ])
@@ -388,7 +395,7 @@ def rows_call(cabi, preps, x, ldx=None, pad=0, accumulate=False, base=None):
 
 @pytest.mark.parametrize("K,N,bits,G", [(4096, 4096, 4, 128), (4096, 11008, 3, 128), (11008, 4096, 4, 128),
                                         (13824, 5120, 3, 128), (8192, 1024, 3, 128), (1024, 200, 3, 64),
-                                        (640, 40, 4, 640)])
+                                        (640, 40, 4, 640), (28672, 1024, 3, 128)])
 @pytest.mark.parametrize("M", [2, 3, 4, 5, 8, 11])
 def test_rows_of_a_batch_are_bit_identical_to_single_row_calls(cabi, K, N, bits, G, M):
     frac = 1 / 256 if K >= 2048 else 1 / 64

@@ -16,10 +16,11 @@ def test_model_round_trip(name):
 
 
 @pytest.mark.parametrize("bits,K,N,Cn,G", [(4, 4096, 11008, 16, 128), (3, 11008, 4096, 40, 128), (3, 640, 40, 0, 64),
-                                           (3, 8192, 28672, 32, 128), (4, 256, 8, 16, 128)])
+                                           (3, 8192, 28672, 32, 128), (4, 256, 8, 16, 128), (3, 28672, 8192, 112, 128),
+                                           (4, 16384, 64, 64, 128)])
 def test_model_dims_match_library(bits, K, N, Cn, G):
     from cherryq_b200 import _cabi
     L = _cabi.rlayer_init(bits, K, N, Cn, G)
     d = RM.dims(bits, K, N, Cn, G)
-    for key in ("Kc", "NG", "sets", "Cp", "NT", "tile_bytes", "off_tiles", "off_perm", "off_cidx", "blob_bytes"):
+    for key in ("Kc", "NG", "sets", "Cp", "NT", "tile_bytes", "ksplit", "off_tiles", "off_perm", "off_cidx", "off_work", "blob_bytes"):
         assert getattr(L, key) == d[key], key
