@@ -388,6 +388,16 @@ int cq_peer_region_close(void* region);
 int cq_peer_allgather(void* const* regions, int world, int rank, size_t capacity, const void* x_f16,
                       void* out_f16, int rows, int cols_local, int timeout_ms,
                       uint32_t* status_word, cq_stream_t stream);
+/* cq_rlayers_matvec on one layer shard followed by the exchange in the SAME launch: every CTA stores
+ * its rows of the local slice y_local (M, N) fp16 (contiguous, 8-byte aligned, 1 <= M <= 4), the CTA
+ * of the grid that finishes last runs the exchange described above (same regions, same call sequence
+ * as cq_peer_allgather: the two may be mixed, every rank making the same sequence of calls) and
+ * y_all (M, P * N) fp16 is complete when the next kernel of the stream starts.  Saves the kernel
+ * boundary between the matvec and the exchange. */
+int cq_rlayer_matvec_gather(const cq_rlayer* layer, const void* x_f16, int ldx, void* y_local_f16,
+                            int M, void* const* regions, int world, int rank, size_t capacity,
+                            void* y_all_f16, int timeout_ms, uint32_t* status_word,
+                            cq_stream_t stream);
 
 #ifdef __cplusplus
 }

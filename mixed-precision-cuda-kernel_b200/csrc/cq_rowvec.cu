@@ -32,6 +32,7 @@
 #include <utility>
 
 #include "cq_common.cuh"
+#include "cq_peer.cuh"
 
 namespace {
 
@@ -77,6 +78,11 @@ struct RowvecParams {
   int slice_halves;         // halves of a warp's raw activation slice in shared memory
   int off_slice, off_part, off_bar, off_tiles;   // shared-memory sections (bytes)
   int accumulate;
+  // Column-parallel deployments: with gather != 0 the CTA of the grid that finishes last runs the
+  // exchange of the ranks' output slices over peer memory (cq_peer.cuh) before the kernel ends, so the
+  // gathered rows are complete when the next kernel of the stream starts.  One layer per launch.
+  int gather;
+  cq_peer::PeerGatherParams peer;
 #ifdef CQ_ROWVEC_TRACE
   int trace_launch;
   unsigned long long* trace;   // passed as a kernel parameter: a stamp must not cost a global load
@@ -643,6 +649,23 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
       if (tid == 0) sg.counters[tile0] = 0u;               // ready for the next launch
     }
   }
+  if (p.gather) {
+    // every CTA has stored its rows of the local slice; the last one to get here exchanges the slices
+    uint8_t* own = nullptr;
+#pragma unroll
+    for (int r = 0; r < cq_peer::MAX_RANKS; ++r)
+      if (r == p.peer.rank) own = p.peer.region[r];
+    unsigned int* done = reinterpret_cast<unsigned int*>(own + cq_peer::DONE_OFF);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(done, 1u) == gridDim.x - 1u;
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      cq_peer::exchange<NTHR>(p.peer, &s_abort);          // (s_abort has no other use any more: every copy has landed)
+      if (tid == 0) *done = 0u;                            // ready for the next launch
+    }
+  }
   RV_STAMP(5);
 }
 
@@ -971,7 +994,8 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
 // that take the same activation row x; ys[i] receives layer i's output.
 // inflight: tiles the copy warp keeps outstanding.
 int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, const __half* x, int ldx,
-              __half* const* ys, int ldy, int M, int accumulate, uint32_t* status, cudaStream_t st) {
+              __half* const* ys, int ldy, int M, int accumulate, uint32_t* status, cudaStream_t st,
+              const cq_peer::PeerGatherParams* peer = nullptr) {
   int dev = 0;
   CQ_CUDA_TRY(cudaGetDevice(&dev));
   const RvDevice di = rv_device(dev);
@@ -994,6 +1018,8 @@ int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_r
   p.x = x; p.status = status;
   p.M = M; p.ldx = ldx; p.ldy = ldy;
   p.accumulate = accumulate;
+  p.gather = peer ? 1 : 0;
+  if (peer) p.peer = *peer; else p.peer = cq_peer::PeerGatherParams{};
 #ifdef CQ_ROWVEC_TRACE
   static int launch_no = 0;
   p.trace_launch = launch_no++;
@@ -1124,6 +1150,24 @@ extern "C" int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, c
     if (rc != CQ_OK) return rc;
   }
   return CQ_OK;
+}
+
+extern "C" int cq_rlayer_matvec_gather(const cq_rlayer* L, const void* x, int ldx, void* y_local, int M, void* const* regions,
+                                       int world, int rank, size_t capacity, void* y_all, int timeout_ms,
+                                       uint32_t* status_word, cq_stream_t stream) {
+  if (!L || !L->blob || !x || !y_local || !y_all) return CQ_ERR_BAD_ARG;
+  if (M < 1 || M > RV_MAX_ROWS || ldx < L->K) return CQ_ERR_BAD_ARG;
+  if (((uintptr_t)x & 1) || ((uintptr_t)y_local & 7)) return CQ_ERR_BAD_ARG;
+  cq_peer::PeerGatherParams pg;
+  int rc = cq_peer::fill_params(&pg, regions, world, rank, capacity, y_local, y_all, M, L->N, timeout_ms, status_word);
+  if (rc != CQ_OK) return rc;
+  __half* yp = (__half*)y_local;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (rv_gpw_for(L)) {
+    case 2: return rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, M), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, &L, 1, (const __half*)x, ldx, &yp, L->N, M, 0, status_word, st, &pg);
+    case 4: return rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, M), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, &L, 1, (const __half*)x, ldx, &yp, L->N, M, 0, status_word, st, &pg);
+    default: return CQ_ERR_UNSUPPORTED;
+  }
 }
 
 extern "C" int cq_rlayer_preferred_rows(const cq_rlayer* L) {

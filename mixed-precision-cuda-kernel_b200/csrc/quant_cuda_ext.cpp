@@ -343,6 +343,27 @@ struct RowLayer {
                  "RowLayer.matvec");
   }
 
+  // Column-parallel shard: y_local (M, N) = x (M, K) . W^T and, in the same launch, the exchange of the ranks'
+  // slices over peer memory: y_all (M, P * N).  regions: the P mapped region addresses (parallel.PeerAllGather).
+  void matvec_gather(torch::Tensor x, torch::Tensor y_local, torch::Tensor y_all, std::vector<int64_t> regions, int rank,
+                     int64_t capacity, int timeout_ms, torch::Tensor status) {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(x));
+    check_tensor(x, "x", torch::kFloat16, blob);
+    check_tensor(y_local, "y_local", torch::kFloat16, blob);
+    check_tensor(y_all, "y_all", torch::kFloat16, blob);
+    check_tensor(status, "status", torch::kInt32, blob);
+    TORCH_CHECK(x.numel() % layer.K == 0 && x.numel() > 0, "x must hold rows of ", layer.K, " activations");
+    const int M = (int)(x.numel() / layer.K), P = (int)regions.size();
+    TORCH_CHECK(y_local.numel() == (int64_t)M * layer.N && y_all.numel() == (int64_t)M * layer.N * P,
+                "y_local must be (M, N) and y_all (M, P * N)");
+    std::vector<void*> rp(P);
+    for (int i = 0; i < P; ++i) rp[i] = (void*)(uintptr_t)regions[i];
+    check_status(cq_rlayer_matvec_gather(&layer, x.data_ptr(), layer.K, y_local.data_ptr(), M, rp.data(), P, rank,
+                                         (size_t)capacity, y_all.data_ptr(), timeout_ms, (uint32_t*)status.data_ptr(),
+                                         current_stream()),
+                 "RowLayer.matvec_gather");
+  }
+
   // Back to the reference's four buffers: (qweight, scales, cherry_weight, cherry_indices).
   std::vector<torch::Tensor> unprepare() {
     const at::cuda::OptionalCUDAGuard device_guard(device_of(blob));
@@ -581,6 +602,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def(py::init<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int, int, int>())
       .def_static("supported", &RowLayer::supported)
       .def("matvec", &RowLayer::matvec)
+      .def("matvec_gather", &RowLayer::matvec_gather)
       .def("unprepare", &RowLayer::unprepare)
       .def_readonly("blob", &RowLayer::blob)
       .def_property_readonly("preferred_rows", [](const RowLayer& p) { return cq_rlayer_preferred_rows(&p.layer); })

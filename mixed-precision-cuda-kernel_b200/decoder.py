@@ -190,6 +190,15 @@ class CherryDecoder:
             return [F.linear(x, lay[n].dense_weight) for n in names]
         return forward_shared_input([lay[n] for n in names], x)
 
+    def _lin_gather(self, ql: QuantLinear, x: torch.Tensor) -> torch.Tensor:
+        """A sharded projection followed by the exchange of its slices; for decode batches of up to four rows
+        both happen in one launch of the row-tile kernel."""
+        if self.tp > 1 and self.peer is not None and not self.dense and x.shape[0] <= 4 and x.dtype == torch.float16:
+            row = ql.row_layer()
+            if row is not None and self.peer.fits(x.shape[0], ql.out_features):
+                return self.peer.matvec_gather(row, x.contiguous())
+        return self._gather(self._lin(ql, x))
+
     def _gather(self, x: torch.Tensor) -> torch.Tensor:
         """(t, n_local) slices of all ranks -> (t, tp * n_local), in rank order."""
         if self.tp == 1:
@@ -229,10 +238,10 @@ class CherryDecoder:
             a = F.scaled_dot_product_attention(q.view(nb, ts, nh, hd).transpose(1, 2), k.view(nb, ts, kv, hd).transpose(1, 2),
                                                v.view(nb, ts, kv, hd).transpose(1, 2), is_causal=True, enable_gqa=(kv != nh))
             a = a.transpose(1, 2).reshape(t, nh * hd)
-        xn, h = self._norm(h, self._gather(self._lin(lay["o"], self._gather(a))), lay["norm2"])
+        xn, h = self._norm(h, self._lin_gather(lay["o"], self._gather(a)), lay["norm2"])
         gate, up = self._lins(lay, ("gate", "up"), xn)
         act = self.qc.silu_mul(gate, up)
-        return h, self._gather(self._lin(lay["down"], self._gather(act)))
+        return h, self._lin_gather(lay["down"], self._gather(act))
 
     def _logits(self, h: torch.Tensor, delta) -> torch.Tensor:
         return F.linear(self._norm(h, delta, self.final_norm)[0], self.lm_head)

@@ -159,6 +159,7 @@ class PeerAllGather:
                 raise RuntimeError("peer memory could not be mapped on every rank "
                                    f"(per-rank success: {oks}); use the NCCL all-gather instead")
             self.regions = (C.c_void_p * self.world)(*ptrs)
+            self._region_ints = [int(v) for v in ptrs]
         dist.barrier(group=group)          # every region is zeroed and mapped before the first launch
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
@@ -181,6 +182,18 @@ class PeerAllGather:
         self._cabi.check(self.lib.cq_peer_allgather(self.regions, self.world, self.rank, self.capacity,
                                                     cv(x.data_ptr()), cv(out.data_ptr()), rows, cols, self.timeout_ms,
                                                     cv(self.status.data_ptr()), cv(stream.cuda_stream)), "peer all-gather")
+        return out
+
+    def matvec_gather(self, row_layer, x: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+        """This rank's shard of a layer (a `quant_cuda.RowLayer`) applied to x (rows <= 4, K) AND the exchange of
+        the ranks' output slices, in one launch: returns (rows, world * N_local).  Counts as one call of the
+        exchange sequence (every rank makes the same calls in the same order)."""
+        rows, n = x.shape[0], row_layer.out_features
+        y_local = torch.empty(rows, n, dtype=torch.float16, device=x.device)
+        if out is None:
+            out = torch.empty(rows, self.world * n, dtype=torch.float16, device=x.device)
+        row_layer.matvec_gather(x, y_local, out, self._region_ints, self.rank,
+                                self.capacity, self.timeout_ms, self.status)
         return out
 
     def fits(self, rows: int, cols_local: int) -> bool:

@@ -53,6 +53,25 @@ def main():
             graph.replay()
             s.synchronize()
             ok &= torch.equal(out, nccl_gather(x, world))
+    # the matvec that ends with the exchange (one launch) against matvec + NCCL, mixed with plain exchanges
+    import math
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    for K, N, bits in [(4096, 1376, 4), (11008, 512, 3), (2048, 40, 4)]:
+        gw = torch.Generator(device=dev).manual_seed(7)            # same full layer on every rank
+        c = math.ceil(K / 256) // 8 * 8
+        w = (torch.randn(N * world, K, device=dev, generator=gw) * 0.02).half()
+        idx = torch.randperm(K, device=dev, generator=gw)[:c].to(torch.int32)
+        q, sc, cw, ci = qc.pack(w[rank * N:(rank + 1) * N].contiguous(), idx.contiguous(), bits, 128)
+        row = qc.RowLayer(q, sc, cw, ci, bits, K, 128)
+        for rows in (1, 3, 4):
+            xa = torch.randn(rows, K, device=dev, generator=gw).half()   # the same activations on every rank
+            y = torch.empty(rows, N, dtype=torch.float16, device=dev)
+            row.matvec(xa, y, False)
+            want_all = nccl_gather(y, world)
+            for _ in range(3):
+                ok &= torch.equal(peer.matvec_gather(row, xa), want_all)
+                ok &= torch.equal(peer(y), want_all)                      # a plain exchange in between
     peer.check()
     peer.close()                      # collective: unmap the peers, meet, free the own region
     flag = torch.tensor([1 if ok else 0], device=dev)

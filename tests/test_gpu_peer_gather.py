@@ -77,6 +77,63 @@ def test_absent_peer_runs_into_the_time_limit(region):
     assert torch.equal(out1, x) and int(status.item()) == 0
 
 
+def _one_layer(K=2048, N=264, bits=4):
+    import math
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    c = math.ceil(K / 256) // 8 * 8
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).half()
+    idx = torch.randperm(K, device="cuda", generator=g)[:c].to(torch.int32)
+    q, s, cw, ci = qc.pack(w, idx.contiguous(), bits, 128)
+    return qc, qc.RowLayer(q, s, cw, ci, bits, K, 128)
+
+
+def test_matvec_with_exchange_in_one_launch_single_rank(region):
+    """cq_rlayer_matvec_gather on a world of one: the last CTA of the matvec runs the exchange with itself;
+    repeated and mixed with plain exchanges on the same region (one call sequence)."""
+    lib, _cabi, p = region
+    qc, row = _one_layer()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for rows in (1, 4, 2, 1):
+        x = torch.randn(rows, 2048, device="cuda").half()
+        want = torch.empty(rows, 264, dtype=torch.float16, device="cuda")
+        row.matvec(x, want, False)
+        y_local = torch.zeros_like(want)
+        y_all = torch.zeros_like(want)
+        for _ in range(3):
+            row.matvec_gather(x, y_local, y_all, [p.value], 0, CAP, 500, status)
+            torch.cuda.synchronize()
+            assert torch.equal(y_all, want) and torch.equal(y_local, want)
+            regions = (C.c_void_p * 1)(p.value)
+            out = torch.zeros_like(want)
+            _cabi.check(_gather(lib, regions, 1, 0, want, out, status), "gather")
+            assert torch.equal(out, want)
+    assert int(status.item()) == 0
+
+
+def test_matvec_with_exchange_absent_peer_times_out(region):
+    lib, _cabi, p = region
+    qc, row = _one_layer()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x = torch.randn(1, 2048, device="cuda").half()
+    want = torch.empty(1, 264, dtype=torch.float16, device="cuda")
+    row.matvec(x, want, False)
+    y_local = torch.zeros_like(want)
+    y_all = torch.full((1, 528), 7.0, dtype=torch.float16, device="cuda")
+    # "two ranks" whose regions are both this one: rank 1 does not exist and never delivers
+    row.matvec_gather(x, y_local, y_all, [p.value, p.value], 0, CAP, 200, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 8                                             # CQ_ERR_DEVICE_TIMEOUT
+    assert torch.equal(y_local, want) and bool(torch.isnan(y_all).all())
+    # the context and the region stay usable
+    status.zero_()
+    y_all1 = torch.zeros_like(want)
+    row.matvec_gather(x, y_local, y_all1, [p.value], 0, CAP, 500, status)
+    torch.cuda.synchronize()
+    assert torch.equal(y_all1, want) and int(status.item()) == 0
+
+
 def test_two_ranks_match_nccl(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
