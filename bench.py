@@ -350,6 +350,10 @@ def run_ours(args):
                 _cabi.check(lib.cq_rlayer_matvec(C.byref(Lf), ptr(x), ptr(yf), 0, ptr(status), sp), "matvec")
                 stream.synchronize()
                 ok[0] = int(torch.equal(yf.view(torch.int16), y_all.view(torch.int16)))
+                if not int(ok.item()):
+                    bad = (yf.view(torch.int16) != y_all.view(torch.int16)).view(-1).nonzero().view(-1)
+                    print(f"gathered vector: {bad.numel()} of {N_OUT} elements differ, first at {bad[:4].tolist()}, last at "
+                          f"{bad[-4:].tolist()} (rows per rank {n_local})", file=sys.stderr)
                 del qf, sf, cwf, cif, bf, yf
             dist.broadcast(ok, src=0)
             gather_checked = bool(int(ok.item()))
