@@ -340,6 +340,7 @@ def run_ours(args):
             step(i)
         stream.synchronize()
         if world > 1:
+            barrier()        # every stream of the device (a library collective may run on one of its own), every rank
             # rank 0 computes the whole vector from the unsharded layer with the same kernel: every output element
             # is the same arithmetic whichever rank owns its row, so the gathered vector must match bit for bit
             ok = torch.ones(1, dtype=torch.int32, device=dev)
@@ -353,7 +354,9 @@ def run_ours(args):
                 if not int(ok.item()):
                     bad = (yf.view(torch.int16) != y_all.view(torch.int16)).view(-1).nonzero().view(-1)
                     print(f"gathered vector: {bad.numel()} of {N_OUT} elements differ, first at {bad[:4].tolist()}, last at "
-                          f"{bad[-4:].tolist()} (rows per rank {n_local})", file=sys.stderr)
+                          f"{bad[-4:].tolist()} (rows per rank {n_local}); zeros in the gathered vector: "
+                          f"{int((y_all == 0).sum())}; values {y_all.view(-1)[bad[:4]].tolist()} against {yf.view(-1)[bad[:4]].tolist()}; "
+                          f"own slice equal: {torch.equal(y.view(-1), yf.view(-1)[:n_local])}", file=sys.stderr)
                 del qf, sf, cwf, cif, bf, yf
             dist.broadcast(ok, src=0)
             gather_checked = bool(int(ok.item()))
