@@ -14,9 +14,11 @@ metric  : algorithmic bytes of the reference format (qweight + scales + cherry v
           + x + y) per second, in GB/s - the number the HBM roofline is judged against.
 value   : inputs resident in HBM, the one-row decode kernel through the C ABI (cq_rlayer_matvec), every launch
           of the timed region a CUDA-graph node; the region is timed --repeats times, the median is reported.
-e2e     : the same metric through the drop-in `quant_cuda.vecquant4matmul_cherryq` call with HOST
-          activations: every step copies x from pinned host memory, zero-fills the output (the
-          operator accumulates, as the reference's forward does), runs the op and reads y back.
+e2e     : the same metric with HOST buffers, one synchronous call per step: x comes from pinned host memory and
+          y is complete in pinned host memory when the call returns.  At N = 1 through the C ABI's
+          cq_rlayer_matvec_host; the record also holds the same through the drop-in torch op
+          `quant_cuda.vecquant4matmul_cherryq` (copy x in, zero-fill the output because the operator
+          accumulates as the reference's does, run the op, read y back), which is the path at N > 1.
 N > 1   : the layer is sharded column-parallel (N/P output rows per GPU), every rank runs its
           shard and the slices are exchanged (peer-memory kernel, or NCCL): strong scaling of one layer.
           Rank 0 checks the gathered vector bit for bit against the unsharded layer before timing.

@@ -196,8 +196,10 @@ int cq_rlayer_preferred_rows(const cq_rlayer* layer);
  * binding with no device tensors of its own; the reference's op only takes device tensors,
  * csrc/quant_cuda.cpp:56-69): copies x_host (K fp16) to the device staging buffer x_dev, runs the
  * kernel into y_dev, copies the N fp16 results to y_host and returns when y_host is complete (the
- * stream is synchronised).  Page-locked host memory keeps the two copies asynchronous and short;
- * pageable memory works.  x_dev / y_dev: device memory of K and N fp16 owned by the caller. */
+ * stream is synchronised).  With page-locked (mapped) host buffers no copy engine is involved: a
+ * one-CTA kernel fetches x across the bus while the matvec already streams its weights, and the
+ * matvec stores y straight into y_host.  Pageable memory works (two asynchronous copies).
+ * x_dev / y_dev: device memory of K and N fp16 owned by the caller, x_dev 16-byte aligned. */
 int cq_rlayer_matvec_host(const cq_rlayer* layer, const void* x_host_f16, void* y_host_f16,
                           void* x_dev_f16, void* y_dev_f16, uint32_t* status_word,
                           cq_stream_t stream);

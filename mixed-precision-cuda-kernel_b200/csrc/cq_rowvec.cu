@@ -1186,14 +1186,59 @@ extern "C" int cq_rlayer_matvec(const cq_rlayer* L, const void* x, void* y, int 
   return cq_rlayers_matvec(&L, 1, x, L->K, &y, L->N, 1, accumulate, status_word, stream);
 }
 
+namespace {
+// x from mapped host memory into device memory: one CTA, 16-byte loads across PCIe.  The dependent matvec
+// is released at once, so its weight copies run while these loads are under way.
+__global__ void __launch_bounds__(256) rl_copy_in_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int n16,
+                                                         const unsigned short* __restrict__ src_tail,
+                                                         unsigned short* __restrict__ dst_tail, int ntail) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int i = threadIdx.x; i < n16; i += 256) dst[i] = src[i];
+  for (int i = threadIdx.x; i < ntail; i += 256) dst_tail[i] = src_tail[i];
+}
+
+// true if the GPU can address this host pointer directly (page-locked, mapped memory)
+bool rl_host_mapped(const void* p) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return at.type == cudaMemoryTypeHost && at.devicePointer == p;
+}
+}  // namespace
+
 extern "C" int cq_rlayer_matvec_host(const cq_rlayer* L, const void* x_host, void* y_host, void* x_dev, void* y_dev,
                                      uint32_t* status_word, cq_stream_t stream) {
   if (!L || !x_host || !y_host || !x_dev || !y_dev) return CQ_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
-  CQ_CUDA_TRY(cudaMemcpyAsync(x_dev, x_host, (size_t)L->K * sizeof(__half), cudaMemcpyHostToDevice, st));
+  const size_t xb = (size_t)L->K * sizeof(__half), yb = (size_t)L->N * sizeof(__half);
+  if (rl_host_mapped(x_host) && rl_host_mapped(y_host) && !((uintptr_t)x_host & 15) && !((uintptr_t)x_dev & 15)) {
+    // page-locked buffers: no DMA operations at all.  A one-CTA kernel fetches x across the bus, the matvec
+    // (released at once: its weights stream meanwhile) stores y straight into the host buffer.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int n16 = (int)(xb / 16), ntail = (int)((xb - (size_t)n16 * 16) / 2);
+    CQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, rl_copy_in_kernel, (const uint4*)x_host, (uint4*)x_dev, n16,
+                                   (const unsigned short*)((const uint8_t*)x_host + (size_t)n16 * 16),
+                                   (unsigned short*)((uint8_t*)x_dev + (size_t)n16 * 16), ntail));
+    const int rc = cq_rlayer_matvec(L, x_dev, y_host, 0, status_word, stream);
+    if (rc != CQ_OK) return rc;
+    CQ_CUDA_TRY(cudaStreamSynchronize(st));
+    return CQ_OK;
+  }
+  CQ_CUDA_TRY(cudaMemcpyAsync(x_dev, x_host, xb, cudaMemcpyHostToDevice, st));
   const int rc = cq_rlayer_matvec(L, x_dev, y_dev, 0, status_word, stream);
   if (rc != CQ_OK) return rc;
-  CQ_CUDA_TRY(cudaMemcpyAsync(y_host, y_dev, (size_t)L->N * sizeof(__half), cudaMemcpyDeviceToHost, st));
+  CQ_CUDA_TRY(cudaMemcpyAsync(y_host, y_dev, yb, cudaMemcpyDeviceToHost, st));
   CQ_CUDA_TRY(cudaStreamSynchronize(st));
   return CQ_OK;
 }
