@@ -524,7 +524,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_DRAM_BYTES_PER_LAUNCH * alg_local / alg if NCU_DRAM_BYTES_PER_LAUNCH else None,
                          "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
-                         "kernel": "cq_rowvec_kernel<4,1,16,2>", "alg_bytes_per_launch": alg_local,
+                         "kernel": "cq_rowvec_kernel<4,1,16,2,1>", "alg_bytes_per_launch": alg_local,
                          "launch_us": kern_ms * 1e3},
             "e2e": e2e, "gpu_launches": args.steps * world * own_kernels_per_step,
             "clocks": clocks,

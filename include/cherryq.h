@@ -188,6 +188,14 @@ int cq_rlayer_check(const cq_rlayer* layer);
  * kernel's own bulk copies ever runs out; may be NULL. */
 int cq_rlayer_matvec(const cq_rlayer* layer, const void* x_f16, void* y_f16, int accumulate,
                      uint32_t* status_word, cq_stream_t stream);
+/* The down projection of a gated MLP with the SwiGLU folded into its input staging:
+ *   y (M, N) fp16 = (silu(gate) * up) (M, K) . W^T
+ * (the reference's LlamaMLP.forward, llama/modeling_llama_quant.py, computes act_fn(gate_proj(x)) *
+ * up_proj(x) as separate PyTorch ops before down_proj).  The product is formed with the roundings of
+ * those ops (the activation is rounded to fp16, then an fp16 multiplication), so the result equals
+ * cq_rlayers_matvec on the separately computed product bit for bit.  gate and up share the row stride. */
+int cq_rlayer_matvec_swiglu(const cq_rlayer* layer, const void* gate_f16, const void* up_f16, int ld,
+                            void* y_f16, int ldy, int M, uint32_t* status_word, cq_stream_t stream);
 /* The largest batch for which cq_rlayers_matvec is the faster path for this layer (beyond it
  * cq_tlayer_gemm is): 16 for layers of up to 8192 quantized columns, 8 for wider ones, 0 for layers
  * the kernel does not take.  No GPU work. */

@@ -22,7 +22,7 @@ SYMBOLS = [
     "cq_selftest_bounded_wait", "cq_rmsnorm", "cq_rope_cache", "cq_silu_mul", "cq_attn_decode", "cq_attn_decode_workspace_bytes",
     "cq_peer_region_bytes", "cq_peer_region_create", "cq_peer_region_destroy", "cq_peer_region_export",
     "cq_peer_region_open", "cq_peer_region_close", "cq_peer_allgather",
-    "cq_rlayer_init", "cq_rlayer_prepare", "cq_rlayer_unprepare", "cq_rlayer_check", "cq_rlayer_matvec", "cq_rlayers_matvec", "cq_rlayer_matvec_host", "cq_rlayer_preferred_rows", "cq_rlayer_matvec_gather",
+    "cq_rlayer_init", "cq_rlayer_prepare", "cq_rlayer_unprepare", "cq_rlayer_check", "cq_rlayer_matvec", "cq_rlayers_matvec", "cq_rlayer_matvec_host", "cq_rlayer_preferred_rows", "cq_rlayer_matvec_gather", "cq_rlayer_matvec_swiglu",
 ]
 
 
@@ -76,6 +76,7 @@ def lib():
     L.cq_rlayer_check.argtypes = [C.POINTER(cq_rlayer)]
     L.cq_rlayer_matvec.argtypes = [C.POINTER(cq_rlayer), vp, vp, i32, vp, vp]
     L.cq_rlayer_preferred_rows.argtypes = [C.POINTER(cq_rlayer)]
+    L.cq_rlayer_matvec_swiglu.argtypes = [C.POINTER(cq_rlayer), vp, vp, i32, vp, i32, i32, vp, vp]
     L.cq_rlayer_matvec_gather.argtypes = [C.POINTER(cq_rlayer), vp, i32, vp, i32, C.POINTER(vp), i32, i32, C.c_size_t, vp, i32, vp, vp]
     L.cq_rlayer_matvec_host.argtypes = [C.POINTER(cq_rlayer), vp, vp, vp, vp, vp, vp]
     L.cq_rlayers_matvec.argtypes = [C.POINTER(C.POINTER(cq_rlayer)), i32, vp, i32, C.POINTER(vp), i32, i32, i32, vp, vp]

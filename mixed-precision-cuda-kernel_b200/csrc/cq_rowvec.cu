@@ -63,6 +63,8 @@ struct RowvecParams {
   RowvecSeg seg[RV_MAX_SEG];
   int nseg;
   const __half* x;
+  const __half* x2;         // not null: the activations are silu(x) * x2, element by element (the SwiGLU of a gated MLP
+                            // computed while the down projection stages its input); same shape and stride as x
   int M, ldx, ldy;          // activation rows of the call (1..4) and the row strides of x and y, in elements
   uint32_t* status;         // may be null
   int K, C, NG, ncb;        // common to the layers of a launch; ncb = cherry blocks of 16 columns
@@ -135,6 +137,21 @@ __device__ __forceinline__ bool rv_mbar_wait(uint32_t bar, uint32_t parity, vola
 __device__ __forceinline__ void rv_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// silu(g) * u as the decode harness computes it in two kernels' worth of roundings: the activation is an
+// fp16 tensor, the product an fp16 multiplication
+__device__ __forceinline__ __half rv_swiglu(__half g, __half u) {
+  const float gf = __half2float(g);
+  return __hmul(__float2half(gf / (1.f + __expf(-gf))), u);
+}
+__device__ __forceinline__ uint4 rv_swiglu8(uint4 g, uint4 u) {
+  uint4 r;
+  const __half* gh = reinterpret_cast<const __half*>(&g);
+  const __half* uh = reinterpret_cast<const __half*>(&u);
+  __half* rh = reinterpret_cast<__half*>(&r);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) rh[i] = rv_swiglu(gh[i], uh[i]);
+  return r;
 }
 // D (16 x 8, s32) += A (16 x 32, u8) . B (32 x 8, s8)
 __device__ __forceinline__ void rv_imma(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -322,7 +339,17 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   const bool owns_tail = ngw > 0 && g0 + ngw == p.NG;       // the warp whose last group may hold padding columns
   int ccol = -1;
   if (has_cherry && lane < 16 && warp * 16 + lane < p.C) ccol = sg.cidx[warp * 16 + lane];
-  const bool x_aligned = ((reinterpret_cast<uintptr_t>(p.x) | (uintptr_t)(p.ldx * 2)) & 15) == 0;
+  const bool gated = p.x2 != nullptr;
+  const bool x_aligned = ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.x2) | (uintptr_t)(p.ldx * 2)) & 15) == 0;
+  // 16 bytes / one element of the activations at element offset `at` of the matrix
+  auto ld8 = [&](size_t at) {
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(p.x + at));
+    return gated ? rv_swiglu8(v, __ldcg(reinterpret_cast<const uint4*>(p.x2 + at))) : v;
+  };
+  auto ld1 = [&](size_t at) {
+    const __half v = __ldcg(p.x + at);
+    return gated ? rv_swiglu(v, __ldcg(p.x2 + at)) : v;
+  };
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -354,10 +381,10 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
     for (int c = 0; c < XCH; ++c) {
       const int ch = lane + 32 * c;
       xv[c] = make_uint4(0, 0, 0, 0);
-      if (ch < nchunk) xv[c] = __ldcg(reinterpret_cast<const uint4*>(p.x + lo8) + ch);
+      if (ch < nchunk) xv[c] = ld8((size_t)lo8 + 8 * ch);
     }
   }
-  if (ccol >= 0) xcv_next = (uint32_t)__half_as_ushort(__ldcg(p.x + ccol));
+  if (ccol >= 0) xcv_next = (uint32_t)__half_as_ushort(ld1((size_t)ccol));
 #pragma unroll 1
   for (int m = 0; m < Mrows; ++m) {
   const uint32_t xcv = xcv_next;
@@ -368,19 +395,19 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
       if (ch < nchunk) reinterpret_cast<uint4*>(slice)[ch] = xv[c];
     }
   } else {
-    const __half* xr = p.x + (size_t)m * p.ldx;
-    for (int i = lane; i < nchunk * 8; i += 32) slice[i] = xr[lo8 + i];
+    const size_t xr = (size_t)m * p.ldx + lo8;
+    for (int i = lane; i < nchunk * 8; i += 32) slice[i] = ld1(xr + i);
   }
   if (MR > 1 && m + 1 < Mrows) {
-    const __half* xn = p.x + (size_t)(m + 1) * p.ldx;
+    const size_t xn = (size_t)(m + 1) * p.ldx;
     if (x_aligned) {
 #pragma unroll
       for (int c = 0; c < XCH; ++c) {
         const int ch = lane + 32 * c;
-        if (ch < nchunk) xv[c] = __ldcg(reinterpret_cast<const uint4*>(xn + lo8) + ch);
+        if (ch < nchunk) xv[c] = ld8(xn + lo8 + 8 * ch);
       }
     }
-    if (ccol >= 0) xcv_next = (uint32_t)__half_as_ushort(__ldcg(xn + ccol));
+    if (ccol >= 0) xcv_next = (uint32_t)__half_as_ushort(ld1(xn + ccol));
   }
   if (owns_tail && lane == 0) slice[p.K - lo8] = __float2half(0.f);   // zero slot for padding columns
   __syncwarp();
@@ -995,7 +1022,7 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
 // inflight: tiles the copy warp keeps outstanding.
 int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, const __half* x, int ldx,
               __half* const* ys, int ldy, int M, int accumulate, uint32_t* status, cudaStream_t st,
-              const cq_peer::PeerGatherParams* peer = nullptr) {
+              const cq_peer::PeerGatherParams* peer = nullptr, const __half* x2 = nullptr) {
   int dev = 0;
   CQ_CUDA_TRY(cudaGetDevice(&dev));
   const RvDevice di = rv_device(dev);
@@ -1015,7 +1042,7 @@ int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_r
     p.seg[i].counters = (unsigned int*)(blob + Ls[j]->off_work + (size_t)Ls[j]->ksplit * Ls[j]->NT * 16 * RV_MAX_ROWS * sizeof(float));
     if (i >= n) { p.seg[i].N = 0; p.seg[i].cta0 = grid; p.seg[i].tiles_q = 0; p.seg[i].tiles_r = 0; }
   }
-  p.x = x; p.status = status;
+  p.x = x; p.x2 = x2; p.status = status;
   p.M = M; p.ldx = ldx; p.ldy = ldy;
   p.accumulate = accumulate;
   p.gather = peer ? 1 : 0;
@@ -1168,6 +1195,28 @@ extern "C" int cq_rlayer_matvec_gather(const cq_rlayer* L, const void* x, int ld
     case 4: return rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, M), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, &L, 1, (const __half*)x, ldx, &yp, L->N, M, 0, status_word, st, &pg);
     default: return CQ_ERR_UNSUPPORTED;
   }
+}
+
+extern "C" int cq_rlayer_matvec_swiglu(const cq_rlayer* L, const void* gate, const void* up, int ld, void* y, int ldy, int M,
+                                       uint32_t* status_word, cq_stream_t stream) {
+  if (!L || !L->blob || !gate || !up || !y || M < 1) return CQ_ERR_BAD_ARG;
+  if (((uintptr_t)gate | (uintptr_t)up | (uintptr_t)y) & 1) return CQ_ERR_BAD_ARG;
+  if (ld < L->K || ldy < L->N) return CQ_ERR_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  for (int m0 = 0; m0 < M; m0 += RV_MAX_ROWS) {
+    const int rows = M - m0 < RV_MAX_ROWS ? M - m0 : RV_MAX_ROWS;
+    const __half* gp = (const __half*)gate + (size_t)m0 * ld;
+    const __half* up2 = (const __half*)up + (size_t)m0 * ld;
+    __half* yp = (__half*)y + (size_t)m0 * ldy;
+    int rc = CQ_ERR_UNSUPPORTED;
+    switch (rv_gpw_for(L)) {
+      case 2: rc = rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, rows), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, &L, 1, gp, ld, &yp, ldy, rows, 0, status_word, st, nullptr, up2); break;
+      case 4: rc = rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, rows), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, &L, 1, gp, ld, &yp, ldy, rows, 0, status_word, st, nullptr, up2); break;
+      default: break;
+    }
+    if (rc != CQ_OK) return rc;
+  }
+  return CQ_OK;
 }
 
 extern "C" int cq_rlayer_preferred_rows(const cq_rlayer* L) {

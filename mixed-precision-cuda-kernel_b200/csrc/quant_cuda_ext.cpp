@@ -343,6 +343,23 @@ struct RowLayer {
                  "RowLayer.matvec");
   }
 
+  // out (M, N) fp16 = (silu(gate) * up) (M, K) . W^T: the SwiGLU of a gated MLP folded into the down projection
+  void matvec_swiglu(torch::Tensor gate, torch::Tensor up, torch::Tensor out) {
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(gate));
+    check_tensor(gate, "gate", torch::kFloat16, blob);
+    check_tensor(up, "up", torch::kFloat16, blob);
+    check_tensor(out, "out", torch::kFloat16, blob);
+    TORCH_CHECK(gate.sizes() == up.sizes() && gate.numel() % layer.K == 0 && gate.numel() > 0,
+                "gate and up must hold the same rows of ", layer.K, " values");
+    const int M = (int)(gate.numel() / layer.K);
+    TORCH_CHECK(out.numel() == (int64_t)M * layer.N, "out must hold ", M, " rows of ", layer.N, " values");
+    auto scratch = scratch_for(gate.device());
+    uint8_t* sp = scratch.data_ptr<uint8_t>();
+    check_status(cq_rlayer_matvec_swiglu(&layer, gate.data_ptr(), up.data_ptr(), layer.K, out.data_ptr(), layer.N, M,
+                                         (uint32_t*)(sp + cq_scratch_bytes()), current_stream()),
+                 "RowLayer.matvec_swiglu");
+  }
+
   // Column-parallel shard: y_local (M, N) = x (M, K) . W^T and, in the same launch, the exchange of the ranks'
   // slices over peer memory: y_all (M, P * N).  regions: the P mapped region addresses (parallel.PeerAllGather).
   void matvec_gather(torch::Tensor x, torch::Tensor y_local, torch::Tensor y_all, std::vector<int64_t> regions, int rank,
@@ -603,6 +620,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_static("supported", &RowLayer::supported)
       .def("matvec", &RowLayer::matvec)
       .def("matvec_gather", &RowLayer::matvec_gather)
+      .def("matvec_swiglu", &RowLayer::matvec_swiglu)
       .def("unprepare", &RowLayer::unprepare)
       .def_readonly("blob", &RowLayer::blob)
       .def_property_readonly("preferred_rows", [](const RowLayer& p) { return cq_rlayer_preferred_rows(&p.layer); })

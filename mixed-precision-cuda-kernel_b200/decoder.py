@@ -240,6 +240,9 @@ class CherryDecoder:
             a = a.transpose(1, 2).reshape(t, nh * hd)
         xn, h = self._norm(h, self._lin_gather(lay["o"], self._gather(a)), lay["norm2"])
         gate, up = self._lins(lay, ("gate", "up"), xn)
+        if self.tp == 1 and not self.dense and t <= 16:
+            # one GPU, decode batch: the SwiGLU rides in the down projection's input staging
+            return h, lay["down"].forward_swiglu(gate, up)
         act = self.qc.silu_mul(gate, up)
         return h, self._lin_gather(lay["down"], self._gather(act))
 

@@ -156,6 +156,26 @@ class QuantLinear(nn.Module):
             self._row = qc.RowLayer(q, s, cw, ci, self.w_bits, self.in_features, self.group_size)
         return self._row
 
+    @torch.inference_mode()
+    def forward_swiglu(self, gate: torch.Tensor, up: torch.Tensor):
+        """This layer applied to silu(gate) * up (the down projection of the reference's LlamaMLP.forward,
+        llama/modeling_llama_quant.py): for decode batches the product is formed while the kernel stages its
+        input (no separate element-wise kernel, no intermediate tensor), with the same roundings, so the
+        result equals forward(silu(gate) * up) bit for bit; other cases compute the product first."""
+        rows = gate.numel() // gate.shape[-1]
+        row = self.row_layer() if (self._layerwise_dequantize and self.w_bits in (3, 4) and gate.dtype == torch.float16
+                                   and rows <= ROW_KERNEL_MAX_ROWS) else None
+        if row is None or rows > row.preferred_rows:
+            return self(nn.functional.silu(gate.float()).to(gate.dtype) * up)
+        g2 = gate.reshape(rows, gate.shape[-1]).contiguous()
+        u2 = up.reshape(rows, up.shape[-1]).contiguous()
+        out = torch.empty(rows, self.out_features, dtype=torch.float16, device=g2.device)
+        row.matvec_swiglu(g2, u2, out)
+        out = out.reshape(gate.shape[:-1] + (self.out_features,))
+        if self.bias is not None:
+            out += self.bias
+        return out
+
     def release_reference_buffers(self):
         """Keeps only the re-packed copies (roughly halves the weight memory);
         `restore_reference_buffers` rebuilds the four buffers bit-exactly."""

@@ -457,3 +457,35 @@ def test_drop_in_ops_route_decode_batches_to_the_row_kernel(bits, M):
     torch.cuda.synchronize()
     ref = base.double().cpu().numpy() + ref64(x, dense)
     assert rel_err(out.float().cpu().numpy(), ref) <= TIGHT_TOL
+
+
+@pytest.mark.parametrize("K,N,bits,M", [(11008, 4096, 4, 1), (11008, 4096, 3, 4), (4096, 512, 4, 3), (28672, 1024, 3, 1),
+                                        (2048, 264, 4, 6)])
+def test_swiglu_folded_into_the_down_projection(cabi, K, N, bits, M):
+    """cq_rlayer_matvec_swiglu against the element-wise kernel followed by the plain call: bit-identical."""
+    import cherryq_b200
+    qc = cherryq_b200.load_quant_cuda()
+    q, s, cw, ci, dense = gpu_layer(K, N, bits, 128, seed=K + N + M)
+    p = RowPrepared(cabi, q, s, cw, ci, bits, K, 128)
+    g = torch.Generator(device="cuda").manual_seed(M)
+    gate = (torch.randn(M, K, device="cuda", generator=g) * 2).half()
+    up = torch.randn(M, K, device="cuda", generator=g).half()
+    act = qc.silu_mul(gate, up)
+    _, (want,) = rows_call(cabi, [p], act)
+    y = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cabi.check(cabi.lib().cq_rlayer_matvec_swiglu(C.byref(p.L), ptr(gate), ptr(up), K, ptr(y), N, M, ptr(status), None), "swiglu")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(y.view(torch.int16), want.contiguous().view(torch.int16))
+    ref = ref64(torch.nn.functional.silu(gate.float()).half() * up, dense)
+    assert rel_err(y.float().cpu().numpy(), ref) <= TIGHT_TOL
+    # unaligned rows take the scalar staging path
+    wide_g = torch.zeros(M, K + 8, dtype=torch.float16, device="cuda")
+    wide_u = torch.zeros(M, K + 8, dtype=torch.float16, device="cuda")
+    wide_g[:, 1:1 + K], wide_u[:, 1:1 + K] = gate, up
+    y2 = torch.zeros_like(y)
+    cabi.check(cabi.lib().cq_rlayer_matvec_swiglu(C.byref(p.L), ptr(wide_g[:, 1:]), ptr(wide_u[:, 1:]), K + 8, ptr(y2), N, M,
+                                                  ptr(status), None), "swiglu")
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y)
