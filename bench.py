@@ -837,7 +837,7 @@ def model_measure(args, torch, dist, dev, world, rank, local, name, gen=256, pro
                                 "far larger than L2",
                    "parallelism": "single GPU" if world == 1 else
                                   f"column-parallel over {world} GPUs, 4 all-gathers per layer inside the graph "
-                                  f"({'peer-memory kernel cq_peer_allgather' if model.peer is not None else 'NCCL'})",
+                                  f"({'peer-memory exchange, for the o and down projections inside their own launch' if model.peer is not None else 'NCCL'})",
                    "launch": f"one CUDA graph per decode step ({cfg.n_layers * 7} quantized projections, attention, "
                              "norms, lm_head, argmax)"},
         "roofline": {"bound": "hbm", "achieved": (qbytes + hbytes) / (ms_tok * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
