@@ -160,6 +160,13 @@ __device__ __forceinline__ void rv_imma(int (&d)[4], const uint32_t (&a)[4], uin
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// D (16 x 8, s32) = A (16 x 32, u8) . B (32 x 8, s8): the first product of a chain, no accumulator to initialise
+__device__ __forceinline__ void rv_imma_z(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
 // D (16 x 8, f32) += A (16 x 16, f16) . B (16 x 8, f16)
 __device__ __forceinline__ void rv_hmma(float (&d)[4], const uint4 a, uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -550,10 +557,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
         const unsigned char* gp = gp0 + slot_off + gi * GRP_BYTES;
         const unsigned char* gq = gq0 + slot_off + gi * GRP_BYTES;
         int dP[SETS][4], dH[SETS][4];
-#pragma unroll
-        for (int s = 0; s < SETS; ++s)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) { dP[s][e] = 0; dH[s][e] = 0; }
         if (BITS == 4) {
           const uint4 w0 = *reinterpret_cast<const uint4*>(gp);
           const uint4 w1 = *reinterpret_cast<const uint4*>(gq);
@@ -561,12 +564,17 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
           uint32_t aP[4], aH[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) { aP[j] = wa[j] & 0x0F0F0F0Fu; aH[j] = wa[j] & 0xF0F0F0F0u; }
-          rv_imma(dP[0], aP, xb[gi][0], xb[gi][1]);          // columns 0..31
-          rv_imma(dH[0], aH, xb[gi][2], xb[gi][3]);          // columns 32..63, as 16 u
+          rv_imma_z(dP[0], aP, xb[gi][0], xb[gi][1]);        // columns 0..31
+          rv_imma_z(dH[0], aH, xb[gi][2], xb[gi][3]);        // columns 32..63, as 16 u
 #pragma unroll
           for (int j = 0; j < 4; ++j) { aP[j] = wc[j] & 0x0F0F0F0Fu; aH[j] = wc[j] & 0xF0F0F0F0u; }
-          rv_imma(dP[SETS - 1], aP, xb[gi][4], xb[gi][5]);   // columns 64..95
-          rv_imma(dH[SETS - 1], aH, xb[gi][6], xb[gi][7]);   // columns 96..127
+          if (SETS == 1) {
+            rv_imma(dP[0], aP, xb[gi][4], xb[gi][5]);        // columns 64..95
+            rv_imma(dH[0], aH, xb[gi][6], xb[gi][7]);        // columns 96..127
+          } else {
+            rv_imma_z(dP[SETS - 1], aP, xb[gi][4], xb[gi][5]);
+            rv_imma_z(dH[SETS - 1], aH, xb[gi][6], xb[gi][7]);
+          }
         } else {
           const uint4 w0 = *reinterpret_cast<const uint4*>(gp);
           const uint2 w1 = *reinterpret_cast<const uint2*>(gq);
@@ -581,8 +589,13 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
             aP[2] = Cw & 0x07070707u; aH[2] = Cw & 0x70707070u;
             aP[3] = (A3 & 0x01010101u) | (B2 & 0x02020202u) | (C1 & 0x04040404u);
             aH[3] = (A3 & 0x10101010u) | (B2 & 0x20202020u) | (C1 & 0x40404040u);
-            rv_imma(dP[s * (SETS - 1)], aP, xb[gi][4 * s], xb[gi][4 * s + 1]);       // columns 64 s .. 64 s + 31
-            rv_imma(dH[s * (SETS - 1)], aH, xb[gi][4 * s + 2], xb[gi][4 * s + 3]);   // columns 64 s + 32 .. 64 s + 63, as 16 u
+            if (s == 0 || SETS == 2) {                       // the first product into an accumulator
+              rv_imma_z(dP[s * (SETS - 1)], aP, xb[gi][4 * s], xb[gi][4 * s + 1]);   // columns 64 s .. 64 s + 31
+              rv_imma_z(dH[s * (SETS - 1)], aH, xb[gi][4 * s + 2], xb[gi][4 * s + 3]);   // columns 64 s + 32 .. 64 s + 63, as 16 u
+            } else {
+              rv_imma(dP[0], aP, xb[gi][4 * s], xb[gi][4 * s + 1]);
+              rv_imma(dH[0], aH, xb[gi][4 * s + 2], xb[gi][4 * s + 3]);
+            }
           }
         }
         // lanes with t4 == 0 hold column 0 (hi sums) and column 1 (lo sums) of rows g8, g8 + 8
