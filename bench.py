@@ -905,10 +905,8 @@ def run_sweep(args):
                 alg = algorithmic_bytes(k, n, bits, GROUP, m, c)
                 row = {"K": k, "N": n, "bits": bits, "batch": m, "us_per_call": us, "GBps": alg / us / 1e3,
                        "frac_of_measured_hbm": alg / us / 1e3 / peak,
-                       "route": ("row-tile kernel, " + ("1 launch" if m <= 4 or k > 8300 and False else f"{(m + 3) // 4} launches")) if m <= (4 if k - c > 8192 else 16)
-                                else "tensor-core tile GEMM"}
-                if k - c > 8192 and 1 < m <= 4:
-                    row["route"] = f"row-tile kernel, {m} launches (one activation row each: wide layer)"
+                       "route": (f"row-tile kernel, {(m + 3) // 4} launch(es)" + (", tiles shared by 2 CTAs" if k - c > 8192 else ""))
+                                if m <= (8 if k - c > 8192 else 12) else "tensor-core tile GEMM"}
                 if rmod is not None and m == 1:        # the reference's kernels race in shared memory beyond batch 1
                     torch.cuda.synchronize()
                     r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

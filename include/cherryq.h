@@ -197,7 +197,7 @@ int cq_rlayer_matvec(const cq_rlayer* layer, const void* x_f16, void* y_f16, int
 int cq_rlayer_matvec_swiglu(const cq_rlayer* layer, const void* gate_f16, const void* up_f16, int ld,
                             void* y_f16, int ldy, int M, uint32_t* status_word, cq_stream_t stream);
 /* The largest batch for which cq_rlayers_matvec is the faster path for this layer (beyond it
- * cq_tlayer_gemm is): 16 for layers of up to 8192 quantized columns, 8 for wider ones, 0 for layers
+ * cq_tlayer_gemm is): 12 for layers of up to 8192 quantized columns, 8 for wider ones, 0 for layers
  * the kernel does not take.  No GPU work. */
 int cq_rlayer_preferred_rows(const cq_rlayer* layer);
 /* cq_rlayer_matvec for callers that hold their activations in HOST memory (a foreign-function

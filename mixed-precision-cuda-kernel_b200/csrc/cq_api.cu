@@ -128,7 +128,7 @@ int legacy_matmul(int bits, const void* vec, const uint8_t* qweight, const void*
   const CacheKey key{dev, qweight, scales, cherry_weight, cherry_indices, bits, vec_height, width,
                      cherry_size, group_size, tag};
   // decode batches: the row-tile kernel (four activation rows per launch) up to the batch where the tile
-  // GEMM overtakes it (16 rows, 8 for layers split along K); layers the row kernel does not take: the stream kernel
+  // GEMM overtakes it (12 rows, 8 for layers split along K); layers the row kernel does not take: the stream kernel
   // below 8 rows
   int row_limit = PREFILL_MIN_ROWS - 1;
   {

@@ -1236,10 +1236,10 @@ extern "C" int cq_rlayer_preferred_rows(const cq_rlayer* L) {
   if (!L) return 0;
   const int gpw = rv_gpw_for(L);
   if (!gpw) return 0;
-  // measured on B200 against the tile GEMM at 16 rows: four launches of four rows take 24 / 32 us on
-  // 4096 -> 4096 / 11008 against the GEMM's 25 / 36; layers split along K (11008 -> 4096: 4 x 13.8 us
-  // against 35) give way to the GEMM beyond 8 rows
-  return L->ksplit > 1 ? 8 : 16;
+  // measured on B200 through the drop-in ops against the tile GEMM: 8 rows (two launches) take 12 - 16 us
+  // against the GEMM's 25 - 33; 16 rows (four launches) 30 / 35 us on 4096 -> 4096 / 11008 against 25 / 32,
+  // so three launches are the limit; layers split along K (11008 -> 4096: 14 us per launch) stop at two
+  return L->ksplit > 1 ? 8 : 12;
 }
 
 extern "C" int cq_rlayer_matvec(const cq_rlayer* L, const void* x, void* y, int accumulate, uint32_t* status_word,
