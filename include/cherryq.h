@@ -381,7 +381,8 @@ int cq_unpack_dense(const uint8_t* qweight, const void* scales_f16,
  * the output is filled with NaN) and writes the gathered (rows, P * cols_local) fp16 matrix.
  * One rank per GPU: ranks never share a device.  Every rank makes the same sequence of calls.
  *
- * A region is cq_peer_region_bytes(capacity) bytes of device memory, zeroed at creation;
+ * A region is cq_peer_region_bytes(capacity) bytes of device memory, zeroed at creation (its header
+ * keeps the capacity: a call that states another one sends nothing and reports like a time-out);
  * capacity (a multiple of 16) bounds 4 * rows * cols_local * P of one call (twice the payload).
  * Peers map it through the 64-byte CUDA IPC handle.  regions[] holds P device pointers,
  * regions[rank] the own one.

@@ -6,6 +6,7 @@
 // Every rank owns one "region" of device memory that its peers map through CUDA IPC:
 //
 //   byte 0     epoch uint32                      this rank's own call counter (peers never touch it)
+//   byte 8     capacity uint64                   bytes of one landing area, checked by every call against its argument
 //   byte 64    done uint32                       arrivals of the CTAs of a decode kernel that ends with the exchange
 //   byte 256   landing[0]  (capacity bytes)      slices of even epochs, [rank][8-byte words]
 //   ...        landing[1]  (capacity bytes)      slices of odd epochs
@@ -49,6 +50,8 @@ extern "C" int cq_peer_region_create(size_t capacity, void** region) {
   void* p = nullptr;
   CQ_CUDA_TRY(cudaMalloc(&p, cq_peer_region_bytes(capacity)));
   cudaError_t e = cudaMemset(p, 0, cq_peer_region_bytes(capacity));
+  const unsigned long long cap = capacity;
+  if (e == cudaSuccess) e = cudaMemcpy((uint8_t*)p + CAPACITY_OFF, &cap, sizeof(cap), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     cudaFree(p);

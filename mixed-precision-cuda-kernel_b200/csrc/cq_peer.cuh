@@ -6,8 +6,9 @@
 namespace cq_peer {
 
 constexpr int MAX_RANKS = 8;
-// region header: this rank's call counter at byte 0, the decode kernel's CTA arrival counter at byte 64
-constexpr size_t EPOCH_OFF = 0, DONE_OFF = 64, LANDING_OFF = 256;
+// region header: this rank's call counter at byte 0, the capacity the region was created with at byte 8, the
+// decode kernel's CTA arrival counter at byte 64
+constexpr size_t EPOCH_OFF = 0, CAPACITY_OFF = 8, DONE_OFF = 64, LANDING_OFF = 256;
 
 struct PeerGatherParams {
   uint8_t* region[MAX_RANKS];     // region[rank] is this rank's own
@@ -46,9 +47,12 @@ __device__ __forceinline__ void exchange(const PeerGatherParams& p, int* s_fail)
     if (r == p.rank) own = p.region[r];
   const uint32_t e = *reinterpret_cast<volatile uint32_t*>(own + EPOCH_OFF) + 1u;
   const size_t area = LANDING_OFF + (size_t)(e & 1u) * p.capacity;
+  // a call whose capacity is not the one the region was created with would address the landing areas wrongly:
+  // nothing is sent, the call ends like one whose peers never delivered
+  const bool geometry_ok = *reinterpret_cast<volatile unsigned long long*>(own + CAPACITY_OFF) == p.capacity;
 
   // 1. deliver the own slice to every rank (this one included): 8 payload bytes -> 16 bytes {d0, e, d1, e}
-  for (uint32_t i = tid; i < p.slice8; i += THREADS) {
+  for (uint32_t i = tid; geometry_ok && i < p.slice8; i += THREADS) {
     const uint2 d = __ldcg(p.x + i);
     const uint4 w = make_uint4(d.x, e, d.y, e);
     const size_t at = area + ((size_t)p.rank * p.slice8 + i) * 16;
@@ -62,7 +66,7 @@ __device__ __forceinline__ void exchange(const PeerGatherParams& p, int* s_fail)
   const uint4* land = reinterpret_cast<const uint4*>(own + area);
   const uint32_t total = p.slice8 * (uint32_t)p.world;
   const unsigned long long t0 = now_ns();
-  bool failed = false;
+  bool failed = !geometry_ok;
   for (uint32_t idx = tid; idx < total && !failed; idx += THREADS) {
     for (;;) {
       const uint4 w = ld_landing(land + idx);

@@ -77,6 +77,25 @@ def test_absent_peer_runs_into_the_time_limit(region):
     assert torch.equal(out1, x) and int(status.item()) == 0
 
 
+def test_capacity_mismatch_is_reported(region):
+    """A call that states another capacity than the region was created with would address the landing areas
+    wrongly: it sends nothing and ends with the time-out status and a NaN output."""
+    lib, _cabi, p = region
+    regions = (C.c_void_p * 1)(p.value)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x = torch.randn(1, 256, device="cuda").half()
+    out = torch.zeros(1, 256, dtype=torch.float16, device="cuda")
+    cv = C.c_void_p
+    rc = lib.cq_peer_allgather(regions, 1, 0, CAP // 2, cv(x.data_ptr()), cv(out.data_ptr()), 1, 256, 200, cv(status.data_ptr()),
+                               cv(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) & 8 and bool(torch.isnan(out).all())
+    status.zero_()
+    _cabi.check(_gather(lib, regions, 1, 0, x, out, status), "gather")           # the right capacity works afterwards
+    assert torch.equal(out, x) and int(status.item()) == 0
+
+
 def _one_layer(K=2048, N=264, bits=4):
     import math
     import cherryq_b200
