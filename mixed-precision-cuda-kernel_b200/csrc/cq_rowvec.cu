@@ -36,9 +36,6 @@
 
 namespace {
 
-#ifndef CQ_ROWVEC_INFLIGHT
-#define CQ_ROWVEC_INFLIGHT 0   // tiles the copy warp keeps outstanding; 0 = chosen per layer
-#endif
 constexpr uint32_t RV_WAIT_LIMIT = 1u << 22;
 constexpr int RV_MAX_SLOTS = 16;            // ring slots (tiles resident in shared memory at a time)
 
@@ -85,10 +82,6 @@ struct RowvecParams {
   // gathered rows are complete when the next kernel of the stream starts.  One layer per launch.
   int gather;
   cq_peer::PeerGatherParams peer;
-#ifdef CQ_ROWVEC_TRACE
-  int trace_launch;
-  unsigned long long* trace;   // passed as a kernel parameter: a stamp must not cost a global load
-#endif
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -175,31 +168,6 @@ __device__ __forceinline__ void rv_hmma(float (&d)[4], const uint4 a, uint32_t b
       : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
 
-#ifdef CQ_ROWVEC_TRACE   // tuning builds: per-CTA stamps, buffer [16 launches][1024 CTAs][16]
-// Slot 0 holds %globaltimer at entry (one slow read), slot 1 the SM cycle counter at entry; every other slot
-// holds the cycle counter (cheap), so intervals inside a CTA are not distorted by the stamping itself.
-unsigned long long* cq_rv_trace_host = nullptr;
-__device__ __forceinline__ void rv_stamp_to(unsigned long long* buf, int launch, int slot) {
-  if (buf) {
-    unsigned long long* row = buf + ((size_t)(launch & 15) * 1024 + blockIdx.x) * 16;
-    if (slot == 0) {
-      unsigned long long t;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-      row[0] = t;
-      row[1] = (unsigned long long)clock64();
-    } else {
-      row[slot] = (unsigned long long)clock64();
-    }
-  }
-}
-#ifndef CQ_ROWVEC_TRACE_TID
-#define CQ_ROWVEC_TRACE_TID 0
-#endif
-__device__ __forceinline__ void rv_stamp(unsigned long long* buf, int launch, int slot) { if (threadIdx.x == CQ_ROWVEC_TRACE_TID) rv_stamp_to(buf, launch, slot); }
-#define RV_STAMP(s) rv_stamp(p.trace, p.trace_launch, s)
-#else
-#define RV_STAMP(s)
-#endif
 
 // Requests tile `tile` of the layer (the groups [gb, gb + gn) of it, with the cherry blocks if `cherry`)
 // into ring slot `slot`; one thread calls it.
@@ -244,7 +212,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   constexpr float OFF = BITS == 4 ? 7.5f : 3.5f;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
-  RV_STAMP(0);
 
   __half* slice = reinterpret_cast<__half*>(smem + p.off_slice) + (size_t)warp * p.slice_halves;
   uint32_t* plane = reinterpret_cast<uint32_t*>(slice);      // the planes replace the raw slice once it has been read
@@ -301,14 +268,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
         if (++slot == S) { slot = 0; if (next >= S) ephase ^= 1u; }
       }
     }
-#ifdef CQ_ROWVEC_TRACE
-    if (lane == 1 && p.trace) {      // arrival time of each tile of the first round
-      for (int i = 0; i < min(nt, S) && i < 8; ++i) {
-        rv_mbar_wait(bar_full + 8 * i, 0, &s_abort, p.status);
-        rv_stamp_to(p.trace, p.trace_launch, 8 + i);
-      }
-    }
-#endif
   } else {
   // ---- this warp's groups (contiguous) and cherry block
   const uint16_t* seg_perm = sg.perm;
@@ -329,7 +288,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   // byte offsets inside the slice here, ahead of the wait: two 16-bit fields per word, no field
   // underflows (every column is >= lo8) or overflows (the slice is a few hundred halves).  Padding
   // columns (= K) land on the zero slot at slice[K - lo8], which only the last group's warp has.
-  const uint32_t padpair = (uint32_t)p.K * 0x10001u;
   uint4 pv[PVW];
 #pragma unroll
   for (int u = 0; u < PVW; ++u) {
@@ -342,7 +300,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
     }
     pv[u] = c;
   }
-  (void)padpair;
   const bool owns_tail = ngw > 0 && g0 + ngw == p.NG;       // the warp whose last group may hold padding columns
   int ccol = -1;
   if (has_cherry && lane < 16 && warp * 16 + lane < p.C) ccol = sg.cidx[warp * 16 + lane];
@@ -360,7 +317,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  RV_STAMP(2);
 
   // What a lane keeps of the activations.  The integer MMA's B operand has 8 columns: column 2 m holds
   // the high plane of activation row m, column 2 m + 1 its low plane, so up to four rows ride in the MMAs
@@ -418,7 +374,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   }
   if (owns_tail && lane == 0) slice[p.K - lo8] = __float2half(0.f);   // zero slot for padding columns
   __syncwarp();
-  RV_STAMP(6);
 
   // ---- gather every octet of this lane first: the planes written below re-use the slice's memory
   uint32_t xg[PVW][4];
@@ -535,7 +490,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
   }
   __syncwarp();                                       // the next row re-uses the slice
   }   // activation rows
-  RV_STAMP(3);
 
   // ---- tiles.  Addresses: one base per kind (codes, scales, cherry, partial sums) computed here,
   // the ring slot's offset kept incrementally, everything else is a compile-time displacement.
@@ -549,7 +503,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
 #pragma unroll 1
   for (int i = 0; i < nt; ++i) {
     rv_mbar_wait(bar_full + 8 * slot, phase, &s_abort, p.status);
-    if (i == nt - 1) RV_STAMP(7);
     float acc0 = 0.f, acc1 = 0.f;                            // rows g8 and g8 + 8 of the tile
 #pragma unroll
     for (int gi = 0; gi < GPW; ++gi) {
@@ -617,9 +570,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
       acc0 += dc[0];
       acc1 += dc[2];
     }
-#ifdef CQ_ROWVEC_TRACE
-    if (i < 3) RV_STAMP(13 + i);
-#endif
     if (t4 < Mrows) {                                        // the sums of activation row t4
       pp[0] = acc0;
       pp[8] = acc1;
@@ -634,7 +584,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
     slot_off += (uint32_t)p.slot_bytes;
     if (slot == S) { slot = 0; slot_off = 0; phase ^= 1u; }
   }
-  RV_STAMP(4);
   }   // working warps
   __syncthreads();
   // ---- the warps' partial sums of every row, in warp order
@@ -706,7 +655,6 @@ __global__ void __launch_bounds__((W + 1) * 32, 1) cq_rowvec_kernel(const Rowvec
       if (tid == 0) *done = 0u;                            // ready for the next launch
     }
   }
-  RV_STAMP(5);
 }
 
 // ------------------------------------------------------------------ layout kernels
@@ -939,7 +887,7 @@ RowvecFn rv_pick(int bits, int sets, int M = 1) {
 // group size, hence the same tile record size): how the CTAs are divided among the layers, the
 // shared-memory sections, the ring.  W working warps own up to GPW groups each.  Fills the launch
 // parameters that do not depend on the call.  Returns a status code.
-int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, int M, const RvDevice& di,
+int rv_plan(int W, int GPW, const cq_rlayer* const* Ls, int n, int M, const RvDevice& di,
             RowvecParams* p, int* grid_out, int* smem_out) {
   if (n < 1 || n > RV_MAX_SEG || M < 1 || M > RV_MAX_ROWS) return CQ_ERR_BAD_ARG;
   const cq_rlayer* L = Ls[0];
@@ -1015,7 +963,6 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
   p->off_bar = off;   off = rv_align(off + 2 * RV_MAX_SLOTS * 8, 128);
   p->off_tiles = off;
   int budget = di.max_smem - 1024;          // the kernel also has a small static allocation; keep clear of the limit
-  if (smem_kb > 0 && smem_kb * 1024 < budget) budget = smem_kb * 1024;
   int slots = (budget - off) / p->slot_bytes;
   if (slots > nt_max) slots = nt_max;
   if (slots > RV_MAX_SLOTS) slots = RV_MAX_SLOTS;
@@ -1023,7 +970,7 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
   p->slots = slots;
   // measured on B200: two tiles outstanding stream best when a CTA has several tiles (4096 -> 11008: 5.7 us
   // against 6.6 with one and 6.1 with three); with one or two tiles per CTA a single outstanding tile is faster
-  if (inflight <= 0) inflight = nt_max >= 3 ? 2 : 1;
+  const int inflight = nt_max >= 3 ? 2 : 1;
   p->inflight = inflight > slots ? slots : inflight;
   *grid_out = grid;
   *smem_out = off + slots * p->slot_bytes;
@@ -1032,8 +979,7 @@ int rv_plan(int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* L
 
 // One launch of a kernel whose warp count is W and whose warps can own GPW groups, over `n` layers
 // that take the same activation row x; ys[i] receives layer i's output.
-// inflight: tiles the copy warp keeps outstanding.
-int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_rlayer* const* Ls, int n, const __half* x, int ldx,
+int rv_launch(RowvecFn fn, int W, int GPW, const cq_rlayer* const* Ls, int n, const __half* x, int ldx,
               __half* const* ys, int ldy, int M, int accumulate, uint32_t* status, cudaStream_t st,
               const cq_peer::PeerGatherParams* peer = nullptr, const __half* x2 = nullptr) {
   int dev = 0;
@@ -1042,7 +988,7 @@ int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_r
   if (!di.ok) return CQ_ERR_NO_DEVICE;
   RowvecParams p;
   int grid = 0, smem = 0;
-  const int rc = rv_plan(W, GPW, inflight, smem_kb, Ls, n, M, di, &p, &grid, &smem);
+  const int rc = rv_plan(W, GPW, Ls, n, M, di, &p, &grid, &smem);
   if (rc != CQ_OK) return rc;
   for (int i = 0; i < RV_MAX_SEG; ++i) {
     const int j = i < n ? i : 0;                 // unused entries repeat the first layer (never selected)
@@ -1060,11 +1006,6 @@ int rv_launch(RowvecFn fn, int W, int GPW, int inflight, int smem_kb, const cq_r
   p.accumulate = accumulate;
   p.gather = peer ? 1 : 0;
   if (peer) p.peer = *peer; else p.peer = cq_peer::PeerGatherParams{};
-#ifdef CQ_ROWVEC_TRACE
-  static int launch_no = 0;
-  p.trace_launch = launch_no++;
-  p.trace = cq_rv_trace_host;
-#endif
   {
     // opt in to the dynamic shared memory this launch needs (remembered per kernel and device)
     static std::mutex mu;
@@ -1160,7 +1101,7 @@ extern "C" int cq_rlayer_check(const cq_rlayer* L) {
   if (!gpw) return CQ_ERR_UNSUPPORTED;
   RowvecParams p;
   int grid = 0, smem = 0;
-  return rv_plan(RV_W, gpw, CQ_ROWVEC_INFLIGHT, 0, &L, 1, RV_MAX_ROWS, di, &p, &grid, &smem);
+  return rv_plan(RV_W, gpw, &L, 1, RV_MAX_ROWS, di, &p, &grid, &smem);
 }
 
 extern "C" int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, const void* x, int ldx, void* const* ys, int ldy,
@@ -1183,8 +1124,8 @@ extern "C" int cq_rlayers_matvec(const cq_rlayer* const* layers, int n_layers, c
     for (int i = 0; i < n_layers; ++i) yp[i] = (__half*)ys[i] + (size_t)m0 * ldy;
     int rc = CQ_ERR_UNSUPPORTED;
     switch (rv_gpw_for(L)) {
-      case 2: rc = rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, rows), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
-      case 4: rc = rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, rows), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
+      case 2: rc = rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, rows), RV_W, 2, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
+      case 4: rc = rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, rows), RV_W, 4, layers, n_layers, xp, ldx, yp, ldy, rows, accumulate, status_word, st); break;
       default: break;
     }
     if (rc != CQ_OK) return rc;
@@ -1204,8 +1145,8 @@ extern "C" int cq_rlayer_matvec_gather(const cq_rlayer* L, const void* x, int ld
   __half* yp = (__half*)y_local;
   cudaStream_t st = (cudaStream_t)stream;
   switch (rv_gpw_for(L)) {
-    case 2: return rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, M), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, &L, 1, (const __half*)x, ldx, &yp, L->N, M, 0, status_word, st, &pg);
-    case 4: return rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, M), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, &L, 1, (const __half*)x, ldx, &yp, L->N, M, 0, status_word, st, &pg);
+    case 2: return rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, M), RV_W, 2, &L, 1, (const __half*)x, ldx, &yp, L->N, M, 0, status_word, st, &pg);
+    case 4: return rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, M), RV_W, 4, &L, 1, (const __half*)x, ldx, &yp, L->N, M, 0, status_word, st, &pg);
     default: return CQ_ERR_UNSUPPORTED;
   }
 }
@@ -1223,8 +1164,8 @@ extern "C" int cq_rlayer_matvec_swiglu(const cq_rlayer* L, const void* gate, con
     __half* yp = (__half*)y + (size_t)m0 * ldy;
     int rc = CQ_ERR_UNSUPPORTED;
     switch (rv_gpw_for(L)) {
-      case 2: rc = rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, rows), RV_W, 2, CQ_ROWVEC_INFLIGHT, 0, &L, 1, gp, ld, &yp, ldy, rows, 0, status_word, st, nullptr, up2); break;
-      case 4: rc = rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, rows), RV_W, 4, CQ_ROWVEC_INFLIGHT, 0, &L, 1, gp, ld, &yp, ldy, rows, 0, status_word, st, nullptr, up2); break;
+      case 2: rc = rv_launch(rv_pick<RV_W, 2>(L->bits, L->sets, rows), RV_W, 2, &L, 1, gp, ld, &yp, ldy, rows, 0, status_word, st, nullptr, up2); break;
+      case 4: rc = rv_launch(rv_pick<RV_W, 4>(L->bits, L->sets, rows), RV_W, 4, &L, 1, gp, ld, &yp, ldy, rows, 0, status_word, st, nullptr, up2); break;
       default: break;
     }
     if (rc != CQ_OK) return rc;
@@ -1305,21 +1246,3 @@ extern "C" int cq_rlayer_matvec_host(const cq_rlayer* L, const void* x_host, voi
   return CQ_OK;
 }
 
-#ifdef CQ_ROWVEC_SWEEP
-// Tuning build only (not part of the library): a table of kernel shapes behind one entry point.
-#define RV_CASE(id, W, GPW, SMEM_KB, INFL) \
-  case id: { __half* yv = (__half*)y; return rv_launch(rv_pick<W, GPW>(L->bits, L->sets), W, GPW, INFL, SMEM_KB, &L, 1, (const __half*)x, L->K, &yv, L->N, 1, accumulate, status_word, (cudaStream_t)stream); }
-extern "C" int cq_rlayer_matvec_variant(int variant, const cq_rlayer* L, const void* x, void* y, int accumulate,
-                                        uint32_t* status_word, cq_stream_t stream) {
-  switch (variant) {
-    CQ_ROWVEC_SWEEP
-    default: return CQ_ERR_UNSUPPORTED;
-  }
-}
-#ifdef CQ_ROWVEC_TRACE
-extern "C" int cq_rv_set_trace(void* device_buffer) {
-  cq_rv_trace_host = (unsigned long long*)device_buffer;
-  return CQ_OK;
-}
-#endif
-#endif
