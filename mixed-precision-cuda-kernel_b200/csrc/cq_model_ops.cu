@@ -272,6 +272,201 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __half* 
   if (tid == 0) counters[hidx] = 0u;                                  // ready for the next launch
 }
 
+// The same for grouped-query models and long caches: one CTA per KV head (blockIdx.x), sequence and range
+// of positions handles all G = H / KV query heads that share the KV head, so every K and V row is read
+// once (with one CTA per query head it is read G times through L2).  A group of D / 8 lanes takes one
+// position with 16-byte loads (8 values a lane), GT >= G query heads at a time in registers.  Partial
+// results of the ranges as in the kernel above; the arrival counter is per (sequence, KV head).
+constexpr int GQA_THREADS = 256, GQA_WARPS = GQA_THREADS / 32;
+template <int GT>
+__global__ void __launch_bounds__(GQA_THREADS) attn_decode_gqa_kernel(const __half* __restrict__ q,
+                                                                      const __half* __restrict__ k_cache,
+                                                                      const __half* __restrict__ v_cache,
+                                                                      const long long* __restrict__ pos,
+                                                                      __half* __restrict__ out, float* __restrict__ part,
+                                                                      unsigned int* __restrict__ counters, int H, int KV,
+                                                                      int D, int max_seq, float scale) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  extern __shared__ float sm[];              // [GT][range] scores, later [warps][GT][D] partial sums of V
+  __shared__ float s_m[GT], s_l[GT];
+  __shared__ int s_last;
+  const int kvh = blockIdx.x, seq = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+  const int G = H / KV, head0 = kvh * G;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lpp = D >> 3;                    // lanes per position: 8, 16 or 32
+  const int ppw = 32 / lpp;                  // positions a warp takes per turn
+  const int sub = lane / lpp, l = lane - sub * lpp;
+  const long long pl = pos[seq];
+  const int n_all = pl < 0 ? 1 : (pl >= max_seq ? max_seq : (int)pl + 1);
+  const int range = (max_seq + nsplit - 1) / nsplit;
+  const int chunk = (n_all + nsplit - 1) / nsplit;
+  const int pbeg = split * chunk;
+  const int n_pos = max(0, min(n_all - pbeg, chunk));
+  const size_t row = (size_t)KV * D;         // elements between consecutive positions of a cache
+  const __half* kb = k_cache + ((size_t)seq * max_seq + pbeg) * row + (size_t)kvh * D + l * 8;
+  const __half* vb = v_cache + ((size_t)seq * max_seq + pbeg) * row + (size_t)kvh * D + l * 8;
+
+  // ---- scores
+  {
+    uint4 qr[GT];
+#pragma unroll
+    for (int g = 0; g < GT; ++g)
+      qr[g] = g < G ? *reinterpret_cast<const uint4*>(q + ((size_t)seq * H + head0 + g) * D + l * 8) : make_uint4(0, 0, 0, 0);
+    const int stride = GQA_WARPS * ppw;
+    constexpr int UF = 4;                                 // positions per lane group in flight (loads first, then math)
+    for (int base = warp * ppw; base < n_pos; base += UF * stride) {
+      uint4 kk[UF];
+#pragma unroll
+      for (int j = 0; j < UF; ++j) {
+        const int pj = base + sub + j * stride;
+        kk[j] = pj < n_pos ? __ldg(reinterpret_cast<const uint4*>(kb + (size_t)pj * row)) : make_uint4(0, 0, 0, 0);
+      }
+      float2 kf[UF][4];                                   // converted once, used by every query head
+#pragma unroll
+      for (int j = 0; j < UF; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) kf[j][i] = __half22float2(reinterpret_cast<const __half2*>(&kk[j])[i]);
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        if (g < G) {
+          const __half2* qh = reinterpret_cast<const __half2*>(&qr[g]);
+          float2 qf[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) qf[i] = __half22float2(qh[i]);
+          float d[UF];
+#pragma unroll
+          for (int j = 0; j < UF; ++j) {
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a += qf[i].x * kf[j][i].x + qf[i].y * kf[j][i].y;
+            d[j] = a;
+          }
+          for (int o = lpp >> 1; o > 0; o >>= 1) {
+#pragma unroll
+            for (int j = 0; j < UF; ++j) d[j] += __shfl_xor_sync(0xffffffffu, d[j], o);
+          }
+          if (l == 0) {
+#pragma unroll
+            for (int j = 0; j < UF; ++j) {
+              const int pj = base + sub + j * stride;
+              if (pj < n_pos) sm[g * range + pj] = d[j] * scale;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // ---- softmax pieces: warp g takes query head g (GT <= number of warps)
+  if (warp < G) {
+    float* sg = sm + warp * range;
+    float m = -INFINITY;
+    for (int p = lane; p < n_pos; p += 32) m = fmaxf(m, sg[p]);
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+    for (int p = lane; p < n_pos; p += 32) {
+      const float e = __expf(sg[p] - m);
+      sg[p] = e;
+      sum += e;
+    }
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = sum; }
+  }
+  __syncthreads();
+  // ---- weighted sums of V: a lane keeps 8 head-dimension values of every query head
+  float acc[GT][8];
+#pragma unroll
+  for (int g = 0; g < GT; ++g)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+  {
+    const int stride = GQA_WARPS * ppw;
+    constexpr int UF = 4;
+    for (int base = warp * ppw; base < n_pos; base += UF * stride) {
+      uint4 vv[UF];
+#pragma unroll
+      for (int j = 0; j < UF; ++j) {
+        const int pj = base + sub + j * stride;
+        vv[j] = pj < n_pos ? __ldg(reinterpret_cast<const uint4*>(vb + (size_t)pj * row)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < UF; ++j) {
+        const int pj = base + sub + j * stride;
+        const bool ok = pj < n_pos;
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 a = __half22float2(reinterpret_cast<const __half2*>(&vv[j])[i]);
+          f[2 * i] = a.x; f[2 * i + 1] = a.y;
+        }
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+          if (g < G) {
+            const float w = ok ? sm[g * range + pj] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][i] += w * f[i];
+          }
+        }
+      }
+    }
+  }
+  // the position groups of a warp hold the same head-dimension values: add them (lanes l of every group)
+#pragma unroll
+  for (int g = 0; g < GT; ++g)
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      for (int o = lpp; o < 32; o <<= 1) acc[g][i] += __shfl_xor_sync(0xffffffffu, acc[g][i], o);
+  __syncthreads();                                     // every warp is done with the scores: the memory is re-used
+  float* red = sm;                                     // [warps][GT][D]
+  if (sub == 0) {
+#pragma unroll
+    for (int g = 0; g < GT; ++g)
+      if (g < G)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) red[((size_t)warp * GT + g) * D + l * 8 + i] = acc[g][i];
+  }
+  __syncthreads();
+  const size_t hbase = (size_t)seq * H + head0;
+  for (int e = tid; e < G * D; e += GQA_THREADS) {
+    const int g = e / D, d = e - g * D;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < GQA_WARPS; ++w) v += red[((size_t)w * GT + g) * D + d];
+    if (nsplit == 1) {
+      out[(hbase + g) * D + d] = __float2half(v / s_l[g]);
+    } else {
+      float* mine = part + ((hbase + g) * nsplit + split) * (size_t)(D + 2);
+      mine[2 + d] = v;
+      if (d == 0) { mine[0] = s_m[g]; mine[1] = s_l[g]; }
+    }
+  }
+  if (nsplit == 1) return;
+  __threadfence();
+  __syncthreads();
+  const size_t cidx = (size_t)seq * KV + kvh;
+  if (tid == 0) s_last = atomicAdd(&counters[cidx], 1u) == (unsigned int)(nsplit - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int e = tid; e < G * D; e += GQA_THREADS) {
+    const int g = e / D, d = e - g * D;
+    const float* all = part + (hbase + g) * nsplit * (size_t)(D + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, __ldcg(all + (size_t)s * (D + 2)));
+    float lsum = 0.f, v = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float* ps = all + (size_t)s * (D + 2);
+      const float ms = __ldcg(ps);
+      const float w = ms == -INFINITY ? 0.f : __expf(ms - mm);       // an empty range carries no weight
+      lsum += w * __ldcg(ps + 1);
+      v += w * __ldcg(ps + 2 + d);
+    }
+    out[(hbase + g) * D + d] = __float2half(v / lsum);
+  }
+  if (tid == 0) counters[cidx] = 0u;                                  // ready for the next launch
+}
+
 int blocks_for(long long total, int threads, int cap) {
   long long b = (total + threads - 1) / threads;
   if (b < 1) b = 1;
@@ -349,7 +544,8 @@ extern "C" size_t cq_attn_decode_workspace_bytes(int sequences, int n_heads, int
   if (sequences < 1 || n_heads < 1 || head_dim < 2 || max_seq < 1) return 0;
   const size_t heads = (size_t)sequences * n_heads;
   // [heads] counters (zero before the first use; every launch leaves them zero), then the ranges' partial results
-  return heads * sizeof(unsigned int) + 256 + heads * attn_splits(sequences, n_heads, max_seq) * (size_t)(head_dim + 2) * sizeof(float);
+  // (the grouped-query kernel divides by KV heads and may use more ranges than the per-head one: room for the maximum)
+  return heads * sizeof(unsigned int) + 256 + heads * ATT_MAX_SPLITS * (size_t)(head_dim + 2) * sizeof(float);
 }
 
 extern "C" int cq_attn_decode(const void* q, const void* k_cache, const void* v_cache, const long long* position,
@@ -360,15 +556,32 @@ extern "C" int cq_attn_decode(const void* q, const void* k_cache, const void* v_
   if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads || head_dim < 2 || head_dim > 256 || (head_dim & 1) ||
       256 % head_dim || max_seq < 1 || max_seq > 65536)
     return CQ_ERR_BAD_SHAPE;
+  const size_t heads = (size_t)sequences * n_heads;
+  unsigned int* counters = (unsigned int*)workspace;
+  float* part = (float*)((uint8_t*)workspace + (heads * sizeof(unsigned int) + 255) / 256 * 256);
+  const int G = n_heads / n_kv_heads;
+  if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && G <= 8) {
+    // one CTA per KV head: every cache row is read once for the query heads that share it
+    const int splits = attn_splits(sequences, n_kv_heads, max_seq);
+    const int range = (max_seq + splits - 1) / splits;
+    const int gt = G <= 1 ? 1 : (G <= 2 ? 2 : (G <= 4 ? 4 : 8));
+    const int words = gt * range > GQA_WARPS * gt * head_dim ? gt * range : GQA_WARPS * gt * head_dim;
+    const int smem = words * (int)sizeof(float);
+    if (smem > 200 * 1024) return CQ_ERR_TOO_LARGE;
+    void (*fn)(const __half*, const __half*, const __half*, const long long*, __half*, float*, unsigned int*, int, int, int, int, float) =
+        gt == 1 ? attn_decode_gqa_kernel<1> : (gt == 2 ? attn_decode_gqa_kernel<2> : (gt == 4 ? attn_decode_gqa_kernel<4> : attn_decode_gqa_kernel<8>));
+    if (smem > 48 * 1024) CQ_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CQ_CUDA_TRY(launch_pdl(fn, dim3(n_kv_heads, sequences, splits), dim3(GQA_THREADS), (size_t)smem, (cudaStream_t)stream,
+                           (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, position, (__half*)out, part,
+                           counters, n_heads, n_kv_heads, head_dim, max_seq, scale));
+    return CQ_OK;
+  }
   const int splits = attn_splits(sequences, n_heads, max_seq);
   const int range = (max_seq + splits - 1) / splits;
   const int smem = (range + ATT_THREADS) * (int)sizeof(float);
   if (smem > 200 * 1024) return CQ_ERR_TOO_LARGE;
   if (smem > 48 * 1024)
     CQ_CUDA_TRY(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  const size_t heads = (size_t)sequences * n_heads;
-  unsigned int* counters = (unsigned int*)workspace;
-  float* part = (float*)((uint8_t*)workspace + (heads * sizeof(unsigned int) + 255) / 256 * 256);
   CQ_CUDA_TRY(launch_pdl(attn_decode_kernel, dim3(n_heads, sequences, splits), dim3(ATT_THREADS), (size_t)smem,
                          (cudaStream_t)stream, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, position,
                          (__half*)out, part, counters, n_heads, n_kv_heads, head_dim, max_seq, scale));

@@ -85,15 +85,16 @@ class CherryDecoder:
         self.cfg, self.dev, self.dense = cfg, torch.device(device), dense
         self.batch = batch          # sequences decoded in lockstep (same prompt length, one position counter)
         # decode attention over the KV cache: "own" = this library's kernel (cq_attn_decode); "flash" = the
-        # flash_attn package's flash_attn_with_kvcache (a library call, like the lm_head's cuBLAS matmul: it reads
-        # a KV head once for all the query heads that share it, which matters for grouped-query models at long
-        # context); "auto" = flash for caches of more than 1024 positions where that package imports, else own
-        # (measured on the 7B architecture at a few hundred positions the own kernel, which sits in the
-        # programmatic-launch chain of the other kernels, gives 668 tokens/s against 585)
+        # flash_attn package's flash_attn_with_kvcache (a library call, like the lm_head's cuBLAS matmul);
+        # "auto" = own, except for grouped-query models with caches of more than 1024 positions where that
+        # package imports.  Measured on B200: without grouped queries the own kernel is ahead at every size
+        # tried (13B shapes at 2100 positions: 19 us against 22 at batch 1, 91 against 159 at batch 8; 7B at 200
+        # positions 9 against 21); with 8 query heads per KV head at 4000 positions its SIMT dot products lose to
+        # flash_attn's tensor-core tiles (45 us against 25 at batch 1, 110 against 29 at batch 4).
         if attention not in ("auto", "own", "flash"):
             raise ValueError("attention is 'auto', 'own' or 'flash'")
         self._flash = None
-        if attention == "flash" or (attention == "auto" and cfg.max_seq > 1024):
+        if attention == "flash" or (attention == "auto" and cfg.max_seq > 1024 and cfg.n_kv_heads < cfg.n_heads):
             try:
                 from flash_attn import flash_attn_with_kvcache
                 self._flash = flash_attn_with_kvcache
