@@ -273,7 +273,9 @@ def run_ours(args):
         _cabi.check(lib.cq_rlayer_check(C.byref(L)), "cq_rlayer_check")
         b = torch.empty(L.blob_bytes, dtype=torch.uint8, device=dev)
         L.blob = b.data_ptr()
-        _cabi.check(lib.cq_rlayer_prepare(C.byref(L), ptr(qq), ptr(ss), ptr(cc), ptr(ii), None), "prepare")
+        # on the stream the buffers were packed on (torch's current one), then everything is awaited
+        cur = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _cabi.check(lib.cq_rlayer_prepare(C.byref(L), ptr(qq), ptr(ss), ptr(cc), ptr(ii), cur), "prepare")
         torch.cuda.synchronize()
         return L, b
 
