@@ -339,6 +339,7 @@ def run_ours(args):
     repeats = max(1, args.repeats)
     gather_checked = None
     own_kernels_per_step = 1       # the matvec (at N > 1 its last CTA runs the exchange; NCCL's kernel is not counted)
+    torch.cuda.synchronize()       # the inputs above were written on the default stream
     with torch.cuda.stream(stream):
         for i in range(max(args.warmup, 3)):          # warm-up: also sets kernel attributes before any capture
             step(i)
@@ -644,6 +645,7 @@ def prefill_measure(torch, dist, dev, world, rank, local, steps_arg, warmup_arg)
             dist.all_gather_into_tensor(y_all, y)
 
     steps = min(steps_arg, 200)
+    torch.cuda.synchronize()       # the inputs above were written on the default stream
     with torch.cuda.stream(stream):
         for i in range(max(warmup_arg, 3)):
             launch(i)
@@ -905,6 +907,7 @@ def run_sweep(args):
                     else:
                         mod.vecquant3matmul_cherryq(x, qq, cc, ii, ss, out, GROUP, True)
 
+                torch.cuda.synchronize()               # the buffers above were written on the default stream
                 with torch.cuda.stream(stream):
                     for i in range(ncopies + 2):       # first use builds the re-packed copies (not capturable)
                         call(i)
