@@ -418,7 +418,10 @@ def run_ours(args):
         qq, cc, ii, ss = refs[i % ncopies]
         xd.copy_(xh, non_blocking=True)
         out.zero_()
-        qc.vecquant4matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP)
+        if BITS == 4:
+            qc.vecquant4matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP)
+        else:
+            qc.vecquant3matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP, True)
         if world > 1:
             if peer is not None:
                 peer.gather_into(out, out_all)
@@ -480,19 +483,24 @@ def run_ours(args):
             rmod = None
         if rmod is not None:
             rsteps = 10 * ncopies
+            def ref_call(qq, cc, ii, ss):
+                if BITS == 4:
+                    rmod.vecquant4matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP)
+                else:
+                    rmod.vecquant3matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP, True)
             for i in range(ncopies):
                 qq, cc, ii, ss = refs[i]
-                rmod.vecquant4matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP)
+                ref_call(qq, cc, ii, ss)
             torch.cuda.synchronize()
             r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             r0.record()
             for i in range(rsteps):
                 qq, cc, ii, ss = refs[i % ncopies]
-                rmod.vecquant4matmul_cherryq(xd, qq, cc, ii, ss, out, GROUP)
+                ref_call(qq, cc, ii, ss)
             r1.record()
             torch.cuda.synchronize()
             rms = r0.elapsed_time(r1) / rsteps
-            ref_gpu = {"kernel": "VecQuant4MatMulKernelCherryQBatchedHalf (reference csrc/quant_cuda_kernel.cu, unmodified, sm_100a)",
+            ref_gpu = {"kernel": f"VecQuant{BITS}MatMulKernelCherryQBatchedHalf (reference csrc/quant_cuda_kernel.cu, unmodified, sm_100a)",
                        "us_per_call": rms * 1e3, "GBps": alg / (rms * 1e-3) / 1e9, "steps": rsteps}
 
     region_what = region.what
@@ -534,9 +542,9 @@ def run_ours(args):
             "pct_of_nominal_8TBps": value / world / 8000.0 * 100.0 if world == 1 else None,
             "region_ms": {"median": median(times), "min": min(times), "max": max(times), "repeats": repeats},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH * alg_local / alg if NCU_DRAM_BYTES_PER_LAUNCH else None,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH * alg_local / alg if NCU_DRAM_BYTES_PER_LAUNCH and not args.shape else None,
                          "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)",
-                         "kernel": "cq_rowvec_kernel<4,1,16,2,1>", "alg_bytes_per_launch": alg_local,
+                         "kernel": "cq_rowvec_kernel<4,1,16,2,1>" if (K_IN, BITS) == (4096, 4) else "cq_rowvec_kernel", "alg_bytes_per_launch": alg_local,
                          "launch_us": kern_ms * 1e3},
             "e2e": e2e, "gpu_launches": args.steps * world * own_kernels_per_step,
             "clocks": clocks,
@@ -1001,7 +1009,14 @@ def main():
     ap.add_argument("--repeats", type=int, default=50,
                     help="timed regions of --steps steps run back to back; the median is reported")
     ap.add_argument("--no-model", action="store_true", help="skip the 70B-architecture decode leg")
+    ap.add_argument("--shape", default=None, metavar="KxNxBITS",
+                    help="decode workload on another layer than the headline one, e.g. 28672x8192x3 (the 70B down "
+                         "projection); for profiling: the line then names that layer as its workload")
     args = ap.parse_args()
+    if args.shape:
+        global K_IN, N_OUT, BITS, WORKLOAD
+        K_IN, N_OUT, BITS = (int(v) for v in args.shape.lower().split("x"))
+        WORKLOAD = f"linear_{K_IN}x{N_OUT}_{BITS}bit_g128_cherry1/256_batch1"
     if args.impl == "reference":
         if args.steps > 200:
             args.steps = 200        # each step is a full-layer CPU call (tens of ms): keep the run within minutes
