@@ -455,7 +455,7 @@ def run_ours(args):
     e2e_steps = min(args.steps, 2000)
     op_ms = timed_host_loop(e2e_step, e2e_steps)
     qc.poll()
-    op_path = ("quant_cuda.vecquant4matmul_cherryq with pinned host x per rank" +
+    op_path = (f"quant_cuda.vecquant{BITS}matmul_cherryq with pinned host x per rank" +
                (f", {gather_kind}, the whole y read back on rank 0" if world > 1 else " and y"))
     if world == 1:
         # the C ABI's host-buffer call: x from pinned host memory, y in pinned host memory when it returns
