@@ -71,11 +71,25 @@ def test_decoder_checkpoint_round_trip_in_the_reference_layout(mods, tmp_path):
     state, conf = P.load_quantized_state(str(tmp_path))
     assert conf["w_bits"] == 4 and conf["group_size"] == 128
     b = D.CherryDecoder(cfg, seed=99)        # different weights, then overwritten from the file
-    P.load_decoder_state_dict(b, state)
     prompt = torch.randint(0, cfg.vocab, (12,), device="cuda", generator=torch.Generator(device="cuda").manual_seed(0))
+    # b runs with its own weights first (one-row, batch and prefill paths: every re-packed copy and the
+    # drop-in ops' cache are populated), then takes a's weights: nothing of the old copies may survive
+    b.prefill(prompt)
+    old = b.generate(16, use_graph=False)
+    P.load_decoder_state_dict(b, state)
     a.prefill(prompt)
     b.prefill(prompt)
-    assert torch.equal(a.generate(16, use_graph=False), b.generate(16, use_graph=False))
+    new_a, new_b = a.generate(16, use_graph=False), b.generate(16, use_graph=False)
+    assert torch.equal(new_a, new_b)
+    assert not torch.equal(old, new_b)       # the two weight sets really decode differently
+    # and once more into a decoder that already captured its decode graph (the loader drops the graph, which
+    # holds the old layers' copies)
+    c = D.CherryDecoder(cfg, seed=77)
+    c.prefill(prompt)
+    c.generate(4, use_graph=True)
+    P.load_decoder_state_dict(c, state)
+    c.prefill(prompt)
+    assert torch.equal(c.generate(16, use_graph=True), new_a)
 
 
 @pytest.mark.parametrize("k,fraction", [(4096, 1 / 256), (11008, 1 / 256), (28672, 1 / 256), (512, 1 / 16)])
