@@ -528,12 +528,12 @@ extern "C" int cq_silu_mul(const void* gate, const void* up, void* out, long lon
 }
 
 namespace {
-// ranges of positions per head: enough CTAs for about two per SM, at least 64 positions per range
+// ranges of positions per head: enough CTAs for about two per SM, at least 256 cache positions per range
 int attn_splits(int sequences, int n_heads, int max_seq) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int s = (2 * sms + sequences * n_heads - 1) / (sequences * n_heads);
-  const int by_len = (max_seq + 63) / 64;
+  const int by_len = (max_seq + 255) / 256;
   if (s > by_len) s = by_len;
   if (s > ATT_MAX_SPLITS) s = ATT_MAX_SPLITS;
   return s < 1 ? 1 : s;
